@@ -1,0 +1,165 @@
+/*
+ * stk_b200 — C ABI of the B200 (sm_100a) block-sparse matmul backend.
+ *
+ * This header is the whole drop-in boundary: plain pointers, sizes and flags, no
+ * torch types.  Every pointer is a DEVICE pointer owned by the caller unless the
+ * comment says "host".  Every call is asynchronous on `stream` (a cudaStream_t
+ * passed as void*), never synchronises the device, and allocates nothing.
+ * Return value: 0 on success, a negative STK_ERR_* code otherwise (see
+ * stk_b200_error_string).  Nothing aborts and no kernel traps.
+ *
+ * Each entry point names the interface of the reference project
+ * (stanford-futuredata/stk, paths relative to its root) that it replaces.
+ *
+ * Sparse operand format (blocked CSR-COO, blocking = 128 for the matmuls):
+ *   data            [nnz,128,128]  fp16/bf16, blocks ordered by (block-row, block-col)
+ *   row_indices     [nnz]          int16
+ *   column_indices  [nnz]          int16
+ *   offsets         [R+1]          int32   (R = block rows)
+ *   column_indices_t[nnz]          int16   (block-row of the k-th block in column-major order)
+ *   offsets_t       [Cb+1]         int32   (Cb = block columns)
+ *   block_offsets_t [nnz]          int32   (index into data of the k-th block in column-major order)
+ */
+#ifndef STK_B200_H_
+#define STK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define STK_B200_VERSION 100
+
+/* element types of the matmul operands */
+#define STK_F16 0
+#define STK_BF16 1
+
+/* status codes */
+#define STK_OK 0
+#define STK_ERR_NULL_POINTER (-1)   /* a required pointer is NULL */
+#define STK_ERR_BAD_DIMS (-2)       /* M,N not multiples of 128, K not a multiple of 32, negative size ... */
+#define STK_ERR_BAD_DTYPE (-3)      /* dtype / element size not supported */
+#define STK_ERR_BAD_LAYOUT (-4)     /* pointer not 16-byte aligned or leading dimension not a multiple of 8 elements */
+#define STK_ERR_TENSOR_MAP (-5)     /* cuTensorMapEncodeTiled failed */
+#define STK_ERR_LAUNCH (-6)         /* kernel launch / CUDA runtime error */
+#define STK_ERR_WORKSPACE (-7)      /* workspace missing or too small */
+#define STK_ERR_DRIVER (-8)         /* driver entry point unavailable */
+#define STK_ERR_TOO_LARGE (-9)      /* size beyond what the entry point supports */
+#define STK_ERR_DEVICE_TIMEOUT (-10)/* a bounded wait inside a kernel ran out (reported by stk_b200_device_status) */
+
+int stk_b200_version(void);
+const char* stk_b200_error_string(int code);
+
+/*
+ * Reads and clears this device's kernel status word (0 = no kernel has reported a
+ * problem since the last call).  Synchronises the device: debugging / tests only.
+ * No counterpart in the reference (its kernels cannot report anything).
+ */
+int stk_b200_device_status(int* status_host);
+
+/*
+ * SDD: out[p] = lhs[r_p*128:+128, :] @ rhs[:, c_p*128:+128] for every nonzero block p,
+ * fp32 accumulation, output rounded to `dtype`.
+ * Replaces stk/backend/triton_kernels.py:332-379 (sdd) and :21-68 (_sdd_kernel).
+ *   lhs: logical [M,K]; row-major (lhs_colmajor=0, element (m,k) at m*ld_lhs+k) or
+ *        column-major (lhs_colmajor=1, element (m,k) at k*ld_lhs+m — an exact .t() view).
+ *   rhs: logical [K,N]; same convention with ld_rhs.
+ *   out: [nnz,128,128] contiguous.
+ * nnz == 0 is a no-op.
+ */
+int stk_b200_sdd(const void* lhs, const void* rhs, void* out,
+                 const int16_t* row_indices, const int16_t* column_indices,
+                 int64_t M, int64_t N, int64_t K, int64_t nnz,
+                 int lhs_colmajor, int64_t ld_lhs, int rhs_colmajor, int64_t ld_rhs,
+                 int dtype, void* stream);
+
+/*
+ * DSD: out[M,N] = op(S)[M,K] @ rhs[K,N].
+ * Replaces stk/backend/triton_kernels.py:222-276 (dsd) and :70-145 (_dsd_kernel).
+ *   trans_sparse = 0: pass offsets, column_indices and block_offsets = NULL
+ *                     (block j of block-row i is data[j]).
+ *   trans_sparse = 1: pass offsets_t, column_indices_t and block_offsets_t
+ *                     (block j of block-row i of S^T is data[block_offsets_t[j]]^T).
+ *   M,K: logical (already transposed) shape of op(S).  Block rows without blocks give zeros.
+ *   rhs: row-major or column-major as for stk_b200_sdd.  out: row-major, leading dimension ld_out.
+ */
+int stk_b200_dsd(const void* data, const int32_t* offsets, const int16_t* column_indices,
+                 const int32_t* block_offsets, const void* rhs, void* out,
+                 int64_t M, int64_t N, int64_t K, int64_t nnz,
+                 int trans_sparse, int rhs_colmajor, int64_t ld_rhs, int64_t ld_out,
+                 int dtype, void* stream);
+
+/*
+ * DDS: out[M,N] = lhs[M,K] @ op(S)[K,N].
+ * Replaces stk/backend/triton_kernels.py:278-330 (dds) and :147-220 (_dds_kernel).
+ *   trans_sparse = 0: pass offsets_t, column_indices_t and block_offsets_t (the block
+ *                     columns of S are walked through the transposed metadata).
+ *   trans_sparse = 1: pass offsets, column_indices and block_offsets = NULL
+ *                     (block column n of S^T is block row n of S, blocks used transposed).
+ *   K,N: logical shape of op(S).
+ */
+int stk_b200_dds(const void* lhs, const void* data, const int32_t* offsets,
+                 const int16_t* column_indices, const int32_t* block_offsets, void* out,
+                 int64_t M, int64_t N, int64_t K, int64_t nnz,
+                 int lhs_colmajor, int64_t ld_lhs, int trans_sparse, int64_t ld_out,
+                 int dtype, void* stream);
+
+/*
+ * CSR offsets -> COO row index of every block (int16).
+ * Replaces stk/backend/triton_kernels.py:381-393 (_row_indices_kernel, row_indices).
+ */
+int stk_b200_row_indices(const int32_t* offsets, int16_t* out, int64_t block_rows, int64_t nnz,
+                         void* stream);
+
+/*
+ * Transpose metadata: stable counting sort of the blocks by column.
+ * Replaces stk/matrix.py:105-123 (_transpose: argsort + gather + histc + cumsum).
+ * Ties (blocks of one column) come out in ascending storage order, i.e. ascending block row.
+ * The caller supplies `workspace` of at least stk_b200_transpose_meta_workspace_bytes()
+ * bytes, 16-byte aligned; its contents on entry do not matter.
+ */
+size_t stk_b200_transpose_meta_workspace_bytes(int64_t nnz, int64_t block_cols);
+int stk_b200_transpose_meta(const int16_t* row_indices, const int16_t* column_indices,
+                            int64_t nnz, int64_t block_cols,
+                            int16_t* column_indices_t, int32_t* offsets_t, int32_t* block_offsets_t,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * to_sparse, in phases, because the number of nonzero blocks sizes the output.
+ * Together they replace stk/ops/matrix_ops.py:50-85 (_mask, to_sparse).
+ *
+ * 1. block_mask: mask[br*Cb+bc] = 1 iff block (br,bc) of x holds an element that is not +-0
+ *    (NaN and Inf count as nonzero, as sum(|x|) != 0 does in the reference).
+ *    x: [rows, cols] row-major with leading dimension ld (elements), elem_bytes in {2,4}.
+ * 2. mask_to_offsets: offsets[0]=0, offsets[r+1] = number of set bytes in mask rows 0..r.
+ *    The caller reads offsets[R] back to size data / row_indices / column_indices.
+ * 3. mask_to_indices: row-major list of the set positions as int16 row / column indices.
+ * 4. gather_blocks: data[p] = x[r_p*b:+b, c_p*b:+b], copied bit-exactly.
+ */
+int stk_b200_block_mask(const void* x, int64_t rows, int64_t cols, int64_t ld,
+                        int blocking, int elem_bytes, uint8_t* mask, void* stream);
+int stk_b200_mask_to_offsets(const uint8_t* mask, int64_t block_rows, int64_t block_cols,
+                             int32_t* offsets, void* stream);
+int stk_b200_mask_to_indices(const uint8_t* mask, int64_t block_rows, int64_t block_cols,
+                             const int32_t* offsets, int16_t* row_indices, int16_t* column_indices,
+                             void* stream);
+int stk_b200_gather_blocks(const void* x, int64_t rows, int64_t cols, int64_t ld,
+                           int blocking, int elem_bytes,
+                           const int16_t* row_indices, const int16_t* column_indices, int64_t nnz,
+                           void* data, void* stream);
+
+/*
+ * to_dense: out[rows, cols] (row-major, leading dimension ld_out) = zeros with every block
+ * written at (row*b, col*b); every output element is written exactly once.
+ * Replaces stk/ops/matrix_ops.py:36-47 (to_dense) and :15-31 (_expand_for_blocking).
+ */
+int stk_b200_to_dense(const void* data, const int32_t* offsets, const int16_t* column_indices,
+                      int64_t block_rows, int64_t block_cols, int blocking, int elem_bytes,
+                      void* out, int64_t ld_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* STK_B200_H_ */

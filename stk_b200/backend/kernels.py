@@ -1,0 +1,241 @@
+"""Host launchers of the sm_100a kernels.
+
+The four matmul / index launchers keep the names, argument order and meaning of the reference's
+kernel backend (stk/backend/triton_kernels.py: dsd :222-276, dds :278-330, sdd :332-379,
+row_indices :389-393), so the autograd glue above them is unchanged.  Three more launchers replace
+what the reference composes from torch ops: transpose_meta (stk/matrix.py:105-123), the to_sparse
+phases and to_dense (stk/ops/matrix_ops.py:36-85).
+
+Everything here marshals tensors into the C ABI of libstk_b200.so; there is no other code path.
+"""
+import torch
+
+from stk_b200.backend import lib as _lib
+
+BLOCK = 128  # the matmul kernels are built for 128x128 blocks
+
+
+class DimensionError(AssertionError, ValueError):
+    """Incompatible operand sizes (the reference raises AssertionError for these)."""
+
+
+def _validate_matmul_dims(M, K, N):
+    # reference: stk/backend/triton_kernels.py:15-19
+    msg = "incompatible dimensions: tensor has dim with length: {}, which must be divisible by {}"
+    if M % 128 != 0:
+        raise DimensionError(msg.format(M, 128))
+    if K % 32 != 0:
+        raise DimensionError(msg.format(K, 32))
+    if N % 128 != 0:
+        raise DimensionError(msg.format(N, 128))
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                "stk_b200 matmuls run on CUDA tensors only (there is no CPU path); "
+                f"got a tensor on {t.device}")
+
+
+def _dense_layout(x):
+    """(tensor, colmajor, ld) of a 2-D operand the kernels can read in place.
+
+    Row-major (stride (ld, 1)) and exact-transpose views (stride (1, ld)) are consumed as they
+    are; anything else, or a misaligned view, is made contiguous first.
+    """
+    if x.dim() != 2:
+        raise DimensionError(f"expected a 2-D dense operand, got {x.dim()}-D")
+    rows, cols = x.shape
+    s0, s1 = x.stride()
+    aligned = x.data_ptr() % 16 == 0
+    if s1 == 1 and s0 >= cols and s0 % 8 == 0 and aligned:
+        return x, 0, s0
+    if s0 == 1 and s1 >= rows and s1 % 8 == 0 and aligned:
+        return x, 1, s1
+    x = x.contiguous()
+    return x, 0, x.stride(0)
+
+
+def _check_blocks(data):
+    if data.dim() != 3 or data.shape[1] != BLOCK or data.shape[2] != BLOCK:
+        raise DimensionError(
+            f"block-sparse matmuls need [nnz, {BLOCK}, {BLOCK}] blocks, got {tuple(data.shape)}")
+    if not data.is_contiguous():
+        raise DimensionError("sparse values must be contiguous")
+
+
+def dsd(shape, data, offsets, row_indices, column_indices, offsets_t, column_indices_t,
+        block_offsets_t, transpose_a, rhs, out):
+    """out = op(S) @ rhs, S given by its blocked CSR-COO fields; `shape` is op(S)'s shape."""
+    _require_cuda(data, rhs, out)
+    if shape[1] != rhs.shape[0]:
+        raise DimensionError("incompatible dimensions")
+    M, K = shape
+    N = rhs.shape[1]
+    _validate_matmul_dims(M, K, N)
+    _check_blocks(data)
+    rhs, rhs_colmajor, ld_rhs = _dense_layout(rhs)
+    if transpose_a:
+        meta = (offsets_t, column_indices_t, block_offsets_t)
+    else:
+        meta = (offsets, column_indices, None)
+    with torch.cuda.device(out.device):
+        rc = _lib.load().stk_b200_dsd(
+            _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),
+            _lib.ptr(rhs), _lib.ptr(out), M, N, K, data.shape[0], int(bool(transpose_a)),
+            rhs_colmajor, ld_rhs, out.stride(0), _lib.dtype_code(rhs.dtype),
+            _lib.stream_ptr(out.device))
+    _lib.check(rc, "stk_b200_dsd")
+
+
+def dds(lhs, shape, data, offsets, row_indices, column_indices, offsets_t, column_indices_t,
+        block_offsets_t, transpose_b, out):
+    """out = lhs @ op(S); `shape` is op(S)'s shape."""
+    _require_cuda(lhs, data, out)
+    if lhs.shape[1] != shape[0]:
+        raise DimensionError("incompatible dimensions")
+    M, K = lhs.shape
+    N = shape[1]
+    _validate_matmul_dims(M, K, N)
+    _check_blocks(data)
+    lhs, lhs_colmajor, ld_lhs = _dense_layout(lhs)
+    if transpose_b:
+        meta = (offsets, column_indices, None)
+    else:
+        meta = (offsets_t, column_indices_t, block_offsets_t)
+    with torch.cuda.device(out.device):
+        rc = _lib.load().stk_b200_dds(
+            _lib.ptr(lhs), _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),
+            _lib.ptr(out), M, N, K, data.shape[0], lhs_colmajor, ld_lhs, int(bool(transpose_b)),
+            out.stride(0), _lib.dtype_code(lhs.dtype), _lib.stream_ptr(out.device))
+    _lib.check(rc, "stk_b200_dds")
+
+
+def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices):
+    """out[p] = (lhs @ rhs)[block p] for the blocks listed by row_indices / column_indices."""
+    _require_cuda(lhs, rhs, out)
+    if lhs.shape[1] != rhs.shape[0]:
+        raise DimensionError("incompatible dimensions")
+    M, K = lhs.shape
+    N = rhs.shape[1]
+    _validate_matmul_dims(M, K, N)
+    _check_blocks(out)
+    lhs, lhs_colmajor, ld_lhs = _dense_layout(lhs)
+    rhs, rhs_colmajor, ld_rhs = _dense_layout(rhs)
+    with torch.cuda.device(out.device):
+        rc = _lib.load().stk_b200_sdd(
+            _lib.ptr(lhs), _lib.ptr(rhs), _lib.ptr(out), _lib.ptr(row_indices),
+            _lib.ptr(column_indices), M, N, K, out.shape[0], lhs_colmajor, ld_lhs, rhs_colmajor,
+            ld_rhs, _lib.dtype_code(out.dtype), _lib.stream_ptr(out.device))
+    _lib.check(rc, "stk_b200_sdd")
+
+
+def row_indices(shape, data, offsets, column_indices, out):
+    """out[p] = block row of block p (CSR offsets -> COO)."""
+    _require_cuda(offsets, out)
+    block_rows = offsets.numel() - 1
+    with torch.cuda.device(out.device):
+        rc = _lib.load().stk_b200_row_indices(
+            _lib.ptr(offsets), _lib.ptr(out), block_rows, out.numel(), _lib.stream_ptr(out.device))
+    _lib.check(rc, "stk_b200_row_indices")
+
+
+def transpose_meta(row_indices, column_indices, block_cols):
+    """(column_indices_t, offsets_t, block_offsets_t) of a topology, on its (CUDA) device."""
+    _require_cuda(row_indices, column_indices)
+    dev = column_indices.device
+    nnz = column_indices.numel()
+    column_indices_t = torch.empty(nnz, dtype=torch.int16, device=dev)
+    offsets_t = torch.empty(block_cols + 1, dtype=torch.int32, device=dev)
+    block_offsets_t = torch.empty(nnz, dtype=torch.int32, device=dev)
+    lib = _lib.load()
+    ws_bytes = lib.stk_b200_transpose_meta_workspace_bytes(nnz, block_cols)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
+    with torch.cuda.device(dev):
+        rc = lib.stk_b200_transpose_meta(
+            _lib.ptr(row_indices.contiguous()), _lib.ptr(column_indices.contiguous()), nnz,
+            block_cols, _lib.ptr(column_indices_t), _lib.ptr(offsets_t), _lib.ptr(block_offsets_t),
+            _lib.ptr(ws), ws_bytes, _lib.stream_ptr(dev))
+    _lib.check(rc, "stk_b200_transpose_meta")
+    return column_indices_t, offsets_t, block_offsets_t
+
+
+def _elem_bytes(t):
+    n = t.element_size()
+    if n not in (2, 4):
+        raise ValueError(f"conversion kernels handle 2- and 4-byte elements, got {t.dtype}")
+    return n
+
+
+def block_mask(x, blocking):
+    """uint8 [R, Cb]: 1 where the blocking x blocking block of x has an element that is not +-0."""
+    _require_cuda(x)
+    rows, cols = x.shape
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    mask = torch.empty((rows // blocking, cols // blocking), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().stk_b200_block_mask(
+            _lib.ptr(x), rows, cols, x.stride(0) if rows > 1 else max(cols, 1), blocking,
+            _elem_bytes(x), _lib.ptr(mask), _lib.stream_ptr(x.device))
+    _lib.check(rc, "stk_b200_block_mask")
+    return mask
+
+
+def mask_to_topology(mask):
+    """(offsets, row_indices, column_indices) of a uint8 [R, Cb] block mask (row-major order).
+
+    Reads the block count back to the host to size the index tensors, like torch.nonzero does in
+    the reference's to_sparse.
+    """
+    _require_cuda(mask)
+    dev = mask.device
+    block_rows, block_cols = mask.shape
+    mask = mask.contiguous()
+    offsets = torch.empty(block_rows + 1, dtype=torch.int32, device=dev)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        rc = lib.stk_b200_mask_to_offsets(_lib.ptr(mask), block_rows, block_cols, _lib.ptr(offsets),
+                                          _lib.stream_ptr(dev))
+        _lib.check(rc, "stk_b200_mask_to_offsets")
+        nnz = int(offsets[-1].item())
+        row_idx = torch.empty(nnz, dtype=torch.int16, device=dev)
+        col_idx = torch.empty(nnz, dtype=torch.int16, device=dev)
+        rc = lib.stk_b200_mask_to_indices(_lib.ptr(mask), block_rows, block_cols, _lib.ptr(offsets),
+                                          _lib.ptr(row_idx), _lib.ptr(col_idx), _lib.stream_ptr(dev))
+        _lib.check(rc, "stk_b200_mask_to_indices")
+    return offsets, row_idx, col_idx
+
+
+def gather_blocks(x, blocking, row_idx, col_idx):
+    """data [nnz, b, b]: the listed blocks of x, copied bit-exactly."""
+    _require_cuda(x, row_idx, col_idx)
+    rows, cols = x.shape
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    nnz = row_idx.numel()
+    data = torch.empty((nnz, blocking, blocking), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().stk_b200_gather_blocks(
+            _lib.ptr(x), rows, cols, x.stride(0) if rows > 1 else max(cols, 1), blocking,
+            _elem_bytes(x), _lib.ptr(row_idx), _lib.ptr(col_idx), nnz, _lib.ptr(data),
+            _lib.stream_ptr(x.device))
+    _lib.check(rc, "stk_b200_gather_blocks")
+    return data
+
+
+def to_dense(data, offsets, column_indices, block_rows, block_cols, blocking):
+    """Dense [R*b, Cb*b] tensor with the blocks in place and zeros elsewhere."""
+    _require_cuda(data, offsets, column_indices)
+    out = torch.empty((block_rows * blocking, block_cols * blocking), dtype=data.dtype,
+                      device=data.device)
+    if out.numel() == 0:
+        return out
+    with torch.cuda.device(data.device):
+        rc = _lib.load().stk_b200_to_dense(
+            _lib.ptr(data.contiguous()) if data.numel() else None, _lib.ptr(offsets),
+            _lib.ptr(column_indices) if column_indices.numel() else None, block_rows, block_cols,
+            blocking, _elem_bytes(data), _lib.ptr(out), out.stride(0), _lib.stream_ptr(data.device))
+    _lib.check(rc, "stk_b200_to_dense")
+    return out

@@ -1,0 +1,104 @@
+"""ctypes binding of libstk_b200.so (the C ABI declared in include/stk_b200.h).
+
+There is no fallback of any kind: if the library is missing or an entry point reports an
+error, the caller gets an exception.
+"""
+import ctypes
+import os
+
+import torch
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB_PATH = os.path.join(_PKG, "libstk_b200.so")
+
+STK_F16 = 0
+STK_BF16 = 1
+
+_c_i64 = ctypes.c_int64
+_c_int = ctypes.c_int
+_c_ptr = ctypes.c_void_p
+_c_size = ctypes.c_size_t
+
+# name -> (restype, argtypes); one entry per declaration in include/stk_b200.h
+SIGNATURES = {
+    "stk_b200_version": (_c_int, []),
+    "stk_b200_error_string": (ctypes.c_char_p, [_c_int]),
+    "stk_b200_device_status": (_c_int, [ctypes.POINTER(_c_int)]),
+    "stk_b200_sdd": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_i64,
+                              _c_int, _c_i64, _c_int, _c_i64, _c_int, _c_ptr]),
+    "stk_b200_dsd": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64,
+                              _c_i64, _c_int, _c_int, _c_i64, _c_i64, _c_int, _c_ptr]),
+    "stk_b200_dds": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64,
+                              _c_i64, _c_int, _c_i64, _c_int, _c_i64, _c_int, _c_ptr]),
+    "stk_b200_row_indices": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_ptr]),
+    "stk_b200_transpose_meta_workspace_bytes": (_c_size, [_c_i64, _c_i64]),
+    "stk_b200_transpose_meta": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr,
+                                         _c_ptr, _c_size, _c_ptr]),
+    "stk_b200_block_mask": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_ptr, _c_ptr]),
+    "stk_b200_mask_to_offsets": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr]),
+    "stk_b200_mask_to_indices": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr]),
+    "stk_b200_gather_blocks": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_ptr, _c_ptr,
+                                        _c_i64, _c_ptr, _c_ptr]),
+    "stk_b200_to_dense": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_int, _c_ptr,
+                                   _c_i64, _c_ptr]),
+}
+
+_lib = None
+
+
+def load():
+    """Load the shared library once and attach the argument types."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m stk_b200.csrc.build` "
+            "(stk_b200 has no fallback path)")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here means a stale library
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def error_string(code):
+    return load().stk_b200_error_string(code).decode()
+
+
+def check(code, what):
+    """Raise for a non-zero status: ValueError for argument problems, RuntimeError otherwise."""
+    if code == 0:
+        return
+    msg = f"{what}: {error_string(code)} (status {code})"
+    if code in (-1, -2, -3, -4, -9):
+        raise ValueError(msg)
+    raise RuntimeError(msg)
+
+
+def device_status():
+    """Status word written by kernels that had to give up (0 = none).  Synchronises."""
+    out = _c_int(0)
+    check(load().stk_b200_device_status(ctypes.byref(out)), "stk_b200_device_status")
+    return out.value
+
+
+def ptr(t):
+    """Device pointer of a tensor (None -> NULL)."""
+    if t is None:
+        return None
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def stream_ptr(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def dtype_code(dtype):
+    if dtype == torch.float16:
+        return STK_F16
+    if dtype == torch.bfloat16:
+        return STK_BF16
+    raise ValueError(f"stk_b200 matmuls support float16 and bfloat16 operands, got {dtype}")

@@ -1,0 +1,555 @@
+// Block-sparse matmul for sm_100a: SDD, DSD and DDS at 128x128 blocks, fp16/bf16 operands,
+// fp32 accumulation in tensor memory.
+//
+// One persistent, warp-specialised kernel serves the three operations.  Every output tile is
+// 128x128; what differs between the operations is only how a tile's K loop is enumerated from
+// the blocked CSR-COO metadata and where its two operand tiles live:
+//
+//   SDD  tile p        : A = lhs rows of block-row r_p,           B = rhs columns of block-col c_p,
+//                        K loop over the dense inner dimension.
+//   DSD  tile (i, n)   : K loop over the blocks j of block-row i: A = data[blk(j)] (or its transpose),
+//                        B = rhs rows col(j)*128.., columns n*128..
+//   DDS  tile (m, n)   : K loop over the blocks j of block-column n: A = lhs rows m*128.., columns col(j)*128..,
+//                        B = data[blk(j)] (or its transpose).
+//
+// Operand tiles are fetched by TMA with the 128-byte swizzle into a multi-stage shared-memory ring and
+// consumed by tcgen05.mma straight from shared memory.  A transposed operand is never copied: it is a
+// different tensor map plus the "MN-major" bit of the instruction / shared-memory descriptors.
+//
+// Warp roles (192 threads): warp 0 = TMA producer (also walks the metadata), warp 1 = MMA issuer and
+// TMEM owner, warps 2..5 = epilogue (TMEM -> registers -> 16-bit -> global).  Two TMEM accumulators
+// let the epilogue of tile t overlap the main loop of tile t+1.
+//
+// The semantics follow stk/backend/triton_kernels.py of the reference (_sdd_kernel :34-68,
+// _dsd_kernel :83-145, _dds_kernel :160-220 and their launchers :222-379).
+#pragma once
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/stk_b200.h"
+#include "sm100_ptx.cuh"
+#include "status.cuh"
+
+namespace stk {
+
+constexpr int kBlk = 128;                       // sparse block edge = tile edge
+constexpr int kBK = 64;                         // K elements per pipeline stage (one 128-byte swizzle row)
+constexpr int kUmmaK = 16;                      // K of one tcgen05.mma for 16-bit operands
+constexpr int kStages = 6;
+constexpr int kOperandTileBytes = kBlk * kBK * 2;  // 16 KiB
+constexpr int kStageBytes = 2 * kOperandTileBytes;
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 256;                  // two 128-column fp32 accumulators
+constexpr int kNumBars = 2 * kStages + 4;
+constexpr int kSmemBytes = kStages * kStageBytes + kNumBars * 8 + 16 + 1024;  // + alignment slack
+
+enum : int { kModeSDD = 0, kModeDSD = 1, kModeDDS = 2 };
+
+struct BsmmParams {
+  int mode;
+  int a_mn;        // 1: A tile is M-contiguous in memory (transposed operand), 0: K-contiguous
+  int b_mn;        // 1: B tile is N-contiguous in memory, 0: K-contiguous
+  int fmt;         // STK_F16 / STK_BF16
+  int num_tiles;
+  int tiles_inner; // DSD: number of N tiles (n runs fastest); DDS: number of M tiles (m runs fastest)
+  int k_steps;     // SDD: ceil(K / 64)
+  const int16_t* row_idx;   // SDD
+  const int16_t* col_idx;   // SDD: block column; DSD/DDS: position of block j along K, in blocks
+  const int32_t* offsets;   // DSD/DDS: K-loop segment of every block-row / block-column
+  const int32_t* blk_idx;   // DSD/DDS: index into data of block j, or nullptr for the identity
+  void* out;
+  long long ldc;            // DSD/DDS: leading dimension of out in elements
+};
+
+struct TileInfo {
+  int tm, tn;   // DSD/DDS tile coordinates (in tiles); SDD: block row / block column
+  int j0, j1;   // DSD/DDS: segment of the metadata arrays
+  int nk;       // number of 64-wide K steps
+};
+
+__device__ __forceinline__ TileInfo tile_info(const BsmmParams& p, int tile) {
+  TileInfo t;
+  if (p.mode == kModeSDD) {
+    t.tm = p.row_idx[tile];
+    t.tn = p.col_idx[tile];
+    t.j0 = t.j1 = 0;
+    t.nk = p.k_steps;
+  } else {
+    const int outer = tile / p.tiles_inner;
+    const int inner = tile - outer * p.tiles_inner;
+    if (p.mode == kModeDSD) {
+      t.tm = outer;
+      t.tn = inner;
+      t.j0 = p.offsets[t.tm];
+      t.j1 = p.offsets[t.tm + 1];
+    } else {
+      t.tn = outer;
+      t.tm = inner;
+      t.j0 = p.offsets[t.tn];
+      t.j1 = p.offsets[t.tn + 1];
+    }
+    t.nk = 2 * (t.j1 - t.j0);
+  }
+  return t;
+}
+
+// One operand tile (128 rows of M or N by 64 of K) into a stage buffer.
+//   K-major : one box {64 (K), 128 (M/N)} at (k_elem, mn_elem).
+//   MN-major: two boxes {64 (M/N), 64 (K)} at (mn_elem + h*64, k_elem), 8 KiB apart.
+__device__ __forceinline__ void load_operand(const CUtensorMap* tm, uint32_t smem_dst, uint32_t bar,
+                                             int mn_major, int mn_elem, int k_elem) {
+  if (!mn_major) {
+    tma_load_2d(smem_dst, tm, bar, k_elem, mn_elem);
+  } else {
+    tma_load_2d(smem_dst, tm, bar, mn_elem, k_elem);
+    tma_load_2d(smem_dst + kOperandTileBytes / 2, tm, bar, mn_elem + 64, k_elem);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const BsmmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  const uint32_t smem_base = smem_u32(smem);
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  const uint32_t bars_base = smem_base + kStages * kStageBytes;
+  auto full_bar = [&](int s) { return bars_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bars_base + 8u * (kStages + s); };
+  auto tfull_bar = [&](int a) { return bars_base + 8u * (2 * kStages + a); };
+  auto tempty_bar = [&](int a) { return bars_base + 8u * (2 * kStages + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    int stage = 0;
+    uint32_t phase = 0;
+    int ok = 1;
+    auto produce = [&](int a_mn_elem, int a_k_elem, int b_mn_elem, int b_k_elem) {
+      if (lane == 0) {
+        if (mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+          const uint32_t a_dst = smem_base + stage * kStageBytes;
+          const uint32_t b_dst = a_dst + kOperandTileBytes;
+          mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
+          load_operand(&tmA, a_dst, full_bar(stage), p.a_mn, a_mn_elem, a_k_elem);
+          load_operand(&tmB, b_dst, full_bar(stage), p.b_mn, b_mn_elem, b_k_elem);
+        } else {
+          ok = 0;
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (++stage == kStages) {
+        stage = 0;
+        phase ^= 1u;
+      }
+    };
+    for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+      const TileInfo t = tile_info(p, tile);
+      if (p.mode == kModeSDD) {
+        for (int ks = 0; ks < t.nk && ok; ++ks)
+          produce(t.tm * kBlk, ks * kBK, t.tn * kBlk, ks * kBK);
+      } else {
+        for (int jb = t.j0; jb < t.j1 && ok; jb += 32) {
+          // The warp fetches the metadata of up to 32 blocks at once, then replays it.
+          const int j = jb + lane;
+          int my_col = 0, my_blk = 0;
+          if (j < t.j1) {
+            my_col = p.col_idx[j];
+            my_blk = p.blk_idx ? p.blk_idx[j] : j;
+          }
+          const int cnt = min(32, t.j1 - jb);
+          for (int i = 0; i < cnt && ok; ++i) {
+            const int col = __shfl_sync(0xffffffffu, my_col, i);
+            const int blk = __shfl_sync(0xffffffffu, my_blk, i);
+            for (int ks = 0; ks < 2 && ok; ++ks) {
+              if (p.mode == kModeDSD) {
+                // sparse A, dense B
+                const int a_mn_elem = p.a_mn ? 0 : blk * kBlk;
+                const int a_k_elem = p.a_mn ? blk * kBlk + ks * kBK : ks * kBK;
+                produce(a_mn_elem, a_k_elem, t.tn * kBlk, col * kBlk + ks * kBK);
+              } else {
+                // dense A, sparse B
+                const int b_mn_elem = p.b_mn ? 0 : blk * kBlk;
+                const int b_k_elem = p.b_mn ? blk * kBlk + ks * kBK : ks * kBK;
+                produce(t.tm * kBlk, col * kBlk + ks * kBK, b_mn_elem, b_k_elem);
+              }
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(p.fmt, p.a_mn, p.b_mn, kBlk);
+      // Byte step of the descriptor start address per 16 elements of K.
+      const uint32_t a_kstep = p.a_mn ? kUmmaK * 128u : kUmmaK * 2u;
+      const uint32_t b_kstep = p.b_mn ? kUmmaK * 128u : kUmmaK * 2u;
+      const uint32_t a_lbo = p.a_mn ? kOperandTileBytes / 2 : 16u;
+      const uint32_t b_lbo = p.b_mn ? kOperandTileBytes / 2 : 16u;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+        const TileInfo t = tile_info(p, tile);
+        if (t.nk == 0) continue;  // the epilogue writes zeros; no accumulator is used
+        ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kBlk);
+        for (int ks = 0; ks < t.nk; ++ks) {
+          ok = mbar_wait(full_bar(stage), phase, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_src = smem_base + stage * kStageBytes;
+          const uint32_t b_src = a_src + kOperandTileBytes;
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            const uint64_t a_desc = make_smem_desc(a_src + k * a_kstep, a_lbo, 1024u);
+            const uint64_t b_desc = make_smem_desc(b_src + k * b_kstep, b_lbo, 1024u);
+            umma_f16(d_tmem, a_desc, b_desc, idesc, (ks | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));  // the stage is free once these MMAs have read it
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar(acc));  // accumulator complete
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // a warp may only read TMEM lanes 32*(warp%4) .. +31
+    const int row = quarter * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+      const TileInfo t = tile_info(p, tile);
+      uint16_t* out_row;
+      if (p.mode == kModeSDD) {
+        out_row = static_cast<uint16_t*>(p.out) + static_cast<long long>(tile) * (kBlk * kBlk) +
+                  row * kBlk;
+      } else {
+        out_row = static_cast<uint16_t*>(p.out) +
+                  (static_cast<long long>(t.tm) * kBlk + row) * p.ldc +
+                  static_cast<long long>(t.tn) * kBlk;
+      }
+      uint4* out_vec = reinterpret_cast<uint4*>(out_row);
+      if (t.nk == 0) {
+        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int i = 0; i < kBlk / 8; ++i) out_vec[i] = z;
+        continue;
+      }
+      // tcgen05.ld needs the whole warp: make the outcome of the wait warp-uniform.
+      ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(acc), acc_phase, abort_flag) ? 1 : 0) != 0;
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                              static_cast<uint32_t>(acc * kBlk);
+#pragma unroll
+      for (int chunk = 0; chunk < kBlk / 32; ++chunk) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + chunk * 32, r);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float lo = __uint_as_float(r[2 * i]);
+          const float hi = __uint_as_float(r[2 * i + 1]);
+          if (p.fmt == STK_BF16) {
+            const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+            packed[i] = *reinterpret_cast<const uint32_t*>(&v);
+          } else {
+            const __half2 v = __floats2half2_rn(lo, hi);
+            packed[i] = *reinterpret_cast<const uint32_t*>(&v);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          out_vec[chunk * 4 + i] =
+              make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag != 0) {
+    // Something never arrived.  Give copies and MMAs still in flight time to land before the
+    // shared and tensor memory they target is released, then report.
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0) report_status(STK_ERR_DEVICE_TIMEOUT);
+}
+
+// ====================================================================== host side
+
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  }
+  return fn;
+}
+
+// Tensor map of a 2-D 16-bit tensor: `inner` contiguous elements per row, `outer` rows,
+// `ld` elements between rows; boxes of 64 x box_outer with the 128-byte swizzle.
+static int encode_map(CUtensorMap* tm, const void* base, int dtype, int64_t inner, int64_t outer,
+                      int64_t ld, int box_outer) {
+  PFN_cuTensorMapEncodeTiled_v12000 fn = get_encode_fn();
+  if (fn == nullptr) return STK_ERR_DRIVER;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2u};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_outer)};
+  const cuuint32_t estr[2] = {1u, 1u};
+  const CUresult r =
+      fn(tm, dtype == STK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+         2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? STK_OK : STK_ERR_TENSOR_MAP;
+}
+
+// Dense operand with logical shape [mn, k] (the A convention: rows = M; for B pass mn = N):
+//   k_contig = 1: K is contiguous in memory  -> K-major tile, box {64 K, 128 MN}
+//   k_contig = 0: M/N is contiguous          -> MN-major tile, boxes {64 MN, 64 K}
+static int encode_dense(CUtensorMap* tm, const void* base, int dtype, int64_t mn, int64_t k,
+                        int64_t ld, int k_contig) {
+  return k_contig ? encode_map(tm, base, dtype, k, mn, ld, kBlk)
+                  : encode_map(tm, base, dtype, mn, k, ld, kBK);
+}
+
+// Sparse values viewed as a [nnz*128, 128] row-major tensor.
+//   as_stored_k_contig = 1: the block's columns are the K of the product -> K-major
+//   as_stored_k_contig = 0: the block's columns are the M/N of the product -> MN-major
+static int encode_sparse(CUtensorMap* tm, const void* data, int dtype, int64_t nnz, int k_contig) {
+  return encode_map(tm, data, dtype, kBlk, nnz * kBlk, kBlk, k_contig ? kBlk : kBK);
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+struct DeviceInfo {
+  int sms = 0;
+  bool smem_opted_in = false;
+};
+
+static int device_info(DeviceInfo** out) {
+  static DeviceInfo infos[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return STK_ERR_LAUNCH;
+  DeviceInfo& d = infos[dev];
+  if (d.sms == 0) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      return STK_ERR_LAUNCH;
+    d.sms = sms;
+  }
+  if (!d.smem_opted_in) {
+    if (cudaFuncSetAttribute(bsmm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemBytes) != cudaSuccess) {
+      cudaGetLastError();
+      return STK_ERR_LAUNCH;
+    }
+    d.smem_opted_in = true;
+  }
+  *out = &d;
+  return STK_OK;
+}
+
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const BsmmParams& p,
+                  cudaStream_t stream) {
+  DeviceInfo* d = nullptr;
+  const int rc = device_info(&d);
+  if (rc != STK_OK) return rc;
+  const int grid = p.num_tiles < d->sms ? p.num_tiles : d->sms;
+  bsmm_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
+}
+
+static int check_dense(const void* ptr, int64_t ld, int64_t min_ld) {
+  if (ptr == nullptr) return STK_ERR_NULL_POINTER;
+  if (!aligned16(ptr) || ld < min_ld || (ld % 8) != 0) return STK_ERR_BAD_LAYOUT;
+  return STK_OK;
+}
+
+}  // namespace stk
+
+using namespace stk;
+
+extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out,
+                            const int16_t* row_indices, const int16_t* column_indices, int64_t M,
+                            int64_t N, int64_t K, int64_t nnz, int lhs_colmajor, int64_t ld_lhs,
+                            int rhs_colmajor, int64_t ld_rhs, int dtype, void* stream) {
+  if (dtype != STK_F16 && dtype != STK_BF16) return STK_ERR_BAD_DTYPE;
+  if (M <= 0 || N <= 0 || K <= 0 || nnz < 0 || M % kBlk || N % kBlk || K % 32) return STK_ERR_BAD_DIMS;
+  if (nnz == 0) return STK_OK;
+  if (nnz > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return STK_ERR_TOO_LARGE;
+  if (out == nullptr || row_indices == nullptr || column_indices == nullptr)
+    return STK_ERR_NULL_POINTER;
+  if (!aligned16(out)) return STK_ERR_BAD_LAYOUT;
+  int rc;
+  if ((rc = check_dense(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) return rc;
+  if ((rc = check_dense(rhs, ld_rhs, rhs_colmajor ? K : N)) != STK_OK) return rc;
+
+  CUtensorMap tmA, tmB;
+  // lhs [M,K]: row-major means K contiguous.
+  if ((rc = encode_dense(&tmA, lhs, dtype, M, K, ld_lhs, !lhs_colmajor)) != STK_OK) return rc;
+  // rhs [K,N]: row-major means N contiguous; column-major means K contiguous.
+  if ((rc = encode_dense(&tmB, rhs, dtype, N, K, ld_rhs, rhs_colmajor)) != STK_OK) return rc;
+
+  BsmmParams p{};
+  p.mode = kModeSDD;
+  p.a_mn = lhs_colmajor ? 1 : 0;
+  p.b_mn = rhs_colmajor ? 0 : 1;
+  p.fmt = dtype;
+  p.num_tiles = static_cast<int>(nnz);
+  p.tiles_inner = 1;
+  p.k_steps = static_cast<int>((K + kBK - 1) / kBK);
+  p.row_idx = row_indices;
+  p.col_idx = column_indices;
+  p.out = out;
+  p.ldc = kBlk;
+  return launch(tmA, tmB, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int16_t* column_indices,
+                            const int32_t* block_offsets, const void* rhs, void* out, int64_t M,
+                            int64_t N, int64_t K, int64_t nnz, int trans_sparse, int rhs_colmajor,
+                            int64_t ld_rhs, int64_t ld_out, int dtype, void* stream) {
+  if (dtype != STK_F16 && dtype != STK_BF16) return STK_ERR_BAD_DTYPE;
+  if (M <= 0 || N <= 0 || K <= 0 || nnz < 0 || M % kBlk || N % kBlk || K % kBlk) return STK_ERR_BAD_DIMS;
+  if (nnz * kBlk > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX ||
+      (M / kBlk) * (N / kBlk) > INT32_MAX)
+    return STK_ERR_TOO_LARGE;
+  int rc;
+  if ((rc = check_dense(out, ld_out, N)) != STK_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (nnz == 0) {
+    // No blocks at all: the product is zero.
+    return cudaMemset2DAsync(out, ld_out * 2, 0, N * 2, M, s) == cudaSuccess ? STK_OK
+                                                                             : STK_ERR_LAUNCH;
+  }
+  if (data == nullptr || offsets == nullptr || column_indices == nullptr) return STK_ERR_NULL_POINTER;
+  if (trans_sparse && block_offsets == nullptr) return STK_ERR_NULL_POINTER;
+  if (!aligned16(data)) return STK_ERR_BAD_LAYOUT;
+  if ((rc = check_dense(rhs, ld_rhs, rhs_colmajor ? K : N)) != STK_OK) return rc;
+
+  CUtensorMap tmA, tmB;
+  // A = data[blk] as stored (its columns are K) or transposed (its columns are M).
+  if ((rc = encode_sparse(&tmA, data, dtype, nnz, !trans_sparse)) != STK_OK) return rc;
+  if ((rc = encode_dense(&tmB, rhs, dtype, N, K, ld_rhs, rhs_colmajor)) != STK_OK) return rc;
+
+  BsmmParams p{};
+  p.mode = kModeDSD;
+  p.a_mn = trans_sparse ? 1 : 0;
+  p.b_mn = rhs_colmajor ? 0 : 1;
+  p.fmt = dtype;
+  p.tiles_inner = static_cast<int>(N / kBlk);
+  p.num_tiles = static_cast<int>((M / kBlk) * (N / kBlk));
+  p.col_idx = column_indices;
+  p.offsets = offsets;
+  p.blk_idx = block_offsets;
+  p.out = out;
+  p.ldc = ld_out;
+  return launch(tmA, tmB, p, s);
+}
+
+extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* offsets,
+                            const int16_t* column_indices, const int32_t* block_offsets, void* out,
+                            int64_t M, int64_t N, int64_t K, int64_t nnz, int lhs_colmajor,
+                            int64_t ld_lhs, int trans_sparse, int64_t ld_out, int dtype,
+                            void* stream) {
+  if (dtype != STK_F16 && dtype != STK_BF16) return STK_ERR_BAD_DTYPE;
+  if (M <= 0 || N <= 0 || K <= 0 || nnz < 0 || M % kBlk || N % kBlk || K % kBlk) return STK_ERR_BAD_DIMS;
+  if (nnz * kBlk > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX ||
+      (M / kBlk) * (N / kBlk) > INT32_MAX)
+    return STK_ERR_TOO_LARGE;
+  int rc;
+  if ((rc = check_dense(out, ld_out, N)) != STK_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (nnz == 0) {
+    return cudaMemset2DAsync(out, ld_out * 2, 0, N * 2, M, s) == cudaSuccess ? STK_OK
+                                                                             : STK_ERR_LAUNCH;
+  }
+  if (data == nullptr || offsets == nullptr || column_indices == nullptr) return STK_ERR_NULL_POINTER;
+  if (!trans_sparse && block_offsets == nullptr) return STK_ERR_NULL_POINTER;
+  if (!aligned16(data)) return STK_ERR_BAD_LAYOUT;
+  if ((rc = check_dense(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) return rc;
+
+  CUtensorMap tmA, tmB;
+  if ((rc = encode_dense(&tmA, lhs, dtype, M, K, ld_lhs, !lhs_colmajor)) != STK_OK) return rc;
+  // B = data[blk] as stored (its columns are N) or transposed (its columns are K).
+  if ((rc = encode_sparse(&tmB, data, dtype, nnz, trans_sparse)) != STK_OK) return rc;
+
+  BsmmParams p{};
+  p.mode = kModeDDS;
+  p.a_mn = lhs_colmajor ? 1 : 0;
+  p.b_mn = trans_sparse ? 0 : 1;
+  p.fmt = dtype;
+  p.tiles_inner = static_cast<int>(M / kBlk);
+  p.num_tiles = static_cast<int>((M / kBlk) * (N / kBlk));
+  p.col_idx = column_indices;
+  p.offsets = offsets;
+  p.blk_idx = block_offsets;
+  p.out = out;
+  p.ldc = ld_out;
+  return launch(tmA, tmB, p, s);
+}
