@@ -202,6 +202,8 @@ def mask_to_topology(mask):
         nnz = int(offsets[-1].item())
         row_idx = torch.empty(nnz, dtype=torch.int16, device=dev)
         col_idx = torch.empty(nnz, dtype=torch.int16, device=dev)
+        if nnz == 0:
+            return offsets, row_idx, col_idx
         rc = lib.stk_b200_mask_to_indices(_lib.ptr(mask), block_rows, block_cols, _lib.ptr(offsets),
                                           _lib.ptr(row_idx), _lib.ptr(col_idx), _lib.stream_ptr(dev))
         _lib.check(rc, "stk_b200_mask_to_indices")

@@ -1,0 +1,254 @@
+"""GPU parity tests: the CUDA path (through the C ABI) against the oracle and the golden fixtures."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import stk_oracle as oracle
+from tests import cases
+from tests.parity import assert_product_close, bits
+
+pytestmark = pytest.mark.gpu
+
+META_KEYS = ("row_indices", "column_indices", "offsets", "column_indices_t", "offsets_t",
+             "block_offsets_t")
+
+
+@pytest.fixture(scope="module")
+def stk():
+    import stk_b200
+    from stk_b200.backend import lib
+    assert torch.cuda.is_available()
+    lib.load()
+    yield stk_b200
+    assert lib.device_status() == 0, "a kernel reported a bounded wait that ran out"
+
+
+def _check_meta(m, expect, what):
+    for key in META_KEYS:
+        mine = getattr(m, key).cpu().numpy()
+        assert mine.dtype == expect[key].dtype, f"{what}: dtype of {key}"
+        np.testing.assert_array_equal(mine, expect[key], err_msg=f"{what}: {key}")
+
+
+@pytest.mark.parametrize("name", sorted(cases.METADATA_CASES))
+def test_random_mask_bit_exact(stk, golden, name):
+    g = golden["metadata"]
+    rows, cols, sparsity, blocking, seed = cases.METADATA_CASES[name]
+    np.random.seed(seed)
+    m = stk.random.mask(rows, cols, sparsity, blocking)
+    m.validate()
+    assert tuple(m.data.shape) == tuple(g[f"{name}/data_shape"])
+    assert m.data.dtype == torch.float16 and bool((m.data == 1).all())
+    # oracle (stable tie order) ...
+    np.random.seed(seed)
+    _check_meta(m, oracle.mask(rows, cols, sparsity, blocking), name)
+    # ... and the reference's own output, tie order canonicalised
+    for key in ("row_indices", "column_indices", "offsets", "offsets_t"):
+        np.testing.assert_array_equal(getattr(m, key).numpy(), g[f"{name}/{key}"])
+    cit, bot = oracle.canonical_tie_order(g[f"{name}/column_indices_t"], g[f"{name}/offsets_t"],
+                                          g[f"{name}/block_offsets_t"])
+    np.testing.assert_array_equal(m.column_indices_t.numpy(), cit)
+    np.testing.assert_array_equal(m.block_offsets_t.numpy(), bot)
+
+
+@pytest.mark.parametrize("name", sorted(cases.CONVERT_CASES))
+def test_conversion_bit_exact(stk, golden, name):
+    g = golden["convert"]
+    rows, cols, sparsity, blocking, seed, dtype = cases.CONVERT_CASES[name]
+    x = cases.convert_input(name)
+    m = stk.ops.to_sparse(x.cuda(), blocking)
+    assert m.is_cuda and m.size() == x.size()
+    _check_meta(m, oracle.to_sparse(x, blocking), name)
+    assert tuple(m.data.shape) == tuple(g[f"{name}/data_shape"])
+    np.testing.assert_array_equal(bits(m.data).ravel(), g[f"{name}/data_bits"].ravel())
+    dense = stk.ops.to_dense(m)
+    np.testing.assert_array_equal(bits(dense), g[f"{name}/dense_bits"].reshape(rows, cols))
+    ri = stk.ops.row_indices(m.size(), m.data, m.offsets, m.column_indices)
+    assert ri.dtype == torch.int16
+    np.testing.assert_array_equal(ri.cpu().numpy(), g[f"{name}/row_indices"])
+    # host tensors are staged through the GPU and come back to the host
+    mh = stk.ops.to_sparse(x, blocking)
+    assert not mh.is_cuda
+    np.testing.assert_array_equal(bits(mh.data).ravel(), g[f"{name}/data_bits"].ravel())
+    np.testing.assert_array_equal(bits(stk.ops.to_dense(mh)), bits(dense))
+
+
+# The reference's conversion test, stk/ops/matrix_ops_test.py:26-58.
+@pytest.mark.parametrize("rows,cols,sparsity,blocking", [
+    (8, 16, 0.0, 1), (8, 16, 0.5, 1), (8, 16, .95, 1), (16, 8, 0.0, 1), (16, 8, 0.5, 1),
+    (16, 8, .95, 1), (8, 16, 0.0, 8), (8, 16, 0.5, 8), (8, 16, 1.0, 8), (16, 8, 0.0, 8),
+    (16, 8, 0.5, 8), (16, 8, 1.0, 8), (128, 256, 0.5, 16), (256, 128, 0.75, 32),
+    (512, 512, .875, 128)])
+def test_format_conversion_round_trip(stk, rows, cols, sparsity, blocking):
+    mask = stk.random.dense_mask(rows, cols, sparsity, blocking)
+    assert mask.shape == (rows, cols)
+    assert set(mask.unique().tolist()) <= {0.0, 1.0}
+    x = (torch.randn(rows, cols) * mask).type(torch.float16)
+    sparse_x = stk.ops.to_sparse(x, blocking)
+    sparse_x.validate()
+    assert sparse_x.dim() == 2 and tuple(sparse_x.size()) == (rows, cols)
+    numblocks = rows // blocking * cols // blocking
+    nnz = round(numblocks * (1 - sparsity)) * blocking ** 2
+    assert sparse_x.nnz == nnz
+    dense_x = stk.ops.to_dense(sparse_x)
+    assert tuple(dense_x.shape) == (rows, cols)
+    assert torch.count_nonzero(dense_x).item() == nnz
+    assert torch.all(torch.eq(x, dense_x))
+    # stk/random/random_ops_test.py:49-69
+    m = stk.random.mask(rows, cols, sparsity, blocking)
+    m.validate()
+    assert m.nnz == nnz and bool((m.data == 1).all())
+
+
+@pytest.mark.parametrize("shape", [(64, 2048, 0.3), (300, 300, 0.6), (2112, 7168, 0.016),
+                                   (16, 32767, 0.01), (1, 1, 1.0), (40, 1536, 0.5)])
+def test_transpose_meta_bit_exact(stk, shape):
+    """Both transpose paths (single-CTA and multi-kernel) against the stable-sort oracle."""
+    from stk_b200.backend import kernels
+    block_rows, block_cols, density = shape
+    rng = np.random.default_rng(block_rows * 7 + block_cols)
+    r, c = np.nonzero(rng.random((block_rows, block_cols)) < density)
+    r16, c16 = r.astype(np.int16), c.astype(np.int16)
+    expect = oracle.transpose(block_cols, r16, c16)
+    got = kernels.transpose_meta(torch.from_numpy(r16).cuda(), torch.from_numpy(c16).cuda(),
+                                 block_cols)
+    for a, b in zip(got, expect):
+        assert a.cpu().numpy().dtype == b.dtype
+        np.testing.assert_array_equal(a.cpu().numpy(), b)
+    cit, offt, bot = (t.cpu().numpy() for t in got)
+    # invariants that hold for any valid transpose
+    assert np.array_equal(np.sort(bot), np.arange(len(r)))
+    assert np.all(np.diff(c16[bot].astype(np.int64)) >= 0)
+    assert np.array_equal(r16[bot], cit)
+
+
+def _gpu_product(stk, name):
+    op, trans_a, trans_b, dtype = cases.MATMUL_CASES[name]
+    inp = cases.matmul_inputs(name)
+    dev = "cuda"
+    meta = [torch.from_numpy(inp[k]).to(dev) for k in ("row_indices", "column_indices", "offsets")]
+    if op == "sdd":
+        topo = stk.Matrix(inp["topo_shape"], torch.empty(len(inp["row_indices"]), 128, 128,
+                                                        dtype=dtype, device=dev), *meta)
+        a, b = inp["a"].to(dev), inp["b"].to(dev)
+        return stk.ops.sdd(a.t() if trans_a else a, b.t() if trans_b else b, topo).data
+    s = stk.Matrix(inp["sparse_shape"], inp["data"].to(dev), *meta)
+    d = inp["dense"].to(dev)
+    if op == "dsd":
+        return stk.ops.dsd(s.t() if trans_a else s, d.t() if trans_b else d)
+    return stk.ops.dds(d.t() if trans_a else d, s.t() if trans_b else s)
+
+
+@pytest.mark.parametrize("name", sorted(cases.MATMUL_CASES))
+def test_products_match_reference_kernels(stk, golden, name):
+    """Against the outputs of the reference's own kernels and against the oracle."""
+    from tests.test_oracle import _from_bits, oracle_product
+    g = golden["matmul"]
+    dtype = cases.MATMUL_CASES[name][3]
+    out = _gpu_product(stk, name)
+    assert out.dtype == dtype and out.is_contiguous()
+    ref = _from_bits(g[f"{name}/out_bits"], g[f"{name}/out_shape"], dtype)
+    assert_product_close(out, ref, name + " vs reference kernels")
+    assert_product_close(out, oracle_product(name), name + " vs oracle")
+
+
+def test_c1_all_ops(stk):
+    """The benchmark's CPU-runnable configuration: seed-0 1024x1024 topology at 25 % density,
+    A [1024,512], B [512,1024] ~ N(0, 0.02), fp16; every op and transpose against the oracle."""
+    np.random.seed(0)
+    torch.manual_seed(0)
+    topo = stk.random.mask(1024, 1024, 0.75, 128)
+    np.testing.assert_array_equal(topo.block_offsets_t.numpy(),
+                                  [0, 7, 3, 12, 13, 1, 4, 15, 8, 10, 5, 14, 2, 6, 9, 11])
+    a = (torch.randn(1024, 512) * 0.02).half()
+    b = (torch.randn(512, 1024) * 0.02).half()
+    r, c = topo.row_indices.numpy(), topo.column_indices.numpy()
+    topo_d = topo.to("cuda")
+    for ta in (False, True):
+        for tb in (False, True):
+            A = a.t().contiguous().cuda().t() if ta else a.cuda()
+            B = b.t().contiguous().cuda().t() if tb else b.cuda()
+            out = stk.ops.sdd(A, B, topo_d)
+            assert_product_close(out.data, oracle.sdd(a, b, r, c, torch.float16), f"sdd {ta}{tb}")
+    vals = (torch.randn(16, 128, 128) * 0.02).half()
+    s = stk.Matrix(topo.size(), vals.cuda(), topo_d.row_indices, topo_d.column_indices,
+                   topo_d.offsets, topo_d.column_indices_t, topo_d.offsets_t,
+                   topo_d.block_offsets_t)
+    s_dense = oracle.to_dense(vals, r, c, (1024, 1024))
+    d = (torch.randn(1024, 512) * 0.02).half()
+    for ts in (False, True):
+        for td in (False, True):
+            D = d.t().contiguous().cuda().t() if td else d.cuda()
+            S = s.t() if ts else s
+            SD = s_dense.t() if ts else s_dense
+            assert_product_close(stk.ops.dsd(S, D), oracle.dsd(SD, d, torch.float16), f"dsd {ts}{td}")
+            Dt = d.t().cuda() if not td else d.cuda().t()  # [512, 1024] logical either way
+            Dt_ref = d.t()
+            assert_product_close(stk.ops.dds(Dt, S), oracle.dds(Dt_ref, SD, torch.float16),
+                                 f"dds {td}{ts}")
+
+
+def test_empty_and_ragged(stk):
+    dev = "cuda"
+    # no blocks at all: SDD is a no-op, DSD / DDS give zeros
+    x = torch.zeros(256, 384, dtype=torch.float16, device=dev)
+    e = stk.ops.to_sparse(x, 128)
+    assert e.data.shape == (0, 128, 128) and e.offsets.tolist() == [0, 0, 0]
+    assert e.offsets_t.tolist() == [0, 0, 0, 0]
+    a = torch.randn(256, 64, dtype=torch.float16, device=dev)
+    b = torch.randn(64, 384, dtype=torch.float16, device=dev)
+    assert stk.ops.sdd(a, b, e).data.shape == (0, 128, 128)
+    d = torch.randn(384, 128, dtype=torch.float16, device=dev)
+    assert torch.count_nonzero(stk.ops.dsd(e, d)).item() == 0
+    d2 = torch.randn(128, 256, dtype=torch.float16, device=dev)
+    out = stk.ops.dds(d2, e)
+    assert out.shape == (128, 384) and torch.count_nonzero(out).item() == 0
+    # empty block rows and columns inside a non-empty matrix
+    y = torch.zeros(512, 512, dtype=torch.bfloat16)
+    y[128:256, 256:384] = torch.randn(128, 128).bfloat16()
+    y[384:, :128] = torch.randn(128, 128).bfloat16()
+    s = stk.ops.to_sparse(y.cuda(), 128)
+    assert s.offsets.tolist() == [0, 0, 1, 1, 2] and s.offsets_t.tolist() == [0, 1, 1, 2, 2]
+    d = (torch.randn(512, 256) * 0.1).bfloat16()
+    assert_product_close(stk.ops.dsd(s, d.cuda()), oracle.dsd(y, d, torch.bfloat16), "ragged dsd")
+    assert_product_close(stk.ops.dsd(s.t(), d.cuda()), oracle.dsd(y.t(), d, torch.bfloat16), "ragged dsd t")
+    d = (torch.randn(256, 512) * 0.1).bfloat16()
+    assert_product_close(stk.ops.dds(d.cuda(), s), oracle.dds(d, y, torch.bfloat16), "ragged dds")
+    assert_product_close(stk.ops.dds(d.cuda(), s.t()), oracle.dds(d, y.t(), torch.bfloat16), "ragged dds t")
+
+
+def test_sdd_inner_dimension_not_multiple_of_64(stk):
+    """K only has to be a multiple of 32 (stk/backend/triton_kernels.py:15-19)."""
+    np.random.seed(3)
+    topo = stk.random.mask(256, 384, 0.5, 128).to("cuda")
+    for k in (32, 96, 224):
+        a = (torch.randn(256, k) * 0.1).half()
+        b = (torch.randn(k, 384) * 0.1).half()
+        ref = oracle.sdd(a, b, topo.row_indices.cpu().numpy(), topo.column_indices.cpu().numpy(),
+                         torch.float16)
+        assert_product_close(stk.ops.sdd(a.cuda(), b.cuda(), topo).data, ref, f"K={k}")
+        assert_product_close(stk.ops.sdd(a.t().contiguous().cuda().t(),
+                                         b.t().contiguous().cuda().t(), topo).data, ref, f"K={k} TT")
+
+
+def test_strided_views_and_errors(stk):
+    np.random.seed(5)
+    topo = stk.random.mask(256, 256, 0.5, 128).to("cuda")
+    big = (torch.randn(256, 512, device="cuda") * 0.1).half()
+    a = big[:, 128:256 + 128]            # row-major view with a leading dimension of 512
+    b = (torch.randn(256, 256, device="cuda") * 0.1).half()[::1, :]
+    ref = oracle.sdd(a.cpu(), b.cpu(), topo.row_indices.cpu().numpy(),
+                     topo.column_indices.cpu().numpy(), torch.float16)
+    assert_product_close(stk.ops.sdd(a, b, topo).data, ref, "ld view")
+    odd = big[:, 1:257]                  # misaligned view: made contiguous by the launcher
+    ref = oracle.sdd(odd.cpu(), b.cpu(), topo.row_indices.cpu().numpy(),
+                     topo.column_indices.cpu().numpy(), torch.float16)
+    assert_product_close(stk.ops.sdd(odd, b, topo).data, ref, "misaligned view")
+    with pytest.raises((AssertionError, ValueError)):
+        stk.ops.sdd(a[:, :100], b[:100], topo)      # K not a multiple of 32
+    with pytest.raises((AssertionError, ValueError)):
+        stk.ops.dsd(topo, b[:128])                  # inner dimensions differ
+    with pytest.raises(ValueError):
+        stk.ops.sdd(a.float(), b.float(), topo)     # unsupported dtype
+    with pytest.raises(RuntimeError):
+        stk.ops.sdd(a.cpu(), b.cpu(), topo)         # no CPU path
