@@ -60,20 +60,30 @@ const char* stk_b200_error_string(int code);
 int stk_b200_device_status(int* status_host);
 
 /*
+ * pair_mode (sdd / dsd / dds): 0 runs one 128x128 output tile per CTA.  1 runs 256x256 supertiles on
+ * CTA pairs (tcgen05 cta_group::2): two neighbouring block rows / columns of the sparse operand are
+ * processed together over the merge of their block lists, which halves the operand traffic per
+ * FLOP when the neighbours' lists mostly coincide (dMoE topologies) and wastes MMA work when they
+ * do not.  Both modes give the same results; mode 1 needs every block row's column_indices (and
+ * every block column's column_indices_t) in ascending order.
+ */
+
+/*
  * SDD: out[p] = lhs[r_p*128:+128, :] @ rhs[:, c_p*128:+128] for every nonzero block p,
  * fp32 accumulation, output rounded to `dtype`.
  * Replaces stk/backend/triton_kernels.py:332-379 (sdd) and :21-68 (_sdd_kernel).
  *   lhs: logical [M,K]; row-major (lhs_colmajor=0, element (m,k) at m*ld_lhs+k) or
- *        column-major (lhs_colmajor=1, element (m,k) at k*ld_lhs+m — an exact .t() view).
+ *        column-major (lhs_colmajor=1, element (m,k) at k*ld_lhs+m - an exact .t() view).
  *   rhs: logical [K,N]; same convention with ld_rhs.
  *   out: [nnz,128,128] contiguous.
+ *   offsets: CSR offsets [M/128+1]; only read when pair_mode = 1 (may be NULL otherwise).
  * nnz == 0 is a no-op.
  */
-int stk_b200_sdd(const void* lhs, const void* rhs, void* out,
+int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const int32_t* offsets,
                  const int16_t* row_indices, const int16_t* column_indices,
                  int64_t M, int64_t N, int64_t K, int64_t nnz,
                  int lhs_colmajor, int64_t ld_lhs, int rhs_colmajor, int64_t ld_rhs,
-                 int dtype, void* stream);
+                 int dtype, int pair_mode, void* stream);
 
 /*
  * DSD: out[M,N] = op(S)[M,K] @ rhs[K,N].
@@ -89,7 +99,7 @@ int stk_b200_dsd(const void* data, const int32_t* offsets, const int16_t* column
                  const int32_t* block_offsets, const void* rhs, void* out,
                  int64_t M, int64_t N, int64_t K, int64_t nnz,
                  int trans_sparse, int rhs_colmajor, int64_t ld_rhs, int64_t ld_out,
-                 int dtype, void* stream);
+                 int dtype, int pair_mode, void* stream);
 
 /*
  * DDS: out[M,N] = lhs[M,K] @ op(S)[K,N].
@@ -104,7 +114,7 @@ int stk_b200_dds(const void* lhs, const void* data, const int32_t* offsets,
                  const int16_t* column_indices, const int32_t* block_offsets, void* out,
                  int64_t M, int64_t N, int64_t K, int64_t nnz,
                  int lhs_colmajor, int64_t ld_lhs, int trans_sparse, int64_t ld_out,
-                 int dtype, void* stream);
+                 int dtype, int pair_mode, void* stream);
 
 /*
  * CSR offsets -> COO row index of every block (int16).

@@ -8,11 +8,71 @@ phases and to_dense (stk/ops/matrix_ops.py:36-85).
 
 Everything here marshals tensors into the C ABI of libstk_b200.so; there is no other code path.
 """
+import os
+
 import torch
 
 from stk_b200.backend import lib as _lib
 
 BLOCK = 128  # the matmul kernels are built for 128x128 blocks
+
+# Which matmul kernel runs: "0" = one 128x128 tile per CTA, "1" = 256x256 supertiles on CTA pairs,
+# "auto" = per topology, from how well neighbouring block rows / columns pair up (see pair_hints).
+PAIR_MODE = os.environ.get("STK_B200_PAIR_MODE", "auto")
+# Fraction of the pair kernel's MMA work that must be useful for it to be chosen.  The pair kernel
+# moves half the operand bytes per FLOP, so it still wins with a good part of its work wasted.
+PAIR_THRESHOLD = 0.7
+_HINT_ATTR = "_stk_b200_pair_hints"
+
+
+def set_pair_hints(column_indices, rows, cols, tiles, is_sorted=True):
+    """Record how a topology pairs up, for callers that know it by construction (no device sync).
+
+    rows / cols / tiles: useful fraction of the pair kernel's work when block rows (2t, 2t+1),
+    block columns (2u, 2u+1), or both, are processed together."""
+    setattr(column_indices, _HINT_ATTR,
+            (column_indices._version, float(rows), float(cols), float(tiles), bool(is_sorted)))
+
+
+def pair_hints(row_indices, column_indices, block_cols):
+    """(rows, cols, tiles, sorted) for a topology; computed once per column_indices tensor.
+
+    rows  = nnz / (2 * number of distinct (row pair, column) positions): DSD with S as stored,
+            DDS with S transposed.
+    cols  = nnz / (2 * distinct (row, column pair)): DSD with S transposed, DDS with S as stored.
+    tiles = nnz / (4 * distinct (row pair, column pair)): SDD.
+    The first use of an unknown topology reads four numbers back from the device (one sync)."""
+    cached = getattr(column_indices, _HINT_ATTR, None)
+    if cached is not None and cached[0] == column_indices._version:
+        return cached[1:]
+    nnz = column_indices.numel()
+    if nnz == 0:
+        set_pair_hints(column_indices, 0.0, 0.0, 0.0, True)
+        return getattr(column_indices, _HINT_ATTR)[1:]
+    r = row_indices.long()
+    c = column_indices.long()
+    half_cols = (block_cols + 1) // 2
+    in_order = ((c[1:] > c[:-1]) | (r[1:] > r[:-1])).all() if nnz > 1 else torch.ones((), device=c.device)
+    counts = torch.stack([
+        torch.unique((r >> 1) * block_cols + c).numel() * torch.ones((), device=c.device),
+        torch.unique(r * half_cols + (c >> 1)).numel() * torch.ones((), device=c.device),
+        torch.unique((r >> 1) * half_cols + (c >> 1)).numel() * torch.ones((), device=c.device),
+        in_order.to(torch.float32)]).tolist()
+    set_pair_hints(column_indices, nnz / (2.0 * counts[0]), nnz / (2.0 * counts[1]),
+                   nnz / (4.0 * counts[2]), counts[3] != 0)
+    return getattr(column_indices, _HINT_ATTR)[1:]
+
+
+def _use_pairs(kind, row_indices, column_indices, block_cols):
+    """kind: "rows", "cols" or "tiles" - which neighbours the product would pair."""
+    if PAIR_MODE == "0":
+        return 0
+    rows, cols, tiles, is_sorted = pair_hints(row_indices, column_indices, block_cols)
+    if kind == "tiles" and not is_sorted:
+        return 0  # the SDD tile walk needs ascending columns inside every block row
+    if PAIR_MODE == "1":
+        return 1
+    return int({"rows": rows, "cols": cols, "tiles": tiles}[kind] >= PAIR_THRESHOLD)
 
 
 class DimensionError(AssertionError, ValueError):
@@ -78,13 +138,15 @@ def dsd(shape, data, offsets, row_indices, column_indices, offsets_t, column_ind
     rhs, rhs_colmajor, ld_rhs = _dense_layout(rhs)
     if transpose_a:
         meta = (offsets_t, column_indices_t, block_offsets_t)
+        pairs = _use_pairs("cols", row_indices, column_indices, M // BLOCK)
     else:
         meta = (offsets, column_indices, None)
+        pairs = _use_pairs("rows", row_indices, column_indices, K // BLOCK)
     with torch.cuda.device(out.device):
         rc = _lib.load().stk_b200_dsd(
             _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),
             _lib.ptr(rhs), _lib.ptr(out), M, N, K, data.shape[0], int(bool(transpose_a)),
-            rhs_colmajor, ld_rhs, out.stride(0), _lib.dtype_code(rhs.dtype),
+            rhs_colmajor, ld_rhs, out.stride(0), _lib.dtype_code(rhs.dtype), pairs,
             _lib.stream_ptr(out.device))
     _lib.check(rc, "stk_b200_dsd")
 
@@ -102,13 +164,15 @@ def dds(lhs, shape, data, offsets, row_indices, column_indices, offsets_t, colum
     lhs, lhs_colmajor, ld_lhs = _dense_layout(lhs)
     if transpose_b:
         meta = (offsets, column_indices, None)
+        pairs = _use_pairs("rows", row_indices, column_indices, K // BLOCK)
     else:
         meta = (offsets_t, column_indices_t, block_offsets_t)
+        pairs = _use_pairs("cols", row_indices, column_indices, N // BLOCK)
     with torch.cuda.device(out.device):
         rc = _lib.load().stk_b200_dds(
             _lib.ptr(lhs), _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),
             _lib.ptr(out), M, N, K, data.shape[0], lhs_colmajor, ld_lhs, int(bool(transpose_b)),
-            out.stride(0), _lib.dtype_code(lhs.dtype), _lib.stream_ptr(out.device))
+            out.stride(0), _lib.dtype_code(lhs.dtype), pairs, _lib.stream_ptr(out.device))
     _lib.check(rc, "stk_b200_dds")
 
 
@@ -123,17 +187,20 @@ def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices):
     _check_blocks(out)
     lhs, lhs_colmajor, ld_lhs = _dense_layout(lhs)
     rhs, rhs_colmajor, ld_rhs = _dense_layout(rhs)
+    pairs = _use_pairs("tiles", row_indices, column_indices, N // BLOCK)
     with torch.cuda.device(out.device):
         rc = _lib.load().stk_b200_sdd(
-            _lib.ptr(lhs), _lib.ptr(rhs), _lib.ptr(out), _lib.ptr(row_indices),
+            _lib.ptr(lhs), _lib.ptr(rhs), _lib.ptr(out), _lib.ptr(offsets), _lib.ptr(row_indices),
             _lib.ptr(column_indices), M, N, K, out.shape[0], lhs_colmajor, ld_lhs, rhs_colmajor,
-            ld_rhs, _lib.dtype_code(out.dtype), _lib.stream_ptr(out.device))
+            ld_rhs, _lib.dtype_code(out.dtype), pairs, _lib.stream_ptr(out.device))
     _lib.check(rc, "stk_b200_sdd")
 
 
 def row_indices(shape, data, offsets, column_indices, out):
     """out[p] = block row of block p (CSR offsets -> COO)."""
     _require_cuda(offsets, out)
+    if out.dtype != torch.int16:
+        raise ValueError(f"row indices are int16, got an output of {out.dtype}")
     block_rows = offsets.numel() - 1
     with torch.cuda.device(out.device):
         rc = _lib.load().stk_b200_row_indices(

@@ -1,0 +1,209 @@
+// C entry points of the three block-sparse products: argument checks, tensor-map encoding and
+// the choice between the single-CTA 128x128 kernel and the CTA-pair 256x256 kernel.
+#pragma once
+#include "bsmm_pair_sm100.cuh"
+#include "bsmm_sm100.cuh"
+
+namespace stk {
+
+static int check_dtype_dims(int dtype, int64_t M, int64_t N, int64_t K, int64_t nnz, int64_t k_mult) {
+  if (dtype != STK_F16 && dtype != STK_BF16) return STK_ERR_BAD_DTYPE;
+  if (M <= 0 || N <= 0 || K <= 0 || nnz < 0 || M % kBlk || N % kBlk || K % k_mult) return STK_ERR_BAD_DIMS;
+  if (nnz * kBlk > INT32_MAX - 2 * kBlk || M > INT32_MAX / 2 || N > INT32_MAX / 2 || K > INT32_MAX / 2 ||
+      (M / kBlk) * (N / kBlk) > INT32_MAX)
+    return STK_ERR_TOO_LARGE;
+  return STK_OK;
+}
+
+// Work items per CTA pair below which the static round-robin schedule leaves too much idle time.
+constexpr int kItemsPerPairTarget = 16;
+
+}  // namespace stk
+
+using namespace stk;
+
+extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const int32_t* offsets,
+                            const int16_t* row_indices, const int16_t* column_indices, int64_t M,
+                            int64_t N, int64_t K, int64_t nnz, int lhs_colmajor, int64_t ld_lhs,
+                            int rhs_colmajor, int64_t ld_rhs, int dtype, int pair_mode,
+                            void* stream) {
+  int rc = check_dtype_dims(dtype, M, N, K, nnz, 32);
+  if (rc != STK_OK) return rc;
+  if (nnz == 0) return STK_OK;
+  if (out == nullptr || row_indices == nullptr || column_indices == nullptr)
+    return STK_ERR_NULL_POINTER;
+  if (pair_mode && offsets == nullptr) return STK_ERR_NULL_POINTER;
+  if (!aligned16(out)) return STK_ERR_BAD_LAYOUT;
+  if ((rc = check_dense(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) return rc;
+  if ((rc = check_dense(rhs, ld_rhs, rhs_colmajor ? K : N)) != STK_OK) return rc;
+
+  CUtensorMap tmA, tmB;
+  // lhs [M,K]: row-major means K contiguous.
+  if ((rc = encode_dense(&tmA, lhs, dtype, M, K, ld_lhs, !lhs_colmajor)) != STK_OK) return rc;
+  // rhs [K,N]: row-major means N contiguous; column-major means K contiguous.
+  if ((rc = encode_dense(&tmB, rhs, dtype, N, K, ld_rhs, rhs_colmajor)) != STK_OK) return rc;
+  const int k_steps = static_cast<int>((K + kBK - 1) / kBK);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  if (pair_mode) {
+    PairDeviceInfo* d = nullptr;
+    if ((rc = pair_device_info(&d)) != STK_OK) return rc;
+    const int block_rows = static_cast<int>(M / kBlk), block_cols = static_cast<int>(N / kBlk);
+    const int row_pairs = (block_rows + 1) / 2;
+    // Split every row pair's column range into segments until there is enough parallel slack.
+    int segments = (kItemsPerPairTarget * d->max_pairs + row_pairs - 1) / row_pairs;
+    const int max_segments = (block_cols + 1) / 2;
+    if (segments > max_segments) segments = max_segments;
+    if (segments < 1) segments = 1;
+    PairParams p{};
+    p.mode = kModeSDD;
+    p.a_mn = lhs_colmajor ? 1 : 0;
+    p.b_mn = rhs_colmajor ? 0 : 1;
+    p.fmt = dtype;
+    p.inner = segments;
+    p.num_items = row_pairs * segments;
+    p.k_steps = k_steps;
+    p.num_lists = block_rows;
+    p.col_idx = column_indices;
+    p.offsets = offsets;
+    p.out = out;
+    p.ldc = kBlk;
+    CUtensorMap tmC;  // the blocks as one [nnz*128, 128] matrix
+    if ((rc = encode_map(&tmC, out, dtype, kBlk, nnz * kBlk, kBlk, kBlk)) != STK_OK) return rc;
+    return launch_pair(tmA, tmB, tmC, p, s);
+  }
+
+  BsmmParams p{};
+  p.mode = kModeSDD;
+  p.a_mn = lhs_colmajor ? 1 : 0;
+  p.b_mn = rhs_colmajor ? 0 : 1;
+  p.fmt = dtype;
+  p.num_tiles = static_cast<int>(nnz);
+  p.tiles_inner = 1;
+  p.k_steps = k_steps;
+  p.row_idx = row_indices;
+  p.col_idx = column_indices;
+  p.out = out;
+  p.ldc = kBlk;
+  return launch(tmA, tmB, p, s);
+}
+
+extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int16_t* column_indices,
+                            const int32_t* block_offsets, const void* rhs, void* out, int64_t M,
+                            int64_t N, int64_t K, int64_t nnz, int trans_sparse, int rhs_colmajor,
+                            int64_t ld_rhs, int64_t ld_out, int dtype, int pair_mode, void* stream) {
+  int rc = check_dtype_dims(dtype, M, N, K, nnz, kBlk);
+  if (rc != STK_OK) return rc;
+  if ((rc = check_dense(out, ld_out, N)) != STK_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (nnz == 0) {
+    // No blocks at all: the product is zero.
+    return cudaMemset2DAsync(out, ld_out * 2, 0, N * 2, M, s) == cudaSuccess ? STK_OK
+                                                                             : STK_ERR_LAUNCH;
+  }
+  if (data == nullptr || offsets == nullptr || column_indices == nullptr) return STK_ERR_NULL_POINTER;
+  if (trans_sparse && block_offsets == nullptr) return STK_ERR_NULL_POINTER;
+  if (!aligned16(data)) return STK_ERR_BAD_LAYOUT;
+  if ((rc = check_dense(rhs, ld_rhs, rhs_colmajor ? K : N)) != STK_OK) return rc;
+
+  CUtensorMap tmA, tmB;
+  // A = data[blk] as stored (its columns are K) or transposed (its columns are M).
+  if ((rc = encode_sparse(&tmA, data, dtype, nnz, !trans_sparse)) != STK_OK) return rc;
+  if ((rc = encode_dense(&tmB, rhs, dtype, N, K, ld_rhs, rhs_colmajor)) != STK_OK) return rc;
+
+  if (pair_mode) {
+    PairParams p{};
+    p.mode = kModeDSD;
+    p.a_mn = trans_sparse ? 1 : 0;
+    p.b_mn = rhs_colmajor ? 0 : 1;
+    p.fmt = dtype;
+    p.num_lists = static_cast<int>(M / kBlk);
+    p.inner = static_cast<int>((N + 2 * kBlk - 1) / (2 * kBlk));
+    p.num_items = ((p.num_lists + 1) / 2) * p.inner;
+    p.zero_coord = static_cast<int>(nnz * kBlk);
+    p.out_rows = static_cast<int>(M);
+    p.out_cols = static_cast<int>(N);
+    p.col_idx = column_indices;
+    p.offsets = offsets;
+    p.blk_idx = block_offsets;
+    p.out = out;
+    p.ldc = ld_out;
+    CUtensorMap tmC;
+    if ((rc = encode_map(&tmC, out, dtype, N, M, ld_out, kBlk)) != STK_OK) return rc;
+    return launch_pair(tmA, tmB, tmC, p, s);
+  }
+
+  BsmmParams p{};
+  p.mode = kModeDSD;
+  p.a_mn = trans_sparse ? 1 : 0;
+  p.b_mn = rhs_colmajor ? 0 : 1;
+  p.fmt = dtype;
+  p.tiles_inner = static_cast<int>(N / kBlk);
+  p.num_tiles = static_cast<int>((M / kBlk) * (N / kBlk));
+  p.col_idx = column_indices;
+  p.offsets = offsets;
+  p.blk_idx = block_offsets;
+  p.out = out;
+  p.ldc = ld_out;
+  return launch(tmA, tmB, p, s);
+}
+
+extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* offsets,
+                            const int16_t* column_indices, const int32_t* block_offsets, void* out,
+                            int64_t M, int64_t N, int64_t K, int64_t nnz, int lhs_colmajor,
+                            int64_t ld_lhs, int trans_sparse, int64_t ld_out, int dtype,
+                            int pair_mode, void* stream) {
+  int rc = check_dtype_dims(dtype, M, N, K, nnz, kBlk);
+  if (rc != STK_OK) return rc;
+  if ((rc = check_dense(out, ld_out, N)) != STK_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (nnz == 0) {
+    return cudaMemset2DAsync(out, ld_out * 2, 0, N * 2, M, s) == cudaSuccess ? STK_OK
+                                                                             : STK_ERR_LAUNCH;
+  }
+  if (data == nullptr || offsets == nullptr || column_indices == nullptr) return STK_ERR_NULL_POINTER;
+  if (!trans_sparse && block_offsets == nullptr) return STK_ERR_NULL_POINTER;
+  if (!aligned16(data)) return STK_ERR_BAD_LAYOUT;
+  if ((rc = check_dense(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) return rc;
+
+  CUtensorMap tmA, tmB;
+  if ((rc = encode_dense(&tmA, lhs, dtype, M, K, ld_lhs, !lhs_colmajor)) != STK_OK) return rc;
+  // B = data[blk] as stored (its columns are N) or transposed (its columns are K).
+  if ((rc = encode_sparse(&tmB, data, dtype, nnz, trans_sparse)) != STK_OK) return rc;
+
+  if (pair_mode) {
+    PairParams p{};
+    p.mode = kModeDDS;
+    p.a_mn = lhs_colmajor ? 1 : 0;
+    p.b_mn = trans_sparse ? 0 : 1;
+    p.fmt = dtype;
+    p.num_lists = static_cast<int>(N / kBlk);
+    p.inner = static_cast<int>((M + 2 * kBlk - 1) / (2 * kBlk));
+    p.num_items = ((p.num_lists + 1) / 2) * p.inner;
+    p.zero_coord = static_cast<int>(nnz * kBlk);
+    p.out_rows = static_cast<int>(M);
+    p.out_cols = static_cast<int>(N);
+    p.col_idx = column_indices;
+    p.offsets = offsets;
+    p.blk_idx = block_offsets;
+    p.out = out;
+    p.ldc = ld_out;
+    CUtensorMap tmC;
+    if ((rc = encode_map(&tmC, out, dtype, N, M, ld_out, kBlk)) != STK_OK) return rc;
+    return launch_pair(tmA, tmB, tmC, p, s);
+  }
+
+  BsmmParams p{};
+  p.mode = kModeDDS;
+  p.a_mn = lhs_colmajor ? 1 : 0;
+  p.b_mn = trans_sparse ? 0 : 1;
+  p.fmt = dtype;
+  p.tiles_inner = static_cast<int>(M / kBlk);
+  p.num_tiles = static_cast<int>((M / kBlk) * (N / kBlk));
+  p.col_idx = column_indices;
+  p.offsets = offsets;
+  p.blk_idx = block_offsets;
+  p.out = out;
+  p.ldc = ld_out;
+  return launch(tmA, tmB, p, s);
+}

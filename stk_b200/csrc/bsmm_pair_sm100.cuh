@@ -1,0 +1,581 @@
+// Block-sparse matmul on CTA PAIRS (tcgen05 cta_group::2): 256x256 output supertiles.
+//
+// Why: the kernel in bsmm_sm100.cuh computes one 128x128 tile per CTA and has to pull 32 KiB of
+// operands through L2 for every 128x128x64 of MMA work (64 FLOP/B); measured on B200 it saturates
+// the L2->SM fabric at ~11.7 TB/s and stops at ~45 % of the tensor peak.  A pair of CTAs that
+// shares one 256-row MMA needs the same 32 KiB per CTA for twice the work (128 FLOP/B): each CTA
+// loads its own 128 rows of A and its own 128 columns of B, the hardware reads both halves.
+//
+// A supertile needs two A row-blocks that walk the SAME K sequence and two B column-blocks:
+//
+//   DSD  rows (2t, 2t+1) of op(S)  x  256 columns of the dense operand.  The K sequence is the MERGE of
+//        the two block rows' column lists; where a row has no block at a K position its A tile is
+//        fetched from an out-of-range TMA coordinate, which yields zeros.
+//   DDS  256 rows of the dense operand  x  block columns (2t, 2t+1) of op(S), K = merge of their lists.
+//   SDD  block rows (2t, 2t+1)  x  block columns (2u, 2u+1); the four blocks that exist are stored.
+//
+// Results are exact for ANY sorted topology; the layout only pays off when neighbouring block
+// rows / columns share most of their lists (dMoE topologies do: all rows of one expert are alike).
+// The host picks this kernel or the 128x128 kernel per call.
+//
+// Roles per CTA (224 threads): warp 0 = TMA producer of the A tiles, warp 6 = TMA producer of the B
+// tiles, warp 1 = TMEM owner (and, in the leader CTA, the MMA issuer), warps 2..5 = epilogue.  The MMA issuer does not know the tiles: it consumes a
+// stream of pipeline stages, each tagged FIRST / LAST (of a tile) or END by the leader's producer.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/stk_b200.h"
+#include "bsmm_sm100.cuh"
+#include "sm100_ptx.cuh"
+#include "status.cuh"
+
+namespace stk {
+
+constexpr int kPThreads = 224;       // warps: 0 A-producer, 1 MMA / TMEM, 2..5 epilogue, 6 B-producer
+constexpr int kPProducerBWarp = 6;
+constexpr int kPStages = 6;
+constexpr int kPAccCols = 256;   // one accumulator: 128 lanes x 256 fp32 columns per CTA
+constexpr int kPTmemCols = 512;  // two accumulators
+constexpr int kPNumBars = 2 * kPStages + 4;
+constexpr int kOutStageBytes = kBlk * 64 * 2;  // one 128-row x 64-column 16-bit output sub-tile
+constexpr int kPSmemBytes =
+    kPStages * kStageBytes + 2 * kOutStageBytes + kPNumBars * 8 + kPStages * 4 + 16 + 1024;
+constexpr int kNoBlock = 0x7fffffff;
+
+enum : uint32_t { kFlagFirst = 1u, kFlagLast = 2u, kFlagEnd = 4u };
+
+#ifdef STK_EXP_PROFILE  // experiment: where each role of each CTA spends its cycles
+__device__ long long g_prof[160][8];
+#define PROF_DECL long long prof_wait = 0, prof_t0 = clock64(), prof_tmp = 0; (void)prof_tmp
+#define PROF_WAIT_BEGIN prof_tmp = clock64()
+#define PROF_WAIT_END prof_wait += clock64() - prof_tmp
+#define PROF_STORE(slot) do { g_prof[blockIdx.x][slot] = prof_wait; g_prof[blockIdx.x][slot + 1] = clock64() - prof_t0; } while (0)
+#else
+#define PROF_DECL
+#define PROF_WAIT_BEGIN
+#define PROF_WAIT_END
+#define PROF_STORE(slot)
+#endif
+
+struct PairParams {
+  int mode;
+  int a_mn, b_mn, fmt;
+  int num_items;    // static work items, dealt round-robin to the CTA pairs
+  int inner;        // DSD: N supertiles per row pair; DDS: M supertiles per column pair; SDD: segments per row pair
+  int k_steps;      // SDD: ceil(K / 64)
+  int num_lists;    // DSD: block rows of op(S); DDS: block columns of op(S); SDD: block rows of the topology
+  int zero_coord;   // an out-of-range row of the sparse tensor map (nnz * 128): reads as zeros
+  int out_rows, out_cols;  // DSD/DDS: extent of the dense output in elements
+  const int16_t* col_idx;
+  const int32_t* offsets;
+  const int32_t* blk_idx;  // nullptr: block j is data[j]
+  void* out;
+  long long ldc;
+};
+
+// Two-pointer merge of the K lists of a pair of block rows (DSD) / block columns (DDS).
+struct MergeWalker {
+  const int16_t* col;
+  const int32_t* blk;
+  int ia, a1, ib, b1;
+  __device__ __forceinline__ void init(const PairParams& p, int t) {
+    col = p.col_idx;
+    blk = p.blk_idx;
+    const int la = 2 * t, lb = 2 * t + 1;
+    ia = p.offsets[la];
+    a1 = p.offsets[la + 1];
+    if (lb < p.num_lists) {
+      ib = a1;  // consecutive lists are adjacent in the metadata
+      b1 = p.offsets[lb + 1];
+    } else {
+      ib = b1 = 0;
+    }
+  }
+  __device__ __forceinline__ bool empty() const { return ia >= a1 && ib >= b1; }
+  // Next K position; blk_a / blk_b = index into data of the block each list has there, or kNoBlock.
+  __device__ __forceinline__ void next(int& kpos, int& blk_a, int& blk_b) {
+    const int ca = ia < a1 ? static_cast<int>(__ldg(col + ia)) : kNoBlock;
+    const int cb = ib < b1 ? static_cast<int>(__ldg(col + ib)) : kNoBlock;
+    kpos = min(ca, cb);
+    blk_a = blk_b = kNoBlock;
+    if (ca == kpos) {
+      blk_a = blk ? __ldg(blk + ia) : ia;
+      ++ia;
+    }
+    if (cb == kpos) {
+      blk_b = blk ? __ldg(blk + ib) : ib;
+      ++ib;
+    }
+  }
+};
+
+// Walks the 2x2 block tiles of one row pair of an SDD topology inside one column segment.
+struct TileWalker {
+  const int16_t* col;
+  int ia, a1, ib, b1, u_end;
+  __device__ __forceinline__ int lower_bound(int lo, int hi, int c_min) const {
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (static_cast<int>(__ldg(col + mid)) < c_min) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+  }
+  __device__ __forceinline__ void init(const PairParams& p, int t, int seg) {
+    col = p.col_idx;
+    const int ra = 2 * t, rb = 2 * t + 1;
+    int a0 = p.offsets[ra];
+    a1 = p.offsets[ra + 1];
+    int b0 = a1;
+    b1 = rb < p.num_lists ? p.offsets[rb + 1] : a1;
+    ia = a1;
+    ib = b1;
+    u_end = 0;
+    if (a0 >= a1 && b0 >= b1) return;  // no block in either row
+    int c_min = kNoBlock, c_max = -1;
+    if (a0 < a1) {
+      c_min = min(c_min, static_cast<int>(__ldg(col + a0)));
+      c_max = max(c_max, static_cast<int>(__ldg(col + a1 - 1)));
+    }
+    if (b0 < b1) {
+      c_min = min(c_min, static_cast<int>(__ldg(col + b0)));
+      c_max = max(c_max, static_cast<int>(__ldg(col + b1 - 1)));
+    }
+    const int u_min = c_min >> 1, n_u = (c_max >> 1) - u_min + 1;
+    const int u_lo = u_min + static_cast<int>((static_cast<long long>(seg) * n_u) / p.inner);
+    u_end = u_min + static_cast<int>((static_cast<long long>(seg + 1) * n_u) / p.inner);
+    ia = lower_bound(a0, a1, 2 * u_lo);
+    ib = lower_bound(b0, b1, 2 * u_lo);
+  }
+  // Next tile: u = column pair; p[r][h] = block index of (row 2t+r, column 2u+h) or kNoBlock.
+  __device__ __forceinline__ bool next(int& u, int (&p)[2][2]) {
+    const int ca = ia < a1 ? static_cast<int>(__ldg(col + ia)) : kNoBlock;
+    const int cb = ib < b1 ? static_cast<int>(__ldg(col + ib)) : kNoBlock;
+    const int c = min(ca, cb);
+    if (c == kNoBlock || (c >> 1) >= u_end) return false;
+    u = c >> 1;
+    p[0][0] = p[0][1] = p[1][0] = p[1][1] = kNoBlock;
+#pragma unroll
+    for (int rep = 0; rep < 2; ++rep) {
+      if (ia < a1) {
+        const int cc = static_cast<int>(__ldg(col + ia));
+        if ((cc >> 1) == u) { p[0][cc & 1] = ia; ++ia; }
+      }
+      if (ib < b1) {
+        const int cc = static_cast<int>(__ldg(col + ib));
+        if ((cc >> 1) == u) { p[1][cc & 1] = ib; ++ib; }
+      }
+    }
+    return true;
+  }
+};
+
+__device__ __forceinline__ void load_operand_pair(const CUtensorMap* tm, uint32_t smem_dst,
+                                                  uint32_t leader_bar, int mn_major, int mn_elem,
+                                                  int k_elem) {
+  if (!mn_major) {
+    tma_load_2d_pair(smem_dst, tm, leader_bar, k_elem, mn_elem);
+  } else {
+    tma_load_2d_pair(smem_dst, tm, leader_bar, mn_elem, k_elem);
+    tma_load_2d_pair(smem_dst + kOperandTileBytes / 2, tm, leader_bar, mn_elem + 64, k_elem);
+  }
+}
+
+// Barrier among the 128 epilogue threads of a CTA (hardware barrier 1; 0 is __syncthreads).
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// The 128 epilogue threads of one CTA move `ncols` accumulator columns (a multiple of 64, starting
+// at TMEM column `col0`) to the output: TMEM -> registers -> 16-bit -> a 128x64 staging tile in
+// shared memory (128-byte swizzle, conflict-free 16-byte stores) -> one TMA store per sub-tile.
+// Two staging tiles alternate; `sub` counts sub-tiles over the whole kernel.
+__device__ __forceinline__ void drain_to_output(uint32_t t_addr, int col0, int ncols, int fmt,
+                                                const CUtensorMap* tmC, int out_x, int out_y,
+                                                uint32_t staging_base, int row, bool issuer,
+                                                uint32_t& sub) {
+  for (int c = 0; c < ncols; c += 64, ++sub) {
+    const uint32_t buf = staging_base + (sub & 1u) * kOutStageBytes;
+    if (issuer) tma_store_wait_read<1>();  // the store that last read this buffer is done with it
+    epilogue_sync();
+    uint32_t r0[32], r1[32];
+    tmem_ld_32x32(t_addr + col0 + c, r0);
+    tmem_ld_32x32(t_addr + col0 + c + 32, r1);
+    tmem_ld_wait();
+    uint32_t packed[32];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float a0 = __uint_as_float(r0[2 * i]), a1 = __uint_as_float(r0[2 * i + 1]);
+      const float b0 = __uint_as_float(r1[2 * i]), b1 = __uint_as_float(r1[2 * i + 1]);
+      if (fmt == STK_BF16) {
+        const __nv_bfloat162 va = __floats2bfloat162_rn(a0, a1), vb = __floats2bfloat162_rn(b0, b1);
+        packed[i] = *reinterpret_cast<const uint32_t*>(&va);
+        packed[16 + i] = *reinterpret_cast<const uint32_t*>(&vb);
+      } else {
+        const __half2 va = __floats2half2_rn(a0, a1), vb = __floats2half2_rn(b0, b1);
+        packed[i] = *reinterpret_cast<const uint32_t*>(&va);
+        packed[16 + i] = *reinterpret_cast<const uint32_t*>(&vb);
+      }
+    }
+    const uint32_t row_addr = buf + row * 128;
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) {
+      const uint32_t addr = row_addr + ((ch ^ (row & 7)) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * ch]),
+                   "r"(packed[4 * ch + 1]), "r"(packed[4 * ch + 2]), "r"(packed[4 * ch + 3])
+                   : "memory");
+    }
+    fence_proxy_async_smem();
+    epilogue_sync();
+    if (issuer) {
+      tma_store_2d(tmC, buf, out_x + c, out_y);
+      tma_store_commit();
+    }
+  }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1)
+bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const PairParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  const uint32_t smem_base = smem_u32(smem);
+
+  const uint32_t staging_base = smem_base + kPStages * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPStages * kStageBytes + 2 * kOutStageBytes);
+  const uint32_t bars_base = staging_base + 2 * kOutStageBytes;
+  auto full_bar = [&](int s) { return bars_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bars_base + 8u * (kPStages + s); };
+  auto tfull_bar = [&](int a) { return bars_base + 8u * (2 * kPStages + a); };
+  auto tempty_bar = [&](int a) { return bars_base + 8u * (2 * kPStages + 2 + a); };
+  volatile uint32_t* stage_flags = reinterpret_cast<volatile uint32_t*>(bars + kPNumBars);
+  uint32_t* tmem_slot = const_cast<uint32_t*>(stage_flags) + kPStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* epilogue_go = abort_flag + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(cluster_ctarank());  // 0 = leader
+  const int pair_id = static_cast<int>(cluster_id_x());
+  const int num_pairs = static_cast<int>(num_clusters_x());
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPStages; ++s) {
+      mbar_init(full_bar(s), 1);   // leader's copy is the one in use: its producer's arrive + bytes of both CTAs
+      mbar_init(empty_bar(s), 1);  // one multicast commit per phase
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);   // one multicast commit per tile
+      mbar_init(tempty_bar(a), 8);  // leader's copy: four epilogue warps of each CTA
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmC);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), kPTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything is sent to them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 || warp == kPProducerBWarp) {
+    // ------------------------------------------------------------------ TMA producers (both CTAs)
+    // Warp 0 fetches this CTA's A tiles, warp 6 its B tiles; each walks the metadata on its own, so
+    // that neither issue stream has to carry the other's instructions.  One lane works.
+    if (lane == 0) {
+      const bool is_a = warp == 0;
+      const CUtensorMap* tm = is_a ? &tmA : &tmB;
+      const int mn_major = is_a ? p.a_mn : p.b_mn;
+      const uint32_t dst0 = smem_base + (is_a ? 0 : kOperandTileBytes);
+      const uint32_t leader_full0 = map_to_cta(full_bar(0), 0);
+      const bool arms = is_a && rank == 0;  // this thread arms the leader's barrier and tags the stage
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      PROF_DECL;
+      // One pipeline stage of this operand: the tile at (mn_elem, k_elem).
+      auto produce = [&](int mn_elem, int k_elem, uint32_t flags) {
+        PROF_WAIT_BEGIN;
+        ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
+        PROF_WAIT_END;
+        if (!ok) return;
+        if (arms) {
+          stage_flags[stage] = flags;
+#ifdef STK_EXP_SKIP_TMA  // experiment: MMA issue rate with the operand fetch taken out
+          mbar_arrive(full_bar(stage));
+#else
+          mbar_arrive_expect_tx(full_bar(stage), 2 * kStageBytes);
+#endif
+        }
+#ifndef STK_EXP_SKIP_TMA
+        load_operand_pair(tm, dst0 + stage * kStageBytes, leader_full0 + 8u * stage, mn_major, mn_elem,
+                          k_elem);
+#endif
+        if (++stage == kPStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      };
+      // Is this thread's operand the sparse one (DSD: A, DDS: B)?
+      const bool sparse_side = (p.mode == kModeDSD) == is_a;
+      for (int item = pair_id; item < p.num_items && ok; item += num_pairs) {
+        const int outer = item / p.inner, inner = item - outer * p.inner;
+        if (p.mode == kModeSDD) {
+          TileWalker w;
+          w.init(p, outer, inner);
+          int u, blk[2][2];
+          while (ok && w.next(u, blk)) {
+            const int mn_elem = (2 * (is_a ? outer : u) + rank) * kBlk;
+            for (int ks = 0; ks < p.k_steps && ok; ++ks)
+              produce(mn_elem, ks * kBK,
+                      (ks == 0 ? kFlagFirst : 0u) | (ks == p.k_steps - 1 ? kFlagLast : 0u));
+          }
+        } else {
+          MergeWalker w;
+          w.init(p, outer);
+          uint32_t first = kFlagFirst;
+          while (ok && !w.empty()) {
+            int kpos, blk_a, blk_b;
+            w.next(kpos, blk_a, blk_b);
+            const uint32_t last = w.empty() ? kFlagLast : 0u;
+            int mn_elem, k_elem;
+            if (sparse_side) {
+              // this CTA's block of the pair, or an out-of-range coordinate that reads as zeros
+              const int my_blk = rank ? blk_b : blk_a;
+              const int row0 = my_blk == kNoBlock ? p.zero_coord : my_blk * kBlk;
+              mn_elem = mn_major ? 0 : row0;
+              k_elem = mn_major ? row0 : 0;
+            } else {
+              mn_elem = inner * 2 * kBlk + rank * kBlk;
+              k_elem = kpos * kBlk;
+            }
+            produce(mn_elem, k_elem, first);
+            if (ok) produce(mn_elem, k_elem + kBK, last);
+            first = 0u;
+          }
+        }
+      }
+      PROF_STORE(is_a ? 0 : 6);
+      // The leader tells its MMA issuer that the stream is over.
+      if (arms && ok) {
+        if (mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+          stage_flags[stage] = kFlagEnd;
+          mbar_arrive(full_bar(stage));
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (rank == 0 && lane == 0) {
+      const uint32_t idesc = make_idesc_f16(p.fmt, p.a_mn, p.b_mn, 256, 256);
+      const uint32_t a_lo0 = smem_desc_lo(smem_base, p.a_mn ? kOperandTileBytes / 2 : 16u);
+      const uint32_t b_lo0 = smem_desc_lo(smem_base + kOperandTileBytes, p.b_mn ? kOperandTileBytes / 2 : 16u);
+      const uint32_t a_kstep = (p.a_mn ? kUmmaK * 128u : kUmmaK * 2u) >> 4;
+      const uint32_t b_kstep = (p.b_mn ? kUmmaK * 128u : kUmmaK * 2u) >> 4;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      PROF_DECL;
+#ifdef STK_EXP_PROFILE
+      long long prof_acc_wait = 0;
+#endif
+      while (true) {
+        PROF_WAIT_BEGIN;
+        const bool got = mbar_wait(full_bar(stage), phase, abort_flag);
+        PROF_WAIT_END;
+        if (!got) break;
+        const uint32_t flags = stage_flags[stage];
+        if (flags & kFlagEnd) break;
+        if (flags & kFlagFirst) {
+#ifdef STK_EXP_PROFILE
+          const long long t1 = clock64();
+#endif
+          if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) break;
+#ifdef STK_EXP_PROFILE
+          prof_acc_wait += clock64() - t1;
+#endif
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kPAccCols);
+        const uint32_t a_lo = a_lo0 + stage * (kStageBytes >> 4);
+        const uint32_t b_lo = b_lo0 + stage * (kStageBytes >> 4);
+#ifndef STK_EXP_SKIP_MMA  // experiment: operand fetch rate with the MMAs taken out
+        umma_f16_pair(d_tmem, smem_desc_join(a_lo), smem_desc_join(b_lo), idesc, (flags & kFlagFirst) ? 0u : 1u);
+        umma_f16_pair(d_tmem, smem_desc_join(a_lo + a_kstep), smem_desc_join(b_lo + b_kstep), idesc, 1u);
+        umma_f16_pair(d_tmem, smem_desc_join(a_lo + 2 * a_kstep), smem_desc_join(b_lo + 2 * b_kstep), idesc, 1u);
+        umma_f16_pair(d_tmem, smem_desc_join(a_lo + 3 * a_kstep), smem_desc_join(b_lo + 3 * b_kstep), idesc, 1u);
+#endif
+        umma_commit_pair(empty_bar(stage), 3);  // frees the stage in both CTAs
+        if (flags & kFlagLast) {
+          umma_commit_pair(tfull_bar(acc), 3);  // accumulator halves ready in both CTAs
+          acc ^= 1;
+          if (acc == 0) acc_phase ^= 1u;
+        }
+        if (++stage == kPStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      PROF_STORE(2);
+#ifdef STK_EXP_PROFILE
+      g_prof[blockIdx.x][4] = prof_acc_wait;
+#endif
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (both CTAs)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t leader_tempty[2] = {map_to_cta(tempty_bar(0), 0), map_to_cta(tempty_bar(1), 0)};
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    // Waits for the accumulator; returns its TMEM address for this warp.
+    // The epilogue warps meet at hardware barriers while draining, so all four must take the
+    // same decision: one thread reads the abort flag between two barriers, everybody follows it.
+    auto acquire = [&](uint32_t& t_addr) {
+      mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+      epilogue_sync();
+      if (threadIdx.x == 64) *epilogue_go = (*abort_flag == 0) ? 1 : 0;
+      epilogue_sync();
+      ok = *epilogue_go != 0;
+      if (ok) tc_fence_after();
+      t_addr = tmem_base + lane_base + static_cast<uint32_t>(acc * kPAccCols);
+    };
+    auto release = [&]() {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_tempty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    };
+    uint16_t* out = static_cast<uint16_t*>(p.out);
+    const bool issuer = threadIdx.x == 64;  // first epilogue thread issues the TMA stores
+    uint32_t sub = 0;
+    for (int item = pair_id; item < p.num_items && ok; item += num_pairs) {
+      const int outer = item / p.inner, inner = item - outer * p.inner;
+      if (p.mode == kModeSDD) {
+        TileWalker w;
+        w.init(p, outer, inner);
+        int u, blk[2][2];
+        while (ok && w.next(u, blk)) {
+          uint32_t t_addr;
+          acquire(t_addr);
+          if (!ok) break;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int pb = blk[rank][h];
+            if (pb != kNoBlock)
+              drain_to_output(t_addr, h * kBlk, kBlk, p.fmt, &tmC, 0, pb * kBlk, staging_base, row,
+                              issuer, sub);
+          }
+          release();
+        }
+      } else {
+        MergeWalker w;
+        w.init(p, outer);
+        // This CTA's 128 output rows and the 256 output columns of the supertile.
+        const int tile_row = (p.mode == kModeDSD ? 2 * outer + rank : 2 * inner + rank) * kBlk;
+        const int tile_col = (p.mode == kModeDSD ? inner : outer) * 2 * kBlk;
+        const bool rows_valid = tile_row < p.out_rows;
+        const int ncols = min(2 * kBlk, p.out_cols - tile_col);
+        uint16_t* dst = out + (static_cast<long long>(tile_row) + row) * p.ldc + tile_col;
+        if (w.empty()) {
+          if (rows_valid) {
+            const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+            for (int c = 0; c < ncols; c += 8) *reinterpret_cast<uint4*>(dst + c) = z;
+          }
+          continue;
+        }
+        uint32_t t_addr;
+        acquire(t_addr);
+        if (!ok) break;
+        if (rows_valid)
+          drain_to_output(t_addr, 0, ncols, p.fmt, &tmC, tile_col, tile_row, staging_base, row,
+                          issuer, sub);
+        release();
+      }
+    }
+    if (issuer) tma_store_wait_all<0>();  // every output tile has left shared memory and landed
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag != 0) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while its peer may still touch its barriers or TMEM
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kPTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0) report_status(STK_ERR_DEVICE_TIMEOUT);
+}
+
+// ====================================================================== host side
+
+struct PairDeviceInfo {
+  int max_pairs = 0;
+};
+
+static int pair_device_info(PairDeviceInfo** out) {
+  static PairDeviceInfo infos[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return STK_ERR_LAUNCH;
+  PairDeviceInfo& d = infos[dev];
+  if (d.max_pairs == 0) {
+    if (cudaFuncSetAttribute(bsmm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kPSmemBytes) != cudaSuccess) {
+      cudaGetLastError();
+      return STK_ERR_LAUNCH;
+    }
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2)
+      return STK_ERR_LAUNCH;
+    // How many CTA pairs can be resident at once (a pair must sit in one GPC).
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(sms / 2 * 2));
+    cfg.blockDim = dim3(kPThreads);
+    cfg.dynamicSmemBytes = kPSmemBytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, bsmm_pair_kernel, &cfg) != cudaSuccess || clusters < 1) {
+      cudaGetLastError();
+      clusters = sms / 2;
+    }
+    d.max_pairs = clusters < sms / 2 ? clusters : sms / 2;
+  }
+  *out = &d;
+  return STK_OK;
+}
+
+static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
+                       const PairParams& p, cudaStream_t stream) {
+  PairDeviceInfo* d = nullptr;
+  const int rc = pair_device_info(&d);
+  if (rc != STK_OK) return rc;
+  const int pairs = p.num_items < d->max_pairs ? p.num_items : d->max_pairs;
+  bsmm_pair_kernel<<<2 * pairs, kPThreads, kPSmemBytes, stream>>>(tmA, tmB, tmC, p);
+  return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
+}
+
+}  // namespace stk

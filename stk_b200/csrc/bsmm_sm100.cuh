@@ -163,9 +163,13 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           const uint32_t b_dst = a_dst + kOperandTileBytes;
+#ifdef STK_EXP_SKIP_TMA  // experiment: MMA issue rate with the operand fetch taken out
+          mbar_arrive(full_bar(stage));
+#else
           mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
           load_operand(&tmA, a_dst, full_bar(stage), p.a_mn, a_mn_elem, a_k_elem);
           load_operand(&tmB, b_dst, full_bar(stage), p.b_mn, b_mn_elem, b_k_elem);
+#endif
         } else {
           ok = 0;
         }
@@ -215,11 +219,11 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = make_idesc_f16(p.fmt, p.a_mn, p.b_mn, kBlk);
-      // Byte step of the descriptor start address per 16 elements of K.
-      const uint32_t a_kstep = p.a_mn ? kUmmaK * 128u : kUmmaK * 2u;
-      const uint32_t b_kstep = p.b_mn ? kUmmaK * 128u : kUmmaK * 2u;
-      const uint32_t a_lbo = p.a_mn ? kOperandTileBytes / 2 : 16u;
-      const uint32_t b_lbo = p.b_mn ? kOperandTileBytes / 2 : 16u;
+      // Descriptor low words of stage 0 and their step per 16 elements of K and per stage.
+      const uint32_t a_lo0 = smem_desc_lo(smem_base, p.a_mn ? kOperandTileBytes / 2 : 16u);
+      const uint32_t b_lo0 = smem_desc_lo(smem_base + kOperandTileBytes, p.b_mn ? kOperandTileBytes / 2 : 16u);
+      const uint32_t a_kstep = (p.a_mn ? kUmmaK * 128u : kUmmaK * 2u) >> 4;
+      const uint32_t b_kstep = (p.b_mn ? kUmmaK * 128u : kUmmaK * 2u) >> 4;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -232,18 +236,20 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kBlk);
+        uint32_t accumulate = 0;
         for (int ks = 0; ks < t.nk; ++ks) {
           ok = mbar_wait(full_bar(stage), phase, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t a_src = smem_base + stage * kStageBytes;
-          const uint32_t b_src = a_src + kOperandTileBytes;
-#pragma unroll
-          for (int k = 0; k < kBK / kUmmaK; ++k) {
-            const uint64_t a_desc = make_smem_desc(a_src + k * a_kstep, a_lbo, 1024u);
-            const uint64_t b_desc = make_smem_desc(b_src + k * b_kstep, b_lbo, 1024u);
-            umma_f16(d_tmem, a_desc, b_desc, idesc, (ks | k) != 0 ? 1u : 0u);
-          }
+          const uint32_t a_lo = a_lo0 + stage * (kStageBytes >> 4);
+          const uint32_t b_lo = b_lo0 + stage * (kStageBytes >> 4);
+#ifndef STK_EXP_SKIP_MMA  // experiment: operand fetch rate with the MMAs taken out
+          umma_f16(d_tmem, smem_desc_join(a_lo), smem_desc_join(b_lo), idesc, accumulate);
+          umma_f16(d_tmem, smem_desc_join(a_lo + a_kstep), smem_desc_join(b_lo + b_kstep), idesc, 1u);
+          umma_f16(d_tmem, smem_desc_join(a_lo + 2 * a_kstep), smem_desc_join(b_lo + 2 * b_kstep), idesc, 1u);
+          umma_f16(d_tmem, smem_desc_join(a_lo + 3 * a_kstep), smem_desc_join(b_lo + 3 * b_kstep), idesc, 1u);
+#endif
+          accumulate = 1u;
           umma_commit(empty_bar(stage));  // the stage is free once these MMAs have read it
           if (++stage == kStages) {
             stage = 0;
@@ -432,124 +438,3 @@ static int check_dense(const void* ptr, int64_t ld, int64_t min_ld) {
 
 }  // namespace stk
 
-using namespace stk;
-
-extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out,
-                            const int16_t* row_indices, const int16_t* column_indices, int64_t M,
-                            int64_t N, int64_t K, int64_t nnz, int lhs_colmajor, int64_t ld_lhs,
-                            int rhs_colmajor, int64_t ld_rhs, int dtype, void* stream) {
-  if (dtype != STK_F16 && dtype != STK_BF16) return STK_ERR_BAD_DTYPE;
-  if (M <= 0 || N <= 0 || K <= 0 || nnz < 0 || M % kBlk || N % kBlk || K % 32) return STK_ERR_BAD_DIMS;
-  if (nnz == 0) return STK_OK;
-  if (nnz > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return STK_ERR_TOO_LARGE;
-  if (out == nullptr || row_indices == nullptr || column_indices == nullptr)
-    return STK_ERR_NULL_POINTER;
-  if (!aligned16(out)) return STK_ERR_BAD_LAYOUT;
-  int rc;
-  if ((rc = check_dense(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) return rc;
-  if ((rc = check_dense(rhs, ld_rhs, rhs_colmajor ? K : N)) != STK_OK) return rc;
-
-  CUtensorMap tmA, tmB;
-  // lhs [M,K]: row-major means K contiguous.
-  if ((rc = encode_dense(&tmA, lhs, dtype, M, K, ld_lhs, !lhs_colmajor)) != STK_OK) return rc;
-  // rhs [K,N]: row-major means N contiguous; column-major means K contiguous.
-  if ((rc = encode_dense(&tmB, rhs, dtype, N, K, ld_rhs, rhs_colmajor)) != STK_OK) return rc;
-
-  BsmmParams p{};
-  p.mode = kModeSDD;
-  p.a_mn = lhs_colmajor ? 1 : 0;
-  p.b_mn = rhs_colmajor ? 0 : 1;
-  p.fmt = dtype;
-  p.num_tiles = static_cast<int>(nnz);
-  p.tiles_inner = 1;
-  p.k_steps = static_cast<int>((K + kBK - 1) / kBK);
-  p.row_idx = row_indices;
-  p.col_idx = column_indices;
-  p.out = out;
-  p.ldc = kBlk;
-  return launch(tmA, tmB, p, static_cast<cudaStream_t>(stream));
-}
-
-extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int16_t* column_indices,
-                            const int32_t* block_offsets, const void* rhs, void* out, int64_t M,
-                            int64_t N, int64_t K, int64_t nnz, int trans_sparse, int rhs_colmajor,
-                            int64_t ld_rhs, int64_t ld_out, int dtype, void* stream) {
-  if (dtype != STK_F16 && dtype != STK_BF16) return STK_ERR_BAD_DTYPE;
-  if (M <= 0 || N <= 0 || K <= 0 || nnz < 0 || M % kBlk || N % kBlk || K % kBlk) return STK_ERR_BAD_DIMS;
-  if (nnz * kBlk > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX ||
-      (M / kBlk) * (N / kBlk) > INT32_MAX)
-    return STK_ERR_TOO_LARGE;
-  int rc;
-  if ((rc = check_dense(out, ld_out, N)) != STK_OK) return rc;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (nnz == 0) {
-    // No blocks at all: the product is zero.
-    return cudaMemset2DAsync(out, ld_out * 2, 0, N * 2, M, s) == cudaSuccess ? STK_OK
-                                                                             : STK_ERR_LAUNCH;
-  }
-  if (data == nullptr || offsets == nullptr || column_indices == nullptr) return STK_ERR_NULL_POINTER;
-  if (trans_sparse && block_offsets == nullptr) return STK_ERR_NULL_POINTER;
-  if (!aligned16(data)) return STK_ERR_BAD_LAYOUT;
-  if ((rc = check_dense(rhs, ld_rhs, rhs_colmajor ? K : N)) != STK_OK) return rc;
-
-  CUtensorMap tmA, tmB;
-  // A = data[blk] as stored (its columns are K) or transposed (its columns are M).
-  if ((rc = encode_sparse(&tmA, data, dtype, nnz, !trans_sparse)) != STK_OK) return rc;
-  if ((rc = encode_dense(&tmB, rhs, dtype, N, K, ld_rhs, rhs_colmajor)) != STK_OK) return rc;
-
-  BsmmParams p{};
-  p.mode = kModeDSD;
-  p.a_mn = trans_sparse ? 1 : 0;
-  p.b_mn = rhs_colmajor ? 0 : 1;
-  p.fmt = dtype;
-  p.tiles_inner = static_cast<int>(N / kBlk);
-  p.num_tiles = static_cast<int>((M / kBlk) * (N / kBlk));
-  p.col_idx = column_indices;
-  p.offsets = offsets;
-  p.blk_idx = block_offsets;
-  p.out = out;
-  p.ldc = ld_out;
-  return launch(tmA, tmB, p, s);
-}
-
-extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* offsets,
-                            const int16_t* column_indices, const int32_t* block_offsets, void* out,
-                            int64_t M, int64_t N, int64_t K, int64_t nnz, int lhs_colmajor,
-                            int64_t ld_lhs, int trans_sparse, int64_t ld_out, int dtype,
-                            void* stream) {
-  if (dtype != STK_F16 && dtype != STK_BF16) return STK_ERR_BAD_DTYPE;
-  if (M <= 0 || N <= 0 || K <= 0 || nnz < 0 || M % kBlk || N % kBlk || K % kBlk) return STK_ERR_BAD_DIMS;
-  if (nnz * kBlk > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX ||
-      (M / kBlk) * (N / kBlk) > INT32_MAX)
-    return STK_ERR_TOO_LARGE;
-  int rc;
-  if ((rc = check_dense(out, ld_out, N)) != STK_OK) return rc;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (nnz == 0) {
-    return cudaMemset2DAsync(out, ld_out * 2, 0, N * 2, M, s) == cudaSuccess ? STK_OK
-                                                                             : STK_ERR_LAUNCH;
-  }
-  if (data == nullptr || offsets == nullptr || column_indices == nullptr) return STK_ERR_NULL_POINTER;
-  if (!trans_sparse && block_offsets == nullptr) return STK_ERR_NULL_POINTER;
-  if (!aligned16(data)) return STK_ERR_BAD_LAYOUT;
-  if ((rc = check_dense(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) return rc;
-
-  CUtensorMap tmA, tmB;
-  if ((rc = encode_dense(&tmA, lhs, dtype, M, K, ld_lhs, !lhs_colmajor)) != STK_OK) return rc;
-  // B = data[blk] as stored (its columns are N) or transposed (its columns are K).
-  if ((rc = encode_sparse(&tmB, data, dtype, nnz, trans_sparse)) != STK_OK) return rc;
-
-  BsmmParams p{};
-  p.mode = kModeDDS;
-  p.a_mn = lhs_colmajor ? 1 : 0;
-  p.b_mn = trans_sparse ? 0 : 1;
-  p.fmt = dtype;
-  p.tiles_inner = static_cast<int>(M / kBlk);
-  p.num_tiles = static_cast<int>((M / kBlk) * (N / kBlk));
-  p.col_idx = column_indices;
-  p.offsets = offsets;
-  p.blk_idx = block_offsets;
-  p.out = out;
-  p.ldc = ld_out;
-  return launch(tmA, tmB, p, s);
-}

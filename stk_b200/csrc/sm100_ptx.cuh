@@ -53,7 +53,12 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 // Bounded wait.  `abort_flag` is a CTA-wide shared word: once any role has given up,
 // every other wait in the CTA returns false quickly so that the CTA can tear down.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
+  // Fast path: plain polling.  Reading the global timer costs far more than a poll, and these
+  // waits sit on the critical path of the operand ring, so the clock is only consulted once the
+  // wait has already lasted long.
+#pragma unroll 1
+  for (int i = 0; i < 4096; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
@@ -83,6 +88,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
       " [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(x), "r"(y)
       : "memory");
+}
+
+// Ask L2 to fetch one box of a tensor map ahead of its use (no shared-memory destination).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* tm, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+               ::"l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y)
+               : "memory");
 }
 
 // 2-D tiled store shared -> global (bulk async group).
@@ -159,6 +171,79 @@ __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---------------------------------------------------------------- CTA pairs (cta_group::2)
+// Two CTAs of a cluster cooperate on one 256-row MMA: each loads its own operand halves into its
+// own shared memory, the even ("leader") CTA issues the MMAs and owns the barriers they wait on.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t num_clusters_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+  return r;
+}
+// Address of this CTA's shared-memory location `addr` as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on a barrier that lives in another CTA of the cluster (cluster-mapped address).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
+               : "memory");
+}
+// TMA load into this CTA's shared memory whose completion bytes are counted on a barrier of the
+// pair's leader CTA (cluster-mapped address).  No multicast: each CTA fetches its own tile.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* tm,
+                                                 uint32_t leader_bar, int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+// 256-row MMA over the CTA pair; issued by ONE thread of the leader CTA.
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at the same shared-memory offset in every CTA of `cta_mask` once the
+// MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"(cta_mask)
+      : "memory");
+}
+
 // ---------------------------------------------------------------- descriptors
 // Shared-memory operand descriptor, 128-byte swizzle, for a tile whose rows are 128 bytes
 // (64 16-bit elements) and whose 8-row swizzle atoms (1024 bytes) are contiguous.
@@ -176,11 +261,26 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
   return d;
 }
 
-// Instruction descriptor for kind::f16 with fp32 accumulation, M = 128.
+// The descriptor split for the MMA issue loop, which must stay a handful of instructions per MMA
+// (one thread issues everything; a dependent ALU chain per MMA would cap the tensor pipe):
+// the high word is constant, the low word is (address >> 4) | (LBO >> 4) << 16 and only its
+// address part moves.  Tiles are 1024-byte aligned and below 256 KiB, so adding a k offset to the
+// low word never carries into the LBO field.
+constexpr uint32_t kSmemDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, SWIZZLE_128B
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
+}
+__device__ __forceinline__ uint64_t smem_desc_join(uint32_t lo) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(kSmemDescHi));
+  return d;
+}
+
+// Instruction descriptor for kind::f16 with fp32 accumulation (M = 128 per CTA; 256 for a CTA pair).
 //   fmt: 0 = fp16, 1 = bf16 (both operands);  *_mn_major: 1 if the operand's contiguous
 //   dimension is M (for A) / N (for B) rather than K.
 __host__ __device__ __forceinline__ uint32_t make_idesc_f16(int fmt, int a_mn_major, int b_mn_major,
-                                                            int n) {
+                                                            int n, int m = 128) {
   uint32_t d = 0;
   d |= 1u << 4;                         // D format: F32
   d |= static_cast<uint32_t>(fmt) << 7;   // A format
@@ -188,7 +288,7 @@ __host__ __device__ __forceinline__ uint32_t make_idesc_f16(int fmt, int a_mn_ma
   d |= static_cast<uint32_t>(a_mn_major) << 15;
   d |= static_cast<uint32_t>(b_mn_major) << 16;
   d |= static_cast<uint32_t>(n >> 3) << 17;
-  d |= static_cast<uint32_t>(128 >> 4) << 24;
+  d |= static_cast<uint32_t>(m >> 4) << 24;
   return d;
 }
 

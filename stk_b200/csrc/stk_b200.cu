@@ -5,7 +5,7 @@
 
 #include "../../include/stk_b200.h"
 #include "status.cuh"
-#include "bsmm_sm100.cuh"
+#include "bsmm_api.cuh"
 #include "meta_sm100.cuh"
 
 extern "C" int stk_b200_version(void) { return STK_B200_VERSION; }
@@ -38,3 +38,9 @@ extern "C" int stk_b200_device_status(int* status_host) {
   *status_host = v;
   return STK_OK;
 }
+
+#ifdef STK_EXP_PROFILE
+extern "C" int stk_b200_exp_profile(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, stk::g_prof, sizeof(long long) * 160 * 8) == cudaSuccess ? 0 : -6;
+}
+#endif

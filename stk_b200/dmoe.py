@@ -10,6 +10,7 @@ have nonzero blocks exactly in expert e's ffn / 128 block columns.
 import torch
 import torch.distributed as dist
 
+from stk_b200.backend import kernels as _kernels
 from stk_b200.matrix import Matrix
 
 BLOCK = 128
@@ -42,6 +43,10 @@ def block_diagonal_topology(padded_counts, ffn, dtype, device, block=BLOCK, data
     if data is None:
         data = torch.empty((nnz, block, block), dtype=dtype, device=device)
     size = torch.Size((block_rows * block, num_experts * ffn))
+    if cols_per_expert % 2 == 0:
+        # Known by construction: all block rows of an expert share one column list, column pairs
+        # never straddle experts; only row pairs at expert boundaries fail to pair.
+        _kernels.set_pair_hints(column_indices, 0.9, 1.0, 0.9, True)
     return Matrix(size, data, row_indices, column_indices, offsets)
 
 

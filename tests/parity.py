@@ -8,12 +8,14 @@ RTOL = 1e-2
 ATOL = 1e-2
 
 
-def assert_product_close(out, ref, what=""):
+def assert_product_close(out, ref, what="", roundings=1):
+    """`roundings`: how many independent 16-bit roundings separate `out` from `ref` (a property
+    such as linearity compares one rounded result with the sum of two rounded results)."""
     out32, ref32 = out.float().cpu(), ref.float().cpu()
     assert out32.shape == ref32.shape, f"{what}: shape {tuple(out32.shape)} vs {tuple(ref32.shape)}"
     assert not torch.isnan(out32).any(), f"{what}: NaN in output"
     rms = ref32.pow(2).mean().sqrt().item() if ref32.numel() else 0.0
-    excess = (out32 - ref32).abs() - (ATOL * rms + RTOL * ref32.abs())
+    excess = (out32 - ref32).abs() - roundings * (ATOL * rms + RTOL * ref32.abs())
     worst = excess.max().item() if excess.numel() else -1.0
     assert worst <= 0.0, (f"{what}: {int((excess > 0).sum())} of {excess.numel()} elements outside "
                           f"rtol {RTOL} / atol {ATOL}*RMS (RMS {rms:.3e}, worst excess {worst:.3e})")

@@ -27,11 +27,16 @@ _IDS = [f"{m}x{k}x{n}-s{s}-{'t' if ta else 'n'}{'t' if tb else 'n'}-{str(dt)[6:]
         for m, k, n, s, ta, tb, dt in _CASES]
 
 
-@pytest.fixture(scope="module")
-def stk():
+@pytest.fixture(scope="module", params=["0", "1"], ids=["tile128", "pair256"])
+def stk(request):
+    """The package with the matmul kernel choice forced: one 128x128 tile per CTA, or 256x256
+    supertiles on CTA pairs (both must give the same results on every topology)."""
     import stk_b200
-    from stk_b200.backend import lib
+    from stk_b200.backend import kernels, lib
+    saved = kernels.PAIR_MODE
+    kernels.PAIR_MODE = request.param
     yield stk_b200
+    kernels.PAIR_MODE = saved
     assert lib.device_status() == 0
 
 

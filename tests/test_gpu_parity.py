@@ -13,13 +13,18 @@ META_KEYS = ("row_indices", "column_indices", "offsets", "column_indices_t", "of
              "block_offsets_t")
 
 
-@pytest.fixture(scope="module")
-def stk():
+@pytest.fixture(scope="module", params=["0", "1", "auto"], ids=["tile128", "pair256", "auto"])
+def stk(request):
+    """The package with the matmul kernel choice forced (128x128 tiles per CTA / 256x256 supertiles
+    on CTA pairs) or left to the per-topology heuristic."""
     import stk_b200
-    from stk_b200.backend import lib
+    from stk_b200.backend import kernels, lib
     assert torch.cuda.is_available()
     lib.load()
+    saved = kernels.PAIR_MODE
+    kernels.PAIR_MODE = request.param
     yield stk_b200
+    kernels.PAIR_MODE = saved
     assert lib.device_status() == 0, "a kernel reported a bounded wait that ran out"
 
 
@@ -252,3 +257,56 @@ def test_strided_views_and_errors(stk):
         stk.ops.sdd(a.float(), b.float(), topo)     # unsupported dtype
     with pytest.raises(RuntimeError):
         stk.ops.sdd(a.cpu(), b.cpu(), topo)         # no CPU path
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_dmoe_shaped_products_full_size(stk, dtype):
+    """BASELINE configs[1]-shaped problem at full size (T=16384, h=1024, f=4096, E=8): forward and
+    the four backward products, checked per expert against dense fp32 products of the same 16-bit
+    operands (identical math for a block-diagonal topology), plus two size-independent properties:
+    linearity of DSD in the dense operand and SDD -> to_dense -> to_sparse round trip."""
+    from stk_b200 import dmoe
+    dev = "cuda"
+    T, h, f, E = 16384, 1024, 4096, 8
+    g = torch.Generator().manual_seed(0)
+    ids = torch.multinomial(torch.full((E,), 1.0 / E), T, replacement=True, generator=g).to(dev)
+    slot, padded, starts, total = dmoe.route_top1(ids, E)
+    topo = dmoe.block_diagonal_topology(padded, f, dtype, dev)
+    x = dmoe.permute_tokens((torch.randn(T, h, generator=g) * 0.02).to(dtype).to(dev), slot, total)
+    w1 = (torch.randn(h, E * f, generator=g) * 0.02).to(dtype).to(dev).requires_grad_(True)
+    w2 = (torch.randn(E * f, h, generator=g) * 0.02).to(dtype).to(dev).requires_grad_(True)
+    x.requires_grad_(True)
+    hid = stk.ops.sdd(x, w1, topo)
+    y = stk.ops.dsd(hid, w2)
+    dy = (torch.randn(total, h, generator=g) * 0.02).to(dtype).to(dev)
+    y.backward(dy)
+    rows = (padded // 128).tolist()
+    cpb = f // 128
+    r0 = 0
+    for e in range(E):
+        nr = rows[e]
+        if nr == 0:
+            continue
+        sl = slice(r0 * 128, (r0 + nr) * 128)
+        xe = x.detach()[sl].float()
+        w1e = w1.detach()[:, e * f:(e + 1) * f].float()
+        w2e = w2.detach()[e * f:(e + 1) * f].float()
+        he = hid.data.detach()[r0 * cpb:(r0 + nr) * cpb].view(nr, cpb, 128, 128).permute(0, 2, 1, 3).reshape(nr * 128, f)
+        assert_product_close(he, xe @ w1e, f"sdd expert {e}")
+        he32 = he.float()
+        assert_product_close(y.detach()[sl], he32 @ w2e, f"dsd expert {e}")
+        dye = dy[sl].float()
+        assert_product_close(w2.grad[e * f:(e + 1) * f], he32.t() @ dye, f"dw2 expert {e}")     # dsd, S transposed
+        dhe = dye @ w2e.t()                                                                       # sdd, rhs transposed
+        assert_product_close(x.grad[sl], dhe.to(dtype).float() @ w1e.t(), f"dx expert {e}")       # dsd, rhs transposed
+        assert_product_close(w1.grad[:, e * f:(e + 1) * f], xe.t() @ dhe.to(dtype).float(), f"dw1 expert {e}")  # dds
+        r0 += nr
+    with torch.no_grad():
+        # linearity: dsd(S, a + b) == dsd(S, a) + dsd(S, b) up to output rounding
+        a = (torch.randn(E * f, 256, generator=g) * 0.02).to(dtype).to(dev)
+        b = (torch.randn(E * f, 256, generator=g) * 0.02).to(dtype).to(dev)
+        lhs = stk.ops.dsd(hid, (a.float() + b.float()).to(dtype))
+        rhs = stk.ops.dsd(hid, a).float() + stk.ops.dsd(hid, b).float()
+        assert_product_close(lhs, rhs, "dsd linearity", roundings=3)
+    del y, dy, x, w1, w2
+    torch.cuda.empty_cache()
