@@ -179,8 +179,7 @@ __device__ __forceinline__ void load_operand_pair(const CUtensorMap* tm, uint32_
   if (!mn_major) {
     tma_load_2d_pair(smem_dst, tm, leader_bar, k_elem, mn_elem);
   } else {
-    tma_load_2d_pair(smem_dst, tm, leader_bar, mn_elem, k_elem);
-    tma_load_2d_pair(smem_dst + kOperandTileBytes / 2, tm, leader_bar, mn_elem + 64, k_elem);
+    tma_load_3d_pair(smem_dst, tm, leader_bar, 0, k_elem, mn_elem >> 6);
   }
 }
 

@@ -97,16 +97,16 @@ __device__ __forceinline__ TileInfo tile_info(const BsmmParams& p, int tile) {
   return t;
 }
 
-// One operand tile (128 rows of M or N by 64 of K) into a stage buffer.
-//   K-major : one box {64 (K), 128 (M/N)} at (k_elem, mn_elem).
-//   MN-major: two boxes {64 (M/N), 64 (K)} at (mn_elem + h*64, k_elem), 8 KiB apart.
+// One operand tile (128 rows of M or N by 64 of K) into a stage buffer, one TMA instruction.
+//   K-major : 2-D box {64 (K), 128 (M/N)} at (k_elem, mn_elem).
+//   MN-major: 3-D box {64 (M/N), 64 (K), 2 (groups of 64 M/N)} at (0, k_elem, mn_elem / 64); the two
+//             groups land 8 KiB apart, which is the leading byte offset of the UMMA descriptor.
 __device__ __forceinline__ void load_operand(const CUtensorMap* tm, uint32_t smem_dst, uint32_t bar,
                                              int mn_major, int mn_elem, int k_elem) {
   if (!mn_major) {
     tma_load_2d(smem_dst, tm, bar, k_elem, mn_elem);
   } else {
-    tma_load_2d(smem_dst, tm, bar, mn_elem, k_elem);
-    tma_load_2d(smem_dst + kOperandTileBytes / 2, tm, bar, mn_elem + 64, k_elem);
+    tma_load_3d(smem_dst, tm, bar, 0, k_elem, mn_elem >> 6);
   }
 }
 
@@ -374,20 +374,40 @@ static int encode_map(CUtensorMap* tm, const void* base, int dtype, int64_t inne
   return r == CUDA_SUCCESS ? STK_OK : STK_ERR_TENSOR_MAP;
 }
 
+// Tensor map of an operand whose contiguous dimension is M/N (`mn` elements per row, `k` rows, `ld`
+// elements between rows), described in three dimensions {64, k, mn/64} with boxes {64, 64, 2}.
+static int encode_map_mn_major(CUtensorMap* tm, const void* base, int dtype, int64_t mn, int64_t k,
+                               int64_t ld) {
+  PFN_cuTensorMapEncodeTiled_v12000 fn = get_encode_fn();
+  if (fn == nullptr) return STK_ERR_DRIVER;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(kBK), static_cast<cuuint64_t>(k),
+                              static_cast<cuuint64_t>(mn / kBK)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 2u, static_cast<cuuint64_t>(kBK) * 2u};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(kBK), 2u};
+  const cuuint32_t estr[3] = {1u, 1u, 1u};
+  const CUresult r =
+      fn(tm, dtype == STK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+         3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? STK_OK : STK_ERR_TENSOR_MAP;
+}
+
 // Dense operand with logical shape [mn, k] (the A convention: rows = M; for B pass mn = N):
 //   k_contig = 1: K is contiguous in memory  -> K-major tile, box {64 K, 128 MN}
-//   k_contig = 0: M/N is contiguous          -> MN-major tile, boxes {64 MN, 64 K}
+//   k_contig = 0: M/N is contiguous          -> MN-major tile, box {64 MN, 64 K, 2}
 static int encode_dense(CUtensorMap* tm, const void* base, int dtype, int64_t mn, int64_t k,
                         int64_t ld, int k_contig) {
   return k_contig ? encode_map(tm, base, dtype, k, mn, ld, kBlk)
-                  : encode_map(tm, base, dtype, mn, k, ld, kBK);
+                  : encode_map_mn_major(tm, base, dtype, mn, k, ld);
 }
 
 // Sparse values viewed as a [nnz*128, 128] row-major tensor.
 //   as_stored_k_contig = 1: the block's columns are the K of the product -> K-major
 //   as_stored_k_contig = 0: the block's columns are the M/N of the product -> MN-major
 static int encode_sparse(CUtensorMap* tm, const void* data, int dtype, int64_t nnz, int k_contig) {
-  return encode_map(tm, data, dtype, kBlk, nnz * kBlk, kBlk, k_contig ? kBlk : kBK);
+  return k_contig ? encode_map(tm, data, dtype, kBlk, nnz * kBlk, kBlk, kBlk)
+                  : encode_map_mn_major(tm, data, dtype, kBlk, nnz * kBlk, kBlk);
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -27,11 +27,11 @@ def block_diagonal_topology(padded_counts, ffn, dtype, device, block=BLOCK, data
     """stk.Matrix of shape [sum(padded), E*ffn] whose block row r (belonging to expert e) holds
     the ffn/block consecutive column blocks of expert e.  The transposed metadata comes from the
     library's transpose kernel, as for any user-built Matrix."""
-    padded_counts = padded_counts.to(device)
     num_experts = padded_counts.numel()
     cols_per_expert = ffn // block
-    rows_per_expert = padded_counts // block
-    block_rows = int(rows_per_expert.sum().item())
+    # Counts that already live on the host (the exchange has them there) cost no device sync.
+    block_rows = int((padded_counts // block).sum())
+    rows_per_expert = (padded_counts // block).to(device, non_blocking=True)
     expert_of_row = torch.repeat_interleave(
         torch.arange(num_experts, device=device), rows_per_expert, output_size=block_rows)
     row_indices = torch.repeat_interleave(
@@ -83,10 +83,11 @@ class ExpertParallelExchange:
     [g*E/n, (g+1)*E/n); every rank starts with its own tokens and their expert ids.
 
     dispatch(): tokens travel to the owner of their expert (all_to_all_single with per-rank
-    split sizes, after the counts have been exchanged); the receiver orders them by local expert
-    and pads every expert to a multiple of 128 rows.  combine(): the results travel back and are
-    put in the sender's original token order.  Works with any torch.distributed backend (NCCL over
-    NVLink on the GPUs, gloo on the host for tests).
+    split sizes, after the per-expert counts have been exchanged); the receiver places them by
+    local expert, every expert padded to a multiple of 128 rows.  combine(): the results travel
+    back and are put in the sender's original token order.  One host read-back per dispatch (the
+    counts; NCCL needs the split sizes on the host).  Works with any torch.distributed backend
+    (NCCL over NVLink on the GPUs, gloo on the host for tests).
     """
 
     def __init__(self, num_experts, group=None, block=BLOCK):
@@ -100,32 +101,36 @@ class ExpertParallelExchange:
         self.block = block
 
     def dispatch(self, x, expert_ids):
-        """Returns (x_padded [T'_local, h], padded_counts [local_experts], state)."""
+        """Returns (x_padded [T'_local, h], padded_counts (host int64 [local_experts]), state)."""
         dev = x.device
-        dest = expert_ids // self.local_experts
-        # Send order: by destination rank, then by expert, stable in the token index.
+        world, local = self.world, self.local_experts
+        # Send order: by expert (hence by destination rank), stable in the token index.
         send_order = torch.argsort(expert_ids, stable=True)
-        send_counts_by_expert = torch.bincount(expert_ids, minlength=self.num_experts)
-        recv_counts_by_expert = torch.empty_like(send_counts_by_expert)
-        # counts[e] for the experts of rank g are sent to rank g: one row of E/n counts per peer
-        dist.all_to_all_single(recv_counts_by_expert, send_counts_by_expert, group=self.group)
-        send_splits = send_counts_by_expert.view(self.world, -1).sum(1).tolist()
-        recv_by_peer = recv_counts_by_expert.view(self.world, self.local_experts)
+        counts = torch.empty((2, self.num_experts), dtype=torch.int64, device=dev)
+        counts[0] = torch.bincount(expert_ids, minlength=self.num_experts)
+        # counts[0][e] for the experts of rank g go to rank g: one row of E/n counts per peer
+        dist.all_to_all_single(counts[1], counts[0], group=self.group)
+        host = counts.cpu()                                  # the one synchronisation
+        send_splits = host[0].view(world, local).sum(1).tolist()
+        recv_by_peer = host[1].view(world, local)            # [peer, local expert]
         recv_splits = recv_by_peer.sum(1).tolist()
-        recv = torch.empty((sum(recv_splits), x.shape[1]), dtype=x.dtype, device=dev)
-        dist.all_to_all_single(recv, x[send_order].contiguous(), recv_splits, send_splits,
+        received = sum(recv_splits)
+        recv = torch.empty((received, x.shape[1]), dtype=x.dtype, device=dev)
+        dist.all_to_all_single(recv, x.index_select(0, send_order), recv_splits, send_splits,
                                group=self.group)
-        # Received rows are ordered (peer, local expert); reorder to (local expert, peer) and pad.
-        local_expert_of_row = torch.repeat_interleave(
-            torch.arange(self.local_experts, device=dev).repeat(self.world), recv_by_peer.reshape(-1),
-            output_size=recv.shape[0])
-        counts = recv_by_peer.sum(0)
-        padded, starts, total = padded_bins(counts, self.block)
-        order = torch.argsort(local_expert_of_row, stable=True)
-        sorted_e = local_expert_of_row[order]
-        rank_in_expert = torch.arange(recv.shape[0], device=dev) - (torch.cumsum(counts, 0) - counts)[sorted_e]
-        slot = torch.empty_like(order)
-        slot[order] = starts[sorted_e] + rank_in_expert
+        # Rows arrive ordered (peer, local expert) in world*local contiguous segments; segment
+        # (peer, e) goes to bin e behind the segments of lower peers.  All bookkeeping on the host.
+        per_expert = recv_by_peer.sum(0)
+        padded = ((per_expert + self.block - 1) // self.block) * self.block
+        bin_start = torch.cumsum(padded, 0) - padded
+        seg_len = recv_by_peer.reshape(-1)
+        src_start = torch.cumsum(seg_len, 0) - seg_len
+        within = torch.cumsum(recv_by_peer, 0) - recv_by_peer          # rows of lower peers in bin e
+        dst_start = (bin_start[None, :] + within).reshape(-1)
+        shift = (dst_start - src_start).to(dev, non_blocking=True)
+        slot = torch.arange(received, device=dev) + torch.repeat_interleave(
+            shift, seg_len.to(dev, non_blocking=True), output_size=received)
+        total = int(padded.sum())
         x_padded = permute_tokens(recv, slot, total)
         state = dict(send_order=send_order, send_splits=send_splits, recv_splits=recv_splits,
                      slot=slot, tokens=x.shape[0])
@@ -133,7 +138,7 @@ class ExpertParallelExchange:
 
     def combine(self, y_padded, state):
         """Inverse of dispatch for the per-token results y_padded [T'_local, h_out]."""
-        back = unpermute_tokens(y_padded, state["slot"]).contiguous()
+        back = y_padded.index_select(0, state["slot"])
         out_sorted = torch.empty((state["tokens"], y_padded.shape[1]), dtype=y_padded.dtype,
                                  device=y_padded.device)
         dist.all_to_all_single(out_sorted, back, state["send_splits"], state["recv_splits"],
