@@ -137,6 +137,25 @@ int stk_b200_transpose_meta(const int16_t* row_indices, const int16_t* column_in
                             void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Transpose metadata without any allocation, by the caller or by the library.  No counterpart in
+ * the reference.  It is stk_b200_transpose_meta with the group-by-column counters kept in a
+ * 1 MiB array that is part of the library image on every GPU that loads it, for callers that
+ * cannot obtain device memory at the point of the call: code running under a framework whose
+ * allocator may not be re-entered (inside an allocator callback, while a memory pool is frozen),
+ * or a host language binding that only hands over the buffers it was given.
+ *   Limits: block_cols <= 8192 and nnz <= 1048576; larger sizes return STK_ERR_TOO_LARGE.
+ *   The first call on each device looks up the array's device address (cudaGetSymbolAddress);
+ *   make that first call outside any stream capture.
+ *   All calls on one device share the array: the part a call uses is cleared by that call, and
+ *   two calls whose kernels overlap on the GPU (different streams) race with each other.
+ * Results are identical to stk_b200_transpose_meta.
+ */
+int stk_b200_transpose_meta_static(const int16_t* row_indices, const int16_t* column_indices,
+                                   int64_t nnz, int64_t block_cols,
+                                   int16_t* column_indices_t, int32_t* offsets_t,
+                                   int32_t* block_offsets_t, void* stream);
+
+/*
  * to_sparse, in phases, because the number of nonzero blocks sizes the output.
  * Together they replace stk/ops/matrix_ops.py:50-85 (_mask, to_sparse).
  *

@@ -35,6 +35,8 @@ SIGNATURES = {
     "stk_b200_transpose_meta_workspace_bytes": (_c_size, [_c_i64, _c_i64]),
     "stk_b200_transpose_meta": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr,
                                          _c_ptr, _c_size, _c_ptr]),
+    "stk_b200_transpose_meta_static": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr,
+                                                _c_ptr]),
     "stk_b200_block_mask": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_ptr, _c_ptr]),
     "stk_b200_mask_to_offsets": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr]),
     "stk_b200_mask_to_indices": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr]),

@@ -89,7 +89,8 @@ constexpr int64_t kFusedMaxCols = 1536;    // 32*Cb*4 + (Cb+1)*4 bytes of shared
 constexpr int64_t kFusedMaxNnz = 32768;
 constexpr int64_t kHistEntriesCap = 1 << 20;  // 4 MiB of workspace at most
 
-static inline TransposePlan plan_transpose(int64_t nnz, int64_t block_cols) {
+static inline TransposePlan plan_transpose(int64_t nnz, int64_t block_cols,
+                                           int64_t hist_entries_cap = kHistEntriesCap) {
   TransposePlan pl;
   if (block_cols <= kFusedMaxCols && nnz <= kFusedMaxNnz) {
     pl.fused = true;
@@ -100,7 +101,7 @@ static inline TransposePlan plan_transpose(int64_t nnz, int64_t block_cols) {
     return pl;
   }
   pl.fused = false;
-  int64_t g = kHistEntriesCap / block_cols;
+  int64_t g = hist_entries_cap / block_cols;
   if (g > 1024) g = 1024;
   if (g < 1) g = 1;
   const int64_t windows = (nnz + 31) / 32;
@@ -455,8 +456,8 @@ namespace stk {
 static int transpose_meta_impl(const int16_t* row_indices, const int16_t* column_indices,
                                int64_t nnz, int64_t block_cols, int16_t* column_indices_t,
                                int32_t* offsets_t, int32_t* block_offsets_t, void* workspace,
-                               cudaStream_t s) {
-  const TransposePlan pl = plan_transpose(nnz, block_cols);
+                               cudaStream_t s, int64_t hist_entries_cap = kHistEntriesCap) {
+  const TransposePlan pl = plan_transpose(nnz, block_cols, hist_entries_cap);
   const int n = static_cast<int>(nnz), cb = static_cast<int>(block_cols);
   if (pl.fused) {
     static bool opted_in[64] = {};
@@ -648,4 +649,53 @@ extern "C" int stk_b200_to_dense(const void* data, const int32_t* offsets,
           static_cast<uint32_t*>(out), ld_out);
   }
   return launch_status();
+}
+
+// ------------------------------------------------------------------------------------------
+// transpose_meta with built-in scratch, for callers that cannot allocate device memory.
+
+namespace stk {
+constexpr int64_t kStaticScratchEntries = 1 << 18;        // 1 MiB of int32 counters
+constexpr int64_t kStaticMaxBlockCols = 8192;             // leaves >= 32 groups of counters
+constexpr int64_t kStaticMaxNnz = 1 << 20;
+// The group-by-column counters of the multi-kernel transpose path.  In host code this name is only
+// a handle for cudaGetSymbolAddress; the device address is looked up once per device below.
+static __device__ __align__(256) int32_t g_transpose_scratch[kStaticScratchEntries];
+}  // namespace stk
+
+extern "C" int stk_b200_transpose_meta_static(const int16_t* row_indices,
+                                              const int16_t* column_indices, int64_t nnz,
+                                              int64_t block_cols, int16_t* column_indices_t,
+                                              int32_t* offsets_t, int32_t* block_offsets_t,
+                                              void* stream) {
+  if (nnz < 0 || block_cols <= 0) return STK_ERR_BAD_DIMS;
+  if (block_cols > kStaticMaxBlockCols || nnz > kStaticMaxNnz) return STK_ERR_TOO_LARGE;
+  if (offsets_t == nullptr) return STK_ERR_NULL_POINTER;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (nnz == 0) {
+    return cudaMemsetAsync(offsets_t, 0, (block_cols + 1) * sizeof(int32_t), s) == cudaSuccess
+               ? STK_OK
+               : STK_ERR_LAUNCH;
+  }
+  if (row_indices == nullptr || column_indices == nullptr || column_indices_t == nullptr ||
+      block_offsets_t == nullptr)
+    return STK_ERR_NULL_POINTER;
+  // Device address of the scratch array: resolved on the first call on each device, with that
+  // device current (the first call on a device should therefore come before any stream capture).
+  static void* scratch_addr[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return STK_ERR_LAUNCH;
+  if (scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_transpose_scratch) != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();
+      return STK_ERR_LAUNCH;
+    }
+    scratch_addr[dev] = ptr;
+  }
+  // The counters are cleared inside (cudaMemsetAsync on the part this call uses); the array
+  // keeps whatever the previous call left elsewhere.
+  return transpose_meta_impl(row_indices, column_indices, nnz, block_cols, column_indices_t,
+                             offsets_t, block_offsets_t, scratch_addr[dev], s,
+                             kStaticScratchEntries);
 }
