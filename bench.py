@@ -143,31 +143,33 @@ def run_ours(args):
     w1, w2 = make_weights(rank, dev)
     x_host = make_tokens(rank).pin_memory()
     total_experts = EXPERTS * world
-    ids = expert_ids_for(rank, T_TOKENS, total_experts, dev)
+    ids = expert_ids_for(rank, T_TOKENS, total_experts, dev).to(torch.int32)
     ids_host = ids.cpu().pin_memory()
     exchange = dmoe.ExpertParallelExchange(total_experts) if distributed else None
 
     def full_step(x_dev, ids_dev):
         """Routing bookkeeping + (exchange) + sdd -> GeLU -> dsd + (exchange back)."""
         if distributed:
-            xp, padded, state = exchange.dispatch(x_dev, ids_dev)
-            topo = dmoe.block_diagonal_topology(padded, FFN, DTYPE, dev)
+            xp, bin_rows, state = exchange.dispatch(x_dev, ids_dev)
+            topo = dmoe.topology_from_bins(bin_rows, state["block_rows"], FFN, DTYPE, dev)
             y = expert_step(stk, xp, topo, w1, w2)
             return exchange.combine(y, state), topo
-        slot, padded, _, total = dmoe.route_top1(ids_dev, EXPERTS)
-        topo = dmoe.block_diagonal_topology(padded, FFN, DTYPE, dev)
-        y = expert_step(stk, dmoe.permute_tokens(x_dev, slot, total), topo, w1, w2)
-        return dmoe.unpermute_tokens(y, slot), topo
+        index, padded, bin_rows, total = dmoe.route_top1(ids_dev, EXPERTS)
+        topo = dmoe.topology_from_bins(bin_rows, total // 128, FFN, DTYPE, dev)
+        y = expert_step(stk, dmoe.permute_tokens(x_dev, index, total), topo, w1, w2)
+        return dmoe.unpermute_tokens(y, index, x_dev.shape[0]), topo
 
     with torch.no_grad():
         # ---------------- device-resident leg: inputs and topology already in HBM
         x_dev = x_host.to(dev)
         if distributed:
-            xp, padded, state = exchange.dispatch(x_dev, ids)
+            xp, bin_rows, state = exchange.dispatch(x_dev, ids)
+            block_rows = state["block_rows"]
         else:
-            slot, padded, _, total = dmoe.route_top1(ids, EXPERTS)
-            xp = dmoe.permute_tokens(x_dev, slot, total)
-        topo = dmoe.block_diagonal_topology(padded, FFN, DTYPE, dev)
+            index, padded, bin_rows, total = dmoe.route_top1(ids, EXPERTS)
+            xp = dmoe.permute_tokens(x_dev, index, total)
+            block_rows = total // 128
+        topo = dmoe.topology_from_bins(bin_rows, block_rows, FFN, DTYPE, dev)
         nnz = topo.data.shape[0]
         flops_sdd = 2.0 * nnz * 128 * 128 * HIDDEN
         flops_dsd = 2.0 * nnz * 128 * 128 * HIDDEN
@@ -175,7 +177,7 @@ def run_ours(args):
 
         def resident_step():
             if distributed:
-                xq, pq, st = exchange.dispatch(x_dev, ids)
+                xq, _, st = exchange.dispatch(x_dev, ids)
                 y = expert_step(stk, xq, topo, w1, w2)
                 return exchange.combine(y, st)
             return expert_step(stk, xp, topo, w1, w2)
@@ -190,6 +192,8 @@ def run_ours(args):
             sampler.start()
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
         torch.cuda.synchronize()
+        if not distributed:
+            torch.cuda._sleep(20_000_000)   # let the host run ahead so that launch latency is not timed
         ev[0].record()
         for _ in range(args.steps):
             resident_step()
@@ -204,6 +208,7 @@ def run_ours(args):
         k_ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
         hidden = stk.ops.sdd(xp, w1, topo)
         torch.cuda.synchronize()
+        torch.cuda._sleep(20_000_000)
         for i in range(args.steps):
             k_ev[i][0].record()
             hidden = stk.ops.sdd(xp, w1, topo)
@@ -227,6 +232,7 @@ def run_ours(args):
             torch.matmul(a1, b1), torch.matmul(a2, b2)
         c_ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
         torch.cuda.synchronize()
+        torch.cuda._sleep(20_000_000)
         c_ev[0].record()
         for _ in range(args.steps):
             torch.matmul(a1, b1)
@@ -289,7 +295,7 @@ def run_ours(args):
                    "parallelism": "1 GPU" if world == 1 else f"expert-parallel x{world}, all-to-all",
                    "l2": "no flush: operands + hidden + output of one step are ~335 MB > 126 MB L2"},
         "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s",
-                "h2d_bytes_per_step": x_host.numel() * 2 + ids_host.numel() * 8,
+                "h2d_bytes_per_step": x_host.numel() * 2 + ids_host.numel() * 4,
                 "d2h_bytes_per_step": y_host.numel() * 2,
                 "includes": "H2D tokens+routing, routing/permute, topology build, (exchange), "
                             "sdd, gelu, dsd, un-permute, D2H result"},

@@ -188,6 +188,34 @@ int stk_b200_to_dense(const void* data, const int32_t* offsets, const int16_t* c
                       int64_t block_rows, int64_t block_cols, int blocking, int elem_bytes,
                       void* out, int64_t ld_out, void* stream);
 
+/*
+ * dMoE plumbing around the products (the callers' side of stk.Matrix / sdd / dsd in a dropless-MoE
+ * layer; the reference is a matmul library and has no counterpart for these four).
+ *
+ * gather_rows : dst[i] = index[i] >= 0 ? src[index[i]] : zeros      (i < n_rows output rows)
+ * scatter_rows: dst[index[i]] = src[i] for index[i] >= 0            (i < n_rows input rows)
+ *   Rows are row_bytes long (a multiple of 16), src / dst 16-byte aligned.
+ * bin_index   : gather index that puts the token rows received from `world` peers (each peer's rows
+ *   ordered by local expert; counts[p*local_experts+e] rows from peer p for expert e, int64) into
+ *   per-expert bins padded to a multiple of `block` rows: rows of expert e ordered by peer, then
+ *   padding (index -1).  total_padded = sum of the padded bin sizes (the caller knows the counts).
+ *   If `compose` is not NULL the source row s is replaced by compose[s] (e.g. a sort order).
+ *   bin_rows[e] (optional) receives padded rows of expert e / block.
+ * dmoe_topology: blocked CSR-COO metadata, row- and column-major, of the block-diagonal matrix in
+ *   which expert e owns bin_rows[e] block rows and block columns [e*cpb, (e+1)*cpb).
+ */
+int stk_b200_gather_rows(const void* src, void* dst, const int32_t* index, int64_t n_rows,
+                         int64_t row_bytes, void* stream);
+int stk_b200_scatter_rows(const void* src, void* dst, const int32_t* index, int64_t n_rows,
+                          int64_t row_bytes, void* stream);
+int stk_b200_bin_index(const int64_t* counts, int world, int local_experts, int block,
+                       const int32_t* compose, int32_t* index, int64_t total_padded,
+                       int32_t* bin_rows, void* stream);
+int stk_b200_dmoe_topology(const int32_t* bin_rows, int experts, int cols_per_expert,
+                           int64_t block_rows, int16_t* row_indices, int16_t* column_indices,
+                           int32_t* offsets, int16_t* column_indices_t, int32_t* offsets_t,
+                           int32_t* block_offsets_t, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -20,8 +20,10 @@ BLOCK = 128  # the matmul kernels are built for 128x128 blocks
 # "auto" = per topology, from how well neighbouring block rows / columns pair up (see pair_hints).
 PAIR_MODE = os.environ.get("STK_B200_PAIR_MODE", "auto")
 # Fraction of the pair kernel's MMA work that must be useful for it to be chosen.  The pair kernel
-# moves half the operand bytes per FLOP, so it still wins with a good part of its work wasted.
-PAIR_THRESHOLD = 0.7
+# moves half the operand bytes per FLOP, so it still wins with a good part of its work wasted:
+# measured on random 8192^2 topologies it overtakes the 128x128 kernel for DSD / DDS from about half
+# of the work being useful, for SDD (whose 2x2 tiles waste more) from about 0.7.
+PAIR_THRESHOLD = {"rows": 0.55, "cols": 0.55, "tiles": 0.7}
 _HINT_ATTR = "_stk_b200_pair_hints"
 
 
@@ -72,7 +74,7 @@ def _use_pairs(kind, row_indices, column_indices, block_cols):
         return 0  # the SDD tile walk needs ascending columns inside every block row
     if PAIR_MODE == "1":
         return 1
-    return int({"rows": rows, "cols": cols, "tiles": tiles}[kind] >= PAIR_THRESHOLD)
+    return int({"rows": rows, "cols": cols, "tiles": tiles}[kind] >= PAIR_THRESHOLD[kind])
 
 
 class DimensionError(AssertionError, ValueError):

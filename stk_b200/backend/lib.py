@@ -44,6 +44,12 @@ SIGNATURES = {
                                         _c_i64, _c_ptr, _c_ptr]),
     "stk_b200_to_dense": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_int, _c_ptr,
                                    _c_i64, _c_ptr]),
+    "stk_b200_gather_rows": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_ptr]),
+    "stk_b200_scatter_rows": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_ptr]),
+    "stk_b200_bin_index": (_c_int, [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_i64, _c_ptr,
+                                    _c_ptr]),
+    "stk_b200_dmoe_topology": (_c_int, [_c_ptr, _c_int, _c_int, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
+                                        _c_ptr, _c_ptr, _c_ptr]),
 }
 
 _lib = None

@@ -194,6 +194,9 @@ __device__ __forceinline__ void drain_to_output(uint32_t t_addr, int col0, int n
                                                 const CUtensorMap* tmC, int out_x, int out_y,
                                                 uint32_t staging_base, int row, bool issuer,
                                                 uint32_t& sub) {
+#ifdef STK_EXP_SKIP_EPILOGUE  // experiment: main loop alone, nothing drained or stored
+  return;
+#endif
   for (int c = 0; c < ncols; c += 64, ++sub) {
     const uint32_t buf = staging_base + (sub & 1u) * kOutStageBytes;
     if (issuer) tma_store_wait_read<1>();  // the store that last read this buffer is done with it

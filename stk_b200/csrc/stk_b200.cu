@@ -7,6 +7,7 @@
 #include "status.cuh"
 #include "bsmm_api.cuh"
 #include "meta_sm100.cuh"
+#include "dmoe_sm100.cuh"
 
 extern "C" int stk_b200_version(void) { return STK_B200_VERSION; }
 

@@ -1,19 +1,111 @@
-"""Dropless-MoE plumbing around the block-sparse products: the block-diagonal topology of a
-batch of tokens routed to experts, the token permutation into padded expert order, and the
+"""Dropless-MoE plumbing around the block-sparse products: sorting tokens by expert, moving token
+rows into and out of padded expert bins, the block-diagonal topology of a routed batch, and the
 expert-parallel exchange between GPUs.
 
 This is the caller's side of stk.Matrix / stk.ops.sdd / stk.ops.dsd in a dMoE layer.  The
 reference has no such code (it is a matmul library); the shapes follow the benchmark
 configurations: tokens of expert e occupy ceil(count_e / 128) block rows, and those block rows
 have nonzero blocks exactly in expert e's ffn / 128 block columns.
+
+On CUDA tensors everything below runs as kernels of libstk_b200.so (stable counting sort, row
+gather / scatter with 16-byte accesses, closed-form topology); there is one host read-back per
+routed batch (the per-expert counts, which size the padded buffers and, across GPUs, the NCCL split
+sizes).  Host tensors take plain torch indexing instead - that path exists for the gloo tests of
+the multi-rank bookkeeping, not for production use.
 """
 import torch
 import torch.distributed as dist
 
 from stk_b200.backend import kernels as _kernels
+from stk_b200.backend import lib as _lib
 from stk_b200.matrix import Matrix
 
 BLOCK = 128
+
+
+# ------------------------------------------------------------------------------ building blocks
+def sort_by_expert(expert_ids, num_experts):
+    """Stable sort of token indices by expert: (order int32 [T], offsets int32 [E+1])."""
+    if expert_ids.is_cuda:
+        ids16 = expert_ids.to(torch.int16)
+        _, offsets, order = _kernels.transpose_meta(ids16, ids16, num_experts)
+        return order, offsets
+    order = torch.argsort(expert_ids, stable=True).to(torch.int32)
+    counts = torch.bincount(expert_ids, minlength=num_experts)
+    offsets = torch.cat([counts.new_zeros(1), torch.cumsum(counts, 0)]).to(torch.int32)
+    return order, offsets
+
+
+def gather_rows(src, index, n_out=None):
+    """out[i] = src[index[i]], or a zero row where index[i] < 0."""
+    n_out = index.numel() if n_out is None else n_out
+    if src.is_cuda:
+        src = src.contiguous()
+        out = torch.empty((n_out, src.shape[1]), dtype=src.dtype, device=src.device)
+        with torch.cuda.device(src.device):
+            rc = _lib.load().stk_b200_gather_rows(
+                _lib.ptr(src), _lib.ptr(out), _lib.ptr(index), n_out,
+                src.shape[1] * src.element_size(), _lib.stream_ptr(src.device))
+        _lib.check(rc, "stk_b200_gather_rows")
+        return out
+    out = src.new_zeros((n_out, src.shape[1]))
+    valid = index >= 0
+    out[valid] = src[index[valid].long()]
+    return out
+
+
+def scatter_rows(src, index, n_out):
+    """out[index[i]] = src[i] for index[i] >= 0; rows of `out` that no index names are undefined
+    on CUDA (callers name every row) and zero on the host."""
+    if src.is_cuda:
+        src = src.contiguous()
+        out = torch.empty((n_out, src.shape[1]), dtype=src.dtype, device=src.device)
+        with torch.cuda.device(src.device):
+            rc = _lib.load().stk_b200_scatter_rows(
+                _lib.ptr(src), _lib.ptr(out), _lib.ptr(index), index.numel(),
+                src.shape[1] * src.element_size(), _lib.stream_ptr(src.device))
+        _lib.check(rc, "stk_b200_scatter_rows")
+        return out
+    out = src.new_zeros((n_out, src.shape[1]))
+    valid = index >= 0
+    out[index[valid].long()] = src[valid]
+    return out
+
+
+def bin_index(counts, total_padded, block=BLOCK, compose=None):
+    """Gather index of the padded expert bins.
+
+    counts: int64 [world, local_experts], rows received from each peer for each local expert (the
+    received rows are ordered by peer, then expert).  Returns (index int32 [total_padded],
+    bin_rows int32 [local_experts]); see stk_b200_bin_index in include/stk_b200.h."""
+    world, local = counts.shape
+    if counts.is_cuda:
+        dev = counts.device
+        index = torch.empty(total_padded, dtype=torch.int32, device=dev)
+        bin_rows = torch.empty(local, dtype=torch.int32, device=dev)
+        with torch.cuda.device(dev):
+            rc = _lib.load().stk_b200_bin_index(
+                _lib.ptr(counts.contiguous()), world, local, block, _lib.ptr(compose),
+                _lib.ptr(index), total_padded, _lib.ptr(bin_rows), _lib.stream_ptr(dev))
+        _lib.check(rc, "stk_b200_bin_index")
+        return index, bin_rows
+    per_expert = counts.sum(0)
+    padded = ((per_expert + block - 1) // block) * block
+    index = torch.full((total_padded,), -1, dtype=torch.int32)
+    seg = counts.reshape(-1)
+    src_start = (torch.cumsum(seg, 0) - seg).view(world, local)
+    bin_start = torch.cumsum(padded, 0) - padded
+    for e in range(local):
+        pos = int(bin_start[e])
+        for p in range(world):
+            n = int(counts[p, e])
+            index[pos:pos + n] = torch.arange(int(src_start[p, e]), int(src_start[p, e]) + n,
+                                              dtype=torch.int32)
+            pos += n
+    if compose is not None:
+        valid = index >= 0
+        index[valid] = compose[index[valid].long()]
+    return index, (padded // block).to(torch.int32)
 
 
 def padded_bins(counts, block=BLOCK):
@@ -23,71 +115,78 @@ def padded_bins(counts, block=BLOCK):
     return padded, starts, int(padded.sum().item())
 
 
-def block_diagonal_topology(padded_counts, ffn, dtype, device, block=BLOCK, data=None):
-    """stk.Matrix of shape [sum(padded), E*ffn] whose block row r (belonging to expert e) holds
-    the ffn/block consecutive column blocks of expert e.  The transposed metadata comes from the
-    library's transpose kernel, as for any user-built Matrix."""
-    num_experts = padded_counts.numel()
-    cols_per_expert = ffn // block
-    # Counts that already live on the host (the exchange has them there) cost no device sync.
-    block_rows = int((padded_counts // block).sum())
-    rows_per_expert = (padded_counts // block).to(device, non_blocking=True)
-    expert_of_row = torch.repeat_interleave(
-        torch.arange(num_experts, device=device), rows_per_expert, output_size=block_rows)
-    row_indices = torch.repeat_interleave(
-        torch.arange(block_rows, device=device, dtype=torch.int16), cols_per_expert)
-    column_indices = (expert_of_row[:, None] * cols_per_expert +
-                      torch.arange(cols_per_expert, device=device)[None, :]).reshape(-1).to(torch.int16)
-    offsets = (torch.arange(block_rows + 1, device=device) * cols_per_expert).to(torch.int32)
-    nnz = block_rows * cols_per_expert
+def topology_from_bins(bin_rows, block_rows, ffn, dtype, device, block=BLOCK, data=None):
+    """stk.Matrix [block_rows*128, E*ffn]: expert e owns bin_rows[e] consecutive block rows and its
+    own ffn/128 block columns.  bin_rows: int32 [E] on `device`; block_rows: their sum, known to the
+    host.  All seven metadata arrays are written by one kernel (the transposed ones in closed
+    form, nothing is sorted)."""
+    experts = bin_rows.numel()
+    cpb = ffn // block
+    nnz = block_rows * cpb
+    meta16 = torch.empty((3, max(nnz, 1)), dtype=torch.int16, device=device)
+    offsets = torch.empty(block_rows + 1, dtype=torch.int32, device=device)
+    offsets_t = torch.empty(experts * cpb + 1, dtype=torch.int32, device=device)
+    block_offsets_t = torch.empty(nnz, dtype=torch.int32, device=device)
+    row_idx, col_idx, col_idx_t = (meta16[i, :nnz] for i in range(3))
+    with torch.cuda.device(device):
+        rc = _lib.load().stk_b200_dmoe_topology(
+            _lib.ptr(bin_rows), experts, cpb, block_rows, _lib.ptr(row_idx), _lib.ptr(col_idx),
+            _lib.ptr(offsets), _lib.ptr(col_idx_t), _lib.ptr(offsets_t), _lib.ptr(block_offsets_t),
+            _lib.stream_ptr(device))
+    _lib.check(rc, "stk_b200_dmoe_topology")
     if data is None:
         data = torch.empty((nnz, block, block), dtype=dtype, device=device)
-    size = torch.Size((block_rows * block, num_experts * ffn))
-    if cols_per_expert % 2 == 0:
-        # Known by construction: all block rows of an expert share one column list, column pairs
-        # never straddle experts; only row pairs at expert boundaries fail to pair.
-        _kernels.set_pair_hints(column_indices, 0.9, 1.0, 0.9, True)
-    return Matrix(size, data, row_indices, column_indices, offsets)
+    if cpb % 2 == 0:
+        # Known by construction: all block rows of an expert share one column list and column
+        # pairs never straddle experts; only row pairs at expert boundaries fail to pair.
+        _kernels.set_pair_hints(col_idx, 0.9, 1.0, 0.9, True)
+    return Matrix(torch.Size((block_rows * block, experts * ffn)), data, row_idx, col_idx, offsets,
+                  col_idx_t, offsets_t, block_offsets_t)
 
 
+def block_diagonal_topology(padded_counts, ffn, dtype, device, block=BLOCK, data=None):
+    """Same topology from per-expert padded row counts (host or device tensor)."""
+    bin_rows = (padded_counts // block).to(torch.int32)
+    block_rows = int(bin_rows.sum())
+    return topology_from_bins(bin_rows.to(device), block_rows, ffn, dtype, device, block, data)
+
+
+# ------------------------------------------------------------------------------ one GPU
 def route_top1(expert_ids, num_experts, block=BLOCK):
-    """Permutation of tokens into padded expert order for top-1 routing.
+    """Placement of tokens in padded expert order for top-1 routing on one device.
 
-    Returns (slot, padded, starts, total): token t goes to row slot[t] of the padded buffer;
-    rows that no token maps to are padding and must be zero."""
-    counts = torch.bincount(expert_ids, minlength=num_experts)
-    padded, starts, total = padded_bins(counts, block)
-    order = torch.argsort(expert_ids, stable=True)
-    sorted_experts = expert_ids[order]
-    rank_in_expert = torch.arange(expert_ids.numel(), device=expert_ids.device) - \
-        (torch.cumsum(counts, 0) - counts)[sorted_experts]
-    slot = torch.empty_like(order)
-    slot[order] = starts[sorted_experts] + rank_in_expert
-    return slot, padded, starts, total
+    Returns (index, padded, bin_rows, total): padded row r holds token index[r] (or is zero
+    padding where index[r] < 0); padded = rows per expert bin (host int64 [E]); bin_rows = the same
+    in blocks, on the device."""
+    order, offsets = sort_by_expert(expert_ids, num_experts)
+    counts = (offsets[1:] - offsets[:-1]).to(torch.int64).view(1, num_experts)
+    host_counts = counts.cpu().view(-1)                    # the one synchronisation
+    padded = ((host_counts + block - 1) // block) * block
+    total = int(padded.sum())
+    index, bin_rows = bin_index(counts, total, block, compose=order)
+    return index, padded, bin_rows, total
 
 
-def permute_tokens(x, slot, total_rows):
+def permute_tokens(x, index, total_rows=None):
     """Padded, expert-ordered copy of the token matrix x [T, h] (padding rows are zero)."""
-    out = torch.zeros((total_rows, x.shape[1]), dtype=x.dtype, device=x.device)
-    out[slot] = x
-    return out
+    return gather_rows(x, index, total_rows)
 
 
-def unpermute_tokens(y, slot):
-    """Inverse of permute_tokens: row t of the result is row slot[t] of y."""
-    return y[slot]
+def unpermute_tokens(y, index, tokens):
+    """Inverse of permute_tokens: token t gets the padded row that held it."""
+    return scatter_rows(y, index, tokens)
 
 
+# ------------------------------------------------------------------------------ expert parallel
 class ExpertParallelExchange:
     """Token exchange of an expert-parallel dMoE layer: rank g owns experts
     [g*E/n, (g+1)*E/n); every rank starts with its own tokens and their expert ids.
 
-    dispatch(): tokens travel to the owner of their expert (all_to_all_single with per-rank
-    split sizes, after the per-expert counts have been exchanged); the receiver places them by
-    local expert, every expert padded to a multiple of 128 rows.  combine(): the results travel
-    back and are put in the sender's original token order.  One host read-back per dispatch (the
-    counts; NCCL needs the split sizes on the host).  Works with any torch.distributed backend
-    (NCCL over NVLink on the GPUs, gloo on the host for tests).
+    dispatch(): tokens are sorted by expert (hence by destination rank), the per-expert counts are
+    exchanged, and the rows travel with all_to_all_single; the receiver gathers them into
+    per-expert bins padded to a multiple of 128 rows.  combine(): the inverse.  One host read-back
+    per dispatch (the counts: NCCL needs the split sizes on the host).  Works with any
+    torch.distributed backend: NCCL over NVLink on the GPUs, gloo on the host for tests.
     """
 
     def __init__(self, num_experts, group=None, block=BLOCK):
@@ -101,48 +200,35 @@ class ExpertParallelExchange:
         self.block = block
 
     def dispatch(self, x, expert_ids):
-        """Returns (x_padded [T'_local, h], padded_counts (host int64 [local_experts]), state)."""
+        """Returns (x_padded [T'_local, h], bin_rows int32 [local_experts] on x's device, state);
+        state["block_rows"] is the number of padded block rows (host int)."""
         dev = x.device
         world, local = self.world, self.local_experts
-        # Send order: by expert (hence by destination rank), stable in the token index.
-        send_order = torch.argsort(expert_ids, stable=True)
+        order, offsets = sort_by_expert(expert_ids, self.num_experts)
         counts = torch.empty((2, self.num_experts), dtype=torch.int64, device=dev)
-        counts[0] = torch.bincount(expert_ids, minlength=self.num_experts)
+        counts[0] = offsets[1:] - offsets[:-1]
         # counts[0][e] for the experts of rank g go to rank g: one row of E/n counts per peer
         dist.all_to_all_single(counts[1], counts[0], group=self.group)
-        host = counts.cpu()                                  # the one synchronisation
+        host = counts.cpu()                                   # the one synchronisation
         send_splits = host[0].view(world, local).sum(1).tolist()
-        recv_by_peer = host[1].view(world, local)            # [peer, local expert]
+        recv_by_peer = host[1].view(world, local)
         recv_splits = recv_by_peer.sum(1).tolist()
-        received = sum(recv_splits)
-        recv = torch.empty((received, x.shape[1]), dtype=x.dtype, device=dev)
-        dist.all_to_all_single(recv, x.index_select(0, send_order), recv_splits, send_splits,
-                               group=self.group)
-        # Rows arrive ordered (peer, local expert) in world*local contiguous segments; segment
-        # (peer, e) goes to bin e behind the segments of lower peers.  All bookkeeping on the host.
         per_expert = recv_by_peer.sum(0)
-        padded = ((per_expert + self.block - 1) // self.block) * self.block
-        bin_start = torch.cumsum(padded, 0) - padded
-        seg_len = recv_by_peer.reshape(-1)
-        src_start = torch.cumsum(seg_len, 0) - seg_len
-        within = torch.cumsum(recv_by_peer, 0) - recv_by_peer          # rows of lower peers in bin e
-        dst_start = (bin_start[None, :] + within).reshape(-1)
-        shift = (dst_start - src_start).to(dev, non_blocking=True)
-        slot = torch.arange(received, device=dev) + torch.repeat_interleave(
-            shift, seg_len.to(dev, non_blocking=True), output_size=received)
-        total = int(padded.sum())
-        x_padded = permute_tokens(recv, slot, total)
-        state = dict(send_order=send_order, send_splits=send_splits, recv_splits=recv_splits,
-                     slot=slot, tokens=x.shape[0])
-        return x_padded, padded, state
+        total = int((((per_expert + self.block - 1) // self.block) * self.block).sum())
+        recv = torch.empty((sum(recv_splits), x.shape[1]), dtype=x.dtype, device=dev)
+        dist.all_to_all_single(recv, gather_rows(x, order), recv_splits, send_splits,
+                               group=self.group)
+        index, bin_rows = bin_index(counts[1].view(world, local), total, self.block)
+        x_padded = gather_rows(recv, index, total)
+        state = dict(order=order, send_splits=send_splits, recv_splits=recv_splits, index=index,
+                     received=recv.shape[0], tokens=x.shape[0], block_rows=total // self.block)
+        return x_padded, bin_rows, state
 
     def combine(self, y_padded, state):
         """Inverse of dispatch for the per-token results y_padded [T'_local, h_out]."""
-        back = y_padded.index_select(0, state["slot"])
+        back = scatter_rows(y_padded, state["index"], state["received"])
         out_sorted = torch.empty((state["tokens"], y_padded.shape[1]), dtype=y_padded.dtype,
                                  device=y_padded.device)
         dist.all_to_all_single(out_sorted, back, state["send_splits"], state["recv_splits"],
                                group=self.group)
-        out = torch.empty_like(out_sorted)
-        out[state["send_order"]] = out_sorted
-        return out
+        return scatter_rows(out_sorted, state["order"], state["tokens"])

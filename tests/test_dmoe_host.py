@@ -8,20 +8,25 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 
+def check_routing(dmoe, x, ids, experts):
+    index, padded, bin_rows, total = dmoe.route_top1(ids, experts)
+    assert total == int(padded.sum()) and bool((padded % 128 == 0).all())
+    assert bin_rows.cpu().tolist() == (padded // 128).tolist()
+    xp = dmoe.permute_tokens(x, index, total)
+    assert torch.equal(dmoe.unpermute_tokens(xp, index, x.shape[0]), x)
+    counts = torch.bincount(ids.cpu(), minlength=experts)
+    starts = torch.cumsum(padded, 0) - padded
+    for e in range(experts):
+        rows = xp[starts[e]:starts[e] + padded[e]].cpu()
+        assert torch.equal(rows[:counts[e]], x.cpu()[ids.cpu() == e])   # stable order inside an expert
+        assert torch.count_nonzero(rows[counts[e]:]).item() == 0      # zero padding
+
+
 def test_route_top1_and_padding():
     from stk_b200 import dmoe
     torch.manual_seed(0)
-    ids = torch.randint(0, 4, (1000,))
-    x = torch.randn(1000, 8)
-    slot, padded, starts, total = dmoe.route_top1(ids, 4)
-    assert total == int(padded.sum()) and bool((padded % 128 == 0).all())
-    xp = dmoe.permute_tokens(x, slot, total)
-    assert torch.equal(dmoe.unpermute_tokens(xp, slot), x)
-    counts = torch.bincount(ids, minlength=4)
-    for e in range(4):
-        rows = xp[starts[e]:starts[e] + padded[e]]
-        assert torch.equal(rows[:counts[e]], x[ids == e])       # stable order inside an expert
-        assert torch.count_nonzero(rows[counts[e]:]).item() == 0  # zero padding
+    check_routing(dmoe, torch.randn(1000, 8), torch.randint(0, 4, (1000,)), 4)
+    check_routing(dmoe, torch.randn(300, 8), torch.randint(0, 2, (300,)) * 3, 5)   # empty experts
 
 
 def _exchange_worker(rank, world, port, tmp):
@@ -34,8 +39,9 @@ def _exchange_worker(rank, world, port, tmp):
         ids = torch.randint(0, E, (T,))
         x = torch.randn(T, h)
         ex = dmoe.ExpertParallelExchange(E)
-        xp, padded, state = ex.dispatch(x, ids)
-        assert xp.shape[0] == int(padded.sum()) and bool((padded % 128 == 0).all())
+        xp, bin_rows, state = ex.dispatch(x, ids)
+        padded = bin_rows.long() * 128
+        assert xp.shape[0] == int(padded.sum()) == state["block_rows"] * 128
         # every local expert's bin holds exactly the tokens routed to it from all ranks,
         # ordered by source rank then token index, then zero padding
         gathered = [None] * world

@@ -270,9 +270,9 @@ def test_dmoe_shaped_products_full_size(stk, dtype):
     T, h, f, E = 16384, 1024, 4096, 8
     g = torch.Generator().manual_seed(0)
     ids = torch.multinomial(torch.full((E,), 1.0 / E), T, replacement=True, generator=g).to(dev)
-    slot, padded, starts, total = dmoe.route_top1(ids, E)
-    topo = dmoe.block_diagonal_topology(padded, f, dtype, dev)
-    x = dmoe.permute_tokens((torch.randn(T, h, generator=g) * 0.02).to(dtype).to(dev), slot, total)
+    index, padded, bin_rows, total = dmoe.route_top1(ids, E)
+    topo = dmoe.topology_from_bins(bin_rows, total // 128, f, dtype, dev)
+    x = dmoe.permute_tokens((torch.randn(T, h, generator=g) * 0.02).to(dtype).to(dev), index, total)
     w1 = (torch.randn(h, E * f, generator=g) * 0.02).to(dtype).to(dev).requires_grad_(True)
     w2 = (torch.randn(E * f, h, generator=g) * 0.02).to(dtype).to(dev).requires_grad_(True)
     x.requires_grad_(True)
@@ -310,3 +310,39 @@ def test_dmoe_shaped_products_full_size(stk, dtype):
         assert_product_close(lhs, rhs, "dsd linearity", roundings=3)
     del y, dy, x, w1, w2
     torch.cuda.empty_cache()
+
+
+def test_dmoe_routing_kernels_match_host_logic(stk):
+    """Sort by expert, padded-bin gather index, row gather / scatter and the closed-form topology on
+    the GPU against the same steps done with torch indexing on the host and against the generic
+    transpose kernel."""
+    from stk_b200 import dmoe
+    from tests.test_dmoe_host import check_routing
+    g = torch.Generator().manual_seed(3)
+    for tokens, experts, hidden in [(5000, 8, 64), (16384, 64, 256), (777, 3, 8)]:
+        ids = torch.randint(0, experts, (tokens,), generator=g)
+        if experts == 64:
+            ids[ids == 5] = 6          # an expert without tokens
+        x = torch.randn(tokens, hidden, generator=g).half()
+        check_routing(dmoe, x.cuda(), ids.cuda(), experts)
+        order_d, offsets_d = dmoe.sort_by_expert(ids.cuda(), experts)
+        order_h, offsets_h = dmoe.sort_by_expert(ids, experts)
+        assert torch.equal(order_d.cpu(), order_h) and torch.equal(offsets_d.cpu(), offsets_h)
+        # received-rows layout of a 4-rank exchange: counts [peer, local expert]
+        counts = torch.randint(0, 300, (4, experts // 1 if experts < 8 else 8), generator=g)
+        total = int((((counts.sum(0) + 127) // 128) * 128).sum())
+        idx_h, rows_h = dmoe.bin_index(counts, total)
+        idx_d, rows_d = dmoe.bin_index(counts.cuda(), total)
+        assert torch.equal(idx_d.cpu(), idx_h) and torch.equal(rows_d.cpu(), rows_h)
+        recv = torch.randn(int(counts.sum()), hidden, generator=g).half()
+        padded_d = dmoe.gather_rows(recv.cuda(), idx_d, total)
+        assert torch.equal(padded_d.cpu(), dmoe.gather_rows(recv, idx_h, total))
+        back = dmoe.scatter_rows(padded_d, idx_d, recv.shape[0])
+        assert torch.equal(back.cpu(), recv)
+        # closed-form topology == topology built from its row-major half by the transpose kernel
+        topo = dmoe.topology_from_bins(rows_d, int(rows_h.sum()), 512, torch.float16, "cuda")
+        ref = stk.Matrix(topo.size(), topo.data, topo.row_indices, topo.column_indices, topo.offsets)
+        for key in META_KEYS:
+            assert torch.equal(getattr(topo, key), getattr(ref, key)), key
+        expect_rows = torch.repeat_interleave(torch.arange(int(rows_h.sum())), 4).to(torch.int16)
+        assert torch.equal(topo.row_indices.cpu(), expect_rows)
