@@ -36,6 +36,10 @@ extern "C" {
 #define STK_F16 0
 #define STK_BF16 1
 
+/* epilogue of stk_b200_sdd */
+#define STK_EPILOGUE_NONE 0
+#define STK_EPILOGUE_GELU 1
+
 /* status codes */
 #define STK_OK 0
 #define STK_ERR_NULL_POINTER (-1)   /* a required pointer is NULL */
@@ -77,13 +81,17 @@ int stk_b200_device_status(int* status_host);
  *   rhs: logical [K,N]; same convention with ld_rhs.
  *   out: [nnz,128,128] contiguous.
  *   offsets: CSR offsets [M/128+1]; only read when pair_mode = 1 (may be NULL otherwise).
+ *   epilogue: 0 stores the product; 1 (STK_EPILOGUE_GELU) stores GeLU(product), the exact erf form
+ *             applied to the fp32 accumulator before rounding - the step between SDD and DSD in a
+ *             dMoE layer, fused so that the hidden activations are written once.  The reference
+ *             has no fused form (it runs a separate elementwise kernel on Matrix.data).
  * nnz == 0 is a no-op.
  */
 int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const int32_t* offsets,
                  const int16_t* row_indices, const int16_t* column_indices,
                  int64_t M, int64_t N, int64_t K, int64_t nnz,
                  int lhs_colmajor, int64_t ld_lhs, int rhs_colmajor, int64_t ld_rhs,
-                 int dtype, int pair_mode, void* stream);
+                 int dtype, int pair_mode, int epilogue, void* stream);
 
 /*
  * DSD: out[M,N] = op(S)[M,K] @ rhs[K,N].

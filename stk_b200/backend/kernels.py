@@ -178,8 +178,9 @@ def dds(lhs, shape, data, offsets, row_indices, column_indices, offsets_t, colum
     _lib.check(rc, "stk_b200_dds")
 
 
-def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices):
-    """out[p] = (lhs @ rhs)[block p] for the blocks listed by row_indices / column_indices."""
+def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices, epilogue=0):
+    """out[p] = (lhs @ rhs)[block p] for the blocks listed by row_indices / column_indices;
+    epilogue=1 stores GeLU of the product instead (an extension, see stk_b200.ops.sdd_gelu)."""
     _require_cuda(lhs, rhs, out)
     if lhs.shape[1] != rhs.shape[0]:
         raise DimensionError("incompatible dimensions")
@@ -194,7 +195,7 @@ def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices):
         rc = _lib.load().stk_b200_sdd(
             _lib.ptr(lhs), _lib.ptr(rhs), _lib.ptr(out), _lib.ptr(offsets), _lib.ptr(row_indices),
             _lib.ptr(column_indices), M, N, K, out.shape[0], lhs_colmajor, ld_lhs, rhs_colmajor,
-            ld_rhs, _lib.dtype_code(out.dtype), pairs, _lib.stream_ptr(out.device))
+            ld_rhs, _lib.dtype_code(out.dtype), pairs, epilogue, _lib.stream_ptr(out.device))
     _lib.check(rc, "stk_b200_sdd")
 
 

@@ -26,9 +26,10 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
                             const int16_t* row_indices, const int16_t* column_indices, int64_t M,
                             int64_t N, int64_t K, int64_t nnz, int lhs_colmajor, int64_t ld_lhs,
                             int rhs_colmajor, int64_t ld_rhs, int dtype, int pair_mode,
-                            void* stream) {
+                            int epilogue, void* stream) {
   int rc = check_dtype_dims(dtype, M, N, K, nnz, 32);
   if (rc != STK_OK) return rc;
+  if (epilogue != kEpilogueNone && epilogue != kEpilogueGelu) return STK_ERR_BAD_DIMS;
   if (nnz == 0) return STK_OK;
   if (out == nullptr || row_indices == nullptr || column_indices == nullptr)
     return STK_ERR_NULL_POINTER;
@@ -60,6 +61,7 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
     p.a_mn = lhs_colmajor ? 1 : 0;
     p.b_mn = rhs_colmajor ? 0 : 1;
     p.fmt = dtype;
+    p.epilogue = epilogue;
     p.inner = segments;
     p.num_items = row_pairs * segments;
     p.k_steps = k_steps;
@@ -78,6 +80,7 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
   p.a_mn = lhs_colmajor ? 1 : 0;
   p.b_mn = rhs_colmajor ? 0 : 1;
   p.fmt = dtype;
+  p.epilogue = epilogue;
   p.num_tiles = static_cast<int>(nnz);
   p.tiles_inner = 1;
   p.k_steps = k_steps;

@@ -18,8 +18,9 @@
 // rows / columns share most of their lists (dMoE topologies do: all rows of one expert are alike).
 // The host picks this kernel or the 128x128 kernel per call.
 //
-// Roles per CTA (224 threads): warp 0 = TMA producer of the A tiles, warp 6 = TMA producer of the B
-// tiles, warp 1 = TMEM owner (and, in the leader CTA, the MMA issuer), warps 2..5 = epilogue.  The MMA issuer does not know the tiles: it consumes a
+// Roles per CTA (352 threads): warp 0 = TMA producer of the A tiles, warp 6 = TMA producer of the B
+// tiles, warp 1 = TMEM owner (and, in the leader CTA, the MMA issuer), warps 2..5 and 7..10 = two
+// epilogue groups that drain alternate 64-column sub-tiles of an accumulator.  The MMA issuer does not know the tiles: it consumes a
 // stream of pipeline stages, each tagged FIRST / LAST (of a tile) or END by the leader's producer.
 #pragma once
 #include <cuda.h>
@@ -35,7 +36,8 @@
 
 namespace stk {
 
-constexpr int kPThreads = 224;       // warps: 0 A-producer, 1 MMA / TMEM, 2..5 epilogue, 6 B-producer
+constexpr int kPThreads = 352;       // warps: 0 A-producer, 1 MMA / TMEM, 2..5 and 7..10 epilogue, 6 B-producer
+constexpr int kPEpilogueWarps = 8;   // two groups of four; a group covers the four TMEM lane quarters
 constexpr int kPProducerBWarp = 6;
 constexpr int kPStages = 6;
 constexpr int kPAccCols = 256;   // one accumulator: 128 lanes x 256 fp32 columns per CTA
@@ -43,7 +45,7 @@ constexpr int kPTmemCols = 512;  // two accumulators
 constexpr int kPNumBars = 2 * kPStages + 4;
 constexpr int kOutStageBytes = kBlk * 64 * 2;  // one 128-row x 64-column 16-bit output sub-tile
 constexpr int kPSmemBytes =
-    kPStages * kStageBytes + 2 * kOutStageBytes + kPNumBars * 8 + kPStages * 4 + 16 + 1024;
+    kPStages * kStageBytes + 2 * kOutStageBytes + kPNumBars * 8 + kPStages * 4 + 32 + 1024;
 constexpr int kNoBlock = 0x7fffffff;
 
 enum : uint32_t { kFlagFirst = 1u, kFlagLast = 2u, kFlagEnd = 4u };
@@ -64,6 +66,7 @@ __device__ long long g_prof[160][8];
 struct PairParams {
   int mode;
   int a_mn, b_mn, fmt;
+  int epilogue;     // kEpilogueNone / kEpilogueGelu
   int num_items;    // static work items, dealt round-robin to the CTA pairs
   int inner;        // DSD: N supertiles per row pair; DDS: M supertiles per column pair; SDD: segments per row pair
   int k_steps;      // SDD: ceil(K / 64)
@@ -183,24 +186,25 @@ __device__ __forceinline__ void load_operand_pair(const CUtensorMap* tm, uint32_
   }
 }
 
-// Barrier among the 128 epilogue threads of a CTA (hardware barrier 1; 0 is __syncthreads).
-__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// Barrier among the 128 threads of one epilogue group (hardware barriers 1 and 2; 0 is __syncthreads).
+__device__ __forceinline__ void epilogue_sync(int group) {
+  asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory");
+}
 
-// The 128 epilogue threads of one CTA move `ncols` accumulator columns (a multiple of 64, starting
-// at TMEM column `col0`) to the output: TMEM -> registers -> 16-bit -> a 128x64 staging tile in
-// shared memory (128-byte swizzle, conflict-free 16-byte stores) -> one TMA store per sub-tile.
-// Two staging tiles alternate; `sub` counts sub-tiles over the whole kernel.
+// One epilogue group (four warps, 128 threads) moves its share of `ncols` accumulator columns (a
+// multiple of 64, starting at TMEM column `col0`) to the output: the two groups take alternate
+// 64-column sub-tiles.  TMEM -> registers -> optional activation -> 16-bit -> the group's 128x64
+// staging tile in shared memory (128-byte swizzle, conflict-free 16-byte stores) -> one TMA store.
 __device__ __forceinline__ void drain_to_output(uint32_t t_addr, int col0, int ncols, int fmt,
-                                                const CUtensorMap* tmC, int out_x, int out_y,
-                                                uint32_t staging_base, int row, bool issuer,
-                                                uint32_t& sub) {
+                                                int epilogue, const CUtensorMap* tmC, int out_x,
+                                                int out_y, uint32_t staging, int row, int group,
+                                                bool issuer) {
 #ifdef STK_EXP_SKIP_EPILOGUE  // experiment: main loop alone, nothing drained or stored
   return;
 #endif
-  for (int c = 0; c < ncols; c += 64, ++sub) {
-    const uint32_t buf = staging_base + (sub & 1u) * kOutStageBytes;
-    if (issuer) tma_store_wait_read<1>();  // the store that last read this buffer is done with it
-    epilogue_sync();
+  for (int c = group * 64; c < ncols; c += 128) {
+    if (issuer) tma_store_wait_read<0>();  // the group's previous store is done reading the tile
+    epilogue_sync(group);
     uint32_t r0[32], r1[32];
     tmem_ld_32x32(t_addr + col0 + c, r0);
     tmem_ld_32x32(t_addr + col0 + c + 32, r1);
@@ -208,8 +212,14 @@ __device__ __forceinline__ void drain_to_output(uint32_t t_addr, int col0, int n
     uint32_t packed[32];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const float a0 = __uint_as_float(r0[2 * i]), a1 = __uint_as_float(r0[2 * i + 1]);
-      const float b0 = __uint_as_float(r1[2 * i]), b1 = __uint_as_float(r1[2 * i + 1]);
+      float a0 = __uint_as_float(r0[2 * i]), a1 = __uint_as_float(r0[2 * i + 1]);
+      float b0 = __uint_as_float(r1[2 * i]), b1 = __uint_as_float(r1[2 * i + 1]);
+      if (epilogue == kEpilogueGelu) {
+        a0 = gelu_erf(a0);
+        a1 = gelu_erf(a1);
+        b0 = gelu_erf(b0);
+        b1 = gelu_erf(b1);
+      }
       if (fmt == STK_BF16) {
         const __nv_bfloat162 va = __floats2bfloat162_rn(a0, a1), vb = __floats2bfloat162_rn(b0, b1);
         packed[i] = *reinterpret_cast<const uint32_t*>(&va);
@@ -220,7 +230,7 @@ __device__ __forceinline__ void drain_to_output(uint32_t t_addr, int col0, int n
         packed[16 + i] = *reinterpret_cast<const uint32_t*>(&vb);
       }
     }
-    const uint32_t row_addr = buf + row * 128;
+    const uint32_t row_addr = staging + row * 128;
 #pragma unroll
     for (int ch = 0; ch < 8; ++ch) {
       const uint32_t addr = row_addr + ((ch ^ (row & 7)) << 4);
@@ -229,9 +239,9 @@ __device__ __forceinline__ void drain_to_output(uint32_t t_addr, int col0, int n
                    : "memory");
     }
     fence_proxy_async_smem();
-    epilogue_sync();
+    epilogue_sync(group);
     if (issuer) {
-      tma_store_2d(tmC, buf, out_x + c, out_y);
+      tma_store_2d(tmC, staging, out_x + c, out_y);
       tma_store_commit();
     }
   }
@@ -255,7 +265,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   volatile uint32_t* stage_flags = reinterpret_cast<volatile uint32_t*>(bars + kPNumBars);
   uint32_t* tmem_slot = const_cast<uint32_t*>(stage_flags) + kPStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* epilogue_go = abort_flag + 1;
+  volatile int* epilogue_go = abort_flag + 1;  // [2], one per epilogue group
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -270,7 +280,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);   // one multicast commit per tile
-      mbar_init(tempty_bar(a), 8);  // leader's copy: four epilogue warps of each CTA
+      mbar_init(tempty_bar(a), 2 * kPEpilogueWarps);  // leader's copy: the epilogue warps of both CTAs
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -436,22 +446,25 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs)
-    const int quarter = warp & 3;
+    const int quarter = warp & 3;  // a warp may only read TMEM lanes 32*(warp%4) .. +31
     const int row = quarter * 32 + lane;
+    const int group = warp > kPProducerBWarp ? 1 : 0;
+    const bool issuer = lane == 0 && (warp == 2 || warp == kPProducerBWarp + 1);  // issues the group's TMA stores
+    const uint32_t staging = staging_base + group * kOutStageBytes;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t leader_tempty[2] = {map_to_cta(tempty_bar(0), 0), map_to_cta(tempty_bar(1), 0)};
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
     // Waits for the accumulator; returns its TMEM address for this warp.
-    // The epilogue warps meet at hardware barriers while draining, so all four must take the
-    // same decision: one thread reads the abort flag between two barriers, everybody follows it.
+    // The warps of a group meet at hardware barriers while draining, so all four must take the
+    // same decision: one thread reads the abort flag between two barriers, the group follows it.
     auto acquire = [&](uint32_t& t_addr) {
       mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
-      epilogue_sync();
-      if (threadIdx.x == 64) *epilogue_go = (*abort_flag == 0) ? 1 : 0;
-      epilogue_sync();
-      ok = *epilogue_go != 0;
+      epilogue_sync(group);
+      if (issuer) epilogue_go[group] = (*abort_flag == 0) ? 1 : 0;
+      epilogue_sync(group);
+      ok = epilogue_go[group] != 0;
       if (ok) tc_fence_after();
       t_addr = tmem_base + lane_base + static_cast<uint32_t>(acc * kPAccCols);
     };
@@ -463,8 +476,6 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (acc == 0) acc_phase ^= 1u;
     };
     uint16_t* out = static_cast<uint16_t*>(p.out);
-    const bool issuer = threadIdx.x == 64;  // first epilogue thread issues the TMA stores
-    uint32_t sub = 0;
     for (int item = pair_id; item < p.num_items && ok; item += num_pairs) {
       const int outer = item / p.inner, inner = item - outer * p.inner;
       if (p.mode == kModeSDD) {
@@ -479,8 +490,8 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int h = 0; h < 2; ++h) {
             const int pb = blk[rank][h];
             if (pb != kNoBlock)
-              drain_to_output(t_addr, h * kBlk, kBlk, p.fmt, &tmC, 0, pb * kBlk, staging_base, row,
-                              issuer, sub);
+              drain_to_output(t_addr, h * kBlk, kBlk, p.fmt, p.epilogue, &tmC, 0, pb * kBlk, staging,
+                              row, group, issuer);
           }
           release();
         }
@@ -494,7 +505,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int ncols = min(2 * kBlk, p.out_cols - tile_col);
         uint16_t* dst = out + (static_cast<long long>(tile_row) + row) * p.ldc + tile_col;
         if (w.empty()) {
-          if (rows_valid) {
+          if (rows_valid && group == 0) {
             const uint4 z = make_uint4(0u, 0u, 0u, 0u);
             for (int c = 0; c < ncols; c += 8) *reinterpret_cast<uint4*>(dst + c) = z;
           }
@@ -504,8 +515,8 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         acquire(t_addr);
         if (!ok) break;
         if (rows_valid)
-          drain_to_output(t_addr, 0, ncols, p.fmt, &tmC, tile_col, tile_row, staging_base, row,
-                          issuer, sub);
+          drain_to_output(t_addr, 0, ncols, p.fmt, p.epilogue, &tmC, tile_col, tile_row, staging, row,
+                          group, issuer);
         release();
       }
     }

@@ -49,11 +49,34 @@ constexpr int kSmemBytes = kStages * kStageBytes + kNumBars * 8 + 16 + 1024;  //
 
 enum : int { kModeSDD = 0, kModeDSD = 1, kModeDDS = 2 };
 
+// Optional activation applied to the fp32 accumulator before it is rounded and stored.
+enum : int { kEpilogueNone = 0, kEpilogueGelu = 1 };
+
+// GeLU in its exact form x * Phi(x) (torch.nn.functional.gelu's default).  Phi comes from the
+// Abramowitz-Stegun 7.1.26 approximation of erfc, erfc(z) = t*P(t)*exp(-z^2), t = 1/(1+0.3275911 z),
+// |error| < 1.5e-7 - far below the 16-bit output rounding.  It runs in the epilogue warps, one warp
+// per scheduler, so it is kept to two special-function instructions (approximate reciprocal and
+// exponential, ~2^-22 relative error) and a short Horner chain; the library erff and the
+// IEEE-rounded intrinsics made the epilogue slower than the main loop.
+__device__ __forceinline__ float gelu_erf(float x) {
+  const float az = fabsf(x) * 0.70710678118654752f;
+  float t, e;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, az, 1.0f)));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(az * az * -1.4426950408889634f));
+  float y = fmaf(1.061405429f, t, -1.453152027f);
+  y = fmaf(y, t, 1.421413741f);
+  y = fmaf(y, t, -0.284496736f);
+  y = fmaf(y, t, 0.254829592f);
+  const float half_erfc = 0.5f * y * t * e;             // Phi(-|x|)
+  return x * (x < 0.0f ? half_erfc : 1.0f - half_erfc);  // Phi(x) = 1 - Phi(-x)
+}
+
 struct BsmmParams {
   int mode;
   int a_mn;        // 1: A tile is M-contiguous in memory (transposed operand), 0: K-contiguous
   int b_mn;        // 1: B tile is N-contiguous in memory, 0: K-contiguous
   int fmt;         // STK_F16 / STK_BF16
+  int epilogue;    // kEpilogueNone / kEpilogueGelu
   int num_tiles;
   int tiles_inner; // DSD: number of N tiles (n runs fastest); DDS: number of M tiles (m runs fastest)
   int k_steps;     // SDD: ceil(K / 64)
@@ -302,8 +325,12 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float lo = __uint_as_float(r[2 * i]);
-          const float hi = __uint_as_float(r[2 * i + 1]);
+          float lo = __uint_as_float(r[2 * i]);
+          float hi = __uint_as_float(r[2 * i + 1]);
+          if (p.epilogue == kEpilogueGelu) {
+            lo = gelu_erf(lo);
+            hi = gelu_erf(hi);
+          }
           if (p.fmt == STK_BF16) {
             const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
             packed[i] = *reinterpret_cast<const uint32_t*>(&v);

@@ -36,3 +36,23 @@ def sdd(a, b, topo):
     out = sputnik.sdd(a, b, topo.size(), *_fields(topo))
     return Matrix(topo.size(), out, topo.row_indices, topo.column_indices, topo.offsets,
                   topo.column_indices_t, topo.offsets_t, topo.block_offsets_t)
+
+
+@torch.no_grad()
+def sdd_gelu(a, b, topo):
+    """sparse = GeLU(a @ b) on the nonzero blocks of `topo`, the activation applied to the fp32
+    accumulator inside the matmul kernel (torch.nn.functional.gelu's exact form).
+
+    An extension over the reference API: the sdd -> GeLU -> dsd step of a dMoE layer writes its
+    hidden activations once instead of write / read / write.  Forward only (not differentiable);
+    training code uses sdd followed by gelu on Matrix.data."""
+    from stk_b200.backend import kernels
+    assert isinstance(a, torch.Tensor)
+    assert isinstance(b, torch.Tensor)
+    assert isinstance(topo, Matrix)
+    assert topo.is_contiguous()
+    out = torch.empty(topo.data.shape, dtype=a.dtype, device=a.device)
+    kernels.sdd(a, b, topo.size(), out, topo.offsets, topo.row_indices, topo.column_indices,
+                epilogue=1)
+    return Matrix(topo.size(), out, topo.row_indices, topo.column_indices, topo.offsets,
+                  topo.column_indices_t, topo.offsets_t, topo.block_offsets_t)

@@ -346,3 +346,22 @@ def test_dmoe_routing_kernels_match_host_logic(stk):
             assert torch.equal(getattr(topo, key), getattr(ref, key)), key
         expect_rows = torch.repeat_interleave(torch.arange(int(rows_h.sum())), 4).to(torch.int16)
         assert torch.equal(topo.row_indices.cpu(), expect_rows)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_sdd_with_fused_gelu(stk, dtype):
+    """sdd_gelu == GeLU (exact erf form) of the fp32 product, rounded once."""
+    np.random.seed(9)
+    torch.manual_seed(9)
+    topo = stk.random.mask(512, 768, 0.4, 128).to("cuda")
+    r, c = topo.row_indices.cpu().numpy(), topo.column_indices.cpu().numpy()
+    a = torch.randn(512, 192).to(dtype)
+    b = torch.randn(192, 768).to(dtype)
+    full = torch.nn.functional.gelu(a.float() @ b.float())
+    blocks = full.reshape(4, 128, 6, 128).permute(0, 2, 1, 3)[torch.from_numpy(r).long(), torch.from_numpy(c).long()]
+    out = stk.ops.sdd_gelu(a.cuda(), b.cuda(), topo)
+    assert out.dtype == dtype and isinstance(out, stk.Matrix)
+    assert_product_close(out.data, blocks, "sdd_gelu")
+    # and it equals the unfused pipeline up to the extra rounding of the unfused one
+    unfused = torch.nn.functional.gelu(stk.ops.sdd(a.cuda(), b.cuda(), topo).data.float())
+    assert_product_close(out.data, unfused, "sdd_gelu vs sdd+gelu", roundings=2)
