@@ -29,6 +29,9 @@ sys.path.insert(0, ROOT)
 T_TOKENS, HIDDEN, FFN, EXPERTS = 16384, 1024, 4096, 8   # per GPU
 DTYPE = torch.float16
 METRIC = "nnz_block_tflops_dmoe_fwd_sdd_dsd"
+# dram__bytes_read.sum + dram__bytes_write.sum of the two bsmm_pair_kernel launches of one step, from the ncu
+# capture summarised in profiles/bsmm_pair_kernel_dmoe_fwd.md (sdd+gelu 204.2 MB, dsd 247.1 MB), per launch.
+NCU_DRAM_BYTES_PER_LAUNCH = (204.2e6 + 247.1e6) / 2
 
 
 def measured_peaks():
@@ -296,7 +299,9 @@ def run_ours(args):
         "gpu_launches": 2 * args.steps,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": peak_tflops,
-                     "unit": "TFLOP/s", "frac": round(achieved / peak_tflops, 4), "traffic": None,
+                     "unit": "TFLOP/s", "frac": round(achieved / peak_tflops, 4),
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "traffic_unit": "DRAM bytes per launch (ncu)",
+                     "algorithmic_flops_per_launch": flops_sdd,
                      "kernel": "bsmm_pair_kernel (sdd+gelu and dsd launches)", "peak_kind": peak_kind + " bf16 burst",
                      "nominal_frac": round(achieved / 2250.0, 4)},
         "kernels": {

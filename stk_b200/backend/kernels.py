@@ -144,7 +144,7 @@ def dsd(shape, data, offsets, row_indices, column_indices, offsets_t, column_ind
     else:
         meta = (offsets, column_indices, None)
         pairs = _use_pairs("rows", row_indices, column_indices, K // BLOCK)
-    with torch.cuda.device(out.device):
+    with _lib.on_device(out.device):
         rc = _lib.load().stk_b200_dsd(
             _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),
             _lib.ptr(rhs), _lib.ptr(out), M, N, K, data.shape[0], int(bool(transpose_a)),
@@ -170,7 +170,7 @@ def dds(lhs, shape, data, offsets, row_indices, column_indices, offsets_t, colum
     else:
         meta = (offsets_t, column_indices_t, block_offsets_t)
         pairs = _use_pairs("cols", row_indices, column_indices, N // BLOCK)
-    with torch.cuda.device(out.device):
+    with _lib.on_device(out.device):
         rc = _lib.load().stk_b200_dds(
             _lib.ptr(lhs), _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),
             _lib.ptr(out), M, N, K, data.shape[0], lhs_colmajor, ld_lhs, int(bool(transpose_b)),
@@ -191,7 +191,7 @@ def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices, epilogue=0):
     lhs, lhs_colmajor, ld_lhs = _dense_layout(lhs)
     rhs, rhs_colmajor, ld_rhs = _dense_layout(rhs)
     pairs = _use_pairs("tiles", row_indices, column_indices, N // BLOCK)
-    with torch.cuda.device(out.device):
+    with _lib.on_device(out.device):
         rc = _lib.load().stk_b200_sdd(
             _lib.ptr(lhs), _lib.ptr(rhs), _lib.ptr(out), _lib.ptr(offsets), _lib.ptr(row_indices),
             _lib.ptr(column_indices), M, N, K, out.shape[0], lhs_colmajor, ld_lhs, rhs_colmajor,
@@ -205,7 +205,7 @@ def row_indices(shape, data, offsets, column_indices, out):
     if out.dtype != torch.int16:
         raise ValueError(f"row indices are int16, got an output of {out.dtype}")
     block_rows = offsets.numel() - 1
-    with torch.cuda.device(out.device):
+    with _lib.on_device(out.device):
         rc = _lib.load().stk_b200_row_indices(
             _lib.ptr(offsets), _lib.ptr(out), block_rows, out.numel(), _lib.stream_ptr(out.device))
     _lib.check(rc, "stk_b200_row_indices")
@@ -222,7 +222,7 @@ def transpose_meta(row_indices, column_indices, block_cols):
     lib = _lib.load()
     ws_bytes = lib.stk_b200_transpose_meta_workspace_bytes(nnz, block_cols)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         rc = lib.stk_b200_transpose_meta(
             _lib.ptr(row_indices.contiguous()), _lib.ptr(column_indices.contiguous()), nnz,
             block_cols, _lib.ptr(column_indices_t), _lib.ptr(offsets_t), _lib.ptr(block_offsets_t),
@@ -245,7 +245,7 @@ def block_mask(x, blocking):
     if x.stride(1) != 1:
         x = x.contiguous()
     mask = torch.empty((rows // blocking, cols // blocking), dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    with _lib.on_device(x.device):
         rc = _lib.load().stk_b200_block_mask(
             _lib.ptr(x), rows, cols, x.stride(0) if rows > 1 else max(cols, 1), blocking,
             _elem_bytes(x), _lib.ptr(mask), _lib.stream_ptr(x.device))
@@ -265,7 +265,7 @@ def mask_to_topology(mask):
     mask = mask.contiguous()
     offsets = torch.empty(block_rows + 1, dtype=torch.int32, device=dev)
     lib = _lib.load()
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         rc = lib.stk_b200_mask_to_offsets(_lib.ptr(mask), block_rows, block_cols, _lib.ptr(offsets),
                                           _lib.stream_ptr(dev))
         _lib.check(rc, "stk_b200_mask_to_offsets")
@@ -288,7 +288,7 @@ def gather_blocks(x, blocking, row_idx, col_idx):
         x = x.contiguous()
     nnz = row_idx.numel()
     data = torch.empty((nnz, blocking, blocking), dtype=x.dtype, device=x.device)
-    with torch.cuda.device(x.device):
+    with _lib.on_device(x.device):
         rc = _lib.load().stk_b200_gather_blocks(
             _lib.ptr(x), rows, cols, x.stride(0) if rows > 1 else max(cols, 1), blocking,
             _elem_bytes(x), _lib.ptr(row_idx), _lib.ptr(col_idx), nnz, _lib.ptr(data),
@@ -304,7 +304,7 @@ def to_dense(data, offsets, column_indices, block_rows, block_cols, blocking):
                       device=data.device)
     if out.numel() == 0:
         return out
-    with torch.cuda.device(data.device):
+    with _lib.on_device(data.device):
         rc = _lib.load().stk_b200_to_dense(
             _lib.ptr(data.contiguous()) if data.numel() else None, _lib.ptr(offsets),
             _lib.ptr(column_indices) if column_indices.numel() else None, block_rows, block_cols,

@@ -95,14 +95,42 @@ def device_status():
 
 
 def ptr(t):
-    """Device pointer of a tensor (None -> NULL)."""
-    if t is None:
-        return None
-    return ctypes.c_void_p(t.data_ptr())
+    """Device pointer of a tensor as a plain int (None -> NULL); ctypes converts it to void*."""
+    return None if t is None else t.data_ptr()
+
+
+def _index(device):
+    if isinstance(device, int):
+        return device
+    if not isinstance(device, torch.device):
+        device = torch.device(device)
+    return device.index if device.index is not None else torch.cuda.current_device()
 
 
 def stream_ptr(device):
-    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    """Raw handle of the current stream of `device` (an int; 0 is the legacy default stream)."""
+    return torch._C._cuda_getCurrentRawStream(_index(device)) or None
+
+
+class on_device:
+    """Makes `device` current for the duration of a launch, only if it is not current already."""
+
+    __slots__ = ("index", "prev")
+
+    def __init__(self, device):
+        self.index = _index(device)
+        self.prev = None
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.index:
+            self.prev = cur
+            torch.cuda.set_device(self.index)
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+        return False
 
 
 def dtype_code(dtype):

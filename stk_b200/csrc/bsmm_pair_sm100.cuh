@@ -266,6 +266,9 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint32_t* tmem_slot = const_cast<uint32_t*>(stage_flags) + kPStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* epilogue_go = abort_flag + 1;  // [2], one per epilogue group
+#ifdef STK_EXP_PROFILE
+  __shared__ long long ts_issue[kPStages], ts_commit[kPStages];
+#endif
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -313,12 +316,23 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       PROF_DECL;
+#ifdef STK_EXP_PROFILE
+      long long prof_d2 = 0, prof_n2 = 0;
+      if (is_a && rank == 0) for (int i = 0; i < kPStages; ++i) { ts_issue[i] = 0; ts_commit[i] = 0; }
+#endif
       // One pipeline stage of this operand: the tile at (mn_elem, k_elem).
       auto produce = [&](int mn_elem, int k_elem, uint32_t flags) {
         PROF_WAIT_BEGIN;
         ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
         PROF_WAIT_END;
         if (!ok) return;
+#ifdef STK_EXP_PROFILE
+        if (is_a && rank == 0) {
+          const long long now = clock64();
+          if (ts_commit[stage] != 0) { prof_d2 += now - ts_commit[stage]; ++prof_n2; }
+          ts_issue[stage] = now;
+        }
+#endif
         if (arms) {
           stage_flags[stage] = flags;
 #ifdef STK_EXP_SKIP_TMA  // experiment: MMA issue rate with the operand fetch taken out
@@ -376,6 +390,9 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
       PROF_STORE(is_a ? 0 : 6);
+#ifdef STK_EXP_PROFILE
+      if (is_a && rank == 0) { g_prof[blockIdx.x + 1][0] = prof_d2; g_prof[blockIdx.x + 1][1] = prof_n2; }
+#endif
       // The leader tells its MMA issuer that the stream is over.
       if (arms && ok) {
         if (mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
@@ -399,13 +416,16 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t acc_phase = 0;
       PROF_DECL;
 #ifdef STK_EXP_PROFILE
-      long long prof_acc_wait = 0;
+      long long prof_acc_wait = 0, prof_d1 = 0, prof_n1 = 0, prof_mma = 0;
 #endif
       while (true) {
         PROF_WAIT_BEGIN;
         const bool got = mbar_wait(full_bar(stage), phase, abort_flag);
         PROF_WAIT_END;
         if (!got) break;
+#ifdef STK_EXP_PROFILE
+        { const long long now = clock64(); prof_d1 += now - ts_issue[stage]; ++prof_n1; }
+#endif
         const uint32_t flags = stage_flags[stage];
         if (flags & kFlagEnd) break;
         if (flags & kFlagFirst) {
@@ -427,6 +447,9 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         umma_f16_pair(d_tmem, smem_desc_join(a_lo + 2 * a_kstep), smem_desc_join(b_lo + 2 * b_kstep), idesc, 1u);
         umma_f16_pair(d_tmem, smem_desc_join(a_lo + 3 * a_kstep), smem_desc_join(b_lo + 3 * b_kstep), idesc, 1u);
 #endif
+#ifdef STK_EXP_PROFILE
+        ts_commit[stage] = clock64();
+#endif
         umma_commit_pair(empty_bar(stage), 3);  // frees the stage in both CTAs
         if (flags & kFlagLast) {
           umma_commit_pair(tfull_bar(acc), 3);  // accumulator halves ready in both CTAs
@@ -441,6 +464,8 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       PROF_STORE(2);
 #ifdef STK_EXP_PROFILE
       g_prof[blockIdx.x][4] = prof_acc_wait;
+      g_prof[blockIdx.x + 1][2] = prof_d1;
+      g_prof[blockIdx.x + 1][3] = prof_n1;
 #endif
     }
     __syncwarp();
@@ -576,6 +601,9 @@ static int pair_device_info(PairDeviceInfo** out) {
       clusters = sms / 2;
     }
     d.max_pairs = clusters < sms / 2 ? clusters : sms / 2;
+#ifdef STK_EXP_MAX_PAIRS  // experiment: how the per-stage time depends on the number of active CTA pairs
+    if (d.max_pairs > STK_EXP_MAX_PAIRS) d.max_pairs = STK_EXP_MAX_PAIRS;
+#endif
   }
   *out = &d;
   return STK_OK;

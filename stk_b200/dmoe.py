@@ -42,7 +42,7 @@ def gather_rows(src, index, n_out=None):
     if src.is_cuda:
         src = src.contiguous()
         out = torch.empty((n_out, src.shape[1]), dtype=src.dtype, device=src.device)
-        with torch.cuda.device(src.device):
+        with _lib.on_device(src.device):
             rc = _lib.load().stk_b200_gather_rows(
                 _lib.ptr(src), _lib.ptr(out), _lib.ptr(index), n_out,
                 src.shape[1] * src.element_size(), _lib.stream_ptr(src.device))
@@ -60,7 +60,7 @@ def scatter_rows(src, index, n_out):
     if src.is_cuda:
         src = src.contiguous()
         out = torch.empty((n_out, src.shape[1]), dtype=src.dtype, device=src.device)
-        with torch.cuda.device(src.device):
+        with _lib.on_device(src.device):
             rc = _lib.load().stk_b200_scatter_rows(
                 _lib.ptr(src), _lib.ptr(out), _lib.ptr(index), index.numel(),
                 src.shape[1] * src.element_size(), _lib.stream_ptr(src.device))
@@ -83,7 +83,7 @@ def bin_index(counts, total_padded, block=BLOCK, compose=None):
         dev = counts.device
         index = torch.empty(total_padded, dtype=torch.int32, device=dev)
         bin_rows = torch.empty(local, dtype=torch.int32, device=dev)
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             rc = _lib.load().stk_b200_bin_index(
                 _lib.ptr(counts.contiguous()), world, local, block, _lib.ptr(compose),
                 _lib.ptr(index), total_padded, _lib.ptr(bin_rows), _lib.stream_ptr(dev))
@@ -128,7 +128,7 @@ def topology_from_bins(bin_rows, block_rows, ffn, dtype, device, block=BLOCK, da
     offsets_t = torch.empty(experts * cpb + 1, dtype=torch.int32, device=device)
     block_offsets_t = torch.empty(nnz, dtype=torch.int32, device=device)
     row_idx, col_idx, col_idx_t = (meta16[i, :nnz] for i in range(3))
-    with torch.cuda.device(device):
+    with _lib.on_device(device):
         rc = _lib.load().stk_b200_dmoe_topology(
             _lib.ptr(bin_rows), experts, cpb, block_rows, _lib.ptr(row_idx), _lib.ptr(col_idx),
             _lib.ptr(offsets), _lib.ptr(col_idx_t), _lib.ptr(offsets_t), _lib.ptr(block_offsets_t),
