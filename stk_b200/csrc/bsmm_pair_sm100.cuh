@@ -127,6 +127,19 @@ struct TileWalker {
     }
     return lo;
   }
+  // First position in [lo, hi) whose column is >= c_min.  Rows of dMoE topologies are runs of
+  // consecutive columns, so the position is first guessed by offset and checked with two loads;
+  // only a wrong guess pays for the binary search (a chain of dependent loads).
+  __device__ __forceinline__ int seek(int lo, int hi, int c_min) const {
+    if (lo >= hi) return lo;
+    const int first = static_cast<int>(__ldg(col + lo));
+    if (first >= c_min) return lo;
+    const int guess = lo + (c_min - first);
+    if (guess < hi && static_cast<int>(__ldg(col + guess)) >= c_min &&
+        static_cast<int>(__ldg(col + guess - 1)) < c_min)
+      return guess;
+    return lower_bound(lo, hi, c_min);
+  }
   __device__ __forceinline__ void init(const PairParams& p, int t, int seg) {
     col = p.col_idx;
     const int ra = 2 * t, rb = 2 * t + 1;
@@ -150,8 +163,8 @@ struct TileWalker {
     const int u_min = c_min >> 1, n_u = (c_max >> 1) - u_min + 1;
     const int u_lo = u_min + static_cast<int>((static_cast<long long>(seg) * n_u) / p.inner);
     u_end = u_min + static_cast<int>((static_cast<long long>(seg + 1) * n_u) / p.inner);
-    ia = lower_bound(a0, a1, 2 * u_lo);
-    ib = lower_bound(b0, b1, 2 * u_lo);
+    ia = seek(a0, a1, 2 * u_lo);
+    ib = seek(b0, b1, 2 * u_lo);
   }
   // Next tile: u = column pair; p[r][h] = block index of (row 2t+r, column 2u+h) or kNoBlock.
   __device__ __forceinline__ bool next(int& u, int (&p)[2][2]) {
