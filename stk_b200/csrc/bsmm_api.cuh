@@ -47,6 +47,8 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
   if ((rc = encode_dense(&tmB, rhs, dtype, N, K, ld_rhs, rhs_colmajor)) != STK_OK) return rc;
   const int k_steps = static_cast<int>((K + kBK - 1) / kBK);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CUtensorMap tmC;  // the output blocks as one [nnz*128, 128] matrix, stored 128 x 64 at a time
+  if ((rc = encode_map(&tmC, out, dtype, kBlk, nnz * kBlk, kBlk, kBlk)) != STK_OK) return rc;
 
   if (pair_mode) {
     PairDeviceInfo* d = nullptr;
@@ -72,8 +74,6 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
     p.offsets = offsets;
     p.out = out;
     p.ldc = kBlk;
-    CUtensorMap tmC;  // the blocks as one [nnz*128, 128] matrix
-    if ((rc = encode_map(&tmC, out, dtype, kBlk, nnz * kBlk, kBlk, kBlk)) != STK_OK) return rc;
     return launch_pair(tmA, tmB, tmC, p, s);
   }
 
@@ -90,7 +90,7 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
   p.col_idx = column_indices;
   p.out = out;
   p.ldc = kBlk;
-  return launch(tmA, tmB, p, s);
+  return launch(tmA, tmB, tmC, p, s);
 }
 
 extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int16_t* column_indices,
@@ -116,6 +116,9 @@ extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int1
   if ((rc = encode_sparse(&tmA, data, dtype, nnz, !trans_sparse)) != STK_OK) return rc;
   if ((rc = encode_dense(&tmB, rhs, dtype, N, K, ld_rhs, rhs_colmajor)) != STK_OK) return rc;
 
+  CUtensorMap tmC;
+  if ((rc = encode_map(&tmC, out, dtype, N, M, ld_out, kBlk)) != STK_OK) return rc;
+
   if (pair_mode) {
     PairParams p{};
     p.mode = kModeDSD;
@@ -133,8 +136,6 @@ extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int1
     p.blk_idx = block_offsets;
     p.out = out;
     p.ldc = ld_out;
-    CUtensorMap tmC;
-    if ((rc = encode_map(&tmC, out, dtype, N, M, ld_out, kBlk)) != STK_OK) return rc;
     return launch_pair(tmA, tmB, tmC, p, s);
   }
 
@@ -150,7 +151,7 @@ extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int1
   p.blk_idx = block_offsets;
   p.out = out;
   p.ldc = ld_out;
-  return launch(tmA, tmB, p, s);
+  return launch(tmA, tmB, tmC, p, s);
 }
 
 extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* offsets,
@@ -176,6 +177,9 @@ extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* of
   // B = data[blk] as stored (its columns are N) or transposed (its columns are K).
   if ((rc = encode_sparse(&tmB, data, dtype, nnz, trans_sparse)) != STK_OK) return rc;
 
+  CUtensorMap tmC;
+  if ((rc = encode_map(&tmC, out, dtype, N, M, ld_out, kBlk)) != STK_OK) return rc;
+
   if (pair_mode) {
     PairParams p{};
     p.mode = kModeDDS;
@@ -193,8 +197,6 @@ extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* of
     p.blk_idx = block_offsets;
     p.out = out;
     p.ldc = ld_out;
-    CUtensorMap tmC;
-    if ((rc = encode_map(&tmC, out, dtype, N, M, ld_out, kBlk)) != STK_OK) return rc;
     return launch_pair(tmA, tmB, tmC, p, s);
   }
 
@@ -210,5 +212,5 @@ extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* of
   p.blk_idx = block_offsets;
   p.out = out;
   p.ldc = ld_out;
-  return launch(tmA, tmB, p, s);
+  return launch(tmA, tmB, tmC, p, s);
 }

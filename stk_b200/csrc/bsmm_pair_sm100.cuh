@@ -43,7 +43,6 @@ constexpr int kPStages = 6;
 constexpr int kPAccCols = 256;   // one accumulator: 128 lanes x 256 fp32 columns per CTA
 constexpr int kPTmemCols = 512;  // two accumulators
 constexpr int kPNumBars = 2 * kPStages + 4;
-constexpr int kOutStageBytes = kBlk * 64 * 2;  // one 128-row x 64-column 16-bit output sub-tile
 constexpr int kPSmemBytes =
     kPStages * kStageBytes + 2 * kOutStageBytes + kPNumBars * 8 + kPStages * 4 + 32 + 1024;
 constexpr int kNoBlock = 0x7fffffff;
@@ -196,67 +195,6 @@ __device__ __forceinline__ void load_operand_pair(const CUtensorMap* tm, uint32_
     tma_load_2d_pair(smem_dst, tm, leader_bar, k_elem, mn_elem);
   } else {
     tma_load_3d_pair(smem_dst, tm, leader_bar, 0, k_elem, mn_elem >> 6);
-  }
-}
-
-// Barrier among the 128 threads of one epilogue group (hardware barriers 1 and 2; 0 is __syncthreads).
-__device__ __forceinline__ void epilogue_sync(int group) {
-  asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory");
-}
-
-// One epilogue group (four warps, 128 threads) moves its share of `ncols` accumulator columns (a
-// multiple of 64, starting at TMEM column `col0`) to the output: the two groups take alternate
-// 64-column sub-tiles.  TMEM -> registers -> optional activation -> 16-bit -> the group's 128x64
-// staging tile in shared memory (128-byte swizzle, conflict-free 16-byte stores) -> one TMA store.
-__device__ __forceinline__ void drain_to_output(uint32_t t_addr, int col0, int ncols, int fmt,
-                                                int epilogue, const CUtensorMap* tmC, int out_x,
-                                                int out_y, uint32_t staging, int row, int group,
-                                                bool issuer) {
-#ifdef STK_EXP_SKIP_EPILOGUE  // experiment: main loop alone, nothing drained or stored
-  return;
-#endif
-  for (int c = group * 64; c < ncols; c += 128) {
-    if (issuer) tma_store_wait_read<0>();  // the group's previous store is done reading the tile
-    epilogue_sync(group);
-    uint32_t r0[32], r1[32];
-    tmem_ld_32x32(t_addr + col0 + c, r0);
-    tmem_ld_32x32(t_addr + col0 + c + 32, r1);
-    tmem_ld_wait();
-    uint32_t packed[32];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float a0 = __uint_as_float(r0[2 * i]), a1 = __uint_as_float(r0[2 * i + 1]);
-      float b0 = __uint_as_float(r1[2 * i]), b1 = __uint_as_float(r1[2 * i + 1]);
-      if (epilogue == kEpilogueGelu) {
-        a0 = gelu_erf(a0);
-        a1 = gelu_erf(a1);
-        b0 = gelu_erf(b0);
-        b1 = gelu_erf(b1);
-      }
-      if (fmt == STK_BF16) {
-        const __nv_bfloat162 va = __floats2bfloat162_rn(a0, a1), vb = __floats2bfloat162_rn(b0, b1);
-        packed[i] = *reinterpret_cast<const uint32_t*>(&va);
-        packed[16 + i] = *reinterpret_cast<const uint32_t*>(&vb);
-      } else {
-        const __half2 va = __floats2half2_rn(a0, a1), vb = __floats2half2_rn(b0, b1);
-        packed[i] = *reinterpret_cast<const uint32_t*>(&va);
-        packed[16 + i] = *reinterpret_cast<const uint32_t*>(&vb);
-      }
-    }
-    const uint32_t row_addr = staging + row * 128;
-#pragma unroll
-    for (int ch = 0; ch < 8; ++ch) {
-      const uint32_t addr = row_addr + ((ch ^ (row & 7)) << 4);
-      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * ch]),
-                   "r"(packed[4 * ch + 1]), "r"(packed[4 * ch + 2]), "r"(packed[4 * ch + 3])
-                   : "memory");
-    }
-    fence_proxy_async_smem();
-    epilogue_sync(group);
-    if (issuer) {
-      tma_store_2d(tmC, staging, out_x + c, out_y);
-      tma_store_commit();
-    }
   }
 }
 
@@ -529,7 +467,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int pb = blk[rank][h];
             if (pb != kNoBlock)
               drain_to_output(t_addr, h * kBlk, kBlk, p.fmt, p.epilogue, &tmC, 0, pb * kBlk, staging,
-                              row, group, issuer);
+                              row, group, 2, issuer);
           }
           release();
         }
@@ -554,7 +492,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!ok) break;
         if (rows_valid)
           drain_to_output(t_addr, 0, ncols, p.fmt, p.epilogue, &tmC, tile_col, tile_row, staging, row,
-                          group, issuer);
+                          group, 2, issuer);
         release();
       }
     }

@@ -45,7 +45,8 @@ constexpr int kStageBytes = 2 * kOperandTileBytes;
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 256;                  // two 128-column fp32 accumulators
 constexpr int kNumBars = 2 * kStages + 4;
-constexpr int kSmemBytes = kStages * kStageBytes + kNumBars * 8 + 16 + 1024;  // + alignment slack
+constexpr int kSmemBytes =
+    kStages * kStageBytes + kBlk * 64 * 2 + kNumBars * 8 + 32 + 1024;  // stages, output staging tile, barriers, slack
 
 enum : int { kModeSDD = 0, kModeDSD = 1, kModeDDS = 2 };
 
@@ -133,22 +134,87 @@ __device__ __forceinline__ void load_operand(const CUtensorMap* tm, uint32_t sme
   }
 }
 
+constexpr int kOutStageBytes = kBlk * 64 * 2;  // one 128-row x 64-column 16-bit output sub-tile
+
+// Barrier among the 128 threads of one epilogue group (hardware barriers 1 and 2; 0 is __syncthreads).
+__device__ __forceinline__ void epilogue_sync(int group) {
+  asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory");
+}
+
+// One epilogue group (four warps, 128 threads) moves its share of `ncols` accumulator columns (a
+// multiple of 64, starting at TMEM column `col0`) to the output: with `groups` groups at work,
+// group g takes the 64-column sub-tiles g, g + groups, ...  TMEM -> registers -> optional activation -> 16-bit -> the group's 128x64
+// staging tile in shared memory (128-byte swizzle, conflict-free 16-byte stores) -> one TMA store.
+__device__ __forceinline__ void drain_to_output(uint32_t t_addr, int col0, int ncols, int fmt,
+                                                int epilogue, const CUtensorMap* tmC, int out_x,
+                                                int out_y, uint32_t staging, int row, int group,
+                                                int groups, bool issuer) {
+#ifdef STK_EXP_SKIP_EPILOGUE  // experiment: main loop alone, nothing drained or stored
+  return;
+#endif
+  for (int c = group * 64; c < ncols; c += groups * 64) {
+    if (issuer) tma_store_wait_read<0>();  // the group's previous store is done reading the tile
+    epilogue_sync(group);
+    uint32_t r0[32], r1[32];
+    tmem_ld_32x32(t_addr + col0 + c, r0);
+    tmem_ld_32x32(t_addr + col0 + c + 32, r1);
+    tmem_ld_wait();
+    uint32_t packed[32];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float a0 = __uint_as_float(r0[2 * i]), a1 = __uint_as_float(r0[2 * i + 1]);
+      float b0 = __uint_as_float(r1[2 * i]), b1 = __uint_as_float(r1[2 * i + 1]);
+      if (epilogue == kEpilogueGelu) {
+        a0 = gelu_erf(a0);
+        a1 = gelu_erf(a1);
+        b0 = gelu_erf(b0);
+        b1 = gelu_erf(b1);
+      }
+      if (fmt == STK_BF16) {
+        const __nv_bfloat162 va = __floats2bfloat162_rn(a0, a1), vb = __floats2bfloat162_rn(b0, b1);
+        packed[i] = *reinterpret_cast<const uint32_t*>(&va);
+        packed[16 + i] = *reinterpret_cast<const uint32_t*>(&vb);
+      } else {
+        const __half2 va = __floats2half2_rn(a0, a1), vb = __floats2half2_rn(b0, b1);
+        packed[i] = *reinterpret_cast<const uint32_t*>(&va);
+        packed[16 + i] = *reinterpret_cast<const uint32_t*>(&vb);
+      }
+    }
+    const uint32_t row_addr = staging + row * 128;
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) {
+      const uint32_t addr = row_addr + ((ch ^ (row & 7)) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * ch]),
+                   "r"(packed[4 * ch + 1]), "r"(packed[4 * ch + 2]), "r"(packed[4 * ch + 3])
+                   : "memory");
+    }
+    fence_proxy_async_smem();
+    epilogue_sync(group);
+    if (issuer) {
+      tma_store_2d(tmC, staging, out_x + c, out_y);
+      tma_store_commit();
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const BsmmParams p) {
+            const __grid_constant__ CUtensorMap tmC, const BsmmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
   const uint32_t smem_base = smem_u32(smem);
 
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
-  const uint32_t bars_base = smem_base + kStages * kStageBytes;
+  const uint32_t staging = smem_base + kStages * kStageBytes;  // 128 x 64 output tile, 1024-aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes + kOutStageBytes);
+  const uint32_t bars_base = staging + kOutStageBytes;
   auto full_bar = [&](int s) { return bars_base + 8u * s; };
   auto empty_bar = [&](int s) { return bars_base + 8u * (kStages + s); };
   auto tfull_bar = [&](int a) { return bars_base + 8u * (2 * kStages + a); };
   auto tempty_bar = [&](int a) { return bars_base + 8u * (2 * kStages + 2 + a); };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* epilogue_go = abort_flag + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -166,6 +232,7 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
@@ -290,6 +357,7 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // ------------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // a warp may only read TMEM lanes 32*(warp%4) .. +31
     const int row = quarter * 32 + lane;
+    const bool issuer = threadIdx.x == 64;  // first epilogue thread issues the TMA stores
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -311,45 +379,31 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         for (int i = 0; i < kBlk / 8; ++i) out_vec[i] = z;
         continue;
       }
-      // tcgen05.ld needs the whole warp: make the outcome of the wait warp-uniform.
-      ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(acc), acc_phase, abort_flag) ? 1 : 0) != 0;
+      // The four warps meet at a hardware barrier while draining, so they must all take the same
+      // decision: one thread reads the abort flag between two barriers, the others follow it.
+      mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+      epilogue_sync(0);
+      if (issuer) *epilogue_go = (*abort_flag == 0) ? 1 : 0;
+      epilogue_sync(0);
+      ok = *epilogue_go != 0;
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                               static_cast<uint32_t>(acc * kBlk);
-#pragma unroll
-      for (int chunk = 0; chunk < kBlk / 32; ++chunk) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_addr + chunk * 32, r);
-        tmem_ld_wait();
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float lo = __uint_as_float(r[2 * i]);
-          float hi = __uint_as_float(r[2 * i + 1]);
-          if (p.epilogue == kEpilogueGelu) {
-            lo = gelu_erf(lo);
-            hi = gelu_erf(hi);
-          }
-          if (p.fmt == STK_BF16) {
-            const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-            packed[i] = *reinterpret_cast<const uint32_t*>(&v);
-          } else {
-            const __half2 v = __floats2half2_rn(lo, hi);
-            packed[i] = *reinterpret_cast<const uint32_t*>(&v);
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          out_vec[chunk * 4 + i] =
-              make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-      }
+      // TMEM -> registers -> 16-bit -> swizzled staging tile -> TMA store, 64 columns at a time
+      if (p.mode == kModeSDD)
+        drain_to_output(t_addr, 0, kBlk, p.fmt, p.epilogue, &tmC, 0, tile * kBlk, staging, row, 0, 1,
+                        issuer);
+      else
+        drain_to_output(t_addr, 0, kBlk, p.fmt, p.epilogue, &tmC, t.tn * kBlk, t.tm * kBlk, staging,
+                        row, 0, 1, issuer);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (issuer) tma_store_wait_all<0>();  // every output tile has left shared memory and landed
   }
 
   // ------------------------------------------------------------------ teardown
@@ -467,13 +521,13 @@ static int device_info(DeviceInfo** out) {
   return STK_OK;
 }
 
-static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const BsmmParams& p,
-                  cudaStream_t stream) {
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
+                  const BsmmParams& p, cudaStream_t stream) {
   DeviceInfo* d = nullptr;
   const int rc = device_info(&d);
   if (rc != STK_OK) return rc;
   const int grid = p.num_tiles < d->sms ? p.num_tiles : d->sms;
-  bsmm_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, p);
+  bsmm_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmC, p);
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 
