@@ -68,8 +68,12 @@ int stk_b200_device_status(int* status_host);
  * CTA pairs (tcgen05 cta_group::2): two neighbouring block rows / columns of the sparse operand are
  * processed together over the merge of their block lists, which halves the operand traffic per
  * FLOP when the neighbours' lists mostly coincide (dMoE topologies) and wastes MMA work when they
- * do not.  Both modes give the same results; mode 1 needs every block row's column_indices (and
- * every block column's column_indices_t) in ascending order.
+ * do not.  2 (dsd / dds only; sdd treats it as 1) keeps the CTA pairs but gives every work item two
+ * dense tiles, 256x512 (dsd) or 512x256 (dds) of output, so that each sparse tile fetched is used
+ * twice: less operand traffic, no overlap of one item's epilogue with the next item's MMAs; it pays
+ * only for long block lists and is never chosen by this package's own heuristic.  All modes give
+ * the same results; modes 1 and 2 need every block row's column_indices (and every block column's
+ * column_indices_t) in ascending order.
  */
 
 /*

@@ -17,6 +17,7 @@ from stk_b200.backend import lib as _lib
 BLOCK = 128  # the matmul kernels are built for 128x128 blocks
 
 # Which matmul kernel runs: "0" = one 128x128 tile per CTA, "1" = 256x256 supertiles on CTA pairs,
+# "2" = CTA pairs with two dense tiles per item for DSD / DDS (opt-in, never picked by "auto"),
 # "auto" = per topology, from how well neighbouring block rows / columns pair up (see pair_hints).
 PAIR_MODE = os.environ.get("STK_B200_PAIR_MODE", "auto")
 # Fraction of the pair kernel's MMA work that must be useful for it to be chosen.  The pair kernel
@@ -72,8 +73,8 @@ def _use_pairs(kind, row_indices, column_indices, block_cols):
     rows, cols, tiles, is_sorted = pair_hints(row_indices, column_indices, block_cols)
     if kind == "tiles" and not is_sorted:
         return 0  # the SDD tile walk needs ascending columns inside every block row
-    if PAIR_MODE == "1":
-        return 1
+    if PAIR_MODE in ("1", "2"):
+        return 1 if kind == "tiles" else int(PAIR_MODE)
     return int({"rows": rows, "cols": cols, "tiles": tiles}[kind] >= PAIR_THRESHOLD[kind])
 
 

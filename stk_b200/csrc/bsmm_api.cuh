@@ -2,6 +2,7 @@
 // the choice between the single-CTA 128x128 kernel and the CTA-pair 256x256 kernel.
 #pragma once
 #include "bsmm_pair_sm100.cuh"
+#include "bsmm_wide_sm100.cuh"
 #include "bsmm_sm100.cuh"
 
 namespace stk {
@@ -126,7 +127,8 @@ extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int1
     p.b_mn = rhs_colmajor ? 0 : 1;
     p.fmt = dtype;
     p.num_lists = static_cast<int>(M / kBlk);
-    p.inner = static_cast<int>((N + 2 * kBlk - 1) / (2 * kBlk));
+    const int64_t span = pair_mode == 2 ? 4 * kBlk : 2 * kBlk;  // dense columns per work item
+    p.inner = static_cast<int>((N + span - 1) / span);
     p.num_items = ((p.num_lists + 1) / 2) * p.inner;
     p.zero_coord = static_cast<int>(nnz * kBlk);
     p.out_rows = static_cast<int>(M);
@@ -136,7 +138,7 @@ extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int1
     p.blk_idx = block_offsets;
     p.out = out;
     p.ldc = ld_out;
-    return launch_pair(tmA, tmB, tmC, p, s);
+    return pair_mode == 2 ? launch_wide(tmA, tmB, tmC, p, s) : launch_pair(tmA, tmB, tmC, p, s);
   }
 
   BsmmParams p{};
@@ -187,7 +189,8 @@ extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* of
     p.b_mn = trans_sparse ? 0 : 1;
     p.fmt = dtype;
     p.num_lists = static_cast<int>(N / kBlk);
-    p.inner = static_cast<int>((M + 2 * kBlk - 1) / (2 * kBlk));
+    const int64_t span = pair_mode == 2 ? 4 * kBlk : 2 * kBlk;  // dense rows per work item
+    p.inner = static_cast<int>((M + span - 1) / span);
     p.num_items = ((p.num_lists + 1) / 2) * p.inner;
     p.zero_coord = static_cast<int>(nnz * kBlk);
     p.out_rows = static_cast<int>(M);
@@ -197,7 +200,7 @@ extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* of
     p.blk_idx = block_offsets;
     p.out = out;
     p.ldc = ld_out;
-    return launch_pair(tmA, tmB, tmC, p, s);
+    return pair_mode == 2 ? launch_wide(tmA, tmB, tmC, p, s) : launch_pair(tmA, tmB, tmC, p, s);
   }
 
   BsmmParams p{};

@@ -467,7 +467,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int pb = blk[rank][h];
             if (pb != kNoBlock)
               drain_to_output(t_addr, h * kBlk, kBlk, p.fmt, p.epilogue, &tmC, 0, pb * kBlk, staging,
-                              row, group, 2, issuer);
+                              row, group, group, 2, issuer);
           }
           release();
         }
@@ -492,7 +492,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!ok) break;
         if (rows_valid)
           drain_to_output(t_addr, 0, ncols, p.fmt, p.epilogue, &tmC, tile_col, tile_row, staging, row,
-                          group, 2, issuer);
+                          group, group, 2, issuer);
         release();
       }
     }

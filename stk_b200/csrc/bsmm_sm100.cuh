@@ -142,17 +142,17 @@ __device__ __forceinline__ void epilogue_sync(int group) {
 }
 
 // One epilogue group (four warps, 128 threads) moves its share of `ncols` accumulator columns (a
-// multiple of 64, starting at TMEM column `col0`) to the output: with `groups` groups at work,
-// group g takes the 64-column sub-tiles g, g + groups, ...  TMEM -> registers -> optional activation -> 16-bit -> the group's 128x64
+// multiple of 64, starting at TMEM column `col0`) to the output: the 64-column sub-tiles `first`,
+// `first + step`, ...  `group` names the group's hardware barrier.  TMEM -> registers -> optional activation -> 16-bit -> the group's 128x64
 // staging tile in shared memory (128-byte swizzle, conflict-free 16-byte stores) -> one TMA store.
 __device__ __forceinline__ void drain_to_output(uint32_t t_addr, int col0, int ncols, int fmt,
                                                 int epilogue, const CUtensorMap* tmC, int out_x,
                                                 int out_y, uint32_t staging, int row, int group,
-                                                int groups, bool issuer) {
+                                                int first, int step, bool issuer) {
 #ifdef STK_EXP_SKIP_EPILOGUE  // experiment: main loop alone, nothing drained or stored
   return;
 #endif
-  for (int c = group * 64; c < ncols; c += groups * 64) {
+  for (int c = first * 64; c < ncols; c += step * 64) {
     if (issuer) tma_store_wait_read<0>();  // the group's previous store is done reading the tile
     epilogue_sync(group);
     uint32_t r0[32], r1[32];
@@ -392,11 +392,11 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                               static_cast<uint32_t>(acc * kBlk);
       // TMEM -> registers -> 16-bit -> swizzled staging tile -> TMA store, 64 columns at a time
       if (p.mode == kModeSDD)
-        drain_to_output(t_addr, 0, kBlk, p.fmt, p.epilogue, &tmC, 0, tile * kBlk, staging, row, 0, 1,
-                        issuer);
+        drain_to_output(t_addr, 0, kBlk, p.fmt, p.epilogue, &tmC, 0, tile * kBlk, staging, row, 0, 0,
+                        1, issuer);
       else
         drain_to_output(t_addr, 0, kBlk, p.fmt, p.epilogue, &tmC, t.tn * kBlk, t.tm * kBlk, staging,
-                        row, 0, 1, issuer);
+                        row, 0, 0, 1, issuer);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
