@@ -303,6 +303,9 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       };
       // Is this thread's operand the sparse one (DSD: A, DDS: B)?
       const bool sparse_side = (p.mode == kModeDSD) == is_a;
+#ifdef STK_EXP_ONE_PRODUCER  // experiment (DSD only): one thread per CTA issues both operands' loads
+      if (p.mode == kModeDSD && !is_a) goto producer_done;
+#endif
       for (int item = pair_id; item < p.num_items && ok; item += num_pairs) {
         const int outer = item / p.inner, inner = item - outer * p.inner;
         if (p.mode == kModeSDD) {
@@ -334,12 +337,33 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               mn_elem = inner * 2 * kBlk + rank * kBlk;
               k_elem = kpos * kBlk;
             }
+#ifdef STK_EXP_ONE_PRODUCER
+            if (p.mode == kModeDSD) {
+              const int b_mn_elem = inner * 2 * kBlk + rank * kBlk, b_k_elem = kpos * kBlk;
+              for (int ks = 0; ks < 2 && ok; ++ks) {
+                ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
+                if (!ok) break;
+                if (arms) {
+                  stage_flags[stage] = ks == 0 ? first : last;
+                  mbar_arrive_expect_tx(full_bar(stage), 2 * kStageBytes);
+                }
+                load_operand_pair(&tmA, smem_base + stage * kStageBytes, leader_full0 + 8u * stage, p.a_mn, mn_elem, k_elem + ks * kBK);
+                load_operand_pair(&tmB, smem_base + kOperandTileBytes + stage * kStageBytes, leader_full0 + 8u * stage, p.b_mn, b_mn_elem, b_k_elem + ks * kBK);
+                if (++stage == kPStages) { stage = 0; phase ^= 1u; }
+              }
+              first = 0u;
+              continue;
+            }
+#endif
             produce(mn_elem, k_elem, first);
             if (ok) produce(mn_elem, k_elem + kBK, last);
             first = 0u;
           }
         }
       }
+#ifdef STK_EXP_ONE_PRODUCER
+    producer_done:
+#endif
       PROF_STORE(is_a ? 0 : 6);
 #ifdef STK_EXP_PROFILE
       if (is_a && rank == 0) { g_prof[blockIdx.x + 1][0] = prof_d2; g_prof[blockIdx.x + 1][1] = prof_n2; }
@@ -369,15 +393,24 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #ifdef STK_EXP_PROFILE
       long long prof_acc_wait = 0, prof_d1 = 0, prof_n1 = 0, prof_mma = 0;
 #endif
+      // The tensor pipe queues only an MMA or two ahead of the one it executes, so whatever this
+      // thread does between the last MMA of a stage and the first of the next (a barrier poll costs
+      // over a hundred cycles even when the phase is complete) shows up as idle tensor cycles.  The
+      // next stage's barrier is therefore probed, and its flags read, between the MMAs of the
+      // current stage; the blocking wait only runs when that probe found the operands missing.
+      bool ready = false;
+      uint32_t flags = 0;
       while (true) {
-        PROF_WAIT_BEGIN;
-        const bool got = mbar_wait(full_bar(stage), phase, abort_flag);
-        PROF_WAIT_END;
-        if (!got) break;
+        if (!ready) {
+          PROF_WAIT_BEGIN;
+          const bool got = mbar_wait(full_bar(stage), phase, abort_flag);
+          PROF_WAIT_END;
+          if (!got) break;
+          flags = stage_flags[stage];
+        }
 #ifdef STK_EXP_PROFILE
         { const long long now = clock64(); prof_d1 += now - ts_issue[stage]; ++prof_n1; }
 #endif
-        const uint32_t flags = stage_flags[stage];
         if (flags & kFlagEnd) break;
         if (flags & kFlagFirst) {
 #ifdef STK_EXP_PROFILE
@@ -392,9 +425,15 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kPAccCols);
         const uint32_t a_lo = a_lo0 + stage * (kStageBytes >> 4);
         const uint32_t b_lo = b_lo0 + stage * (kStageBytes >> 4);
+        const int next_stage = stage + 1 == kPStages ? 0 : stage + 1;
+        const uint32_t next_phase = stage + 1 == kPStages ? phase ^ 1u : phase;
 #ifndef STK_EXP_SKIP_MMA  // experiment: operand fetch rate with the MMAs taken out
         umma_f16_pair(d_tmem, smem_desc_join(a_lo), smem_desc_join(b_lo), idesc, (flags & kFlagFirst) ? 0u : 1u);
         umma_f16_pair(d_tmem, smem_desc_join(a_lo + a_kstep), smem_desc_join(b_lo + b_kstep), idesc, 1u);
+#endif
+        ready = mbar_test_wait(full_bar(next_stage), next_phase);
+        const uint32_t next_flags = ready ? stage_flags[next_stage] : 0u;
+#ifndef STK_EXP_SKIP_MMA
         umma_f16_pair(d_tmem, smem_desc_join(a_lo + 2 * a_kstep), smem_desc_join(b_lo + 2 * b_kstep), idesc, 1u);
         umma_f16_pair(d_tmem, smem_desc_join(a_lo + 3 * a_kstep), smem_desc_join(b_lo + 3 * b_kstep), idesc, 1u);
 #endif
@@ -407,10 +446,9 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           acc ^= 1;
           if (acc == 0) acc_phase ^= 1u;
         }
-        if (++stage == kPStages) {
-          stage = 0;
-          phase ^= 1u;
-        }
+        stage = next_stage;
+        phase = next_phase;
+        flags = next_flags;
       }
       PROF_STORE(2);
 #ifdef STK_EXP_PROFILE
@@ -490,9 +528,11 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t t_addr;
         acquire(t_addr);
         if (!ok) break;
+#ifndef STK_EXP_SKIP_EPILOGUE  // experiment: the main loop without the drain of the accumulators
         if (rows_valid)
           drain_to_output(t_addr, 0, ncols, p.fmt, p.epilogue, &tmC, tile_col, tile_row, staging, row,
                           group, group, 2, issuer);
+#endif
         release();
       }
     }
