@@ -432,7 +432,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         umma_f16_pair(d_tmem, smem_desc_join(a_lo + a_kstep), smem_desc_join(b_lo + b_kstep), idesc, 1u);
 #endif
         ready = mbar_test_wait(full_bar(next_stage), next_phase);
-        const uint32_t next_flags = ready ? stage_flags[next_stage] : 0u;
+        const uint32_t next_flags = stage_flags[next_stage];  // not waited for here; only used if `ready`
 #ifndef STK_EXP_SKIP_MMA
         umma_f16_pair(d_tmem, smem_desc_join(a_lo + 2 * a_kstep), smem_desc_join(b_lo + 2 * b_kstep), idesc, 1u);
         umma_f16_pair(d_tmem, smem_desc_join(a_lo + 3 * a_kstep), smem_desc_join(b_lo + 3 * b_kstep), idesc, 1u);

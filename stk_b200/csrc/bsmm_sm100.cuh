@@ -319,32 +319,44 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      // The tensor pipe does not run ahead of this thread: every cycle it stalls between two MMAs
+      // (a barrier poll whose result it needs, a metadata load) is an idle tensor cycle.  So the
+      // next stage's barrier is probed (not waited for) between the MMAs of the current stage, and
+      // the next tile's metadata is fetched while the current tile's MMAs are issued.
+      bool ready = false;
+      TileInfo t_next = {};
+      if (static_cast<int>(blockIdx.x) < p.num_tiles) t_next = tile_info(p, blockIdx.x);
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-        const TileInfo t = tile_info(p, tile);
+        const TileInfo t = t_next;
+        if (tile + static_cast<int>(gridDim.x) < p.num_tiles) t_next = tile_info(p, tile + gridDim.x);
         if (t.nk == 0) continue;  // the epilogue writes zeros; no accumulator is used
         ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag);
         if (!ok) break;
-        tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kBlk);
         uint32_t accumulate = 0;
         for (int ks = 0; ks < t.nk; ++ks) {
-          ok = mbar_wait(full_bar(stage), phase, abort_flag);
-          if (!ok) break;
+          if (!ready) {
+            ok = mbar_wait(full_bar(stage), phase, abort_flag);
+            if (!ok) break;
+          }
           tc_fence_after();
           const uint32_t a_lo = a_lo0 + stage * (kStageBytes >> 4);
           const uint32_t b_lo = b_lo0 + stage * (kStageBytes >> 4);
+          const int next_stage = stage + 1 == kStages ? 0 : stage + 1;
+          const uint32_t next_phase = stage + 1 == kStages ? phase ^ 1u : phase;
 #ifndef STK_EXP_SKIP_MMA  // experiment: operand fetch rate with the MMAs taken out
           umma_f16(d_tmem, smem_desc_join(a_lo), smem_desc_join(b_lo), idesc, accumulate);
           umma_f16(d_tmem, smem_desc_join(a_lo + a_kstep), smem_desc_join(b_lo + b_kstep), idesc, 1u);
+#endif
+          ready = mbar_test_wait(full_bar(next_stage), next_phase);
+#ifndef STK_EXP_SKIP_MMA
           umma_f16(d_tmem, smem_desc_join(a_lo + 2 * a_kstep), smem_desc_join(b_lo + 2 * b_kstep), idesc, 1u);
           umma_f16(d_tmem, smem_desc_join(a_lo + 3 * a_kstep), smem_desc_join(b_lo + 3 * b_kstep), idesc, 1u);
 #endif
           accumulate = 1u;
           umma_commit(empty_bar(stage));  // the stage is free once these MMAs have read it
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
+          stage = next_stage;
+          phase = next_phase;
         }
         if (!ok) break;
         umma_commit(tfull_bar(acc));  // accumulator complete

@@ -143,9 +143,14 @@ bsmm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t d_kstep = (d_mn ? kUmmaK * 128u : kUmmaK * 2u) >> 4;
       int stage = 0;
       uint32_t phase = 0, tile_phase = 0;
+      // As in the pair kernel: the next stage's barrier is probed between the MMAs of this one.
+      bool ready = false;
+      uint32_t flags = 0;
       while (true) {
-        if (!mbar_wait(full_bar(stage), phase, abort_flag)) break;
-        const uint32_t flags = stage_flags[stage];
+        if (!ready) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) break;
+          flags = stage_flags[stage];
+        }
         if (flags & kFlagEnd) break;
         if (flags & kFlagFirst) {
           if (!mbar_wait(tempty_bar(0), tile_phase ^ 1u, abort_flag)) break;
@@ -154,7 +159,10 @@ bsmm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_fence_after();
         const uint32_t s_lo = s_lo0 + stage * (kWStageBytes >> 4);
         const uint32_t d_lo = d_lo0 + stage * (kWStageBytes >> 4);
+        const int next_stage = stage + 1 == kWStages ? 0 : stage + 1;
+        const uint32_t next_phase = stage + 1 == kWStages ? phase ^ 1u : phase;
         uint32_t accumulate = (flags & kFlagFirst) ? 0u : 1u;
+        uint32_t next_flags = 0;
 #pragma unroll
         for (int k = 0; k < kBK / kUmmaK; ++k) {
           const uint64_t s_desc = smem_desc_join(s_lo + k * s_kstep);
@@ -168,16 +176,19 @@ bsmm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             umma_f16_pair(tmem_base + kPAccCols, d1, s_desc, idesc, accumulate);
           }
           accumulate = 1u;
+          if (k == 1) {
+            ready = mbar_test_wait(full_bar(next_stage), next_phase);
+            next_flags = stage_flags[next_stage];  // only used if `ready`
+          }
         }
         umma_commit_pair(empty_bar(stage), 3);
         if (flags & kFlagLast) {
           umma_commit_pair(tfull_bar, 3);
           tile_phase ^= 1u;
         }
-        if (++stage == kWStages) {
-          stage = 0;
-          phase ^= 1u;
-        }
+        stage = next_stage;
+        phase = next_phase;
+        flags = next_flags;
       }
     }
     __syncwarp();
