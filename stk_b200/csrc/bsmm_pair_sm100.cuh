@@ -43,8 +43,9 @@ constexpr int kPStages = 6;
 constexpr int kPAccCols = 256;   // one accumulator: 128 lanes x 256 fp32 columns per CTA
 constexpr int kPTmemCols = 512;  // two accumulators
 constexpr int kPNumBars = 2 * kPStages + 4;
+constexpr int kMaxSplits = 64;  // row pairs with disjoint block lists that are run as two single rows
 constexpr int kPSmemBytes =
-    kPStages * kStageBytes + 2 * kOutStageBytes + kPNumBars * 8 + kPStages * 4 + 32 + 1024;
+    kPStages * kStageBytes + 2 * kOutStageBytes + kPNumBars * 8 + kPStages * 4 + 32 + (kMaxSplits + 1) * 4 + 1024;
 constexpr int kNoBlock = 0x7fffffff;
 
 enum : uint32_t { kFlagFirst = 1u, kFlagLast = 2u, kFlagEnd = 4u };
@@ -84,18 +85,20 @@ struct MergeWalker {
   const int16_t* col;
   const int32_t* blk;
   int ia, a1, ib, b1;
-  __device__ __forceinline__ void init(const PairParams& p, int t) {
+  // part: 0 = both lists of pair t, 1 = the first list only, 2 = the second list only.
+  __device__ __forceinline__ void init(const PairParams& p, int t, int part = 0) {
     col = p.col_idx;
     blk = p.blk_idx;
     const int la = 2 * t, lb = 2 * t + 1;
     ia = p.offsets[la];
     a1 = p.offsets[la + 1];
-    if (lb < p.num_lists) {
+    if (lb < p.num_lists && part != 1) {
       ib = a1;  // consecutive lists are adjacent in the metadata
       b1 = p.offsets[lb + 1];
     } else {
       ib = b1 = 0;
     }
+    if (part == 2) ia = a1 = 0;
   }
   __device__ __forceinline__ bool empty() const { return ia >= a1 && ib >= b1; }
   // Next K position; blk_a / blk_b = index into data of the block each list has there, or kNoBlock.
@@ -198,6 +201,34 @@ __device__ __forceinline__ void load_operand_pair(const CUtensorMap* tm, uint32_
   }
 }
 
+// DSD work items.  A pair of block rows whose block lists cannot overlap (the last column of one
+// lies before the first column of the other: two experts of a dMoE topology meeting at an odd
+// block row) would run for the sum of both lists with half of every MMA wasted; it is run as two
+// single-row items instead, which keeps all items of such a topology equally long, so that dealing
+// them round-robin balances the CTA pairs.  `splits` lists those pairs in ascending order.
+struct PairItem {
+  int t, part, inner;  // pair of lists, which of its lists (see MergeWalker::init), dense supertile
+};
+__device__ __forceinline__ PairItem decode_item(int item, int inner_count, const int* splits,
+                                                int num_splits) {
+  PairItem it;
+  const int g = item / inner_count;
+  it.inner = item - g * inner_count;
+  int k = 0;
+  while (k < num_splits && splits[k] + k < g) ++k;  // split pairs whose first half comes before g
+  if (k < num_splits && splits[k] + k == g) {
+    it.t = splits[k];
+    it.part = 1;
+  } else if (k > 0 && splits[k - 1] + k == g) {
+    it.t = splits[k - 1];
+    it.part = 2;
+  } else {
+    it.t = g - k;
+    it.part = 0;
+  }
+  return it;
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1)
 bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const PairParams p) {
@@ -217,6 +248,8 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint32_t* tmem_slot = const_cast<uint32_t*>(stage_flags) + kPStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* epilogue_go = abort_flag + 1;  // [2], one per epilogue group
+  int* split_count = const_cast<int*>(epilogue_go) + 2;
+  int* splits = split_count + 1;  // [kMaxSplits]
 #ifdef STK_EXP_PROFILE
   __shared__ long long ts_issue[kPStages], ts_commit[kPStages];
 #endif
@@ -237,6 +270,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(tempty_bar(a), 2 * kPEpilogueWarps);  // leader's copy: the epilogue warps of both CTAs
     }
     *abort_flag = 0;
+    *split_count = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
@@ -246,11 +280,41 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tmem_alloc_pair(smem_u32(tmem_slot), kPTmemCols);
     tmem_relinquish_pair();
   }
+  __syncthreads();
+  // Every CTA finds the row pairs to split by itself (same metadata, same answer in both CTAs).
+  const int list_pairs = (p.num_lists + 1) / 2;
+  if (p.mode == kModeDSD) {
+    for (int t = threadIdx.x; t < list_pairs; t += kPThreads) {
+      if (2 * t + 1 >= p.num_lists) continue;
+      const int a0 = p.offsets[2 * t], a1 = p.offsets[2 * t + 1], b1 = p.offsets[2 * t + 2];
+      if (a0 >= a1 || a1 >= b1) continue;
+      const int a_first = __ldg(p.col_idx + a0), a_last = __ldg(p.col_idx + a1 - 1);
+      const int b_first = __ldg(p.col_idx + a1), b_last = __ldg(p.col_idx + b1 - 1);
+      if (a_last < b_first || b_last < a_first) {
+        const int pos = atomicAdd(split_count, 1);
+        if (pos < kMaxSplits) splits[pos] = t;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int n = *split_count;
+    if (n > kMaxSplits) n = 0;  // not a dMoE-like topology: keep every pair whole
+    for (int i = 1; i < n; ++i) {  // the appends came in any order
+      const int v = splits[i];
+      int j = i - 1;
+      for (; j >= 0 && splits[j] > v; --j) splits[j + 1] = splits[j];
+      splits[j + 1] = v;
+    }
+    *split_count = n;
+  }
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();  // the peer's barriers exist before anything is sent to them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const int num_splits = *split_count;
+  const int num_items = p.mode == kModeDSD ? (list_pairs + num_splits) * p.inner : p.num_items;
 
   if (warp == 0 || warp == kPProducerBWarp) {
     // ------------------------------------------------------------------ TMA producers (both CTAs)
@@ -306,7 +370,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #ifdef STK_EXP_ONE_PRODUCER  // experiment (DSD only): one thread per CTA issues both operands' loads
       if (p.mode == kModeDSD && !is_a) goto producer_done;
 #endif
-      for (int item = pair_id; item < p.num_items && ok; item += num_pairs) {
+      for (int item = pair_id; item < num_items && ok; item += num_pairs) {
         const int outer = item / p.inner, inner = item - outer * p.inner;
         if (p.mode == kModeSDD) {
           TileWalker w;
@@ -319,8 +383,9 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                       (ks == 0 ? kFlagFirst : 0u) | (ks == p.k_steps - 1 ? kFlagLast : 0u));
           }
         } else {
+          const PairItem it = decode_item(item, p.inner, splits, num_splits);
           MergeWalker w;
-          w.init(p, outer);
+          w.init(p, it.t, it.part);
           uint32_t first = kFlagFirst;
           while (ok && !w.empty()) {
             int kpos, blk_a, blk_b;
@@ -334,12 +399,12 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               mn_elem = mn_major ? 0 : row0;
               k_elem = mn_major ? row0 : 0;
             } else {
-              mn_elem = inner * 2 * kBlk + rank * kBlk;
+              mn_elem = it.inner * 2 * kBlk + rank * kBlk;
               k_elem = kpos * kBlk;
             }
 #ifdef STK_EXP_ONE_PRODUCER
             if (p.mode == kModeDSD) {
-              const int b_mn_elem = inner * 2 * kBlk + rank * kBlk, b_k_elem = kpos * kBlk;
+              const int b_mn_elem = it.inner * 2 * kBlk + rank * kBlk, b_k_elem = kpos * kBlk;
               for (int ks = 0; ks < 2 && ok; ++ks) {
                 ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
                 if (!ok) break;
@@ -490,7 +555,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (acc == 0) acc_phase ^= 1u;
     };
     uint16_t* out = static_cast<uint16_t*>(p.out);
-    for (int item = pair_id; item < p.num_items && ok; item += num_pairs) {
+    for (int item = pair_id; item < num_items && ok; item += num_pairs) {
       const int outer = item / p.inner, inner = item - outer * p.inner;
       if (p.mode == kModeSDD) {
         TileWalker w;
@@ -510,12 +575,14 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           release();
         }
       } else {
+        const PairItem it = decode_item(item, p.inner, splits, num_splits);
         MergeWalker w;
-        w.init(p, outer);
-        // This CTA's 128 output rows and the 256 output columns of the supertile.
-        const int tile_row = (p.mode == kModeDSD ? 2 * outer + rank : 2 * inner + rank) * kBlk;
-        const int tile_col = (p.mode == kModeDSD ? inner : outer) * 2 * kBlk;
-        const bool rows_valid = tile_row < p.out_rows;
+        w.init(p, it.t, it.part);
+        // This CTA's 128 output rows and the 256 output columns of the supertile.  In a single-row
+        // item the other CTA's rows belong to another item.
+        const int tile_row = (p.mode == kModeDSD ? 2 * it.t + rank : 2 * it.inner + rank) * kBlk;
+        const int tile_col = (p.mode == kModeDSD ? it.inner : it.t) * 2 * kBlk;
+        const bool rows_valid = tile_row < p.out_rows && (it.part == 0 || it.part == rank + 1);
         const int ncols = min(2 * kBlk, p.out_cols - tile_col);
         uint16_t* dst = out + (static_cast<long long>(tile_row) + row) * p.ldc + tile_col;
         if (w.empty()) {
