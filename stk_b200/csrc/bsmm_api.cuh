@@ -58,7 +58,10 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
     const int row_pairs = (block_rows + 1) / 2;
     // Split every row pair's column range into segments until there is enough parallel slack.
     int segments = (kItemsPerPairTarget * d->max_pairs + row_pairs - 1) / row_pairs;
-    const int max_segments = (block_cols + 1) / 2;
+    // No finer than one 2x2 tile per segment on average (a row pair that shares its columns has
+    // about half as many tiles as a row has blocks): finer segments come out unequal.
+    int max_segments = static_cast<int>(nnz / block_rows / 2);
+    if (max_segments > (block_cols + 1) / 2) max_segments = (block_cols + 1) / 2;
     if (segments > max_segments) segments = max_segments;
     if (segments < 1) segments = 1;
     PairParams p{};

@@ -142,13 +142,16 @@ struct TileWalker {
       return guess;
     return lower_bound(lo, hi, c_min);
   }
-  __device__ __forceinline__ void init(const PairParams& p, int t, int seg) {
+  // part: 0 = both rows of pair t, 1 = the first row only, 2 = the second row only.
+  __device__ __forceinline__ void init(const PairParams& p, int t, int seg, int part = 0) {
     col = p.col_idx;
     const int ra = 2 * t, rb = 2 * t + 1;
     int a0 = p.offsets[ra];
     a1 = p.offsets[ra + 1];
     int b0 = a1;
     b1 = rb < p.num_lists ? p.offsets[rb + 1] : a1;
+    if (part == 1) b0 = b1;
+    if (part == 2) a0 = a1;
     ia = a1;
     ib = b1;
     u_end = 0;
@@ -201,7 +204,7 @@ __device__ __forceinline__ void load_operand_pair(const CUtensorMap* tm, uint32_
   }
 }
 
-// DSD work items.  A pair of block rows whose block lists cannot overlap (the last column of one
+// DSD / SDD work items.  A pair of block rows whose block lists cannot overlap (the last column of one
 // lies before the first column of the other: two experts of a dMoE topology meeting at an odd
 // block row) would run for the sum of both lists with half of every MMA wasted; it is run as two
 // single-row items instead, which keeps all items of such a topology equally long, so that dealing
@@ -283,7 +286,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   // Every CTA finds the row pairs to split by itself (same metadata, same answer in both CTAs).
   const int list_pairs = (p.num_lists + 1) / 2;
-  if (p.mode == kModeDSD) {
+  if (p.mode != kModeDDS) {
     for (int t = threadIdx.x; t < list_pairs; t += kPThreads) {
       if (2 * t + 1 >= p.num_lists) continue;
       const int a0 = p.offsets[2 * t], a1 = p.offsets[2 * t + 1], b1 = p.offsets[2 * t + 2];
@@ -314,7 +317,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int num_splits = *split_count;
-  const int num_items = p.mode == kModeDSD ? (list_pairs + num_splits) * p.inner : p.num_items;
+  const int num_items = p.mode != kModeDDS ? (list_pairs + num_splits) * p.inner : p.num_items;
 
   if (warp == 0 || warp == kPProducerBWarp) {
     // ------------------------------------------------------------------ TMA producers (both CTAs)
@@ -371,13 +374,13 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (p.mode == kModeDSD && !is_a) goto producer_done;
 #endif
       for (int item = pair_id; item < num_items && ok; item += num_pairs) {
-        const int outer = item / p.inner, inner = item - outer * p.inner;
         if (p.mode == kModeSDD) {
+          const PairItem it = decode_item(item, p.inner, splits, num_splits);
           TileWalker w;
-          w.init(p, outer, inner);
+          w.init(p, it.t, it.inner, it.part);
           int u, blk[2][2];
           while (ok && w.next(u, blk)) {
-            const int mn_elem = (2 * (is_a ? outer : u) + rank) * kBlk;
+            const int mn_elem = (2 * (is_a ? it.t : u) + rank) * kBlk;
             for (int ks = 0; ks < p.k_steps && ok; ++ks)
               produce(mn_elem, ks * kBK,
                       (ks == 0 ? kFlagFirst : 0u) | (ks == p.k_steps - 1 ? kFlagLast : 0u));
@@ -556,15 +559,16 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     };
     uint16_t* out = static_cast<uint16_t*>(p.out);
     for (int item = pair_id; item < num_items && ok; item += num_pairs) {
-      const int outer = item / p.inner, inner = item - outer * p.inner;
       if (p.mode == kModeSDD) {
+        const PairItem it = decode_item(item, p.inner, splits, num_splits);
         TileWalker w;
-        w.init(p, outer, inner);
+        w.init(p, it.t, it.inner, it.part);
         int u, blk[2][2];
         while (ok && w.next(u, blk)) {
           uint32_t t_addr;
           acquire(t_addr);
           if (!ok) break;
+#ifndef STK_EXP_SKIP_EPILOGUE
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int pb = blk[rank][h];
@@ -572,6 +576,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               drain_to_output(t_addr, h * kBlk, kBlk, p.fmt, p.epilogue, &tmC, 0, pb * kBlk, staging,
                               row, group, group, 2, issuer);
           }
+#endif
           release();
         }
       } else {
