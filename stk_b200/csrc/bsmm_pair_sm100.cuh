@@ -43,9 +43,9 @@ constexpr int kPStages = 6;
 constexpr int kPAccCols = 256;   // one accumulator: 128 lanes x 256 fp32 columns per CTA
 constexpr int kPTmemCols = 512;  // two accumulators
 constexpr int kPNumBars = 2 * kPStages + 4;
-constexpr int kMaxSplits = 64;  // row pairs with disjoint block lists that are run as two single rows
+constexpr int kMaxBreaks = 64;  // places where the rows are cut into runs (more: no cuts at all)
 constexpr int kPSmemBytes =
-    kPStages * kStageBytes + 2 * kOutStageBytes + kPNumBars * 8 + kPStages * 4 + 32 + (kMaxSplits + 1) * 4 + 1024;
+    kPStages * kStageBytes + 2 * kOutStageBytes + kPNumBars * 8 + kPStages * 4 + 32 + (3 * kMaxBreaks + 8) * 4 + 1024;
 constexpr int kNoBlock = 0x7fffffff;
 
 enum : uint32_t { kFlagFirst = 1u, kFlagLast = 2u, kFlagEnd = 4u };
@@ -85,11 +85,11 @@ struct MergeWalker {
   const int16_t* col;
   const int32_t* blk;
   int ia, a1, ib, b1;
-  // part: 0 = both lists of pair t, 1 = the first list only, 2 = the second list only.
-  __device__ __forceinline__ void init(const PairParams& p, int t, int part = 0) {
+  // Lists la and la + 1 (part 0), or list la alone (part 1).
+  __device__ __forceinline__ void init(const PairParams& p, int la, int part = 0) {
     col = p.col_idx;
     blk = p.blk_idx;
-    const int la = 2 * t, lb = 2 * t + 1;
+    const int lb = la + 1;
     ia = p.offsets[la];
     a1 = p.offsets[la + 1];
     if (lb < p.num_lists && part != 1) {
@@ -98,7 +98,6 @@ struct MergeWalker {
     } else {
       ib = b1 = 0;
     }
-    if (part == 2) ia = a1 = 0;
   }
   __device__ __forceinline__ bool empty() const { return ia >= a1 && ib >= b1; }
   // Next K position; blk_a / blk_b = index into data of the block each list has there, or kNoBlock.
@@ -142,16 +141,15 @@ struct TileWalker {
       return guess;
     return lower_bound(lo, hi, c_min);
   }
-  // part: 0 = both rows of pair t, 1 = the first row only, 2 = the second row only.
-  __device__ __forceinline__ void init(const PairParams& p, int t, int seg, int part = 0) {
+  // Rows ra and ra + 1 (part 0), or row ra alone (part 1).
+  __device__ __forceinline__ void init(const PairParams& p, int ra, int seg, int part = 0) {
     col = p.col_idx;
-    const int ra = 2 * t, rb = 2 * t + 1;
+    const int rb = ra + 1;
     int a0 = p.offsets[ra];
     a1 = p.offsets[ra + 1];
     int b0 = a1;
     b1 = rb < p.num_lists ? p.offsets[rb + 1] : a1;
     if (part == 1) b0 = b1;
-    if (part == 2) a0 = a1;
     ia = a1;
     ib = b1;
     u_end = 0;
@@ -171,7 +169,7 @@ struct TileWalker {
     ia = seek(a0, a1, 2 * u_lo);
     ib = seek(b0, b1, 2 * u_lo);
   }
-  // Next tile: u = column pair; p[r][h] = block index of (row 2t+r, column 2u+h) or kNoBlock.
+  // Next tile: u = column pair; p[r][h] = block index of (row ra+r, column 2u+h) or kNoBlock.
   __device__ __forceinline__ bool next(int& u, int (&p)[2][2]) {
     const int ca = ia < a1 ? static_cast<int>(__ldg(col + ia)) : kNoBlock;
     const int cb = ib < b1 ? static_cast<int>(__ldg(col + ib)) : kNoBlock;
@@ -204,31 +202,26 @@ __device__ __forceinline__ void load_operand_pair(const CUtensorMap* tm, uint32_
   }
 }
 
-// DSD / SDD work items.  A pair of block rows whose block lists cannot overlap (the last column of one
-// lies before the first column of the other: two experts of a dMoE topology meeting at an odd
-// block row) would run for the sum of both lists with half of every MMA wasted; it is run as two
-// single-row items instead, which keeps all items of such a topology equally long, so that dealing
-// them round-robin balances the CTA pairs.  `splits` lists those pairs in ascending order.
+// Work items.  The block rows (DSD, SDD) or block columns (DDS) are taken two at a time, each CTA
+// of the pair computing one of them.  Blind pairs (0,1), (2,3), ... go wrong where two experts of a
+// dMoE topology meet at an odd row: the two rows' block lists cannot overlap (the last column of one
+// lies before the first column of the other), so the pair runs for the sum of both lists with half
+// of every MMA wasted, and every pair behind it may be misaligned as well.  The kernel therefore
+// cuts the rows into runs at those places and pairs inside each run; a run of odd length ends in a
+// single row.  Items of such a topology are then equally long, and dealing them round-robin
+// balances the CTA pairs.  run_start[k] = first row of run k, run_cum[k] = groups before run k.
 struct PairItem {
-  int t, part, inner;  // pair of lists, which of its lists (see MergeWalker::init), dense supertile
+  int r, part, inner;  // first row of the group, 0 = rows r and r + 1 / 1 = row r alone, dense supertile
 };
-__device__ __forceinline__ PairItem decode_item(int item, int inner_count, const int* splits,
-                                                int num_splits) {
+__device__ __forceinline__ PairItem decode_item(int item, int inner_count, const int* run_start,
+                                                const int* run_cum, int num_runs) {
   PairItem it;
   const int g = item / inner_count;
   it.inner = item - g * inner_count;
   int k = 0;
-  while (k < num_splits && splits[k] + k < g) ++k;  // split pairs whose first half comes before g
-  if (k < num_splits && splits[k] + k == g) {
-    it.t = splits[k];
-    it.part = 1;
-  } else if (k > 0 && splits[k - 1] + k == g) {
-    it.t = splits[k - 1];
-    it.part = 2;
-  } else {
-    it.t = g - k;
-    it.part = 0;
-  }
+  while (k + 1 < num_runs && run_cum[k + 1] <= g) ++k;
+  it.r = run_start[k] + 2 * (g - run_cum[k]);
+  it.part = it.r + 1 >= run_start[k + 1] ? 1 : 0;
   return it;
 }
 
@@ -251,8 +244,10 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint32_t* tmem_slot = const_cast<uint32_t*>(stage_flags) + kPStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* epilogue_go = abort_flag + 1;  // [2], one per epilogue group
-  int* split_count = const_cast<int*>(epilogue_go) + 2;
-  int* splits = split_count + 1;  // [kMaxSplits]
+  int* break_count = const_cast<int*>(epilogue_go) + 2;
+  int* breaks = break_count + 1;           // [kMaxBreaks]
+  int* run_start = breaks + kMaxBreaks;    // [kMaxBreaks + 2]
+  int* run_cum = run_start + kMaxBreaks + 2;  // [kMaxBreaks + 2]
 #ifdef STK_EXP_PROFILE
   __shared__ long long ts_issue[kPStages], ts_commit[kPStages];
 #endif
@@ -273,7 +268,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(tempty_bar(a), 2 * kPEpilogueWarps);  // leader's copy: the epilogue warps of both CTAs
     }
     *abort_flag = 0;
-    *split_count = 0;
+    *break_count = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
@@ -284,40 +279,46 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tmem_relinquish_pair();
   }
   __syncthreads();
-  // Every CTA finds the row pairs to split by itself (same metadata, same answer in both CTAs).
-  const int list_pairs = (p.num_lists + 1) / 2;
+  // Every CTA finds the cuts by itself (same metadata, same answer in both CTAs).
   if (p.mode != kModeDDS) {
-    for (int t = threadIdx.x; t < list_pairs; t += kPThreads) {
-      if (2 * t + 1 >= p.num_lists) continue;
-      const int a0 = p.offsets[2 * t], a1 = p.offsets[2 * t + 1], b1 = p.offsets[2 * t + 2];
+    for (int r = threadIdx.x; r + 1 < p.num_lists; r += kPThreads) {
+      const int a0 = p.offsets[r], a1 = p.offsets[r + 1], b1 = p.offsets[r + 2];
       if (a0 >= a1 || a1 >= b1) continue;
       const int a_first = __ldg(p.col_idx + a0), a_last = __ldg(p.col_idx + a1 - 1);
       const int b_first = __ldg(p.col_idx + a1), b_last = __ldg(p.col_idx + b1 - 1);
       if (a_last < b_first || b_last < a_first) {
-        const int pos = atomicAdd(split_count, 1);
-        if (pos < kMaxSplits) splits[pos] = t;
+        const int pos = atomicAdd(break_count, 1);
+        if (pos < kMaxBreaks) breaks[pos] = r;
       }
     }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    int n = *split_count;
-    if (n > kMaxSplits) n = 0;  // not a dMoE-like topology: keep every pair whole
+    int n = *break_count;
+    if (n > kMaxBreaks) n = 0;  // not a dMoE-like topology: one run, blind pairs
     for (int i = 1; i < n; ++i) {  // the appends came in any order
-      const int v = splits[i];
+      const int v = breaks[i];
       int j = i - 1;
-      for (; j >= 0 && splits[j] > v; --j) splits[j + 1] = splits[j];
-      splits[j + 1] = v;
+      for (; j >= 0 && breaks[j] > v; --j) breaks[j + 1] = breaks[j];
+      breaks[j + 1] = v;
     }
-    *split_count = n;
+    run_start[0] = 0;
+    run_cum[0] = 0;
+    for (int k = 0; k < n; ++k) {
+      run_start[k + 1] = breaks[k] + 1;
+      run_cum[k + 1] = run_cum[k] + (run_start[k + 1] - run_start[k] + 1) / 2;
+    }
+    run_start[n + 1] = p.num_lists;
+    run_cum[n + 1] = run_cum[n] + (p.num_lists - run_start[n] + 1) / 2;
+    *break_count = n;
   }
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();  // the peer's barriers exist before anything is sent to them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int num_splits = *split_count;
-  const int num_items = p.mode != kModeDDS ? (list_pairs + num_splits) * p.inner : p.num_items;
+  const int num_runs = *break_count + 1;
+  const int num_items = run_cum[num_runs] * p.inner;
 
   if (warp == 0 || warp == kPProducerBWarp) {
     // ------------------------------------------------------------------ TMA producers (both CTAs)
@@ -375,20 +376,20 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #endif
       for (int item = pair_id; item < num_items && ok; item += num_pairs) {
         if (p.mode == kModeSDD) {
-          const PairItem it = decode_item(item, p.inner, splits, num_splits);
+          const PairItem it = decode_item(item, p.inner, run_start, run_cum, num_runs);
           TileWalker w;
-          w.init(p, it.t, it.inner, it.part);
+          w.init(p, it.r, it.inner, it.part);
           int u, blk[2][2];
           while (ok && w.next(u, blk)) {
-            const int mn_elem = (2 * (is_a ? it.t : u) + rank) * kBlk;
+            const int mn_elem = ((is_a ? it.r : 2 * u) + rank) * kBlk;
             for (int ks = 0; ks < p.k_steps && ok; ++ks)
               produce(mn_elem, ks * kBK,
                       (ks == 0 ? kFlagFirst : 0u) | (ks == p.k_steps - 1 ? kFlagLast : 0u));
           }
         } else {
-          const PairItem it = decode_item(item, p.inner, splits, num_splits);
+          const PairItem it = decode_item(item, p.inner, run_start, run_cum, num_runs);
           MergeWalker w;
-          w.init(p, it.t, it.part);
+          w.init(p, it.r, it.part);
           uint32_t first = kFlagFirst;
           while (ok && !w.empty()) {
             int kpos, blk_a, blk_b;
@@ -560,9 +561,9 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint16_t* out = static_cast<uint16_t*>(p.out);
     for (int item = pair_id; item < num_items && ok; item += num_pairs) {
       if (p.mode == kModeSDD) {
-        const PairItem it = decode_item(item, p.inner, splits, num_splits);
+        const PairItem it = decode_item(item, p.inner, run_start, run_cum, num_runs);
         TileWalker w;
-        w.init(p, it.t, it.inner, it.part);
+        w.init(p, it.r, it.inner, it.part);
         int u, blk[2][2];
         while (ok && w.next(u, blk)) {
           uint32_t t_addr;
@@ -580,14 +581,15 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           release();
         }
       } else {
-        const PairItem it = decode_item(item, p.inner, splits, num_splits);
+        const PairItem it = decode_item(item, p.inner, run_start, run_cum, num_runs);
         MergeWalker w;
-        w.init(p, it.t, it.part);
+        w.init(p, it.r, it.part);
         // This CTA's 128 output rows and the 256 output columns of the supertile.  In a single-row
         // item the other CTA's rows belong to another item.
-        const int tile_row = (p.mode == kModeDSD ? 2 * it.t + rank : 2 * it.inner + rank) * kBlk;
-        const int tile_col = (p.mode == kModeDSD ? it.inner : it.t) * 2 * kBlk;
-        const bool rows_valid = tile_row < p.out_rows && (it.part == 0 || it.part == rank + 1);
+        const int tile_row = (p.mode == kModeDSD ? it.r + rank : 2 * it.inner + rank) * kBlk;
+        const int tile_col = (p.mode == kModeDSD ? 2 * it.inner : it.r) * kBlk;
+        const bool rows_valid =
+            tile_row < p.out_rows && (p.mode != kModeDSD || it.part == 0 || rank == 0);
         const int ncols = min(2 * kBlk, p.out_cols - tile_col);
         uint16_t* dst = out + (static_cast<long long>(tile_row) + row) * p.ldc + tile_col;
         if (w.empty()) {

@@ -87,7 +87,7 @@ bsmm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int item = pair_id; item < p.num_items && ok; item += num_pairs) {
         const int outer = item / p.inner, inner = item - outer * p.inner;
         MergeWalker w;
-        w.init(p, outer);
+        w.init(p, 2 * outer);
         uint32_t first = kFlagFirst;
         while (ok && !w.empty()) {
           int kpos, blk_a, blk_b;
@@ -209,7 +209,7 @@ bsmm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int item = pair_id; item < p.num_items && ok; item += num_pairs) {
       const int outer = item / p.inner, inner = item - outer * p.inner;
       MergeWalker w;
-      w.init(p, outer);
+      w.init(p, 2 * outer);
       const int tile_row = dsd ? (2 * outer + rank) * kBlk : ((2 * inner + group) * 2 + rank) * kBlk;
       const int tile_col = dsd ? (2 * inner + group) * 2 * kBlk : outer * 2 * kBlk;
       const bool rows_valid = tile_row < p.out_rows;
