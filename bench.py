@@ -18,7 +18,6 @@ import json
 import os
 import statistics
 import sys
-import threading
 import time
 
 import torch
@@ -43,58 +42,71 @@ def measured_peaks():
     return 1590.0, 6650.0, "fallback"
 
 
+_SAMPLER_CODE = r"""
+import json, signal, sys, time
+import pynvml
+index, period = int(sys.argv[1]), float(sys.argv[2])
+pynvml.nvmlInit()
+handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+smax = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
+stop = []
+signal.signal(signal.SIGTERM, lambda *a: stop.append(1))
+print("ready", flush=True)
+sm, mask = [], 0
+while not stop:
+    sm.append(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+    mask |= pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+    time.sleep(period)
+print(json.dumps({"sm": sm, "mask": mask, "smax": smax}), flush=True)
+"""
+
+
 class ClockSampler:
-    """Polls SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+    """Polls SM clock and throttle reasons through NVML (read-only) while the timed region runs.
+
+    The polling runs in a child process: a thread in this process competes for the interpreter lock
+    with the launch loop, which slowed the host-bound multi-GPU step by a third."""
 
     REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
                ("sw_power_cap", 0x4))
 
     def __init__(self, index, period_s=0.002):
         self.index, self.period = index, period_s
-        self.sm, self.mask, self.smax = [], 0, None
-        self.stop_flag = threading.Event()
-        self.thread = None
-        self.error = None
+        self.proc, self.error = None, None
 
     def start(self):
+        import subprocess
+        # NVML enumerates physical GPUs; honour CUDA_VISIBLE_DEVICES if it lists indices
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        phys = self.index
+        if visible:
+            ids = [v.strip() for v in visible.split(",") if v.strip()]
+            if self.index < len(ids) and ids[self.index].isdigit():
+                phys = int(ids[self.index])
         try:
-            import pynvml
-            pynvml.nvmlInit()
-            self.nvml = pynvml
-            # NVML enumerates physical GPUs; honour CUDA_VISIBLE_DEVICES if it lists indices
-            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
-            phys = self.index
-            if visible:
-                ids = [v.strip() for v in visible.split(",") if v.strip()]
-                if self.index < len(ids) and ids[self.index].isdigit():
-                    phys = int(ids[self.index])
-            self.handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
-            self.smax = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.proc = subprocess.Popen([sys.executable, "-c", _SAMPLER_CODE, str(phys), str(self.period)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+            if self.proc.stdout.readline().strip() != "ready":
+                raise RuntimeError(self.proc.stderr.read()[-300:])
         except Exception as exc:  # NVML missing: report, do not fail the benchmark
             self.error = repr(exc)
-            return
-        self.thread = threading.Thread(target=self._poll, daemon=True)
-        self.thread.start()
-
-    def _poll(self):
-        nv = self.nvml
-        while not self.stop_flag.is_set():
-            try:
-                self.sm.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
-                self.mask |= nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
-            except Exception as exc:
-                self.error = repr(exc)
-                return
-            time.sleep(self.period)
+            if self.proc is not None:
+                self.proc.kill()
+            self.proc = None
 
     def stop(self):
-        if self.thread is None:
+        if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable: " + str(self.error)]}
-        self.stop_flag.set()
-        self.thread.join(timeout=2)
-        reasons = [name for name, bit in self.REASONS if self.mask & bit]
-        return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.smax,
-                "reasons": reasons, "samples": len(self.sm)}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+            data = json.loads(out.strip().splitlines()[-1])
+        except Exception as exc:
+            self.proc.kill()
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock sampler failed: " + repr(exc)]}
+        reasons = [name for name, bit in self.REASONS if data["mask"] & bit]
+        return {"sm_mhz": statistics.median(data["sm"]) if data["sm"] else None, "sm_max_mhz": data["smax"],
+                "reasons": reasons, "samples": len(data["sm"])}
 
 
 def expert_ids_for(rank, tokens, experts, device):
@@ -145,7 +157,20 @@ def run_ours(args):
     total_experts = EXPERTS * world
     ids = expert_ids_for(rank, T_TOKENS, total_experts, dev).to(torch.int32)
     ids_host = ids.cpu().pin_memory()
-    exchange = dmoe.ExpertParallelExchange(total_experts) if distributed else None
+    exchange, exchange_kind = None, "none"
+    if distributed:
+        # Rows travel with this library's own kernels over peer memory; NCCL all-to-all only if torch's
+        # symmetric memory cannot be set up here (or STK_B200_EXCHANGE=nccl asks for it).
+        exchange_kind = os.environ.get("STK_B200_EXCHANGE", "peer")
+        if exchange_kind == "peer":
+            try:
+                exchange = dmoe.PeerExchange(total_experts, T_TOKENS, HIDDEN, HIDDEN, DTYPE, dev)
+            except Exception as exc:  # noqa: BLE001 - any failure of the symmetric allocation
+                if rank == 0:
+                    print(f"peer exchange unavailable ({type(exc).__name__}: {exc}); using NCCL", file=sys.stderr)
+                exchange_kind = "nccl"
+        if exchange is None:
+            exchange = dmoe.ExpertParallelExchange(total_experts)
 
     def full_step(x_dev, ids_dev):
         """Routing bookkeeping + (exchange) + sdd -> GeLU -> dsd + (exchange back)."""
@@ -289,7 +314,9 @@ def run_ours(args):
                    "tokens_per_gpu": T_TOKENS, "hidden": HIDDEN, "ffn": FFN,
                    "experts_per_gpu": EXPERTS, "routing": "top-1 multinomial(uniform)",
                    "blocking": 128, "nnz_blocks_rank0": nnz, "padded_rows_rank0": rows,
-                   "parallelism": "1 GPU" if world == 1 else f"expert-parallel x{world}, all-to-all",
+                   "parallelism": "1 GPU" if world == 1 else (
+                       f"expert-parallel x{world}, token rows pushed / pulled over NVLink peer memory by the library's kernels"
+                       if exchange_kind == "peer" else f"expert-parallel x{world}, NCCL all-to-all"),
                    "l2": "no flush: operands + hidden + output of one step are ~335 MB > 126 MB L2"},
         "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s",
                 "h2d_bytes_per_step": x_host.numel() * 2 + ids_host.numel() * 4,

@@ -228,6 +228,39 @@ int stk_b200_dmoe_topology(const int32_t* bin_rows, int experts, int cols_per_ex
                            int32_t* offsets, int16_t* column_indices_t, int32_t* offsets_t,
                            int32_t* block_offsets_t, void* stream);
 
+/*
+ * Expert-parallel token exchange over peer memory (NVLink).  No counterpart in the reference, which
+ * is single-GPU; these move the rows that stk.ops.sdd / dsd work on between the ranks of an
+ * expert-parallel dMoE layer without a host-side collective: every rank pushes its token rows into
+ * the padded expert bins of the owning rank and pulls the results back.  `peer_bufs[r]` is rank r's
+ * buffer as mapped in THIS process (symmetric memory), `cap_rows` its capacity in rows; the caller
+ * puts a barrier between ranks after the count exchange, after dispatch and before combine.
+ * A row that would fall outside a buffer is skipped and STK_ERR_WORKSPACE is recorded in the status
+ * word (stk_b200_device_status).
+ *   ep_share_counts: row `rank` of every rank's count matrix (peer_counts[r], int32
+ *               [world*experts]) <- offsets[e+1] - offsets[e], this rank's tokens per expert.
+ *   ep_plan:    counts_all[s*experts+e] = tokens of rank s for global expert e (int32, the same
+ *               matrix on every rank).  Writes dest_base[e] (row in the owner's buffer where this
+ *               rank's rows of expert e start), bin_rows[le] (blocks of this rank's local bins),
+ *               totals[0] = padded rows of this rank, totals[1] = rows it receives.
+ *   ep_zero_padding: zero rows that close each local bin in `recv`.
+ *   ep_dispatch: x[order[q]] -> owner's buffer row dest_base[e] + (q - offsets[e]) for every sorted
+ *               position q in expert segment e (order / offsets as produced by a stable sort of
+ *               the tokens by expert); dest[t] = owner << 40 | row for token t.
+ *   ep_combine: out[t] = row dest[t] of the owner's result buffer (zeros for a skipped token).
+ */
+int stk_b200_ep_share_counts(const int32_t* offsets, const uint64_t* peer_counts, int world, int experts,
+                             int rank, void* stream);
+int stk_b200_ep_plan(const int32_t* counts_all, int world, int experts, int rank, int block,
+                     int64_t* dest_base, int32_t* bin_rows, int64_t* totals, void* stream);
+int stk_b200_ep_zero_padding(const int32_t* counts_all, int world, int experts, int rank, int block,
+                             void* recv, int64_t row_bytes, int64_t cap_rows, void* stream);
+int stk_b200_ep_dispatch(const void* x, const int32_t* order, const int32_t* offsets,
+                         const int64_t* dest_base, const uint64_t* peer_bufs, int64_t tokens, int world,
+                         int experts, int64_t row_bytes, int64_t cap_rows, int64_t* dest, void* stream);
+int stk_b200_ep_combine(const uint64_t* peer_bufs, const int64_t* dest, void* out, int64_t tokens,
+                        int64_t row_bytes, int64_t cap_rows, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

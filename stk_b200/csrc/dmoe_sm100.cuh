@@ -142,6 +142,145 @@ dmoe_topology_kernel(const int32_t* __restrict__ bin_rows, int experts, int cpb,
   block_offsets_t[q] = static_cast<int32_t>(p);
 }
 
+// ------------------------------------------------------------------ expert-parallel exchange
+// Token exchange over peer memory (NVLink): every rank PUSHES its token rows straight into the
+// padded expert bins of the rank that owns the expert, and later PULLS its results from there.  The
+// peers' buffers are ordinary device pointers (symmetric memory); the kernels only ever issue plain
+// loads and stores to them.  A barrier between ranks (not part of these kernels) separates the
+// steps.  Every address sent to a peer is checked against the buffer's capacity first; a row that
+// would not fit is skipped and reported through the status word.
+//
+// Layout on rank d: bin of local expert le = rows [bin_start[le], bin_start[le] + padded[le]), the
+// rows from rank 0 first, then rank 1, ..., each rank's rows in its own (stable) token order, then
+// zero rows up to a multiple of `block`.
+
+// Row `rank` of every rank's count matrix <- this rank's tokens per expert (offsets[e+1] - offsets[e]).
+__global__ void __launch_bounds__(128)
+ep_share_counts_kernel(const int32_t* __restrict__ offsets, const uint64_t* __restrict__ peer_counts,
+                       int world, int experts, int rank) {
+  for (int i = threadIdx.x; i < experts * world; i += blockDim.x) {
+    const int peer = i / experts, e = i - peer * experts;
+    reinterpret_cast<int32_t*>(peer_counts[peer])[rank * experts + e] = offsets[e + 1] - offsets[e];
+  }
+}
+
+// counts_all[s * E + e] = tokens of rank s routed to global expert e.  One CTA, E*world small.
+//   dest_base[e]  = row in the owner's buffer where THIS rank's rows for expert e start
+//   bin_rows[le]  = padded rows / block of this rank's local expert le;  totals[0] = sum of padded rows,
+//   totals[1] = rows this rank receives (unpadded)
+__global__ void __launch_bounds__(128)
+ep_plan_kernel(const int32_t* __restrict__ counts_all, int world, int experts, int local, int rank,
+               int block, int64_t* __restrict__ dest_base, int32_t* __restrict__ bin_rows,
+               int64_t* __restrict__ totals) {
+  // column sums first (one round of loads), so that the serial parts below run out of shared memory
+  extern __shared__ int32_t ep_sm[];
+  int32_t* col_sum = ep_sm;            // [experts] tokens of all ranks per expert
+  int32_t* before_me = ep_sm + experts;  // [experts] tokens of the ranks before this one
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    int32_t n = 0, b = 0;
+    for (int s = 0; s < world; ++s) {
+      const int32_t c = counts_all[s * experts + e];
+      n += c;
+      if (s < rank) b += c;
+    }
+    col_sum[e] = n;
+    before_me[e] = b;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    const int owner = e / local, le = e - owner * local;
+    int64_t start = 0;
+    for (int k = 0; k < le; ++k)
+      start += (static_cast<int64_t>(col_sum[owner * local + k]) + block - 1) / block * block;
+    dest_base[e] = start + before_me[e];
+  }
+  if (threadIdx.x == 0) {
+    int64_t padded_total = 0, received = 0;
+    for (int le = 0; le < local; ++le) {
+      const int64_t n = col_sum[rank * local + le];
+      const int64_t padded = (n + block - 1) / block * block;
+      bin_rows[le] = static_cast<int32_t>(padded / block);
+      padded_total += padded;
+      received += n;
+    }
+    totals[0] = padded_total;
+    totals[1] = received;
+  }
+}
+
+// Zero rows that close each local bin (nobody writes them).  One warp per padding row.
+__global__ void __launch_bounds__(256)
+ep_zero_padding_kernel(const int32_t* __restrict__ counts_all, int world, int experts, int local,
+                       int rank, int block, uint4* __restrict__ recv, int vec_per_row,
+                       int64_t cap_rows) {
+  const int le = blockIdx.y;
+  int64_t start = 0, n = 0;
+  for (int k = 0; k <= le; ++k) {
+    n = 0;
+    for (int s = 0; s < world; ++s) n += counts_all[s * experts + rank * local + k];
+    if (k < le) start += (n + block - 1) / block * block;
+  }
+  const int64_t pad = (n + block - 1) / block * block - n;
+  const int64_t w = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= pad) return;
+  const int64_t row = start + n + w;
+  if (row >= cap_rows) return;
+  const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+  for (int v = lane; v < vec_per_row; v += 32) recv[row * vec_per_row + v] = z;
+}
+
+// Sorted position q (tokens ordered by expert: token order[q], expert segments offsets[e..e+1]) goes
+// to row dest_base[e] + (q - offsets[e]) of the buffer of rank e / local.  One warp per row.
+// dest[t] = owner rank << 40 | row, kept for the way back.
+__global__ void __launch_bounds__(256)
+ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ order,
+                   const int32_t* __restrict__ offsets, const int64_t* __restrict__ dest_base,
+                   const uint64_t* __restrict__ peer_bufs, int64_t tokens, int experts, int local,
+                   int vec_per_row, int64_t cap_rows, int64_t* __restrict__ dest) {
+  const int64_t q = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (q >= tokens) return;
+  int lo = 0, hi = experts;  // last e with offsets[e] <= q
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (offsets[mid] <= q) lo = mid; else hi = mid;
+  }
+  const int e = lo, owner = e / local;
+  const int64_t row = dest_base[e] + (q - offsets[e]);
+  const int32_t t = order[q];
+  if (row < 0 || row >= cap_rows) {
+    if (lane == 0) {
+      dest[t] = -1;
+      report_status(STK_ERR_WORKSPACE);
+    }
+    return;
+  }
+  if (lane == 0) dest[t] = (static_cast<int64_t>(owner) << 40) | row;
+  const uint4* in = x + static_cast<int64_t>(t) * vec_per_row;
+  uint4* out = reinterpret_cast<uint4*>(peer_bufs[owner]) + row * vec_per_row;
+  for (int v = lane; v < vec_per_row; v += 32) out[v] = __ldg(in + v);
+}
+
+// out[t] = row dest[t] of the result buffer of the rank that computed it.  One warp per token.
+__global__ void __launch_bounds__(256)
+ep_combine_kernel(const uint64_t* __restrict__ peer_bufs, const int64_t* __restrict__ dest,
+                  uint4* __restrict__ out, int64_t tokens, int vec_per_row, int64_t cap_rows) {
+  const int64_t t = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  const int64_t d = dest[t];
+  uint4* o = out + t * vec_per_row;
+  const int64_t row = d & ((1ll << 40) - 1);
+  if (d < 0 || row >= cap_rows) {
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    for (int v = lane; v < vec_per_row; v += 32) o[v] = z;
+    return;
+  }
+  const uint4* in = reinterpret_cast<const uint4*>(peer_bufs[d >> 40]) + row * vec_per_row;
+  for (int v = lane; v < vec_per_row; v += 32) o[v] = in[v];
+}
+
 }  // namespace stk
 
 using namespace stk;
@@ -215,5 +354,67 @@ extern "C" int stk_b200_dmoe_topology(const int32_t* bin_rows, int experts, int 
                          static_cast<cudaStream_t>(stream)>>>(
       bin_rows, experts, cols_per_expert, nnz, static_cast<int>(block_rows), row_indices,
       column_indices, offsets, column_indices_t, offsets_t, block_offsets_t);
+  return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
+}
+
+extern "C" int stk_b200_ep_share_counts(const int32_t* offsets, const uint64_t* peer_counts, int world,
+                                        int experts, int rank, void* stream) {
+  if (!offsets || !peer_counts) return STK_ERR_NULL_POINTER;
+  if (world < 1 || experts < 1 || rank < 0 || rank >= world) return STK_ERR_BAD_DIMS;
+  stk::ep_share_counts_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(offsets, peer_counts,
+                                                                                 world, experts, rank);
+  return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
+}
+
+extern "C" int stk_b200_ep_plan(const int32_t* counts_all, int world, int experts, int rank, int block,
+                                int64_t* dest_base, int32_t* bin_rows, int64_t* totals, void* stream) {
+  if (!counts_all || !dest_base || !bin_rows || !totals) return STK_ERR_NULL_POINTER;
+  if (world < 1 || experts < 1 || experts % world != 0 || rank < 0 || rank >= world || block < 1)
+    return STK_ERR_BAD_DIMS;
+  if (experts > 4096) return STK_ERR_TOO_LARGE;
+  stk::ep_plan_kernel<<<1, 128, 2 * experts * sizeof(int32_t), static_cast<cudaStream_t>(stream)>>>(
+      counts_all, world, experts, experts / world, rank, block, dest_base, bin_rows, totals);
+  return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
+}
+
+extern "C" int stk_b200_ep_zero_padding(const int32_t* counts_all, int world, int experts, int rank,
+                                        int block, void* recv, int64_t row_bytes, int64_t cap_rows,
+                                        void* stream) {
+  if (!counts_all || !recv) return STK_ERR_NULL_POINTER;
+  if (world < 1 || experts < 1 || experts % world != 0 || rank < 0 || rank >= world || block < 1 ||
+      row_bytes <= 0 || row_bytes % 16 != 0 || cap_rows < 0)
+    return STK_ERR_BAD_DIMS;
+  const int local = experts / world;
+  const dim3 grid(static_cast<unsigned>((block * 32 + 255) / 256), static_cast<unsigned>(local));
+  stk::ep_zero_padding_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      counts_all, world, experts, local, rank, block, static_cast<uint4*>(recv),
+      static_cast<int>(row_bytes / 16), cap_rows);
+  return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
+}
+
+extern "C" int stk_b200_ep_dispatch(const void* x, const int32_t* order, const int32_t* offsets,
+                                    const int64_t* dest_base, const uint64_t* peer_bufs, int64_t tokens,
+                                    int world, int experts, int64_t row_bytes, int64_t cap_rows,
+                                    int64_t* dest, void* stream) {
+  if (tokens == 0) return STK_OK;
+  if (!x || !order || !offsets || !dest_base || !peer_bufs || !dest) return STK_ERR_NULL_POINTER;
+  if (tokens < 0 || world < 1 || experts < 1 || experts % world != 0 || row_bytes <= 0 ||
+      row_bytes % 16 != 0 || cap_rows < 0)
+    return STK_ERR_BAD_DIMS;
+  const int64_t blocks = (tokens * 32 + 255) / 256;
+  stk::ep_dispatch_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), order, offsets, dest_base, peer_bufs, tokens, experts,
+      experts / world, static_cast<int>(row_bytes / 16), cap_rows, dest);
+  return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
+}
+
+extern "C" int stk_b200_ep_combine(const uint64_t* peer_bufs, const int64_t* dest, void* out,
+                                   int64_t tokens, int64_t row_bytes, int64_t cap_rows, void* stream) {
+  if (tokens == 0) return STK_OK;
+  if (!peer_bufs || !dest || !out) return STK_ERR_NULL_POINTER;
+  if (tokens < 0 || row_bytes <= 0 || row_bytes % 16 != 0 || cap_rows < 0) return STK_ERR_BAD_DIMS;
+  const int64_t blocks = (tokens * 32 + 255) / 256;
+  stk::ep_combine_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      peer_bufs, dest, static_cast<uint4*>(out), tokens, static_cast<int>(row_bytes / 16), cap_rows);
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }

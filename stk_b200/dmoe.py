@@ -232,3 +232,137 @@ class ExpertParallelExchange:
         dist.all_to_all_single(out_sorted, back, state["send_splits"], state["recv_splits"],
                                group=self.group)
         return scatter_rows(out_sorted, state["order"], state["tokens"])
+
+
+# ------------------------------------------------------------------------------ exchange over peer memory
+def _ep_call(name, device, *args):
+    with _lib.on_device(device):
+        rc = getattr(_lib.load(), name)(*args, _lib.stream_ptr(device))
+    _lib.check(rc, name)
+
+
+class PeerExchangeBuffers:
+    """One rank's share of the exchange state: the count matrix, the padded bins the peers push token
+    rows into, and the result rows the peers pull from.  `peer_*` are int64 device arrays with the
+    address of the same region on every rank, as mapped in this process."""
+
+    def __init__(self, counts, recv, result, peer_counts, peer_recv, peer_result):
+        self.counts, self.recv, self.result = counts, recv, result
+        self.peer_counts, self.peer_recv, self.peer_result = peer_counts, peer_recv, peer_result
+
+
+class PeerExchange:
+    """ExpertParallelExchange with this library's own kernels moving the rows over NVLink.
+
+    Every rank pushes its token rows straight into the padded expert bins of the rank that owns
+    the expert (peer stores) and pulls its results from that rank's result buffer (peer loads); the
+    buffers live in torch symmetric memory, allocated once for `capacity_rows` padded rows.  There
+    is no NCCL call in a step: the per-expert counts travel the same way, and the steps are
+    separated by the symmetric-memory barrier.  One host read-back per dispatch (the number of
+    padded rows, which sizes the topology).  Same results, row for row, as ExpertParallelExchange.
+
+    `buffers` / `barrier` can be given to run several ranks of this logic inside one process on one
+    GPU (tests): then nothing is allocated here and `barrier()` is called where ranks must meet.
+    """
+
+    def __init__(self, num_experts, tokens, hidden, out_hidden, dtype, device, group=None,
+                 block=BLOCK, capacity_rows=None, world=None, rank=None, buffers=None, barrier=None):
+        self.world = dist.get_world_size(group) if world is None else world
+        self.rank = dist.get_rank(group) if rank is None else rank
+        if num_experts % self.world != 0:
+            raise ValueError(f"{num_experts} experts do not divide over {self.world} ranks")
+        self.num_experts, self.local_experts = num_experts, num_experts // self.world
+        self.block, self.device, self.dtype = block, torch.device(device), dtype
+        self.hidden, self.out_hidden = hidden, out_hidden
+        if capacity_rows is None:
+            capacity_rows = 2 * tokens + self.local_experts * block
+        self.capacity_rows = (capacity_rows + block - 1) // block * block
+        if buffers is None:
+            # symmetric allocations have the same size on every rank
+            cap = torch.tensor([self.capacity_rows], dtype=torch.int64, device=self.device)
+            dist.all_reduce(cap, op=dist.ReduceOp.MAX, group=group)
+            self.capacity_rows = int(cap.item())
+            buffers, barrier = self._allocate(group)
+        self.buf, self.barrier = buffers, barrier
+        self._totals_host = torch.empty(2, dtype=torch.int64).pin_memory()
+
+    def _allocate(self, group):
+        import torch.distributed._symmetric_memory as symm_mem
+        elem = torch.empty((), dtype=self.dtype).element_size()
+        align = lambda n: (n + 255) // 256 * 256
+        n_counts = align(4 * self.world * self.num_experts)
+        n_recv = align(self.capacity_rows * self.hidden * elem)
+        n_result = align(self.capacity_rows * self.out_hidden * elem)
+        raw = symm_mem.empty(n_counts + n_recv + n_result, dtype=torch.uint8, device=self.device)
+        handle = symm_mem.rendezvous(raw, group if group is not None else dist.group.WORLD)
+        ptrs = [int(p) for p in handle.buffer_ptrs]
+        dev_ptrs = lambda off: torch.tensor([p + off for p in ptrs], dtype=torch.int64, device=self.device)
+        counts = raw[:4 * self.world * self.num_experts].view(torch.int32).view(self.world, self.num_experts)
+        recv = raw[n_counts:n_counts + self.capacity_rows * self.hidden * elem].view(self.dtype)
+        result = raw[n_counts + n_recv:n_counts + n_recv + self.capacity_rows * self.out_hidden * elem].view(self.dtype)
+        buffers = PeerExchangeBuffers(counts, recv.view(self.capacity_rows, self.hidden),
+                                      result.view(self.capacity_rows, self.out_hidden),
+                                      dev_ptrs(0), dev_ptrs(n_counts), dev_ptrs(n_counts + n_recv))
+        self._raw, self._handle = raw, handle
+        return buffers, handle.barrier
+
+    # The three phases of dispatch are separate so that a single-process emulation can interleave
+    # the ranks; dispatch() runs them back to back with the barriers in between.
+    def share_counts(self, expert_ids):
+        order, offsets = sort_by_expert(expert_ids, self.num_experts)
+        _ep_call("stk_b200_ep_share_counts", self.device, _lib.ptr(offsets), _lib.ptr(self.buf.peer_counts),
+                 self.world, self.num_experts, self.rank)
+        return order, offsets
+
+    def push(self, x, order, offsets):
+        dev, tokens = self.device, x.shape[0]
+        x = x.contiguous()
+        dest_base = torch.empty(self.num_experts, dtype=torch.int64, device=dev)
+        bin_rows = torch.empty(self.local_experts, dtype=torch.int32, device=dev)
+        totals = torch.empty(2, dtype=torch.int64, device=dev)
+        _ep_call("stk_b200_ep_plan", dev, _lib.ptr(self.buf.counts), self.world, self.num_experts, self.rank,
+                 self.block, _lib.ptr(dest_base), _lib.ptr(bin_rows), _lib.ptr(totals))
+        self._totals_host.copy_(totals, non_blocking=True)
+        row_bytes = self.hidden * x.element_size()
+        _ep_call("stk_b200_ep_zero_padding", dev, _lib.ptr(self.buf.counts), self.world, self.num_experts,
+                 self.rank, self.block, _lib.ptr(self.buf.recv), row_bytes, self.capacity_rows)
+        dest = torch.empty(tokens, dtype=torch.int64, device=dev)
+        _ep_call("stk_b200_ep_dispatch", dev, _lib.ptr(x), _lib.ptr(order), _lib.ptr(offsets),
+                 _lib.ptr(dest_base), _lib.ptr(self.buf.peer_recv), tokens, self.world, self.num_experts,
+                 row_bytes, self.capacity_rows, _lib.ptr(dest))
+        return dest, bin_rows
+
+    def padded_rows(self):
+        """Host value of this rank's padded row count (waits for the stream)."""
+        torch.cuda.current_stream(self.device).synchronize()       # the one synchronisation
+        total = int(self._totals_host[0])
+        if total > self.capacity_rows:
+            raise RuntimeError(f"{total} padded rows arrive at rank {self.rank} but the exchange buffers hold "
+                               f"{self.capacity_rows}: construct PeerExchange with a larger capacity_rows")
+        return total
+
+    def dispatch(self, x, expert_ids):
+        """Returns (x_padded [T'_local, h] - a view of the receive buffer, valid until the next
+        dispatch -, bin_rows int32 [local_experts], state)."""
+        order, offsets = self.share_counts(expert_ids)
+        self.barrier(0)
+        dest, bin_rows = self.push(x, order, offsets)
+        total = self.padded_rows()
+        self.barrier(1)
+        state = dict(dest=dest, tokens=x.shape[0], block_rows=total // self.block, total=total)
+        return self.buf.recv[:total], bin_rows, state
+
+    def publish(self, y_padded, state):
+        self.buf.result[:state["total"]].copy_(y_padded)
+
+    def pull(self, state):
+        out = torch.empty((state["tokens"], self.out_hidden), dtype=self.dtype, device=self.device)
+        _ep_call("stk_b200_ep_combine", self.device, _lib.ptr(self.buf.peer_result), _lib.ptr(state["dest"]),
+                 _lib.ptr(out), state["tokens"], self.out_hidden * out.element_size(), self.capacity_rows)
+        return out
+
+    def combine(self, y_padded, state):
+        """Inverse of dispatch for the per-token results y_padded [T'_local, out_hidden]."""
+        self.publish(y_padded, state)
+        self.barrier(2)
+        return self.pull(state)
