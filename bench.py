@@ -70,7 +70,9 @@ class ClockSampler:
     REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
                ("sw_power_cap", 0x4))
 
-    def __init__(self, index, period_s=0.002):
+    def __init__(self, index, period_s=None):
+        if period_s is None:
+            period_s = float(os.environ.get("STK_BENCH_CLOCK_PERIOD_MS", "5")) / 1e3
         self.index, self.period = index, period_s
         self.proc, self.error = None, None
 
@@ -209,12 +211,12 @@ def run_ours(args):
 
         for _ in range(args.warmup):
             resident_step()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()      # before the barrier: the other ranks must not time its start-up
         torch.cuda.synchronize()
         if distributed:
             dist.barrier()
-        sampler = ClockSampler(local_rank)
-        if rank == 0:
-            sampler.start()
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
         torch.cuda.synchronize()
         if not distributed:
