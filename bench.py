@@ -129,10 +129,11 @@ def make_tokens(rank):
     return (torch.randn(T_TOKENS, HIDDEN, generator=g) * 0.02).to(DTYPE)
 
 
-def expert_step(stk, x_padded, topo, w1, w2):
+def expert_step(stk, x_padded, topo, w1, w2, out=None):
     """sdd -> GeLU -> dsd on tokens already in padded expert order; the GeLU runs in the SDD
-    kernel's epilogue (stk.ops.sdd_gelu), so the step is two kernel launches."""
-    return stk.ops.dsd(stk.ops.sdd_gelu(x_padded, w1, topo), w2)
+    kernel's epilogue (stk.ops.sdd_gelu), so the step is two kernel launches.  `out`: where the
+    second product is written (the exchange's result buffer on several GPUs)."""
+    return stk.ops.dsd(stk.ops.sdd_gelu(x_padded, w1, topo), w2, out=out)
 
 
 def run_ours(args):
@@ -174,12 +175,15 @@ def run_ours(args):
         if exchange is None:
             exchange = dmoe.ExpertParallelExchange(total_experts)
 
+    def result_rows(state):
+        return exchange.result_rows(state) if exchange_kind == "peer" else None
+
     def full_step(x_dev, ids_dev):
         """Routing bookkeeping + (exchange) + sdd -> GeLU -> dsd + (exchange back)."""
         if distributed:
             xp, bin_rows, state = exchange.dispatch(x_dev, ids_dev)
             topo = dmoe.topology_from_bins(bin_rows, state["block_rows"], FFN, DTYPE, dev)
-            y = expert_step(stk, xp, topo, w1, w2)
+            y = expert_step(stk, xp, topo, w1, w2, out=result_rows(state))
             return exchange.combine(y, state), topo
         index, padded, bin_rows, total = dmoe.route_top1(ids_dev, EXPERTS)
         topo = dmoe.topology_from_bins(bin_rows, total // 128, FFN, DTYPE, dev)
@@ -205,7 +209,7 @@ def run_ours(args):
         def resident_step():
             if distributed:
                 xq, _, st = exchange.dispatch(x_dev, ids)
-                y = expert_step(stk, xq, topo, w1, w2)
+                y = expert_step(stk, xq, topo, w1, w2, out=result_rows(st))
                 return exchange.combine(y, st)
             return expert_step(stk, xp, topo, w1, w2)
 

@@ -352,8 +352,15 @@ class PeerExchange:
         state = dict(dest=dest, tokens=x.shape[0], block_rows=total // self.block, total=total)
         return self.buf.recv[:total], bin_rows, state
 
+    def result_rows(self, state):
+        """The rows of the result buffer for this dispatch: write the expert outputs here (e.g.
+        stk.ops.dsd(h, w2, out=...)) and combine() has nothing to copy."""
+        return self.buf.result[:state["total"]]
+
     def publish(self, y_padded, state):
-        self.buf.result[:state["total"]].copy_(y_padded)
+        target = self.result_rows(state)
+        if y_padded.data_ptr() != target.data_ptr():
+            target.copy_(y_padded)
 
     def pull(self, state):
         out = torch.empty((state["tokens"], self.out_hidden), dtype=self.dtype, device=self.device)

@@ -4,7 +4,7 @@ S = sparse (stk.Matrix), D = dense (torch.Tensor); the three letters are output,
 """
 import torch
 
-from stk_b200.backend import sputnik
+from stk_b200.backend import kernels, sputnik
 from stk_b200.matrix import Matrix
 
 
@@ -13,11 +13,24 @@ def _fields(m):
             m.block_offsets_t)
 
 
-def dsd(a, b):
-    """dense = a @ b with a sparse (possibly a .t() view) and b dense."""
+def dsd(a, b, out=None):
+    """dense = a @ b with a sparse (possibly a .t() view) and b dense.
+
+    `out` (not in the reference): a row-major [rows of a, columns of b] tensor of b's dtype to write
+    the product into instead of a fresh one, e.g. a buffer other GPUs read.  No gradient flows
+    through a product written this way, and autocast does not apply to it.
+    """
     assert isinstance(a, Matrix)
     assert isinstance(b, torch.Tensor)
-    return sputnik.dsd(a.size(), *_fields(a), not a.is_contiguous(), b)
+    if out is None:
+        return sputnik.dsd(a.size(), *_fields(a), not a.is_contiguous(), b)
+    if torch.is_grad_enabled() and (a.data.requires_grad or b.requires_grad):
+        raise ValueError("dsd(out=...) does not record a gradient; call it under torch.no_grad()")
+    if (out.dim() != 2 or out.shape[0] != a.size()[0] or out.shape[1] != b.shape[1] or out.dtype != b.dtype
+            or out.stride(1) != 1 or out.device != b.device):
+        raise ValueError("out must be a row-major [a.size(0), b.size(1)] tensor of b's dtype on b's device")
+    kernels.dsd(a.size(), *_fields(a), not a.is_contiguous(), b, out)
+    return out
 
 
 def dds(a, b):

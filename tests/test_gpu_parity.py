@@ -259,6 +259,23 @@ def test_strided_views_and_errors(stk):
         stk.ops.sdd(a.cpu(), b.cpu(), topo)         # no CPU path
 
 
+def test_dsd_into_a_given_buffer(stk):
+    """dsd(out=...) writes the same product into the caller's rows (a wider buffer's leading rows)."""
+    np.random.seed(11)
+    s = stk.random.randn((384, 256), 0.5, 128).to("cuda")
+    b = (torch.randn(256, 512, device="cuda") * 0.1).half()
+    with torch.no_grad():
+        ref = stk.ops.dsd(s, b)
+        buf = torch.full((640, 512), float("nan"), dtype=torch.float16, device="cuda")
+        got = stk.ops.dsd(s, b, out=buf[:384])
+        assert got.data_ptr() == buf.data_ptr() and torch.equal(got, ref)
+        assert bool(torch.isnan(buf[384:]).all())
+        with pytest.raises(ValueError):
+            stk.ops.dsd(s, b, out=buf[:256])
+    with pytest.raises(ValueError):
+        stk.ops.dsd(s, b.clone().requires_grad_(True), out=buf[:384])
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_dmoe_shaped_products_full_size(stk, dtype):
     """BASELINE configs[1]-shaped problem at full size (T=16384, h=1024, f=4096, E=8): forward and
