@@ -43,6 +43,10 @@ constexpr int kPStages = 6;
 constexpr int kPAccCols = 256;   // one accumulator: 128 lanes x 256 fp32 columns per CTA
 constexpr int kPTmemCols = 512;  // two accumulators
 constexpr int kPNumBars = 2 * kPStages + 4;
+#ifndef STK_DEPENDENT_LAUNCH
+#define STK_DEPENDENT_LAUNCH 1
+#endif
+constexpr bool kUseDependentLaunch = STK_DEPENDENT_LAUNCH != 0;
 constexpr int kMaxBreaks = 64;  // places where the rows are cut into runs (more: no cuts at all)
 constexpr int kPSmemBytes =
     kPStages * kStageBytes + 2 * kOutStageBytes + kPNumBars * 8 + kPStages * 4 + 32 + (3 * kMaxBreaks + 8) * 4 + 1024;
@@ -278,6 +282,11 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tmem_alloc_pair(smem_u32(tmem_slot), kPTmemCols);
     tmem_relinquish_pair();
   }
+  // Everything above touched only this SM; from here on global memory is read.  With a programmatic
+  // dependent launch this is where the kernel waits for the one before it in the stream, and the
+  // next kernel may be scheduled onto SMs as this grid drains (its set-up then overlaps our tail).
+  pdl_launch_dependents();
+  pdl_wait();
   __syncthreads();
   // Every CTA finds the cuts by itself (same metadata, same answer in both CTAs).
   if (p.mode != kModeDDS) {
@@ -680,8 +689,18 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   const int rc = pair_device_info(&d);
   if (rc != STK_OK) return rc;
   const int pairs = p.num_items < d->max_pairs ? p.num_items : d->max_pairs;
-  bsmm_pair_kernel<<<2 * pairs, kPThreads, kPSmemBytes, stream>>>(tmA, tmB, tmC, p);
-  return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+  cfg.blockDim = dim3(kPThreads);
+  cfg.dynamicSmemBytes = kPSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = kUseDependentLaunch ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, bsmm_pair_kernel, tmA, tmB, tmC, p) == cudaSuccess ? STK_OK
+                                                                                      : STK_ERR_LAUNCH;
 }
 
 }  // namespace stk
