@@ -49,7 +49,7 @@ constexpr int kPNumBars = 2 * kPStages + 4;
 constexpr bool kUseDependentLaunch = STK_DEPENDENT_LAUNCH != 0;
 constexpr int kMaxBreaks = 64;  // places where the rows are cut into runs (more: no cuts at all)
 constexpr int kPSmemBytes =
-    kPStages * kStageBytes + 2 * kOutStageBytes + kPNumBars * 8 + kPStages * 4 + 32 + (3 * kMaxBreaks + 8) * 4 + 1024;
+    kPStages * kStageBytes + 2 * kOutStageBytes + kPNumBars * 8 + kPStages * 4 + 32 + (5 * kMaxBreaks + 12) * 4 + 1024;
 constexpr int kNoBlock = 0x7fffffff;
 
 enum : uint32_t { kFlagFirst = 1u, kFlagLast = 2u, kFlagEnd = 4u };
@@ -213,19 +213,21 @@ __device__ __forceinline__ void load_operand_pair(const CUtensorMap* tm, uint32_
 // of every MMA wasted, and every pair behind it may be misaligned as well.  The kernel therefore
 // cuts the rows into runs at those places and pairs inside each run; a run of odd length ends in a
 // single row.  Items of such a topology are then equally long, and dealing them round-robin
-// balances the CTA pairs.  run_start[k] = first row of run k, run_cum[k] = groups before run k.
+// balances the CTA pairs.  Runs are listed longest block lists first: run_start[k] / run_end[k] = rows of
+// the k-th run in that order, run_cum[k] = groups before it.
 struct PairItem {
   int r, part, inner;  // first row of the group, 0 = rows r and r + 1 / 1 = row r alone, dense supertile
 };
 __device__ __forceinline__ PairItem decode_item(int item, int inner_count, const int* run_start,
-                                                const int* run_cum, int num_runs) {
+                                                const int* run_end, const int* run_cum,
+                                                int num_runs) {
   PairItem it;
   const int g = item / inner_count;
   it.inner = item - g * inner_count;
   int k = 0;
   while (k + 1 < num_runs && run_cum[k + 1] <= g) ++k;
   it.r = run_start[k] + 2 * (g - run_cum[k]);
-  it.part = it.r + 1 >= run_start[k + 1] ? 1 : 0;
+  it.part = it.r + 1 >= run_end[k] ? 1 : 0;
   return it;
 }
 
@@ -249,9 +251,11 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* epilogue_go = abort_flag + 1;  // [2], one per epilogue group
   int* break_count = const_cast<int*>(epilogue_go) + 2;
-  int* breaks = break_count + 1;           // [kMaxBreaks]
-  int* run_start = breaks + kMaxBreaks;    // [kMaxBreaks + 2]
-  int* run_cum = run_start + kMaxBreaks + 2;  // [kMaxBreaks + 2]
+  int* breaks = break_count + 1;                 // [kMaxBreaks + 2]
+  int* run_start = breaks + kMaxBreaks + 2;      // [kMaxBreaks + 2] first row of each run, in dealing order
+  int* run_end = run_start + kMaxBreaks + 2;     // [kMaxBreaks + 2] one past its last row
+  int* run_cum = run_end + kMaxBreaks + 2;       // [kMaxBreaks + 2] groups before each run
+  int* run_cost = run_cum + kMaxBreaks + 2;      // [kMaxBreaks + 2] blocks in the run's first list
 #ifdef STK_EXP_PROFILE
   __shared__ long long ts_issue[kPStages], ts_commit[kPStages];
 #endif
@@ -289,37 +293,53 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   pdl_wait();
   __syncthreads();
   // Every CTA finds the cuts by itself (same metadata, same answer in both CTAs).
-  if (p.mode != kModeDDS) {
-    for (int r = threadIdx.x; r + 1 < p.num_lists; r += kPThreads) {
-      const int a0 = p.offsets[r], a1 = p.offsets[r + 1], b1 = p.offsets[r + 2];
-      if (a0 >= a1 || a1 >= b1) continue;
-      const int a_first = __ldg(p.col_idx + a0), a_last = __ldg(p.col_idx + a1 - 1);
-      const int b_first = __ldg(p.col_idx + a1), b_last = __ldg(p.col_idx + b1 - 1);
-      if (a_last < b_first || b_last < a_first) {
-        const int pos = atomicAdd(break_count, 1);
-        if (pos < kMaxBreaks) breaks[pos] = r;
-      }
+  for (int r = threadIdx.x; r + 1 < p.num_lists; r += kPThreads) {
+    const int a0 = p.offsets[r], a1 = p.offsets[r + 1], b1 = p.offsets[r + 2];
+    if (a0 >= a1 || a1 >= b1) continue;
+    const int a_first = __ldg(p.col_idx + a0), a_last = __ldg(p.col_idx + a1 - 1);
+    const int b_first = __ldg(p.col_idx + a1), b_last = __ldg(p.col_idx + b1 - 1);
+    if (a_last < b_first || b_last < a_first) {
+      const int pos = atomicAdd(break_count, 1);
+      if (pos < kMaxBreaks) breaks[pos] = r;
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  {
+    // The runs, longest block lists first: items are dealt round-robin in this order, so every CTA
+    // pair takes its expensive items first and the cheap ones level the load (experts of a dMoE
+    // layer differ in tokens, i.e. in the K length of the weight-gradient products).  All sorting
+    // is by rank counting, one thread per element.
     int n = *break_count;
     if (n > kMaxBreaks) n = 0;  // not a dMoE-like topology: one run, blind pairs
-    for (int i = 1; i < n; ++i) {  // the appends came in any order
-      const int v = breaks[i];
-      int j = i - 1;
-      for (; j >= 0 && breaks[j] > v; --j) breaks[j + 1] = breaks[j];
-      breaks[j + 1] = v;
+    const int runs = n + 1, k = threadIdx.x;
+    if (k < n) {
+      int rank_k = 0;
+      for (int j2 = 0; j2 < n; ++j2) rank_k += breaks[j2] < breaks[k] ? 1 : 0;
+      run_cum[rank_k] = breaks[k];  // run_cum doubles as the sorted list of cuts
     }
-    run_start[0] = 0;
-    run_cum[0] = 0;
-    for (int k = 0; k < n; ++k) {
-      run_start[k + 1] = breaks[k] + 1;
-      run_cum[k + 1] = run_cum[k] + (run_start[k + 1] - run_start[k] + 1) / 2;
+    __syncthreads();
+    int start = 0, end = 0, cost = 0;
+    if (k < runs && p.num_lists > 0) {
+      start = k == 0 ? 0 : run_cum[k - 1] + 1;
+      end = k == n ? p.num_lists : run_cum[k] + 1;
+      cost = p.offsets[start + 1] - p.offsets[start];
+      run_cost[k] = cost;
     }
-    run_start[n + 1] = p.num_lists;
-    run_cum[n + 1] = run_cum[n] + (p.num_lists - run_start[n] + 1) / 2;
-    *break_count = n;
+    __syncthreads();
+    if (k < runs && p.num_lists > 0) {
+      int rank_k = 0;
+      for (int j2 = 0; j2 < runs; ++j2)
+        rank_k += (run_cost[j2] > cost || (run_cost[j2] == cost && j2 < k)) ? 1 : 0;
+      run_start[rank_k] = start;
+      run_end[rank_k] = end;
+    }
+    __syncthreads();
+    if (k == 0) {
+      run_cum[0] = 0;
+      for (int i2 = 0; i2 < runs; ++i2)
+        run_cum[i2 + 1] = p.num_lists > 0 ? run_cum[i2] + (run_end[i2] - run_start[i2] + 1) / 2 : 0;
+      *break_count = n;
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -385,7 +405,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #endif
       for (int item = pair_id; item < num_items && ok; item += num_pairs) {
         if (p.mode == kModeSDD) {
-          const PairItem it = decode_item(item, p.inner, run_start, run_cum, num_runs);
+          const PairItem it = decode_item(item, p.inner, run_start, run_end, run_cum, num_runs);
           TileWalker w;
           w.init(p, it.r, it.inner, it.part);
           int u, blk[2][2];
@@ -396,7 +416,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                       (ks == 0 ? kFlagFirst : 0u) | (ks == p.k_steps - 1 ? kFlagLast : 0u));
           }
         } else {
-          const PairItem it = decode_item(item, p.inner, run_start, run_cum, num_runs);
+          const PairItem it = decode_item(item, p.inner, run_start, run_end, run_cum, num_runs);
           MergeWalker w;
           w.init(p, it.r, it.part);
           uint32_t first = kFlagFirst;
@@ -570,7 +590,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint16_t* out = static_cast<uint16_t*>(p.out);
     for (int item = pair_id; item < num_items && ok; item += num_pairs) {
       if (p.mode == kModeSDD) {
-        const PairItem it = decode_item(item, p.inner, run_start, run_cum, num_runs);
+        const PairItem it = decode_item(item, p.inner, run_start, run_end, run_cum, num_runs);
         TileWalker w;
         w.init(p, it.r, it.inner, it.part);
         int u, blk[2][2];
@@ -590,7 +610,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           release();
         }
       } else {
-        const PairItem it = decode_item(item, p.inner, run_start, run_cum, num_runs);
+        const PairItem it = decode_item(item, p.inner, run_start, run_end, run_cum, num_runs);
         MergeWalker w;
         w.init(p, it.r, it.part);
         // This CTA's 128 output rows and the 256 output columns of the supertile.  In a single-row
@@ -599,7 +619,9 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int tile_col = (p.mode == kModeDSD ? 2 * it.inner : it.r) * kBlk;
         const bool rows_valid =
             tile_row < p.out_rows && (p.mode != kModeDSD || it.part == 0 || rank == 0);
-        const int ncols = min(2 * kBlk, p.out_cols - tile_col);
+        // (DDS: a single block column's item owns 128 output columns, not 256.)
+        const int ncols =
+            min((p.mode == kModeDDS && it.part == 1) ? kBlk : 2 * kBlk, p.out_cols - tile_col);
         uint16_t* dst = out + (static_cast<long long>(tile_row) + row) * p.ldc + tile_col;
         if (w.empty()) {
           if (rows_valid && group == 0) {
