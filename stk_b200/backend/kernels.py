@@ -22,10 +22,11 @@ BLOCK = 128  # the matmul kernels are built for 128x128 blocks
 PAIR_MODE = os.environ.get("STK_B200_PAIR_MODE", "auto")
 # Fraction of the pair kernel's MMA work that must be useful for it to be chosen.  The pair kernel
 # moves half the operand bytes per FLOP, so it still wins with a good part of its work wasted:
-# measured on random 8192^2 topologies it overtakes the 128x128 kernel for DSD / DDS as soon as
-# slightly more than half of its work is useful (0.51: 566 vs 544 TFLOP/s for the 128x128 kernel,
-# 0.53: 632 vs 706), for SDD (whose 2x2 tiles waste more) only well above 0.53 (757 vs 724).
-PAIR_THRESHOLD = {"rows": 0.52, "cols": 0.52, "tiles": 0.7}
+# measured on random 8192^2 topologies (python -m stk_b200.benchmarks c4) the two kernels are level
+# for DSD / DDS at a useful share of 0.57 (775 vs 765 TFLOP/s), the 128x128 kernel is ahead at 0.53
+# (735 vs 690) and the pair kernel at 0.65 (790 vs 900); for SDD (whose 2x2 tiles waste more) the
+# 128x128 kernel is still ahead at 0.53 (900 vs 690), dMoE topologies are above 0.9.
+PAIR_THRESHOLD = {"rows": 0.58, "cols": 0.58, "tiles": 0.7}
 _HINT_ATTR = "_stk_b200_pair_hints"
 
 
