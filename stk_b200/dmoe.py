@@ -347,8 +347,8 @@ class PeerExchange:
         order, offsets = self.share_counts(expert_ids)
         self.barrier(0)
         dest, bin_rows = self.push(x, order, offsets)
+        self.barrier(1)                  # enqueued before the read-back: it runs while the host wakes up
         total = self.padded_rows()
-        self.barrier(1)
         state = dict(dest=dest, tokens=x.shape[0], block_rows=total // self.block, total=total)
         return self.buf.recv[:total], bin_rows, state
 
