@@ -229,6 +229,13 @@ int stk_b200_dmoe_topology(const int32_t* bin_rows, int experts, int cols_per_ex
                            int32_t* block_offsets_t, void* stream);
 
 /*
+ * Copies up to 1 MiB with a kernel (one CTA) instead of the copy engine.  `dst` may be pinned host
+ * memory: a small read-back (expert counts, padded row count) then does not wait behind a large
+ * device-to-host copy queued on the copy engine.  No counterpart in the reference.
+ */
+int stk_b200_copy_bytes(const void* src, void* dst, int64_t nbytes, void* stream);
+
+/*
  * Expert-parallel token exchange over peer memory (NVLink).  No counterpart in the reference, which
  * is single-GPU; these move the rows that stk.ops.sdd / dsd work on between the ranks of an
  * expert-parallel dMoE layer without a host-side collective: every rank pushes its token rows into

@@ -50,6 +50,7 @@ SIGNATURES = {
                                     _c_ptr]),
     "stk_b200_dmoe_topology": (_c_int, [_c_ptr, _c_int, _c_int, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                                         _c_ptr, _c_ptr, _c_ptr]),
+    "stk_b200_copy_bytes": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_ptr]),
     "stk_b200_ep_share_counts": (_c_int, [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr]),
     "stk_b200_ep_plan": (_c_int, [_c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr]),
     "stk_b200_ep_zero_padding": (_c_int, [_c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_i64, _c_i64,

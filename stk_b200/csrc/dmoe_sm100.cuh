@@ -142,6 +142,21 @@ dmoe_topology_kernel(const int32_t* __restrict__ bin_rows, int experts, int cpb,
   block_offsets_t[q] = static_cast<int32_t>(p);
 }
 
+// A few bytes copied by a kernel instead of the copy engine: the destination may be pinned host
+// memory (mapped into the device's address space), so that a small read-back - expert counts, the
+// number of padded rows - does not queue behind a large device-to-host copy on the copy engine.
+__global__ void __launch_bounds__(256)
+copy_bytes_kernel(const unsigned char* __restrict__ src, unsigned char* __restrict__ dst, int64_t nbytes,
+                  int words) {
+  if (words) {
+    const uint32_t* s4 = reinterpret_cast<const uint32_t*>(src);
+    uint32_t* d4 = reinterpret_cast<uint32_t*>(dst);
+    for (int64_t i = threadIdx.x; i < nbytes / 4; i += blockDim.x) d4[i] = s4[i];
+  } else {
+    for (int64_t i = threadIdx.x; i < nbytes; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
 // ------------------------------------------------------------------ expert-parallel exchange
 // Token exchange over peer memory (NVLink): every rank PUSHES its token rows straight into the
 // padded expert bins of the rank that owns the expert, and later PULLS its results from there.  The
@@ -416,5 +431,17 @@ extern "C" int stk_b200_ep_combine(const uint64_t* peer_bufs, const int64_t* des
   const int64_t blocks = (tokens * 32 + 255) / 256;
   stk::ep_combine_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       peer_bufs, dest, static_cast<uint4*>(out), tokens, static_cast<int>(row_bytes / 16), cap_rows);
+  return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
+}
+
+extern "C" int stk_b200_copy_bytes(const void* src, void* dst, int64_t nbytes, void* stream) {
+  if (nbytes == 0) return STK_OK;
+  if (!src || !dst) return STK_ERR_NULL_POINTER;
+  if (nbytes < 0) return STK_ERR_BAD_DIMS;
+  if (nbytes > (1 << 20)) return STK_ERR_TOO_LARGE;
+  const int words = (reinterpret_cast<uintptr_t>(src) % 4 == 0 && reinterpret_cast<uintptr_t>(dst) % 4 == 0 &&
+                     nbytes % 4 == 0) ? 1 : 0;
+  stk::copy_bytes_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned char*>(src), static_cast<unsigned char*>(dst), nbytes, words);
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }

@@ -151,6 +151,28 @@ def block_diagonal_topology(padded_counts, ffn, dtype, device, block=BLOCK, data
     return topology_from_bins(bin_rows.to(device), block_rows, ffn, dtype, device, block, data)
 
 
+_READ_BACK_BUFFERS = {}
+
+
+def read_back(t):
+    """Host copy of a small device tensor (waits for the current stream).  A kernel writes it into
+    pinned host memory, so the read-back does not queue behind large copies on the copy engine;
+    host tensors are returned as they are.  The returned tensor is a fresh one."""
+    if not t.is_cuda:
+        return t
+    t = t.contiguous()
+    nbytes = t.numel() * t.element_size()
+    key = (t.device, max(256, 1 << (nbytes - 1).bit_length()) if nbytes else 256)
+    buf = _READ_BACK_BUFFERS.get(key)
+    if buf is None:
+        buf = _READ_BACK_BUFFERS[key] = torch.empty(key[1], dtype=torch.uint8).pin_memory()
+    with _lib.on_device(t.device):
+        rc = _lib.load().stk_b200_copy_bytes(_lib.ptr(t), buf.data_ptr(), nbytes, _lib.stream_ptr(t.device))
+    _lib.check(rc, "stk_b200_copy_bytes")
+    torch.cuda.current_stream(t.device).synchronize()
+    return buf[:nbytes].clone().view(t.dtype).view(t.shape)
+
+
 # ------------------------------------------------------------------------------ one GPU
 def route_top1(expert_ids, num_experts, block=BLOCK):
     """Placement of tokens in padded expert order for top-1 routing on one device.
@@ -160,7 +182,7 @@ def route_top1(expert_ids, num_experts, block=BLOCK):
     in blocks, on the device."""
     order, offsets = sort_by_expert(expert_ids, num_experts)
     counts = (offsets[1:] - offsets[:-1]).to(torch.int64).view(1, num_experts)
-    host_counts = counts.cpu().view(-1)                    # the one synchronisation
+    host_counts = read_back(counts).view(-1)               # the one synchronisation
     padded = ((host_counts + block - 1) // block) * block
     total = int(padded.sum())
     index, bin_rows = bin_index(counts, total, block, compose=order)
@@ -209,7 +231,7 @@ class ExpertParallelExchange:
         counts[0] = offsets[1:] - offsets[:-1]
         # counts[0][e] for the experts of rank g go to rank g: one row of E/n counts per peer
         dist.all_to_all_single(counts[1], counts[0], group=self.group)
-        host = counts.cpu()                                   # the one synchronisation
+        host = read_back(counts)                              # the one synchronisation
         send_splits = host[0].view(world, local).sum(1).tolist()
         recv_by_peer = host[1].view(world, local)
         recv_splits = recv_by_peer.sum(1).tolist()
@@ -322,7 +344,10 @@ class PeerExchange:
         totals = torch.empty(2, dtype=torch.int64, device=dev)
         _ep_call("stk_b200_ep_plan", dev, _lib.ptr(self.buf.counts), self.world, self.num_experts, self.rank,
                  self.block, _lib.ptr(dest_base), _lib.ptr(bin_rows), _lib.ptr(totals))
-        self._totals_host.copy_(totals, non_blocking=True)
+        with _lib.on_device(dev):        # by a kernel, not the copy engine (see read_back)
+            rc = _lib.load().stk_b200_copy_bytes(_lib.ptr(totals), self._totals_host.data_ptr(), 16,
+                                                 _lib.stream_ptr(dev))
+        _lib.check(rc, "stk_b200_copy_bytes")
         row_bytes = self.hidden * x.element_size()
         _ep_call("stk_b200_ep_zero_padding", dev, _lib.ptr(self.buf.counts), self.world, self.num_experts,
                  self.rank, self.block, _lib.ptr(self.buf.recv), row_bytes, self.capacity_rows)
@@ -373,3 +398,81 @@ class PeerExchange:
         self.publish(y_padded, state)
         self.barrier(2)
         return self.pull(state)
+
+
+# ------------------------------------------------------------------------------ batches from host memory
+class HostPipeline:
+    """Feeds a device step with batches that live in pinned host memory and returns its results to
+    pinned host memory, with the copies of neighbouring batches overlapping the step: the inputs of
+    batch i+1 travel to the device (copy-in stream) and the result of batch i-1 travels back
+    (copy-out stream) while batch i is computed on the current stream.  Two device input buffers
+    and two host result buffers are reused in turn.
+
+        pipe = HostPipeline(step, device)              # step(*device_inputs) -> device tensor
+        for batch in batches:                          # batch: tuple of pinned host tensors
+            done = pipe.submit(*batch)                 # result of the PREVIOUS batch, or None
+        last = pipe.flush()
+
+    submit() returns the host tensor holding the previous batch's result; it is valid once
+    `pipe.wait(done)` has returned (or after flush()) and until two more batches were submitted.
+    """
+
+    def __init__(self, step, device):
+        self.step, self.device = step, torch.device(device)
+        self.copy_in, self.copy_out = torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)
+        self.inputs = [None, None]           # device input buffers
+        self.results = [None, None]          # pinned host result buffers
+        self.in_ready = [torch.cuda.Event() for _ in range(2)]
+        self.in_free = [None, None]
+        self.out_ready = [None, None]
+        self.count = 0                       # batches submitted
+        self.pending = None                  # slot whose inputs are on their way but not yet computed
+
+    def _upload(self, slot, host_tensors):
+        if self.inputs[slot] is None:
+            self.inputs[slot] = [torch.empty(t.shape, dtype=t.dtype, device=self.device) for t in host_tensors]
+        with torch.cuda.stream(self.copy_in):
+            if self.in_free[slot] is not None:
+                self.copy_in.wait_event(self.in_free[slot])     # the step that read this buffer is done
+            for dst, src in zip(self.inputs[slot], host_tensors):
+                dst.copy_(src, non_blocking=True)
+            self.in_ready[slot].record(self.copy_in)
+
+    def _compute(self, slot):
+        main = torch.cuda.current_stream(self.device)
+        main.wait_event(self.in_ready[slot])
+        out = self.step(*self.inputs[slot])
+        self.in_free[slot] = torch.cuda.Event()
+        self.in_free[slot].record(main)
+        done = torch.cuda.Event()
+        done.record(main)
+        if self.results[slot] is None or self.results[slot].shape != out.shape:
+            self.results[slot] = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+        with torch.cuda.stream(self.copy_out):
+            self.copy_out.wait_event(done)
+            self.results[slot].copy_(out, non_blocking=True)
+            self.out_ready[slot] = torch.cuda.Event()
+            self.out_ready[slot].record(self.copy_out)
+        out.record_stream(self.copy_out)
+        return self.results[slot]
+
+    def submit(self, *host_tensors):
+        slot = self.count % 2
+        self._upload(slot, host_tensors)            # first, so that it overlaps the step below
+        previous = self._compute(self.pending) if self.pending is not None else None
+        self.pending = slot
+        self.count += 1
+        return previous
+
+    def flush(self):
+        """Computes the last submitted batch; returns its host result after all copies are done."""
+        last = self._compute(self.pending) if self.pending is not None else None
+        self.pending = None
+        torch.cuda.current_stream(self.device).wait_stream(self.copy_out)
+        self.copy_out.synchronize()
+        return last
+
+    def wait(self, host_result):
+        for slot in range(2):
+            if self.results[slot] is host_result and self.out_ready[slot] is not None:
+                self.out_ready[slot].synchronize()
