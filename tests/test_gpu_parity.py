@@ -259,6 +259,36 @@ def test_strided_views_and_errors(stk):
         stk.ops.sdd(a.cpu(), b.cpu(), topo)         # no CPU path
 
 
+@pytest.mark.parametrize("experts,cols_per_expert", [(5, 3), (9, 2), (80, 1)])
+def test_block_diagonal_topologies_with_odd_runs(stk, experts, cols_per_expert):
+    """Expert bins of 1 to 3 block rows: runs of odd length (a single row closes them), runs of one
+    row, and - with 80 experts - more cuts than the pair kernel tracks (it then pairs blindly).
+    All six products against the dense path."""
+    from stk_b200 import dmoe
+    g = torch.Generator().manual_seed(experts)
+    bin_rows = torch.randint(1, 4, (experts,), generator=g)
+    bin_rows[experts // 2] = 0                              # an expert without tokens
+    f = cols_per_expert * 128
+    topo = dmoe.block_diagonal_topology(bin_rows * 128, f, torch.float16, "cuda")
+    rows, cols = topo.size()
+    ri, ci = topo.row_indices.cpu().numpy(), topo.column_indices.cpu().numpy()
+    a = (torch.randn(rows, 256, generator=g) * 0.1).half()
+    b = (torch.randn(256, cols, generator=g) * 0.1).half()
+    got = stk.ops.sdd(a.cuda(), b.cuda(), topo)
+    assert_product_close(got.data, oracle.sdd(a, b, ri, ci, torch.float16), "sdd")
+    assert_product_close(stk.ops.sdd(a.t().contiguous().cuda().t(), b.t().contiguous().cuda().t(), topo).data,
+                         oracle.sdd(a, b, ri, ci, torch.float16), "sdd TT")
+    s_dense = oracle.to_dense(got.data.cpu(), ri, ci, (rows, cols))
+    right = (torch.randn(cols, 384, generator=g) * 0.1).half()
+    left = (torch.randn(384, rows, generator=g) * 0.1).half()
+    assert_product_close(stk.ops.dsd(got, right.cuda()), oracle.dsd(s_dense, right, torch.float16), "dsd")
+    assert_product_close(stk.ops.dsd(got.t(), left.t().contiguous().cuda()),
+                         oracle.dsd(s_dense.t(), left.t(), torch.float16), "dsd T")
+    assert_product_close(stk.ops.dds(left.cuda(), got), oracle.dds(left, s_dense, torch.float16), "dds")
+    assert_product_close(stk.ops.dds(right.t().contiguous().cuda(), got.t()),
+                         oracle.dds(right.t(), s_dense.t(), torch.float16), "dds T")
+
+
 def test_dsd_into_a_given_buffer(stk):
     """dsd(out=...) writes the same product into the caller's rows (a wider buffer's leading rows)."""
     np.random.seed(11)
