@@ -18,15 +18,20 @@ BLOCK = 128  # the matmul kernels are built for 128x128 blocks
 
 # Which matmul kernel runs: "0" = one 128x128 tile per CTA, "1" = 256x256 supertiles on CTA pairs,
 # "2" = CTA pairs with two dense tiles per item for DSD / DDS (opt-in, never picked by "auto"),
+# "3" = 128x128 tiles for SDD, one block row / column x 256 dense columns / rows per CTA for DSD / DDS,
 # "auto" = per topology, from how well neighbouring block rows / columns pair up (see pair_hints).
 PAIR_MODE = os.environ.get("STK_B200_PAIR_MODE", "auto")
-# Fraction of the pair kernel's MMA work that must be useful for it to be chosen.  The pair kernel
-# moves half the operand bytes per FLOP, so it still wins with a good part of its work wasted:
-# measured on random 8192^2 topologies (python -m stk_b200.benchmarks c4) the two kernels are level
-# for DSD / DDS at a useful share of 0.57 (775 vs 765 TFLOP/s), the 128x128 kernel is ahead at 0.53
-# (735 vs 690) and the pair kernel at 0.65 (790 vs 900); for SDD (whose 2x2 tiles waste more) the
-# 128x128 kernel is still ahead at 0.53 (900 vs 690), dMoE topologies are above 0.9.
-PAIR_THRESHOLD = {"rows": 0.58, "cols": 0.58, "tiles": 0.7}
+# DSD / DDS products that do not take the pair kernel run the 128x256 row kernel in these modes when
+# the dense operand has at least 256 columns (DSD) / rows (DDS); "3" never takes the pair kernel.
+ROW_KERNEL_MODES = ("3", "auto")
+# Fraction of the pair kernel's MMA work that must be useful for it to be chosen (measured with
+# python -m stk_b200.benchmarks).  DSD / DDS ("rows", "cols"): the alternative is the 128x256 row
+# kernel, which needs no pairing and is within 5 % of the pair kernel even on dMoE topologies
+# (1300 vs 1390 TFLOP/s) and ahead of it as soon as a third of the pair kernel's work is wasted
+# (1080 vs 920 at a useful share of 0.65), so only near-perfect pairings take the pair kernel.
+# SDD ("tiles"): the alternative is the 128x128 kernel, still ahead at 0.53 (900 vs 690); dMoE
+# topologies are above 0.9.
+PAIR_THRESHOLD = {"rows": 0.85, "cols": 0.85, "tiles": 0.7}
 _HINT_ATTR = "_stk_b200_pair_hints"
 
 
@@ -70,7 +75,7 @@ def pair_hints(row_indices, column_indices, block_cols):
 
 def _use_pairs(kind, row_indices, column_indices, block_cols):
     """kind: "rows", "cols" or "tiles" - which neighbours the product would pair."""
-    if PAIR_MODE == "0":
+    if PAIR_MODE in ("0", "3"):
         return 0
     rows, cols, tiles, is_sorted = pair_hints(row_indices, column_indices, block_cols)
     if kind == "tiles" and not is_sorted:
@@ -147,6 +152,8 @@ def dsd(shape, data, offsets, row_indices, column_indices, offsets_t, column_ind
     else:
         meta = (offsets, column_indices, None)
         pairs = _use_pairs("rows", row_indices, column_indices, K // BLOCK)
+    if pairs == 0 and N >= 2 * BLOCK and PAIR_MODE in ROW_KERNEL_MODES:
+        pairs = 3            # one block row x 256 dense columns per CTA
     with _lib.on_device(out.device):
         rc = _lib.load().stk_b200_dsd(
             _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),
@@ -173,6 +180,8 @@ def dds(lhs, shape, data, offsets, row_indices, column_indices, offsets_t, colum
     else:
         meta = (offsets_t, column_indices_t, block_offsets_t)
         pairs = _use_pairs("cols", row_indices, column_indices, N // BLOCK)
+    if pairs == 0 and M >= 2 * BLOCK and PAIR_MODE in ROW_KERNEL_MODES:
+        pairs = 3            # 256 dense rows x one block column per CTA
     with _lib.on_device(out.device):
         rc = _lib.load().stk_b200_dds(
             _lib.ptr(lhs), _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),

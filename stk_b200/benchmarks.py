@@ -4,7 +4,8 @@
     python -m stk_b200.benchmarks c4     # random block sparsity on 8192^3, bf16, all op / transpose combinations
 
 Every line: nonzero-block TFLOP/s (2 * nnz * 128 * 128 * dense extent / time) with the 128x128 kernel
-forced, the CTA-pair kernel forced and the per-topology choice, against a cuBLAS GEMM (torch.matmul)
+forced, the 128x256 row kernel forced (DSD and DDS; SDD runs the 128x128 kernel in that column), the
+CTA-pair kernel forced and the per-topology choice, against a cuBLAS GEMM (torch.matmul)
 of the same useful FLOPs timed in the same run.  CUDA events around 20 back-to-back launches after 5
 warm-up launches; operands (hundreds of MB) exceed the L2, which is not flushed.
 """
@@ -35,19 +36,19 @@ def _time_ms(fn, iters=20, warm=5):
 def _report(name, flops, fn, dense_fn):
     saved, cells = kernels.PAIR_MODE, []
     try:
-        for mode in ("0", "1", "auto"):
+        for mode in ("0", "3", "1", "auto"):
             kernels.PAIR_MODE = mode
             cells.append(_time_ms(fn))
     finally:
         kernels.PAIR_MODE = saved
     dense = _time_ms(dense_fn)
     tf = lambda ms: flops / ms / 1e9
-    print(f"| {name:24s} | {tf(cells[0]):5.0f} | {tf(cells[1]):5.0f} | {tf(cells[2]):5.0f} | {cells[2] * 1e3:7.1f} | "
-          f"{tf(dense):5.0f} | {dense / cells[2]:4.2f} |", flush=True)
+    print(f"| {name:24s} | {tf(cells[0]):5.0f} | {tf(cells[1]):5.0f} | {tf(cells[2]):5.0f} | {tf(cells[3]):5.0f} | "
+          f"{cells[3] * 1e3:7.1f} | {tf(dense):5.0f} | {dense / cells[3]:4.2f} |", flush=True)
 
 
-_HEADER = ("| product                  | 128x128 | pair | auto TFLOP/s | auto us | cuBLAS TFLOP/s | auto / cuBLAS |\n"
-           "|---|---|---|---|---|---|---|")
+_HEADER = ("| product                  | 128x128 | 128x256 | pair | auto TFLOP/s | auto us | cuBLAS TFLOP/s | auto / cuBLAS |\n"
+           "|---|---|---|---|---|---|---|---|")
 
 
 def config3(dev="cuda"):

@@ -3,6 +3,7 @@
 #pragma once
 #include "bsmm_pair_sm100.cuh"
 #include "bsmm_wide_sm100.cuh"
+#include "bsmm_row_sm100.cuh"
 #include "bsmm_sm100.cuh"
 
 namespace stk {
@@ -123,6 +124,22 @@ extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int1
   CUtensorMap tmC;
   if ((rc = encode_map(&tmC, out, dtype, N, M, ld_out, kBlk)) != STK_OK) return rc;
 
+  if (pair_mode == 3) {  // one block row x 256 dense columns per CTA
+    BsmmParams p{};
+    p.mode = kModeDSD;
+    p.a_mn = trans_sparse ? 1 : 0;
+    p.b_mn = rhs_colmajor ? 0 : 1;
+    p.fmt = dtype;
+    p.tiles_inner = static_cast<int>((N + 2 * kBlk - 1) / (2 * kBlk));
+    p.num_tiles = static_cast<int>((M / kBlk) * p.tiles_inner);
+    p.col_idx = column_indices;
+    p.offsets = offsets;
+    p.blk_idx = block_offsets;
+    p.out = out;
+    p.ldc = ld_out;
+    p.out_cols = static_cast<int>(N);
+    return launch_row(tmA, tmB, tmC, p, s);
+  }
   if (pair_mode) {
     PairParams p{};
     p.mode = kModeDSD;
@@ -185,6 +202,22 @@ extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* of
   CUtensorMap tmC;
   if ((rc = encode_map(&tmC, out, dtype, N, M, ld_out, kBlk)) != STK_OK) return rc;
 
+  if (pair_mode == 3) {  // 256 dense rows x one block column per CTA
+    BsmmParams p{};
+    p.mode = kModeDDS;
+    p.a_mn = lhs_colmajor ? 1 : 0;
+    p.b_mn = trans_sparse ? 0 : 1;
+    p.fmt = dtype;
+    p.tiles_inner = static_cast<int>((M + 2 * kBlk - 1) / (2 * kBlk));
+    p.num_tiles = static_cast<int>((N / kBlk) * p.tiles_inner);
+    p.col_idx = column_indices;
+    p.offsets = offsets;
+    p.blk_idx = block_offsets;
+    p.out = out;
+    p.ldc = ld_out;
+    p.out_rows = static_cast<int>(M);
+    return launch_row(tmA, tmB, tmC, p, s);
+  }
   if (pair_mode) {
     PairParams p{};
     p.mode = kModeDDS;

@@ -91,6 +91,8 @@ struct BsmmParams {
   const int32_t* blk_idx;   // DSD/DDS: index into data of block j, or nullptr for the identity
   void* out;
   long long ldc;            // DSD/DDS: leading dimension of out in elements
+  int out_cols;             // row kernel (bsmm_row_sm100.cuh), DSD: dense columns of the output
+  int out_rows;             // row kernel, DDS: dense rows of the output
 };
 
 struct TileInfo {
