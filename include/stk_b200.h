@@ -71,10 +71,12 @@ int stk_b200_device_status(int* status_host);
  * do not.  2 (dsd / dds only; sdd treats it as 1) keeps the CTA pairs but gives every work item two
  * dense tiles, 256x512 (dsd) or 512x256 (dds) of output, so that each sparse tile fetched is used
  * twice: less operand traffic, no overlap of one item's epilogue with the next item's MMAs; it pays
- * only for long block lists and is never chosen by this package's own heuristic.  3 (dsd / dds only;
- * sdd treats it as 0) runs one block row of op(S) x 256 dense columns (dsd) or 256 dense rows x one
- * block column (dds) per CTA with one N = 256 MMA per K step: three quarters of mode 0's operand
- * traffic for any topology, no pairing needed - the choice for topologies that do not pair up.  All modes give
+ * only for long block lists and is never chosen by this package's own heuristic.  3 runs 128x256
+ * tiles on one CTA with one N = 256 MMA per K step: one block row of op(S) x 256 dense columns (dsd),
+ * 256 dense rows x one block column (dds, computed transposed), or two blocks of one block row
+ * (sdd: blocks 2i and 2i+1 of the list; row_indices / column_indices in row-major order).  Three
+ * quarters of mode 0's operand traffic for any topology, no pairing needed - the choice for
+ * topologies that do not pair up.  All modes give
  * the same results; modes 1 and 2 need every block row's column_indices (and every block column's
  * column_indices_t) in ascending order.
  */

@@ -24,6 +24,10 @@ PAIR_MODE = os.environ.get("STK_B200_PAIR_MODE", "auto")
 # DSD / DDS products that do not take the pair kernel run the 128x256 row kernel in these modes when
 # the dense operand has at least 256 columns (DSD) / rows (DDS); "3" never takes the pair kernel.
 ROW_KERNEL_MODES = ("3", "auto")
+# SDD with the row kernel (two blocks of a block row per tile) has half as many, twice as long work
+# items: on 8192^3 it is ahead of the 128x128 kernel from about 1000 blocks (level at 1024, 1190 vs
+# 920 TFLOP/s at 2048) and behind at 512 (685 vs 750), where 256 items leave the 148 SMs unevenly loaded.
+SDD_ROW_MIN_BLOCKS = 1536
 # Fraction of the pair kernel's MMA work that must be useful for it to be chosen (measured with
 # python -m stk_b200.benchmarks).  DSD / DDS ("rows", "cols"): the alternative is the 128x256 row
 # kernel, which needs no pairing and is within 5 % of the pair kernel even on dMoE topologies
@@ -203,6 +207,8 @@ def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices, epilogue=0):
     lhs, lhs_colmajor, ld_lhs = _dense_layout(lhs)
     rhs, rhs_colmajor, ld_rhs = _dense_layout(rhs)
     pairs = _use_pairs("tiles", row_indices, column_indices, N // BLOCK)
+    if pairs == 0 and (PAIR_MODE == "3" or (PAIR_MODE == "auto" and out.shape[0] >= SDD_ROW_MIN_BLOCKS)):
+        pairs = 3            # two blocks of a block row per 128x256 tile
     with _lib.on_device(out.device):
         rc = _lib.load().stk_b200_sdd(
             _lib.ptr(lhs), _lib.ptr(rhs), _lib.ptr(out), _lib.ptr(offsets), _lib.ptr(row_indices),

@@ -37,7 +37,7 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
   if (nnz == 0) return STK_OK;
   if (out == nullptr || row_indices == nullptr || column_indices == nullptr)
     return STK_ERR_NULL_POINTER;
-  if (pair_mode && offsets == nullptr) return STK_ERR_NULL_POINTER;
+  if (pair_mode && pair_mode != 3 && offsets == nullptr) return STK_ERR_NULL_POINTER;
   if (!aligned16(out)) return STK_ERR_BAD_LAYOUT;
   if ((rc = check_dense(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) return rc;
   if ((rc = check_dense(rhs, ld_rhs, rhs_colmajor ? K : N)) != STK_OK) return rc;
@@ -52,6 +52,23 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
   CUtensorMap tmC;  // the output blocks as one [nnz*128, 128] matrix, stored 128 x 64 at a time
   if ((rc = encode_map(&tmC, out, dtype, kBlk, nnz * kBlk, kBlk, kBlk)) != STK_OK) return rc;
 
+  if (pair_mode == 3) {  // two blocks of a block row per tile
+    BsmmParams p{};
+    p.mode = kModeSDD;
+    p.a_mn = lhs_colmajor ? 1 : 0;
+    p.b_mn = rhs_colmajor ? 0 : 1;
+    p.fmt = dtype;
+    p.epilogue = epilogue;
+    p.num_tiles = static_cast<int>((nnz + 1) / 2);
+    p.tiles_inner = 1;
+    p.k_steps = k_steps;
+    p.row_idx = row_indices;
+    p.col_idx = column_indices;
+    p.out = out;
+    p.ldc = kBlk;
+    p.nnz = static_cast<int>(nnz);
+    return launch_row(tmA, tmB, tmC, p, s);
+  }
   if (pair_mode) {
     PairDeviceInfo* d = nullptr;
     if ((rc = pair_device_info(&d)) != STK_OK) return rc;

@@ -262,6 +262,227 @@ bsmm_row_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (threadIdx.x == 0 && *abort_flag != 0) report_status(STK_ERR_DEVICE_TIMEOUT);
 }
 
+// SDD on the same tile shape: two blocks of one block row share the row's lhs panel, their two rhs
+// panels sit side by side as the N = 256 operand, and the two halves of the accumulator go to the two
+// blocks.  Work item i = blocks 2i and 2i + 1 of the (row-major) block list: one tile if they lie in
+// the same block row, else one half-used tile for each (a static enumeration, no prefix sums; a block
+// row of L blocks wastes at most one half tile).  Reference semantics: _sdd_kernel,
+// stk/backend/triton_kernels.py:34-68.
+struct RowSddItem {
+  int tiles;       // 1 or 2
+  int row[2];      // block row of each tile
+  int col[2][2];   // block columns of each tile's halves (second half: -1 if unused)
+  int blk[2][2];   // where each half goes in the output
+};
+__device__ __forceinline__ RowSddItem row_sdd_item(const BsmmParams& p, int item) {
+  RowSddItem it;
+  const int j0 = 2 * item, j1 = 2 * item + 1;
+  const int r0 = p.row_idx[j0], c0 = p.col_idx[j0];
+  it.tiles = 1;
+  it.row[0] = r0;
+  it.col[0][0] = c0;
+  it.blk[0][0] = j0;
+  it.col[0][1] = it.blk[0][1] = -1;
+  it.row[1] = 0;
+  it.col[1][0] = it.col[1][1] = it.blk[1][0] = it.blk[1][1] = -1;
+  if (j1 < p.nnz) {
+    const int r1 = p.row_idx[j1], c1 = p.col_idx[j1];
+    if (r1 == r0) {
+      it.col[0][1] = c1;
+      it.blk[0][1] = j1;
+    } else {
+      it.tiles = 2;
+      it.row[1] = r1;
+      it.col[1][0] = c1;
+      it.blk[1][0] = j1;
+    }
+  }
+  return it;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+bsmm_row_sdd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmC, const BsmmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  const uint32_t smem_base = smem_u32(smem);
+
+  const uint32_t staging = smem_base + kRStages * kRStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kRStages * kRStageBytes + kOutStageBytes);
+  const uint32_t bars_base = staging + kOutStageBytes;
+  auto full_bar = [&](int s) { return bars_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bars_base + 8u * (kRStages + s); };
+  auto tfull_bar = [&](int a) { return bars_base + 8u * (2 * kRStages + a); };
+  auto tempty_bar = [&](int a) { return bars_base + 8u * (2 * kRStages + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kRNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* epilogue_go = abort_flag + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kRStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmC);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kRTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < p.num_tiles && ok; item += gridDim.x) {
+        const RowSddItem it = row_sdd_item(p, item);
+        for (int t = 0; t < it.tiles && ok; ++t) {
+          const bool both = it.col[t][1] >= 0;
+          for (int ks = 0; ks < p.k_steps && ok; ++ks) {
+            ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
+            if (!ok) break;
+            const uint32_t a_dst = smem_base + stage * kRStageBytes;
+            // an unused second half is not fetched: its accumulator columns are never stored
+            mbar_arrive_expect_tx(full_bar(stage), (both ? 3 : 2) * kOperandTileBytes);
+            load_operand(&tmA, a_dst, full_bar(stage), p.a_mn, it.row[t] * kBlk, ks * kBK);
+            load_operand(&tmB, a_dst + kOperandTileBytes, full_bar(stage), p.b_mn, it.col[t][0] * kBlk,
+                         ks * kBK);
+            if (both)
+              load_operand(&tmB, a_dst + 2 * kOperandTileBytes, full_bar(stage), p.b_mn,
+                           it.col[t][1] * kBlk, ks * kBK);
+            if (++stage == kRStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(p.fmt, p.a_mn, p.b_mn, 2 * kBlk);
+      const uint32_t a_lo0 = smem_desc_lo(smem_base, p.a_mn ? kOperandTileBytes / 2 : 16u);
+      const uint32_t b_lo0 = smem_desc_lo(smem_base + kOperandTileBytes, p.b_mn ? kOperandTileBytes / 2 : 16u);
+      const uint32_t a_kstep = (p.a_mn ? kUmmaK * 128u : kUmmaK * 2u) >> 4;
+      const uint32_t b_kstep = (p.b_mn ? kUmmaK * 128u : kUmmaK * 2u) >> 4;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      bool ready = false;  // the next stage's barrier is probed between the MMAs of the current one
+      // tiles of an item: 2 iff its two blocks lie in different block rows (fetched one item ahead)
+      auto tiles_of = [&](int item) {
+        const int j1 = 2 * item + 1;
+        return (j1 < p.nnz && p.row_idx[j1] != p.row_idx[j1 - 1]) ? 2 : 1;
+      };
+      int tiles_next = static_cast<int>(blockIdx.x) < p.num_tiles ? tiles_of(blockIdx.x) : 0;
+      for (int item = blockIdx.x; item < p.num_tiles && ok; item += gridDim.x) {
+        const int tiles = tiles_next;
+        if (item + static_cast<int>(gridDim.x) < p.num_tiles) tiles_next = tiles_of(item + gridDim.x);
+        for (int t = 0; t < tiles && ok; ++t) {
+          ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag);
+          if (!ok) break;
+          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * 2 * kBlk);
+          uint32_t accumulate = 0;
+          for (int ks = 0; ks < p.k_steps; ++ks) {
+            if (!ready) {
+              ok = mbar_wait(full_bar(stage), phase, abort_flag);
+              if (!ok) break;
+            }
+            tc_fence_after();
+            const uint32_t a_lo = a_lo0 + stage * (kRStageBytes >> 4);
+            const uint32_t b_lo = b_lo0 + stage * (kRStageBytes >> 4);
+            const int next_stage = stage + 1 == kRStages ? 0 : stage + 1;
+            const uint32_t next_phase = stage + 1 == kRStages ? phase ^ 1u : phase;
+            umma_f16(d_tmem, smem_desc_join(a_lo), smem_desc_join(b_lo), idesc, accumulate);
+            umma_f16(d_tmem, smem_desc_join(a_lo + a_kstep), smem_desc_join(b_lo + b_kstep), idesc, 1u);
+            ready = mbar_test_wait(full_bar(next_stage), next_phase);
+            umma_f16(d_tmem, smem_desc_join(a_lo + 2 * a_kstep), smem_desc_join(b_lo + 2 * b_kstep), idesc, 1u);
+            umma_f16(d_tmem, smem_desc_join(a_lo + 3 * a_kstep), smem_desc_join(b_lo + 3 * b_kstep), idesc, 1u);
+            accumulate = 1u;
+            umma_commit(empty_bar(stage));
+            stage = next_stage;
+            phase = next_phase;
+          }
+          if (!ok) break;
+          umma_commit(tfull_bar(acc));
+          acc ^= 1;
+          if (acc == 0) acc_phase ^= 1u;
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const bool issuer = threadIdx.x == 64;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < p.num_tiles && ok; item += gridDim.x) {
+      const RowSddItem it = row_sdd_item(p, item);
+      for (int t = 0; t < it.tiles && ok; ++t) {
+        mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+        epilogue_sync(0);
+        if (issuer) *epilogue_go = (*abort_flag == 0) ? 1 : 0;
+        epilogue_sync(0);
+        ok = *epilogue_go != 0;
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                static_cast<uint32_t>(acc * 2 * kBlk);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (it.blk[t][h] >= 0)
+            drain_to_output(t_addr, h * kBlk, kBlk, p.fmt, p.epilogue, &tmC, 0, it.blk[t][h] * kBlk,
+                            staging, row, 0, 0, 1, issuer);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+    if (issuer) tma_store_wait_all<0>();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag != 0) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kRTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0) report_status(STK_ERR_DEVICE_TIMEOUT);
+}
+
 static int launch_row(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                       const BsmmParams& p, cudaStream_t stream) {
   DeviceInfo* d = nullptr;
@@ -272,6 +493,8 @@ static int launch_row(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUte
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return STK_ERR_LAUNCH;
   if (!opted_in[dev]) {
     if (cudaFuncSetAttribute(bsmm_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kRSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(bsmm_row_sdd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kRSmemBytes) != cudaSuccess) {
       cudaGetLastError();
       return STK_ERR_LAUNCH;
@@ -279,7 +502,10 @@ static int launch_row(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUte
     opted_in[dev] = true;
   }
   const int grid = p.num_tiles < d->sms ? p.num_tiles : d->sms;
-  bsmm_row_kernel<<<grid, kThreads, kRSmemBytes, stream>>>(tmA, tmB, tmC, p);
+  if (p.mode == kModeSDD)
+    bsmm_row_sdd_kernel<<<grid, kThreads, kRSmemBytes, stream>>>(tmA, tmB, tmC, p);
+  else
+    bsmm_row_kernel<<<grid, kThreads, kRSmemBytes, stream>>>(tmA, tmB, tmC, p);
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 

@@ -93,6 +93,7 @@ struct BsmmParams {
   long long ldc;            // DSD/DDS: leading dimension of out in elements
   int out_cols;             // row kernel (bsmm_row_sm100.cuh), DSD: dense columns of the output
   int out_rows;             // row kernel, DDS: dense rows of the output
+  int nnz;                  // row kernel, SDD: number of blocks
 };
 
 struct TileInfo {
