@@ -102,7 +102,28 @@ def config4(dev="cuda"):
         _report("dds  a @ s^T", flops, lambda: stk.ops.dds(a, s.t()), lambda: a @ bd)
 
 
+def single(density=0.25, dev="cuda"):
+    """A few launches of s @ b and a @ s on one random topology, kernel chosen by STK_B200_PAIR_MODE:
+    the small case for a profiler capture (python -m stk_b200.benchmarks single 0.25)."""
+    M = N = K = 8192
+    dtype = torch.bfloat16
+    np.random.seed(0)
+    topo = stk.random.mask(M, N, 1 - density, 128).to(dev)
+    nnz = topo.data.shape[0]
+    s = stk.Matrix(topo.size(), torch.randn(nnz, 128, 128, device=dev).to(dtype), topo.row_indices,
+                   topo.column_indices, topo.offsets, topo.column_indices_t, topo.offsets_t, topo.block_offsets_t)
+    a, b = torch.randn(M, K, device=dev).to(dtype), torch.randn(K, N, device=dev).to(dtype)
+    flops = 2.0 * nnz * 128 * 128 * K
+    for name, fn in (("dsd s @ b", lambda: stk.ops.dsd(s, b)), ("dds a @ s", lambda: stk.ops.dds(a, s)),
+                     ("sdd a @ b", lambda: stk.ops.sdd(a, b, s))):
+        ms = _time_ms(fn, iters=3, warm=2)
+        print(f"{name}: {nnz} blocks, mode {kernels.PAIR_MODE}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.0f} TFLOP/s")
+
+
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "c3"
     with torch.no_grad():
-        {"c3": config3, "c4": config4}[which]()
+        if which == "single":
+            single(float(sys.argv[2]) if len(sys.argv) > 2 else 0.25)
+        else:
+            {"c3": config3, "c4": config4}[which]()
