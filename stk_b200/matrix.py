@@ -127,6 +127,14 @@ class Matrix(torch.nn.Module):
                          self._offsets)
 
     def to(self, device):
+        """Moves every tensor to `device` (reference: stk/matrix.py:178-185).  A floating dtype (an
+        extension; the reference leaves it as a TODO) converts the values only - the metadata keeps
+        its integer types."""
+        if isinstance(device, torch.dtype):
+            if device not in (torch.float16, torch.bfloat16):
+                raise ValueError(f"Expected float16 or bfloat16 data. Got {device}.")
+            self._data = self._data.to(device)
+            return self
         for name in ("_data", "_row_indices", "_column_indices", "_offsets", "_column_indices_t",
                      "_offsets_t", "_block_offsets_t"):
             setattr(self, name, getattr(self, name).to(device))

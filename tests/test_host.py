@@ -85,6 +85,11 @@ def test_matrix_api_mirrors_reference():
         m.contiguous()
     c = m.clone()
     assert c.data.data_ptr() != m.data.data_ptr() and torch.equal(c.offsets_t, m.offsets_t)
+    b = m.clone().to(torch.bfloat16)                        # values converted, metadata untouched
+    assert b.dtype == torch.bfloat16 and b.row_indices.dtype == torch.int16 and b.offsets.dtype == torch.int32
+    b.validate()
+    with pytest.raises(ValueError):
+        m.clone().to(torch.float32)
     v = m.view(2, 512, 1024)
     assert v.dim() == 3 and v.size() == (2, 512, 1024)
     with pytest.raises(ValueError):
