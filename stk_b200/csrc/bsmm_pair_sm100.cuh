@@ -1,22 +1,24 @@
 // Block-sparse matmul on CTA PAIRS (tcgen05 cta_group::2): 256x256 output supertiles.
 //
 // Why: the kernel in bsmm_sm100.cuh computes one 128x128 tile per CTA and has to pull 32 KiB of
-// operands through L2 for every 128x128x64 of MMA work (64 FLOP/B); measured on B200 it saturates
-// the L2->SM fabric at ~11.7 TB/s and stops at ~45 % of the tensor peak.  A pair of CTAs that
-// shares one 256-row MMA needs the same 32 KiB per CTA for twice the work (128 FLOP/B): each CTA
-// loads its own 128 rows of A and its own 128 columns of B, the hardware reads both halves.
+// operands through shared memory for every 128x128x64 of MMA work (64 FLOP/B); TMA writes into
+// shared memory and the tensor pipe's reads out of it share its bandwidth, and measured on B200
+// that kernel keeps the tensor pipe busy about a third of the time.  A pair of CTAs that shares
+// one 256-row MMA needs the same 32 KiB per CTA for twice the work (128 FLOP/B): each CTA loads
+// its own 128 rows of A and its own 128 columns of B, the hardware reads both halves.
 //
 // A supertile needs two A row-blocks that walk the SAME K sequence and two B column-blocks:
 //
-//   DSD  rows (2t, 2t+1) of op(S)  x  256 columns of the dense operand.  The K sequence is the MERGE of
+//   DSD  rows (r, r+1) of op(S)  x  256 columns of the dense operand.  The K sequence is the MERGE of
 //        the two block rows' column lists; where a row has no block at a K position its A tile is
 //        fetched from an out-of-range TMA coordinate, which yields zeros.
 //   DDS  256 rows of the dense operand  x  block columns (2t, 2t+1) of op(S), K = merge of their lists.
-//   SDD  block rows (2t, 2t+1)  x  block columns (2u, 2u+1); the four blocks that exist are stored.
+//   SDD  block rows (r, r+1)  x  block columns (2u, 2u+1); the four blocks that exist are stored.
+//   Which rows pair up is decided per launch (see decode_item): runs of rows cut at expert boundaries.
 //
 // Results are exact for ANY sorted topology; the layout only pays off when neighbouring block
 // rows / columns share most of their lists (dMoE topologies do: all rows of one expert are alike).
-// The host picks this kernel or the 128x128 kernel per call.
+// The host picks this kernel, the 128x256 row kernel or the 128x128 kernel per call.
 //
 // Roles per CTA (352 threads): warp 0 = TMA producer of the A tiles, warp 6 = TMA producer of the B
 // tiles, warp 1 = TMEM owner (and, in the leader CTA, the MMA issuer), warps 2..5 and 7..10 = two

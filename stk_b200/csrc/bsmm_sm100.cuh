@@ -17,8 +17,8 @@
 // different tensor map plus the "MN-major" bit of the instruction / shared-memory descriptors.
 //
 // Warp roles (192 threads): warp 0 = TMA producer (also walks the metadata), warp 1 = MMA issuer and
-// TMEM owner, warps 2..5 = epilogue (TMEM -> registers -> 16-bit -> global).  Two TMEM accumulators
-// let the epilogue of tile t overlap the main loop of tile t+1.
+// TMEM owner, warps 2..5 = epilogue (TMEM -> registers -> 16-bit -> swizzled staging tile -> TMA
+// store).  Two TMEM accumulators let the epilogue of tile t overlap the main loop of tile t+1.
 //
 // The semantics follow stk/backend/triton_kernels.py of the reference (_sdd_kernel :34-68,
 // _dsd_kernel :83-145, _dds_kernel :160-220 and their launchers :222-379).
