@@ -39,6 +39,8 @@ extern "C" {
 /* epilogue of stk_b200_sdd */
 #define STK_EPILOGUE_NONE 0
 #define STK_EPILOGUE_GELU 1
+#define STK_EPILOGUE_GELU_KEEP 2
+#define STK_EPILOGUE_GELU_GRAD 3
 
 /* status codes */
 #define STK_OK 0
@@ -89,18 +91,24 @@ int stk_b200_device_status(int* status_host);
  *        column-major (lhs_colmajor=1, element (m,k) at k*ld_lhs+m - an exact .t() view).
  *   rhs: logical [K,N]; same convention with ld_rhs.
  *   out: [nnz,128,128] contiguous.
- *   offsets: CSR offsets [M/128+1]; only read when pair_mode = 1 (may be NULL otherwise).
+ *   offsets: CSR offsets [M/128+1]; only read when pair_mode = 1 or 2 (may be NULL otherwise).
  *   epilogue: 0 stores the product; 1 (STK_EPILOGUE_GELU) stores GeLU(product), the exact erf form
  *             applied to the fp32 accumulator before rounding - the step between SDD and DSD in a
  *             dMoE layer, fused so that the hidden activations are written once.  The reference
  *             has no fused form (it runs a separate elementwise kernel on Matrix.data).
+ *             2 (STK_EPILOGUE_GELU_KEEP) stores the product in `out` AND GeLU(product) in `aux`
+ *             (a training step keeps the pre-activations for the backward pass).
+ *             3 (STK_EPILOGUE_GELU_GRAD) stores product * GeLU'(aux), `aux` holding pre-activations:
+ *             the backward of GeLU fused into the product dy @ w2^T that yields the gradient of
+ *             the activations.
+ *   aux: [nnz,128,128] contiguous like out, written (2) or read (3); NULL for epilogue 0 / 1.
  * nnz == 0 is a no-op.
  */
 int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const int32_t* offsets,
                  const int16_t* row_indices, const int16_t* column_indices,
                  int64_t M, int64_t N, int64_t K, int64_t nnz,
                  int lhs_colmajor, int64_t ld_lhs, int rhs_colmajor, int64_t ld_rhs,
-                 int dtype, int pair_mode, int epilogue, void* stream);
+                 int dtype, int pair_mode, int epilogue, void* aux, void* stream);
 
 /*
  * DSD: out[M,N] = op(S)[M,K] @ rhs[K,N].

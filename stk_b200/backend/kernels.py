@@ -194,10 +194,18 @@ def dds(lhs, shape, data, offsets, row_indices, column_indices, offsets_t, colum
     _lib.check(rc, "stk_b200_dds")
 
 
-def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices, epilogue=0):
-    """out[p] = (lhs @ rhs)[block p] for the blocks listed by row_indices / column_indices;
-    epilogue=1 stores GeLU of the product instead (an extension, see stk_b200.ops.sdd_gelu)."""
+def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices, epilogue=0, aux=None):
+    """out[p] = (lhs @ rhs)[block p] for the blocks listed by row_indices / column_indices.
+    Extensions: epilogue=1 stores GeLU of the product instead (stk_b200.ops.sdd_gelu); epilogue=2
+    stores the product in out and its GeLU in aux; epilogue=3 stores product * GeLU'(aux)
+    (stk_b200.dmoe.expert_mlp).  aux has out's shape and dtype."""
     _require_cuda(lhs, rhs, out)
+    if (epilogue in (2, 3)) != (aux is not None):
+        raise ValueError("epilogues 2 and 3 take an auxiliary tensor, the others do not")
+    if aux is not None:
+        _require_cuda(aux)
+        if aux.shape != out.shape or aux.dtype != out.dtype or not aux.is_contiguous():
+            raise ValueError("aux must be contiguous with out's shape and dtype")
     if lhs.shape[1] != rhs.shape[0]:
         raise DimensionError("incompatible dimensions")
     M, K = lhs.shape
@@ -213,7 +221,7 @@ def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices, epilogue=0):
         rc = _lib.load().stk_b200_sdd(
             _lib.ptr(lhs), _lib.ptr(rhs), _lib.ptr(out), _lib.ptr(offsets), _lib.ptr(row_indices),
             _lib.ptr(column_indices), M, N, K, out.shape[0], lhs_colmajor, ld_lhs, rhs_colmajor,
-            ld_rhs, _lib.dtype_code(out.dtype), pairs, epilogue, _lib.stream_ptr(out.device))
+            ld_rhs, _lib.dtype_code(out.dtype), pairs, epilogue, _lib.ptr(aux), _lib.stream_ptr(out.device))
     _lib.check(rc, "stk_b200_sdd")
 
 

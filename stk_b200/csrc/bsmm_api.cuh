@@ -30,10 +30,13 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
                             const int16_t* row_indices, const int16_t* column_indices, int64_t M,
                             int64_t N, int64_t K, int64_t nnz, int lhs_colmajor, int64_t ld_lhs,
                             int rhs_colmajor, int64_t ld_rhs, int dtype, int pair_mode,
-                            int epilogue, void* stream) {
+                            int epilogue, void* aux, void* stream) {
   int rc = check_dtype_dims(dtype, M, N, K, nnz, 32);
   if (rc != STK_OK) return rc;
-  if (epilogue != kEpilogueNone && epilogue != kEpilogueGelu) return STK_ERR_BAD_DIMS;
+  if (epilogue < kEpilogueNone || epilogue > kEpilogueGeluGrad) return STK_ERR_BAD_DIMS;
+  const bool has_aux = epilogue == kEpilogueGeluKeep || epilogue == kEpilogueGeluGrad;
+  if (has_aux && nnz != 0 && aux == nullptr) return STK_ERR_NULL_POINTER;
+  if (has_aux && !aligned16(aux)) return STK_ERR_BAD_LAYOUT;
   if (nnz == 0) return STK_OK;
   if (out == nullptr || row_indices == nullptr || column_indices == nullptr)
     return STK_ERR_NULL_POINTER;
@@ -51,6 +54,8 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   CUtensorMap tmC;  // the output blocks as one [nnz*128, 128] matrix, stored 128 x 64 at a time
   if ((rc = encode_map(&tmC, out, dtype, kBlk, nnz * kBlk, kBlk, kBlk)) != STK_OK) return rc;
+  CUtensorMap tmX = tmC;  // the auxiliary tensor has the layout of out
+  if (has_aux && (rc = encode_map(&tmX, aux, dtype, kBlk, nnz * kBlk, kBlk, kBlk)) != STK_OK) return rc;
 
   if (pair_mode == 3) {  // two blocks of a block row per tile
     BsmmParams p{};
@@ -67,7 +72,8 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
     p.out = out;
     p.ldc = kBlk;
     p.nnz = static_cast<int>(nnz);
-    return launch_row(tmA, tmB, tmC, p, s);
+    p.aux = aux;
+    return launch_row(tmA, tmB, tmC, tmX, p, s);
   }
   if (pair_mode) {
     PairDeviceInfo* d = nullptr;
@@ -96,7 +102,8 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
     p.offsets = offsets;
     p.out = out;
     p.ldc = kBlk;
-    return launch_pair(tmA, tmB, tmC, p, s);
+    p.aux = aux;
+    return launch_pair(tmA, tmB, tmC, tmX, p, s);
   }
 
   BsmmParams p{};
@@ -112,7 +119,8 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
   p.col_idx = column_indices;
   p.out = out;
   p.ldc = kBlk;
-  return launch(tmA, tmB, tmC, p, s);
+  p.aux = aux;
+  return launch(tmA, tmB, tmC, tmX, p, s);
 }
 
 extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int16_t* column_indices,
@@ -155,7 +163,7 @@ extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int1
     p.out = out;
     p.ldc = ld_out;
     p.out_cols = static_cast<int>(N);
-    return launch_row(tmA, tmB, tmC, p, s);
+    return launch_row(tmA, tmB, tmC, tmC, p, s);
   }
   if (pair_mode) {
     PairParams p{};
@@ -175,7 +183,7 @@ extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int1
     p.blk_idx = block_offsets;
     p.out = out;
     p.ldc = ld_out;
-    return pair_mode == 2 ? launch_wide(tmA, tmB, tmC, p, s) : launch_pair(tmA, tmB, tmC, p, s);
+    return pair_mode == 2 ? launch_wide(tmA, tmB, tmC, p, s) : launch_pair(tmA, tmB, tmC, tmC, p, s);
   }
 
   BsmmParams p{};
@@ -190,7 +198,7 @@ extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int1
   p.blk_idx = block_offsets;
   p.out = out;
   p.ldc = ld_out;
-  return launch(tmA, tmB, tmC, p, s);
+  return launch(tmA, tmB, tmC, tmC, p, s);
 }
 
 extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* offsets,
@@ -233,7 +241,7 @@ extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* of
     p.out = out;
     p.ldc = ld_out;
     p.out_rows = static_cast<int>(M);
-    return launch_row(tmA, tmB, tmC, p, s);
+    return launch_row(tmA, tmB, tmC, tmC, p, s);
   }
   if (pair_mode) {
     PairParams p{};
@@ -253,7 +261,7 @@ extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* of
     p.blk_idx = block_offsets;
     p.out = out;
     p.ldc = ld_out;
-    return pair_mode == 2 ? launch_wide(tmA, tmB, tmC, p, s) : launch_pair(tmA, tmB, tmC, p, s);
+    return pair_mode == 2 ? launch_wide(tmA, tmB, tmC, p, s) : launch_pair(tmA, tmB, tmC, tmC, p, s);
   }
 
   BsmmParams p{};
@@ -268,5 +276,5 @@ extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* of
   p.blk_idx = block_offsets;
   p.out = out;
   p.ldc = ld_out;
-  return launch(tmA, tmB, tmC, p, s);
+  return launch(tmA, tmB, tmC, tmC, p, s);
 }

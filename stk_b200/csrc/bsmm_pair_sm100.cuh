@@ -84,6 +84,7 @@ struct PairParams {
   const int32_t* blk_idx;  // nullptr: block j is data[j]
   void* out;
   long long ldc;
+  const void* aux;  // SDD with kEpilogueGeluKeep / kEpilogueGeluGrad: the auxiliary tensor
 };
 
 // Two-pointer merge of the K lists of a pair of block rows (DSD) / block columns (DDS).
@@ -235,7 +236,8 @@ __device__ __forceinline__ PairItem decode_item(int item, int inner_count, const
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1)
 bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, const PairParams p) {
+                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX,
+                 const PairParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -606,7 +608,8 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int pb = blk[rank][h];
             if (pb != kNoBlock)
               drain_to_output(t_addr, h * kBlk, kBlk, p.fmt, p.epilogue, &tmC, 0, pb * kBlk, staging,
-                              row, group, group, 2, issuer);
+                              row, group, group, 2, issuer,
+                              EpilogueAux{&tmX, static_cast<const uint16_t*>(p.aux)});
           }
 #endif
           release();
@@ -708,7 +711,7 @@ static int pair_device_info(PairDeviceInfo** out) {
 }
 
 static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
-                       const PairParams& p, cudaStream_t stream) {
+                       const CUtensorMap& tmX, const PairParams& p, cudaStream_t stream) {
   PairDeviceInfo* d = nullptr;
   const int rc = pair_device_info(&d);
   if (rc != STK_OK) return rc;
@@ -723,7 +726,7 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = kUseDependentLaunch ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, bsmm_pair_kernel, tmA, tmB, tmC, p) == cudaSuccess ? STK_OK
+  return cudaLaunchKernelEx(&cfg, bsmm_pair_kernel, tmA, tmB, tmC, tmX, p) == cudaSuccess ? STK_OK
                                                                                       : STK_ERR_LAUNCH;
 }
 

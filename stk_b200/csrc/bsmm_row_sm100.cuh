@@ -302,7 +302,8 @@ __device__ __forceinline__ RowSddItem row_sdd_item(const BsmmParams& p, int item
 
 __global__ void __launch_bounds__(kThreads, 1)
 bsmm_row_sdd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const __grid_constant__ CUtensorMap tmC, const BsmmParams p) {
+                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX,
+                    const BsmmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -457,7 +458,8 @@ bsmm_row_sdd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int h = 0; h < 2; ++h) {
           if (it.blk[t][h] >= 0)
             drain_to_output(t_addr, h * kBlk, kBlk, p.fmt, p.epilogue, &tmC, 0, it.blk[t][h] * kBlk,
-                            staging, row, 0, 0, 1, issuer);
+                            staging, row, 0, 0, 1, issuer,
+                            EpilogueAux{&tmX, static_cast<const uint16_t*>(p.aux)});
         }
         tc_fence_before();
         __syncwarp();
@@ -484,7 +486,7 @@ bsmm_row_sdd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 }
 
 static int launch_row(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
-                      const BsmmParams& p, cudaStream_t stream) {
+                      const CUtensorMap& tmX, const BsmmParams& p, cudaStream_t stream) {
   DeviceInfo* d = nullptr;
   const int rc = device_info(&d);
   if (rc != STK_OK) return rc;
@@ -503,7 +505,7 @@ static int launch_row(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUte
   }
   const int grid = p.num_tiles < d->sms ? p.num_tiles : d->sms;
   if (p.mode == kModeSDD)
-    bsmm_row_sdd_kernel<<<grid, kThreads, kRSmemBytes, stream>>>(tmA, tmB, tmC, p);
+    bsmm_row_sdd_kernel<<<grid, kThreads, kRSmemBytes, stream>>>(tmA, tmB, tmC, tmX, p);
   else
     bsmm_row_kernel<<<grid, kThreads, kRSmemBytes, stream>>>(tmA, tmB, tmC, p);
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;

@@ -51,7 +51,11 @@ constexpr int kSmemBytes =
 enum : int { kModeSDD = 0, kModeDSD = 1, kModeDDS = 2 };
 
 // Optional activation applied to the fp32 accumulator before it is rounded and stored.
-enum : int { kEpilogueNone = 0, kEpilogueGelu = 1 };
+// kEpilogueGeluKeep: `out` gets the product itself and the auxiliary tensor GeLU of it (a training
+// step needs both).  kEpilogueGeluGrad: `out` = product * GeLU'(auxiliary tensor), the auxiliary
+// tensor holding the pre-activations (the backward of GeLU fused into the product that yields the
+// gradient of the activations).  The auxiliary tensor has the layout of `out` (SDD only).
+enum : int { kEpilogueNone = 0, kEpilogueGelu = 1, kEpilogueGeluKeep = 2, kEpilogueGeluGrad = 3 };
 
 // GeLU in its exact form x * Phi(x) (torch.nn.functional.gelu's default), written as
 //   gelu(x) = max(x, 0) - |x| * Phi(-|x|),   Phi(-a) = 2^(-q(a)),
@@ -76,6 +80,29 @@ __device__ __forceinline__ float gelu_erf(float x) {
   return fmaf(-a, h, fmaxf(x, 0.0f));
 }
 
+// d/dx of the same GeLU: Phi(x) + x * phi(x), Phi from the same fit, phi(x) = 2^(-x^2 / (2 ln 2)) / sqrt(2 pi).
+__device__ __forceinline__ float gelu_erf_grad(float x) {
+  const float a = fminf(fabsf(x), 8.0f);
+  float q = fmaf(1.8287723e-06f, a, -6.149571e-05f);
+  q = fmaf(q, a, 0.00092985336f);
+  q = fmaf(q, a, -0.008505761f);
+  q = fmaf(q, a, 0.053956695f);
+  q = fmaf(q, a, 0.45846686f);
+  q = fmaf(q, a, 1.1512504f);
+  q = fmaf(q, a, 0.9999953f);
+  float h, e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(h) : "f"(-q));                       // Phi(-|x|)
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(a * a * -0.72134752044f));  // exp(-x^2 / 2)
+  const float cdf = x < 0.0f ? h : 1.0f - h;
+  return fmaf(copysignf(a, x) * 0.3989422804f, e, cdf);
+}
+
+// The auxiliary tensor of the epilogues that have one: its tensor map (stores) and its address (loads).
+struct EpilogueAux {
+  const CUtensorMap* tm;
+  const uint16_t* ptr;
+};
+
 struct BsmmParams {
   int mode;
   int a_mn;        // 1: A tile is M-contiguous in memory (transposed operand), 0: K-contiguous
@@ -94,6 +121,7 @@ struct BsmmParams {
   int out_cols;             // row kernel (bsmm_row_sm100.cuh), DSD: dense columns of the output
   int out_rows;             // row kernel, DDS: dense rows of the output
   int nnz;                  // row kernel, SDD: number of blocks
+  const void* aux;          // SDD with kEpilogueGeluKeep / kEpilogueGeluGrad: the auxiliary tensor
 };
 
 struct TileInfo {
@@ -152,13 +180,11 @@ __device__ __forceinline__ void epilogue_sync(int group) {
 // multiple of 64, starting at TMEM column `col0`) to the output: the 64-column sub-tiles `first`,
 // `first + step`, ...  `group` names the group's hardware barrier.  TMEM -> registers -> optional activation -> 16-bit -> the group's 128x64
 // staging tile in shared memory (128-byte swizzle, conflict-free 16-byte stores) -> one TMA store.
-__device__ __forceinline__ void drain_to_output(uint32_t t_addr, int col0, int ncols, int fmt,
-                                                int epilogue, const CUtensorMap* tmC, int out_x,
-                                                int out_y, uint32_t staging, int row, int group,
-                                                int first, int step, bool issuer) {
-#ifdef STK_EXP_SKIP_EPILOGUE  // experiment: main loop alone, nothing drained or stored
-  return;
-#endif
+template <int kEpi>
+__device__ __forceinline__ void drain_to_output_as(uint32_t t_addr, int col0, int ncols, int fmt,
+                                                   const CUtensorMap* tmC, int out_x, int out_y,
+                                                   uint32_t staging, int row, int group, int first,
+                                                   int step, bool issuer, EpilogueAux aux) {
   for (int c = first * 64; c < ncols; c += step * 64) {
     if (issuer) tma_store_wait_read<0>();  // the group's previous store is done reading the tile
     epilogue_sync(group);
@@ -166,47 +192,99 @@ __device__ __forceinline__ void drain_to_output(uint32_t t_addr, int col0, int n
     tmem_ld_32x32(t_addr + col0 + c, r0);
     tmem_ld_32x32(t_addr + col0 + c + 32, r1);
     tmem_ld_wait();
-    uint32_t packed[32];
+    if constexpr (kEpi == kEpilogueGeluGrad) {
+      // this thread's 64 pre-activations: 128 contiguous bytes of the auxiliary tensor (SDD: rows of 128)
+      const uint4* src = reinterpret_cast<const uint4*>(
+          aux.ptr + (static_cast<long long>(out_y) + row) * kBlk + out_x + c);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float a0 = __uint_as_float(r0[2 * i]), a1 = __uint_as_float(r0[2 * i + 1]);
-      float b0 = __uint_as_float(r1[2 * i]), b1 = __uint_as_float(r1[2 * i + 1]);
-      if (epilogue == kEpilogueGelu) {
-        a0 = gelu_erf(a0);
-        a1 = gelu_erf(a1);
-        b0 = gelu_erf(b0);
-        b1 = gelu_erf(b1);
-      }
-      if (fmt == STK_BF16) {
-        const __nv_bfloat162 va = __floats2bfloat162_rn(a0, a1), vb = __floats2bfloat162_rn(b0, b1);
-        packed[i] = *reinterpret_cast<const uint32_t*>(&va);
-        packed[16 + i] = *reinterpret_cast<const uint32_t*>(&vb);
-      } else {
-        const __half2 va = __floats2half2_rn(a0, a1), vb = __floats2half2_rn(b0, b1);
-        packed[i] = *reinterpret_cast<const uint32_t*>(&va);
-        packed[16 + i] = *reinterpret_cast<const uint32_t*>(&vb);
+      for (int v = 0; v < 8; ++v) {
+        const uint4 w = __ldg(src + v);
+        const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float2 pre;
+          if (fmt == STK_BF16) pre = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&words[k]));
+          else pre = __half22float2(*reinterpret_cast<const __half2*>(&words[k]));
+          const int e = v * 8 + k * 2;  // element index 0..63 within the sub-tile
+          uint32_t* r = e < 32 ? r0 : r1;
+          const int o = e & 31;
+          r[o] = __float_as_uint(__uint_as_float(r[o]) * gelu_erf_grad(pre.x));
+          r[o + 1] = __float_as_uint(__uint_as_float(r[o + 1]) * gelu_erf_grad(pre.y));
+        }
       }
     }
-    const uint32_t row_addr = staging + row * 128;
+    // one pass per output tensor: kEpilogueGeluKeep stores the product, then its activation
+    constexpr int kPasses = kEpi == kEpilogueGeluKeep ? 2 : 1;
 #pragma unroll
-    for (int ch = 0; ch < 8; ++ch) {
-      const uint32_t addr = row_addr + ((ch ^ (row & 7)) << 4);
-      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * ch]),
-                   "r"(packed[4 * ch + 1]), "r"(packed[4 * ch + 2]), "r"(packed[4 * ch + 3])
-                   : "memory");
-    }
-    fence_proxy_async_smem();
-    epilogue_sync(group);
-    if (issuer) {
-      tma_store_2d(tmC, staging, out_x + c, out_y);
-      tma_store_commit();
+    for (int pass = 0; pass < kPasses; ++pass) {
+      const bool activate = kEpi == kEpilogueGelu || pass == 1;
+      if (pass == 1) {
+        if (issuer) tma_store_wait_read<0>();
+        epilogue_sync(group);
+      }
+      uint32_t packed[32];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float a0 = __uint_as_float(r0[2 * i]), a1 = __uint_as_float(r0[2 * i + 1]);
+        float b0 = __uint_as_float(r1[2 * i]), b1 = __uint_as_float(r1[2 * i + 1]);
+        if (activate) {
+          a0 = gelu_erf(a0);
+          a1 = gelu_erf(a1);
+          b0 = gelu_erf(b0);
+          b1 = gelu_erf(b1);
+        }
+        if (fmt == STK_BF16) {
+          const __nv_bfloat162 va = __floats2bfloat162_rn(a0, a1), vb = __floats2bfloat162_rn(b0, b1);
+          packed[i] = *reinterpret_cast<const uint32_t*>(&va);
+          packed[16 + i] = *reinterpret_cast<const uint32_t*>(&vb);
+        } else {
+          const __half2 va = __floats2half2_rn(a0, a1), vb = __floats2half2_rn(b0, b1);
+          packed[i] = *reinterpret_cast<const uint32_t*>(&va);
+          packed[16 + i] = *reinterpret_cast<const uint32_t*>(&vb);
+        }
+      }
+      const uint32_t row_addr = staging + row * 128;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        const uint32_t addr = row_addr + ((ch ^ (row & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * ch]),
+                     "r"(packed[4 * ch + 1]), "r"(packed[4 * ch + 2]), "r"(packed[4 * ch + 3])
+                     : "memory");
+      }
+      fence_proxy_async_smem();
+      epilogue_sync(group);
+      if (issuer) {
+        tma_store_2d(pass == 1 ? aux.tm : tmC, staging, out_x + c, out_y);
+        tma_store_commit();
+      }
     }
   }
 }
 
+__device__ __forceinline__ void drain_to_output(uint32_t t_addr, int col0, int ncols, int fmt,
+                                                int epilogue, const CUtensorMap* tmC, int out_x,
+                                                int out_y, uint32_t staging, int row, int group,
+                                                int first, int step, bool issuer,
+                                                EpilogueAux aux = EpilogueAux{nullptr, nullptr}) {
+#ifdef STK_EXP_SKIP_EPILOGUE  // experiment: main loop alone, nothing drained or stored
+  return;
+#endif
+  // the epilogue kind is a compile-time parameter of the body: the plain and GeLU forms keep their
+  // short code whatever the two training forms need
+  if (epilogue == kEpilogueNone)
+    drain_to_output_as<kEpilogueNone>(t_addr, col0, ncols, fmt, tmC, out_x, out_y, staging, row, group, first, step, issuer, aux);
+  else if (epilogue == kEpilogueGelu)
+    drain_to_output_as<kEpilogueGelu>(t_addr, col0, ncols, fmt, tmC, out_x, out_y, staging, row, group, first, step, issuer, aux);
+  else if (epilogue == kEpilogueGeluKeep)
+    drain_to_output_as<kEpilogueGeluKeep>(t_addr, col0, ncols, fmt, tmC, out_x, out_y, staging, row, group, first, step, issuer, aux);
+  else
+    drain_to_output_as<kEpilogueGeluGrad>(t_addr, col0, ncols, fmt, tmC, out_x, out_y, staging, row, group, first, step, issuer, aux);
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const __grid_constant__ CUtensorMap tmC, const BsmmParams p) {
+            const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX,
+            const BsmmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -412,7 +490,7 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       // TMEM -> registers -> 16-bit -> swizzled staging tile -> TMA store, 64 columns at a time
       if (p.mode == kModeSDD)
         drain_to_output(t_addr, 0, kBlk, p.fmt, p.epilogue, &tmC, 0, tile * kBlk, staging, row, 0, 0,
-                        1, issuer);
+                        1, issuer, EpilogueAux{&tmX, static_cast<const uint16_t*>(p.aux)});
       else
         drain_to_output(t_addr, 0, kBlk, p.fmt, p.epilogue, &tmC, t.tn * kBlk, t.tm * kBlk, staging,
                         row, 0, 0, 1, issuer);
@@ -540,13 +618,14 @@ static int device_info(DeviceInfo** out) {
   return STK_OK;
 }
 
+// tmX: tensor map of the auxiliary tensor of the SDD epilogues that have one (else any valid map).
 static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
-                  const BsmmParams& p, cudaStream_t stream) {
+                  const CUtensorMap& tmX, const BsmmParams& p, cudaStream_t stream) {
   DeviceInfo* d = nullptr;
   const int rc = device_info(&d);
   if (rc != STK_OK) return rc;
   const int grid = p.num_tiles < d->sms ? p.num_tiles : d->sms;
-  bsmm_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmC, p);
+  bsmm_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmC, tmX, p);
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 

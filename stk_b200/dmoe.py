@@ -476,3 +476,57 @@ class HostPipeline:
         for slot in range(2):
             if self.results[slot] is host_result and self.out_ready[slot] is not None:
                 self.out_ready[slot].synchronize()
+
+
+# ------------------------------------------------------------------------------ the experts' MLP, fused
+class _ExpertMLP(torch.autograd.Function):
+    """y = dsd(GeLU(sdd(x, w1, topo)), w2) with both element-wise steps inside the products'
+    epilogues: the forward SDD writes the pre-activations and their GeLU in one pass, and the
+    backward SDD (dy @ w2^T on the topology) multiplies by GeLU'(pre-activations) before it stores,
+    so the hidden-size tensors are never read or written by an element-wise kernel."""
+
+    @staticmethod
+    def forward(ctx, x, w1, w2, shape, offsets, row_indices, column_indices, offsets_t,
+                column_indices_t, block_offsets_t):
+        meta = (offsets, row_indices, column_indices, offsets_t, column_indices_t, block_offsets_t)
+        nnz = row_indices.numel()
+        pre = torch.empty((nnz, BLOCK, BLOCK), dtype=x.dtype, device=x.device)
+        act = torch.empty_like(pre)
+        _kernels.sdd(x, w1, shape, pre, offsets, row_indices, column_indices, epilogue=2, aux=act)
+        y = torch.empty((shape[0], w2.shape[1]), dtype=x.dtype, device=x.device)
+        _kernels.dsd(shape, act, *meta, False, w2, y)
+        ctx.save_for_backward(x, w1, w2, pre, act, *meta)
+        ctx.shape = tuple(shape)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w1, w2, pre, act = ctx.saved_tensors[:5]
+        meta = ctx.saved_tensors[5:]
+        offsets, row_indices, column_indices = meta[:3]
+        shape = ctx.shape
+        dy = dy.contiguous()
+        dx = dw1 = dw2 = None
+        if ctx.needs_input_grad[2]:
+            dw2 = torch.empty_like(w2)                      # act^T @ dy
+            _kernels.dsd((shape[1], shape[0]), act, *meta, True, dy, dw2)
+        if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
+            d_pre = torch.empty_like(pre)                   # (dy @ w2^T) * GeLU'(pre), one kernel
+            _kernels.sdd(dy, w2.t(), shape, d_pre, offsets, row_indices, column_indices, epilogue=3, aux=pre)
+            if ctx.needs_input_grad[0]:
+                dx = torch.empty_like(x)                    # d_pre @ w1^T
+                _kernels.dsd(shape, d_pre, *meta, False, w1.t(), dx)
+            if ctx.needs_input_grad[1]:
+                dw1 = torch.empty_like(w1)                  # x^T @ d_pre
+                _kernels.dds(x.t(), shape, d_pre, *meta, False, dw1)
+        return (dx, dw1, dw2) + (None,) * 7
+
+
+def expert_mlp(x, w1, w2, topo):
+    """The experts' two-layer MLP of a dMoE layer on tokens in padded expert order:
+    y = dsd(GeLU(sdd(x, w1, topo)), w2), differentiable in x, w1 and w2, with GeLU and its
+    backward fused into the block-sparse products (see _ExpertMLP).  x [T', h], w1 [h, E*f],
+    w2 [E*f, h_out] on the GPU, fp16 or bf16; topo: the block-diagonal topology of the batch."""
+    assert isinstance(topo, Matrix) and topo.is_contiguous()
+    return _ExpertMLP.apply(x.contiguous(), w1, w2, tuple(topo.size()), topo.offsets, topo.row_indices,
+                            topo.column_indices, topo.offsets_t, topo.column_indices_t, topo.block_offsets_t)

@@ -289,6 +289,32 @@ def test_block_diagonal_topologies_with_odd_runs(stk, experts, cols_per_expert):
                          oracle.dds(right.t(), s_dense.t(), torch.float16), "dds T")
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fused_expert_mlp_matches_unfused_autograd(stk, dtype):
+    """dmoe.expert_mlp (GeLU and its backward inside the products' epilogues) against
+    sdd -> torch gelu -> dsd differentiated by autograd, forward and all three gradients."""
+    from stk_b200 import dmoe
+    g = torch.Generator().manual_seed(21)
+    bin_rows = torch.tensor([3, 1, 0, 2, 4])
+    h, f = 256, 384
+    topo = dmoe.block_diagonal_topology(bin_rows * 128, f, dtype, "cuda")
+    rows, cols = topo.size()
+    mk = lambda *shape, scale: (torch.randn(*shape, generator=g) * scale).to(dtype).cuda()
+    x, w1, w2, dy = mk(rows, h, scale=1.0), mk(h, cols, scale=0.08), mk(cols, h, scale=0.08), mk(rows, h, scale=1.0)
+    leaves = [t.clone().requires_grad_(True) for t in (x, w1, w2)]
+    y = dmoe.expert_mlp(leaves[0], leaves[1], leaves[2], topo)
+    y.backward(dy)
+    ref_leaves = [t.clone().float().requires_grad_(True) for t in (x, w1, w2)]
+    mask = oracle.to_dense(torch.ones(topo.data.shape), topo.row_indices.cpu().numpy(),
+                           topo.column_indices.cpu().numpy(), (rows, cols)).cuda()
+    pre = (ref_leaves[0] @ ref_leaves[1]) * mask
+    y_ref = (torch.nn.functional.gelu(pre) * mask) @ ref_leaves[2]
+    y_ref.backward(dy.float())
+    assert_product_close(y, y_ref.detach(), "y", roundings=2)
+    for got, ref, name in zip(leaves, ref_leaves, ("dx", "dw1", "dw2")):
+        assert_product_close(got.grad, ref.grad, name, roundings=3)
+
+
 def test_dsd_into_a_given_buffer(stk):
     """dsd(out=...) writes the same product into the caller's rows (a wider buffer's leading rows)."""
     np.random.seed(11)
