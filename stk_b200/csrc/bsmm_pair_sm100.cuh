@@ -234,6 +234,7 @@ __device__ __forceinline__ PairItem decode_item(int item, int inner_count, const
   return it;
 }
 
+template <bool kTrain>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1)
 bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX,
@@ -607,9 +608,9 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int h = 0; h < 2; ++h) {
             const int pb = blk[rank][h];
             if (pb != kNoBlock)
-              drain_to_output(t_addr, h * kBlk, kBlk, p.fmt, p.epilogue, &tmC, 0, pb * kBlk, staging,
-                              row, group, group, 2, issuer,
-                              EpilogueAux{&tmX, static_cast<const uint16_t*>(p.aux)});
+              drain_to_output<kTrain>(t_addr, h * kBlk, kBlk, p.fmt, p.epilogue, &tmC, 0, pb * kBlk,
+                                      staging, row, group, group, 2, issuer,
+                                      EpilogueAux{&tmX, static_cast<const uint16_t*>(p.aux)});
           }
 #endif
           release();
@@ -676,7 +677,9 @@ static int pair_device_info(PairDeviceInfo** out) {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return STK_ERR_LAUNCH;
   PairDeviceInfo& d = infos[dev];
   if (d.max_pairs == 0) {
-    if (cudaFuncSetAttribute(bsmm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(bsmm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kPSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(bsmm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kPSmemBytes) != cudaSuccess) {
       cudaGetLastError();
       return STK_ERR_LAUNCH;
@@ -697,7 +700,7 @@ static int pair_device_info(PairDeviceInfo** out) {
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, bsmm_pair_kernel, &cfg) != cudaSuccess || clusters < 1) {
+    if (cudaOccupancyMaxActiveClusters(&clusters, bsmm_pair_kernel<false>, &cfg) != cudaSuccess || clusters < 1) {
       cudaGetLastError();
       clusters = sms / 2;
     }
@@ -726,8 +729,10 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = kUseDependentLaunch ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, bsmm_pair_kernel, tmA, tmB, tmC, tmX, p) == cudaSuccess ? STK_OK
-                                                                                      : STK_ERR_LAUNCH;
+  const cudaError_t err = p.epilogue >= kEpilogueGeluKeep
+                              ? cudaLaunchKernelEx(&cfg, bsmm_pair_kernel<true>, tmA, tmB, tmC, tmX, p)
+                              : cudaLaunchKernelEx(&cfg, bsmm_pair_kernel<false>, tmA, tmB, tmC, tmX, p);
+  return err == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 
 }  // namespace stk

@@ -300,6 +300,7 @@ __device__ __forceinline__ RowSddItem row_sdd_item(const BsmmParams& p, int item
   return it;
 }
 
+template <bool kTrain>
 __global__ void __launch_bounds__(kThreads, 1)
 bsmm_row_sdd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX,
@@ -457,9 +458,9 @@ bsmm_row_sdd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           if (it.blk[t][h] >= 0)
-            drain_to_output(t_addr, h * kBlk, kBlk, p.fmt, p.epilogue, &tmC, 0, it.blk[t][h] * kBlk,
-                            staging, row, 0, 0, 1, issuer,
-                            EpilogueAux{&tmX, static_cast<const uint16_t*>(p.aux)});
+            drain_to_output<kTrain>(t_addr, h * kBlk, kBlk, p.fmt, p.epilogue, &tmC, 0,
+                                    it.blk[t][h] * kBlk, staging, row, 0, 0, 1, issuer,
+                                    EpilogueAux{&tmX, static_cast<const uint16_t*>(p.aux)});
         }
         tc_fence_before();
         __syncwarp();
@@ -496,7 +497,9 @@ static int launch_row(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUte
   if (!opted_in[dev]) {
     if (cudaFuncSetAttribute(bsmm_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kRSmemBytes) != cudaSuccess ||
-        cudaFuncSetAttribute(bsmm_row_sdd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(bsmm_row_sdd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kRSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(bsmm_row_sdd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kRSmemBytes) != cudaSuccess) {
       cudaGetLastError();
       return STK_ERR_LAUNCH;
@@ -504,10 +507,13 @@ static int launch_row(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUte
     opted_in[dev] = true;
   }
   const int grid = p.num_tiles < d->sms ? p.num_tiles : d->sms;
-  if (p.mode == kModeSDD)
-    bsmm_row_sdd_kernel<<<grid, kThreads, kRSmemBytes, stream>>>(tmA, tmB, tmC, tmX, p);
-  else
+  if (p.mode != kModeSDD) {
     bsmm_row_kernel<<<grid, kThreads, kRSmemBytes, stream>>>(tmA, tmB, tmC, p);
+  } else if (p.epilogue >= kEpilogueGeluKeep) {
+    bsmm_row_sdd_kernel<true><<<grid, kThreads, kRSmemBytes, stream>>>(tmA, tmB, tmC, tmX, p);
+  } else {
+    bsmm_row_sdd_kernel<false><<<grid, kThreads, kRSmemBytes, stream>>>(tmA, tmB, tmC, tmX, p);
+  }
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 

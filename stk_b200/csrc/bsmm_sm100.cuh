@@ -261,6 +261,9 @@ __device__ __forceinline__ void drain_to_output_as(uint32_t t_addr, int col0, in
   }
 }
 
+// kTrain: whether the two training epilogues can occur in this kernel instantiation; the kernels are
+// compiled twice so that the inference forms keep the short epilogue code.
+template <bool kTrain = false>
 __device__ __forceinline__ void drain_to_output(uint32_t t_addr, int col0, int ncols, int fmt,
                                                 int epilogue, const CUtensorMap* tmC, int out_x,
                                                 int out_y, uint32_t staging, int row, int group,
@@ -271,16 +274,18 @@ __device__ __forceinline__ void drain_to_output(uint32_t t_addr, int col0, int n
 #endif
   // the epilogue kind is a compile-time parameter of the body: the plain and GeLU forms keep their
   // short code whatever the two training forms need
-  if (epilogue == kEpilogueNone)
-    drain_to_output_as<kEpilogueNone>(t_addr, col0, ncols, fmt, tmC, out_x, out_y, staging, row, group, first, step, issuer, aux);
-  else if (epilogue == kEpilogueGelu)
-    drain_to_output_as<kEpilogueGelu>(t_addr, col0, ncols, fmt, tmC, out_x, out_y, staging, row, group, first, step, issuer, aux);
-  else if (epilogue == kEpilogueGeluKeep)
+  if constexpr (!kTrain) {
+    if (epilogue == kEpilogueGelu)
+      drain_to_output_as<kEpilogueGelu>(t_addr, col0, ncols, fmt, tmC, out_x, out_y, staging, row, group, first, step, issuer, aux);
+    else
+      drain_to_output_as<kEpilogueNone>(t_addr, col0, ncols, fmt, tmC, out_x, out_y, staging, row, group, first, step, issuer, aux);
+  } else if (epilogue == kEpilogueGeluKeep)
     drain_to_output_as<kEpilogueGeluKeep>(t_addr, col0, ncols, fmt, tmC, out_x, out_y, staging, row, group, first, step, issuer, aux);
   else
     drain_to_output_as<kEpilogueGeluGrad>(t_addr, col0, ncols, fmt, tmC, out_x, out_y, staging, row, group, first, step, issuer, aux);
 }
 
+template <bool kTrain>
 __global__ void __launch_bounds__(kThreads, 1)
 bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX,
@@ -489,8 +494,8 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                               static_cast<uint32_t>(acc * kBlk);
       // TMEM -> registers -> 16-bit -> swizzled staging tile -> TMA store, 64 columns at a time
       if (p.mode == kModeSDD)
-        drain_to_output(t_addr, 0, kBlk, p.fmt, p.epilogue, &tmC, 0, tile * kBlk, staging, row, 0, 0,
-                        1, issuer, EpilogueAux{&tmX, static_cast<const uint16_t*>(p.aux)});
+        drain_to_output<kTrain>(t_addr, 0, kBlk, p.fmt, p.epilogue, &tmC, 0, tile * kBlk, staging, row,
+                                0, 0, 1, issuer, EpilogueAux{&tmX, static_cast<const uint16_t*>(p.aux)});
       else
         drain_to_output(t_addr, 0, kBlk, p.fmt, p.epilogue, &tmC, t.tn * kBlk, t.tm * kBlk, staging,
                         row, 0, 0, 1, issuer);
@@ -607,7 +612,9 @@ static int device_info(DeviceInfo** out) {
     d.sms = sms;
   }
   if (!d.smem_opted_in) {
-    if (cudaFuncSetAttribute(bsmm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(bsmm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(bsmm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kSmemBytes) != cudaSuccess) {
       cudaGetLastError();
       return STK_ERR_LAUNCH;
@@ -625,7 +632,10 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensor
   const int rc = device_info(&d);
   if (rc != STK_OK) return rc;
   const int grid = p.num_tiles < d->sms ? p.num_tiles : d->sms;
-  bsmm_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmC, tmX, p);
+  if (p.epilogue >= kEpilogueGeluKeep)
+    bsmm_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmC, tmX, p);
+  else
+    bsmm_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmC, tmX, p);
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 
