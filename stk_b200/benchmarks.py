@@ -2,6 +2,7 @@
 
     python -m stk_b200.benchmarks c3     # dMoE forward + backward products, 16 experts with Zipf token counts, bf16
     python -m stk_b200.benchmarks c4     # random block sparsity on 8192^3, bf16, all op / transpose combinations
+    python -m stk_b200.benchmarks train  # forward + backward of the experts' MLP, fused against unfused
 
 Every line: nonzero-block TFLOP/s (2 * nnz * 128 * 128 * dense extent / time) with the 128x128 kernel
 forced, the 128x256 row kernel forced (DSD and DDS; SDD runs the 128x128 kernel in that column), the
@@ -120,10 +121,41 @@ def single(density=0.25, dev="cuda"):
         print(f"{name}: {nnz} blocks, mode {kernels.PAIR_MODE}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.0f} TFLOP/s")
 
 
+def train_step(dev="cuda"):
+    """Forward + backward of the experts' MLP on the headline shape (T=16384, h=1024, f=4096, E=8, fp16):
+    dmoe.expert_mlp (GeLU and its backward inside the products' epilogues) against
+    sdd -> torch gelu -> dsd differentiated by autograd."""
+    T, h, f, E, dtype = 16384, 1024, 4096, 8, torch.float16
+    g = torch.Generator().manual_seed(0)
+    ids = torch.multinomial(torch.full((E,), 1.0 / E), T, replacement=True, generator=g).to(dev)
+    _, padded, _, total = dmoe.route_top1(ids, E)
+    topo = dmoe.block_diagonal_topology(padded, f, dtype, dev)
+    rand = lambda *shape: torch.empty(*shape, dtype=dtype, device=dev).normal_(0, 0.02).requires_grad_(True)
+    x, w1, w2 = rand(total, h), rand(h, E * f), rand(E * f, h)
+    dy = torch.empty(total, h, dtype=dtype, device=dev).normal_(0, 0.02)
+
+    def unfused():
+        hid = stk.ops.sdd(x, w1, topo)
+        act = stk.Matrix(hid.size(), torch.nn.functional.gelu(hid.data), hid.row_indices, hid.column_indices,
+                         hid.offsets, hid.column_indices_t, hid.offsets_t, hid.block_offsets_t)
+        stk.ops.dsd(act, w2).backward(dy)
+
+    def fused():
+        dmoe.expert_mlp(x, w1, w2, topo).backward(dy)
+
+    flops = 6 * 2.0 * topo.data.shape[0] * 128 * 128 * h          # two products forward, four backward
+    for name, fn in (("sdd -> gelu -> dsd, autograd", unfused), ("dmoe.expert_mlp", fused)):
+        ms = _time_ms(fn, iters=10, warm=3)
+        print(f"{name:32s} fwd+bwd {ms * 1e3:7.1f} us  {flops / ms / 1e9:5.0f} TFLOP/s")
+
+
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "c3"
-    with torch.no_grad():
-        if which == "single":
-            single(float(sys.argv[2]) if len(sys.argv) > 2 else 0.25)
-        else:
-            {"c3": config3, "c4": config4}[which]()
+    if which == "train":
+        train_step()
+    else:
+        with torch.no_grad():
+            if which == "single":
+                single(float(sys.argv[2]) if len(sys.argv) > 2 else 0.25)
+            else:
+                {"c3": config3, "c4": config4}[which]()
