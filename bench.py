@@ -29,8 +29,8 @@ T_TOKENS, HIDDEN, FFN, EXPERTS = 16384, 1024, 4096, 8   # per GPU
 DTYPE = torch.float16
 METRIC = "nnz_block_tflops_dmoe_fwd_sdd_dsd"
 # dram__bytes_read.sum + dram__bytes_write.sum of the two bsmm_pair_kernel launches of one step, from the ncu
-# capture summarised in profiles/bsmm_pair_kernel_dmoe_fwd.md (sdd+gelu 196.2 MB, dsd 239.3 MB), per launch.
-NCU_DRAM_BYTES_PER_LAUNCH = (196.2e6 + 239.3e6) / 2
+# capture summarised in profiles/bsmm_pair_kernel_dmoe_fwd.md (sdd+gelu 196.6 MB, dsd 239.4 MB), per launch.
+NCU_DRAM_BYTES_PER_LAUNCH = (196.6e6 + 239.4e6) / 2
 
 
 def measured_peaks():
