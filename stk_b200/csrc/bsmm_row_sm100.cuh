@@ -65,6 +65,10 @@ bsmm_row_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     tmem_alloc(smem_u32(tmem_slot), kRTmemCols);
     tmem_relinquish();
   }
+  // nothing above read global memory: with a programmatic dependent launch the kernel before this
+  // one in the stream may still be running up to here
+  pdl_launch_dependents();
+  pdl_wait();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -343,6 +347,10 @@ bsmm_row_sdd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tmem_alloc(smem_u32(tmem_slot), kRTmemCols);
     tmem_relinquish();
   }
+  // nothing above read global memory: with a programmatic dependent launch the kernel before this
+  // one in the stream may still be running up to here
+  pdl_launch_dependents();
+  pdl_wait();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -507,14 +515,14 @@ static int launch_row(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUte
     opted_in[dev] = true;
   }
   const int grid = p.num_tiles < d->sms ? p.num_tiles : d->sms;
-  if (p.mode != kModeSDD) {
-    bsmm_row_kernel<<<grid, kThreads, kRSmemBytes, stream>>>(tmA, tmB, tmC, p);
-  } else if (p.epilogue >= kEpilogueGeluKeep) {
-    bsmm_row_sdd_kernel<true><<<grid, kThreads, kRSmemBytes, stream>>>(tmA, tmB, tmC, tmX, p);
-  } else {
-    bsmm_row_sdd_kernel<false><<<grid, kThreads, kRSmemBytes, stream>>>(tmA, tmB, tmC, tmX, p);
-  }
-  return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
+  cudaError_t err;
+  if (p.mode != kModeSDD)
+    err = launch_dependent(bsmm_row_kernel, grid, kThreads, kRSmemBytes, stream, tmA, tmB, tmC, p);
+  else if (p.epilogue >= kEpilogueGeluKeep)
+    err = launch_dependent(bsmm_row_sdd_kernel<true>, grid, kThreads, kRSmemBytes, stream, tmA, tmB, tmC, tmX, p);
+  else
+    err = launch_dependent(bsmm_row_sdd_kernel<false>, grid, kThreads, kRSmemBytes, stream, tmA, tmB, tmC, tmX, p);
+  return err == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 
 }  // namespace stk

@@ -386,6 +386,10 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
     tmem_relinquish();
   }
+  // nothing above read global memory: with a programmatic dependent launch the kernel before this
+  // one in the stream may still be running up to here
+  pdl_launch_dependents();
+  pdl_wait();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -683,6 +687,25 @@ static int device_info(DeviceInfo** out) {
   return STK_OK;
 }
 
+// Launch with programmatic stream serialization: the kernel's set-up (barriers, TMEM allocation) may
+// overlap the tail of the kernel before it in the stream; it waits (griddepcontrol.wait) before its
+// first global read.
+template <typename... Params, typename... Args>
+static cudaError_t launch_dependent(void (*kernel)(Params...), int grid, int block, int smem_bytes,
+                                    cudaStream_t stream, const Args&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(static_cast<unsigned>(block));
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 // tmX: tensor map of the auxiliary tensor of the SDD epilogues that have one (else any valid map).
 static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                   const CUtensorMap& tmX, const BsmmParams& p, cudaStream_t stream) {
@@ -690,11 +713,11 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensor
   const int rc = device_info(&d);
   if (rc != STK_OK) return rc;
   const int grid = p.num_tiles < d->sms ? p.num_tiles : d->sms;
-  if (p.epilogue >= kEpilogueGeluKeep)
-    bsmm_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmC, tmX, p);
-  else
-    bsmm_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmC, tmX, p);
-  return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
+  const cudaError_t err =
+      p.epilogue >= kEpilogueGeluKeep
+          ? launch_dependent(bsmm_kernel<true>, grid, kThreads, kSmemBytes, stream, tmA, tmB, tmC, tmX, p)
+          : launch_dependent(bsmm_kernel<false>, grid, kThreads, kSmemBytes, stream, tmA, tmB, tmC, tmX, p);
+  return err == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 
 static int check_dense(const void* ptr, int64_t ld, int64_t min_ld) {
