@@ -70,17 +70,13 @@ int stk_b200_device_status(int* status_host);
  * CTA pairs (tcgen05 cta_group::2): two neighbouring block rows / columns of the sparse operand are
  * processed together over the merge of their block lists, which halves the operand traffic per
  * FLOP when the neighbours' lists mostly coincide (dMoE topologies) and wastes MMA work when they
- * do not.  2 (dsd / dds only; sdd treats it as 1) keeps the CTA pairs but gives every work item two
- * dense tiles, 256x512 (dsd) or 512x256 (dds) of output, so that each sparse tile fetched is used
- * twice: less operand traffic, no overlap of one item's epilogue with the next item's MMAs; it pays
- * only for long block lists and is never chosen by this package's own heuristic.  3 runs 128x256
- * tiles on one CTA with one N = 256 MMA per K step: one block row of op(S) x 256 dense columns (dsd),
- * 256 dense rows x one block column (dds, computed transposed), or two blocks of one block row
- * (sdd: blocks 2i and 2i+1 of the list; row_indices / column_indices in row-major order).  Three
- * quarters of mode 0's operand traffic for any topology, no pairing needed - the choice for
- * topologies that do not pair up.  All modes give
- * the same results; modes 1 and 2 need every block row's column_indices (and every block column's
- * column_indices_t) in ascending order.
+ * do not.  3 runs 128x256 tiles on one CTA with one N = 256 MMA per K step: one block row of op(S) x
+ * 256 dense columns (dsd), 256 dense rows x one block column (dds, computed transposed), or two
+ * blocks of one block row (sdd: blocks 2i and 2i+1 of the list; row_indices / column_indices in
+ * row-major order).  Three quarters of mode 0's operand traffic for any topology, no pairing
+ * needed - the choice for topologies that do not pair up.  Any other value is STK_ERR_BAD_DIMS.
+ * All modes give the same results; mode 1 needs every block row's column_indices (and every block
+ * column's column_indices_t) in ascending order.
  */
 
 /*
@@ -91,7 +87,7 @@ int stk_b200_device_status(int* status_host);
  *        column-major (lhs_colmajor=1, element (m,k) at k*ld_lhs+m - an exact .t() view).
  *   rhs: logical [K,N]; same convention with ld_rhs.
  *   out: [nnz,128,128] contiguous.
- *   offsets: CSR offsets [M/128+1]; only read when pair_mode = 1 or 2 (may be NULL otherwise).
+ *   offsets: CSR offsets [M/128+1]; only read when pair_mode = 1 (may be NULL otherwise).
  *   epilogue: 0 stores the product; 1 (STK_EPILOGUE_GELU) stores GeLU(product), the exact erf form
  *             applied to the fp32 accumulator before rounding - the step between SDD and DSD in a
  *             dMoE layer, fused so that the hidden activations are written once.  The reference
@@ -102,13 +98,16 @@ int stk_b200_device_status(int* status_host);
  *             the backward of GeLU fused into the product dy @ w2^T that yields the gradient of
  *             the activations.
  *   aux: [nnz,128,128] contiguous like out, written (2) or read (3); NULL for epilogue 0 / 1.
+ *   pair_plan: work-item table from stk_b200_pair_plan(offsets, column_indices, M/128, ...) for
+ *        pair_mode = 1, or NULL (block rows are then paired blindly; see stk_b200_pair_plan).
  * nnz == 0 is a no-op.
  */
 int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const int32_t* offsets,
                  const int16_t* row_indices, const int16_t* column_indices,
                  int64_t M, int64_t N, int64_t K, int64_t nnz,
                  int lhs_colmajor, int64_t ld_lhs, int rhs_colmajor, int64_t ld_rhs,
-                 int dtype, int pair_mode, int epilogue, void* aux, void* stream);
+                 int dtype, int pair_mode, int epilogue, void* aux, const int32_t* pair_plan,
+                 void* stream);
 
 /*
  * DSD: out[M,N] = op(S)[M,K] @ rhs[K,N].
@@ -119,12 +118,14 @@ int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const int32_t* off
  *                     (block j of block-row i of S^T is data[block_offsets_t[j]]^T).
  *   M,K: logical (already transposed) shape of op(S).  Block rows without blocks give zeros.
  *   rhs: row-major or column-major as for stk_b200_sdd.  out: row-major, leading dimension ld_out.
+ *   pair_plan: table from stk_b200_pair_plan over the SAME offsets / column_indices arrays that are
+ *        passed here (M/128 lists), for pair_mode = 1; or NULL.
  */
 int stk_b200_dsd(const void* data, const int32_t* offsets, const int16_t* column_indices,
                  const int32_t* block_offsets, const void* rhs, void* out,
                  int64_t M, int64_t N, int64_t K, int64_t nnz,
                  int trans_sparse, int rhs_colmajor, int64_t ld_rhs, int64_t ld_out,
-                 int dtype, int pair_mode, void* stream);
+                 int dtype, int pair_mode, const int32_t* pair_plan, void* stream);
 
 /*
  * DDS: out[M,N] = lhs[M,K] @ op(S)[K,N].
@@ -134,12 +135,42 @@ int stk_b200_dsd(const void* data, const int32_t* offsets, const int16_t* column
  *   trans_sparse = 1: pass offsets, column_indices and block_offsets = NULL
  *                     (block column n of S^T is block row n of S, blocks used transposed).
  *   K,N: logical shape of op(S).
+ *   pair_plan: table from stk_b200_pair_plan over the offsets / column_indices arrays passed here
+ *        (N/128 lists), for pair_mode = 1; or NULL.
  */
 int stk_b200_dds(const void* lhs, const void* data, const int32_t* offsets,
                  const int16_t* column_indices, const int32_t* block_offsets, void* out,
                  int64_t M, int64_t N, int64_t K, int64_t nnz,
                  int lhs_colmajor, int64_t ld_lhs, int trans_sparse, int64_t ld_out,
-                 int dtype, int pair_mode, void* stream);
+                 int dtype, int pair_mode, const int32_t* pair_plan, void* stream);
+
+/*
+ * Preparation for pair_mode = 1, once per topology.  No counterpart in the reference (its kernels
+ * take one 128x128 tile per program, stk/backend/triton_kernels.py:21-220).
+ *
+ * pair_stats: how well the topology suits the CTA-pair kernel.  Writes six int32 to `stats`, which
+ *   may be device memory or pinned host memory mapped into the device (the kernel stores to it):
+ *   [0] distinct (row pair, column) positions, [1] distinct (row, column pair) positions,
+ *   [2] distinct (row pair, column pair) positions - the useful share of the pair kernel's MMA work
+ *   is nnz / (2 [0]) when block rows are paired (dsd with S as stored, dds with S transposed),
+ *   nnz / (2 [1]) when block columns are paired, nnz / (4 [2]) for sdd;
+ *   [3] 1 iff the blocks are listed in strictly ascending (row, column) order consistent with
+ *   offsets and all indices are in range (otherwise [0..2] are meaningless and pair_mode 1 must not
+ *   be used); [4] 1 iff every block column's segment of column_indices_t ascends (needed when block
+ *   columns are paired), 0 if not, -1 if offsets_t / column_indices_t were NULL; [5] = 1, stored last.
+ * pair_plan: the pair kernel's work-item table for one list family - (offsets, column_indices) with
+ *   num_lists = block rows, or (offsets_t, column_indices_t) with num_lists = block columns.  Lists
+ *   are cut into runs where two neighbours cannot share a position (expert boundaries of a dMoE
+ *   topology), paired inside each run, and ordered longest first.  `plan` needs
+ *   stk_b200_pair_plan_bytes(num_lists) bytes of device memory and is passed to sdd / dsd / dds.
+ */
+int stk_b200_pair_stats(const int32_t* offsets, const int16_t* row_indices,
+                        const int16_t* column_indices, const int32_t* offsets_t,
+                        const int16_t* column_indices_t, int64_t block_rows, int64_t block_cols,
+                        int64_t nnz, int32_t* stats, void* stream);
+size_t stk_b200_pair_plan_bytes(int64_t num_lists);
+int stk_b200_pair_plan(const int32_t* offsets, const int16_t* column_indices, int64_t num_lists,
+                       int32_t* plan, size_t plan_bytes, void* stream);
 
 /*
  * CSR offsets -> COO row index of every block (int16).

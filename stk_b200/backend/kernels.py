@@ -16,10 +16,10 @@ from stk_b200.backend import lib as _lib
 
 BLOCK = 128  # the matmul kernels are built for 128x128 blocks
 
-# Which matmul kernel runs: "0" = one 128x128 tile per CTA, "1" = 256x256 supertiles on CTA pairs,
-# "2" = CTA pairs with two dense tiles per item for DSD / DDS (opt-in, never picked by "auto"),
-# "3" = 128x128 tiles for SDD, one block row / column x 256 dense columns / rows per CTA for DSD / DDS,
-# "auto" = per topology, from how well neighbouring block rows / columns pair up (see pair_hints).
+# Which matmul kernel runs: "0" = one 128x128 tile per CTA, "1" = 256x256 supertiles on CTA pairs
+# wherever the metadata allows it, "3" = 128x256 tiles on one CTA (two blocks of a block row for SDD,
+# one block row / column x 256 dense columns / rows for DSD / DDS), "auto" = per topology, from how
+# well neighbouring block rows / columns pair up (see pair_hints).
 PAIR_MODE = os.environ.get("STK_B200_PAIR_MODE", "auto")
 # DSD / DDS products that do not take the pair kernel run the 128x256 row kernel in these modes when
 # the dense operand has at least 256 columns (DSD) / rows (DDS); "3" never takes the pair kernel.
@@ -37,56 +37,157 @@ SDD_ROW_MIN_BLOCKS = 1536
 # topologies are above 0.9.
 PAIR_THRESHOLD = {"rows": 0.85, "cols": 0.85, "tiles": 0.7}
 _HINT_ATTR = "_stk_b200_pair_hints"
+_PLAN_ATTR = "_stk_b200_pair_plan"
 
 
-def set_pair_hints(column_indices, rows, cols, tiles, is_sorted=True):
-    """Record how a topology pairs up, for callers that know it by construction (no device sync).
+class _Hints:
+    """What is known about how a topology pairs up; hangs on its column_indices tensor.
+
+    values: (rows, cols, tiles, in_order, t_in_order) once known - useful fraction of the pair
+    kernel's work when block rows / block columns / both are processed two at a time, whether the
+    blocks are in ascending (row, column) order, and whether every block column's segment of
+    column_indices_t ascends (None: not examined).  pending: a stats kernel that has been launched
+    but whose result has not been read yet."""
+
+    __slots__ = ("version", "values", "pending", "t_ptr")
+
+    def __init__(self, version):
+        self.version, self.values, self.pending, self.t_ptr = version, None, None, None
+
+
+class _StatsSlots:
+    """Pinned host memory the stats kernel writes its six numbers into: one arena, slots handed out in
+    turn, so that asking about a topology allocates nothing and never waits for the device."""
+
+    SLOTS, INTS = 1024, 8
+
+    def __init__(self):
+        self.arena = torch.zeros((self.SLOTS, self.INTS), dtype=torch.int32).pin_memory()
+        self.next = 0
+
+    def take(self):
+        i = self.next % self.SLOTS
+        self.next += 1
+        self.arena[i].zero_()
+        return self.next - 1, self.arena[i]
+
+    def still_mine(self, ticket):
+        return self.next - ticket <= self.SLOTS
+
+
+_stats_slots = None
+
+
+def set_pair_hints(column_indices, rows, cols, tiles, is_sorted=True, t_sorted=True):
+    """Record how a topology pairs up, for callers that know it by construction.
 
     rows / cols / tiles: useful fraction of the pair kernel's work when block rows (2t, 2t+1),
-    block columns (2u, 2u+1), or both, are processed together."""
-    setattr(column_indices, _HINT_ATTR,
-            (column_indices._version, float(rows), float(cols), float(tiles), bool(is_sorted)))
+    block columns (2u, 2u+1), or both, are processed together; is_sorted: blocks in ascending
+    (row, column) order; t_sorted: every block column's rows ascend in column_indices_t."""
+    h = _Hints(column_indices._version)
+    h.values = (float(rows), float(cols), float(tiles), bool(is_sorted), bool(t_sorted))
+    setattr(column_indices, _HINT_ATTR, h)
 
 
-def pair_hints(row_indices, column_indices, block_cols):
-    """(rows, cols, tiles, sorted) for a topology; computed once per column_indices tensor.
+def _launch_stats(h, offsets, row_indices, column_indices, offsets_t, column_indices_t, block_cols):
+    global _stats_slots
+    if _stats_slots is None:
+        _stats_slots = _StatsSlots()
+    ticket, slot = _stats_slots.take()
+    dev = column_indices.device
+    row_indices, column_indices = row_indices.contiguous(), column_indices.contiguous()
+    with _lib.on_device(dev):
+        rc = _lib.load().stk_b200_pair_stats(
+            _lib.ptr(offsets), _lib.ptr(row_indices), _lib.ptr(column_indices), _lib.ptr(offsets_t),
+            _lib.ptr(column_indices_t), offsets.numel() - 1, block_cols, column_indices.numel(),
+            slot.data_ptr(), _lib.stream_ptr(dev))
+        _lib.check(rc, "stk_b200_pair_stats")
+        event = torch.cuda.Event()
+        event.record(torch.cuda.current_stream(dev))
+    h.pending = (ticket, slot, event, column_indices.numel())
+    h.t_ptr = None if column_indices_t is None else column_indices_t.data_ptr()
+
+
+def pair_hints(offsets, row_indices, column_indices, block_cols, offsets_t=None, column_indices_t=None,
+               need_t=False, wait=False):
+    """(rows, cols, tiles, in_order, t_in_order) of a topology, or None while that is not known yet.
 
     rows  = nnz / (2 * number of distinct (row pair, column) positions): DSD with S as stored,
             DDS with S transposed.
     cols  = nnz / (2 * distinct (row, column pair)): DSD with S transposed, DDS with S as stored.
     tiles = nnz / (4 * distinct (row pair, column pair)): SDD.
-    The first use of an unknown topology reads four numbers back from the device (one sync)."""
-    cached = getattr(column_indices, _HINT_ATTR, None)
-    if cached is not None and cached[0] == column_indices._version:
-        return cached[1:]
-    nnz = column_indices.numel()
-    if nnz == 0:
-        set_pair_hints(column_indices, 0.0, 0.0, 0.0, True)
-        return getattr(column_indices, _HINT_ATTR)[1:]
-    r = row_indices.long()
-    c = column_indices.long()
-    half_cols = (block_cols + 1) // 2
-    in_order = ((c[1:] > c[:-1]) | (r[1:] > r[:-1])).all() if nnz > 1 else torch.ones((), device=c.device)
-    counts = torch.stack([
-        torch.unique((r >> 1) * block_cols + c).numel() * torch.ones((), device=c.device),
-        torch.unique(r * half_cols + (c >> 1)).numel() * torch.ones((), device=c.device),
-        torch.unique((r >> 1) * half_cols + (c >> 1)).numel() * torch.ones((), device=c.device),
-        in_order.to(torch.float32)]).tolist()
-    set_pair_hints(column_indices, nnz / (2.0 * counts[0]), nnz / (2.0 * counts[1]),
-                   nnz / (4.0 * counts[2]), counts[3] != 0)
-    return getattr(column_indices, _HINT_ATTR)[1:]
+    Nothing here waits for the device (unless wait=True): the first question about an unknown
+    topology launches one small kernel that writes its answer into pinned host memory, and the
+    answer is picked up by whichever later call finds it complete; until then the caller gets None
+    and runs a kernel that needs no pairing.  need_t: the caller pairs block COLUMNS and therefore
+    needs the order inside column_indices_t examined as well."""
+    h = getattr(column_indices, _HINT_ATTR, None)
+    if h is None or h.version != column_indices._version:
+        h = _Hints(column_indices._version)
+        setattr(column_indices, _HINT_ATTR, h)
+    if h.values is not None and not (need_t and h.values[4] is None):
+        return h.values
+    if column_indices.numel() == 0:
+        h.values = (0.0, 0.0, 0.0, True, True)
+        return h.values
+    if h.pending is not None:
+        ticket, slot, event, nnz = h.pending
+        covers_t = h.t_ptr is not None and (column_indices_t is None or h.t_ptr == column_indices_t.data_ptr())
+        if not _stats_slots.still_mine(ticket) or (need_t and not covers_t):
+            h.pending = None
+        else:
+            if wait:
+                event.synchronize()
+            if not event.query():
+                return None
+            n_rp, n_cp, n_t, in_order, t_order = (int(v) for v in slot[:5])
+            h.values = (nnz / (2.0 * max(n_rp, 1)), nnz / (2.0 * max(n_cp, 1)), nnz / (4.0 * max(n_t, 1)),
+                        in_order == 1, None if t_order < 0 else t_order == 1)
+            h.pending = None
+            return h.values
+    _launch_stats(h, offsets, row_indices, column_indices, offsets_t, column_indices_t, block_cols)
+    if wait:
+        return pair_hints(offsets, row_indices, column_indices, block_cols, offsets_t, column_indices_t,
+                          need_t, wait)
+    return None
 
 
-def _use_pairs(kind, row_indices, column_indices, block_cols):
-    """kind: "rows", "cols" or "tiles" - which neighbours the product would pair."""
+def _use_pairs(kind, offsets, row_indices, column_indices, block_cols, offsets_t=None, column_indices_t=None):
+    """kind: "rows", "cols" or "tiles" - which neighbours the product would pair.  1 = pair kernel."""
     if PAIR_MODE in ("0", "3"):
         return 0
-    rows, cols, tiles, is_sorted = pair_hints(row_indices, column_indices, block_cols)
-    if kind == "tiles" and not is_sorted:
-        return 0  # the SDD tile walk needs ascending columns inside every block row
-    if PAIR_MODE in ("1", "2"):
-        return 1 if kind == "tiles" else int(PAIR_MODE)
+    forced = PAIR_MODE == "1"
+    hints = pair_hints(offsets, row_indices, column_indices, block_cols, offsets_t, column_indices_t,
+                       need_t=kind == "cols", wait=forced)
+    if hints is None:
+        return 0
+    rows, cols, tiles, in_order, t_order = hints
+    # the merge walks need ascending columns inside every block row (and, when block columns are
+    # paired, ascending rows inside every block column); anything else takes a kernel that does not
+    if not in_order or (kind == "cols" and not t_order):
+        return 0
+    if forced:
+        return 1
     return int({"rows": rows, "cols": cols, "tiles": tiles}[kind] >= PAIR_THRESHOLD[kind])
+
+
+def pair_plan(offsets, indices):
+    """The pair kernel's work-item table for one family of lists - (offsets, column_indices) for
+    block rows, (offsets_t, column_indices_t) for block columns -, computed once per topology by a
+    small kernel on the current stream and kept on the index tensor."""
+    cached = getattr(indices, _PLAN_ATTR, None)
+    if cached is not None and cached[0] == (indices._version, offsets.data_ptr(), offsets._version):
+        return cached[1]
+    num_lists = offsets.numel() - 1
+    lib = _lib.load()
+    nbytes = lib.stk_b200_pair_plan_bytes(num_lists)
+    plan = torch.empty(nbytes // 4, dtype=torch.int32, device=indices.device)
+    with _lib.on_device(indices.device):
+        rc = lib.stk_b200_pair_plan(_lib.ptr(offsets), _lib.ptr(indices), num_lists, _lib.ptr(plan), nbytes,
+                                    _lib.stream_ptr(indices.device))
+    _lib.check(rc, "stk_b200_pair_plan")
+    setattr(indices, _PLAN_ATTR, ((indices._version, offsets.data_ptr(), offsets._version), plan))
+    return plan
 
 
 class DimensionError(AssertionError, ValueError):
@@ -139,10 +240,20 @@ def _check_blocks(data):
         raise DimensionError("sparse values must be contiguous")
 
 
+def _same_dtype(what, *tensors):
+    """The kernels read every operand with one element type; mixed float16 / bfloat16 operands would
+    be reinterpreted bit for bit."""
+    dtypes = {t.dtype for t in tensors if t is not None}
+    if len(dtypes) > 1:
+        raise ValueError(f"{what}: all operands and the output must share one dtype, got "
+                         + ", ".join(sorted(str(d) for d in dtypes)))
+
+
 def dsd(shape, data, offsets, row_indices, column_indices, offsets_t, column_indices_t,
         block_offsets_t, transpose_a, rhs, out):
     """out = op(S) @ rhs, S given by its blocked CSR-COO fields; `shape` is op(S)'s shape."""
     _require_cuda(data, rhs, out)
+    _same_dtype("dsd", data, rhs, out)
     if shape[1] != rhs.shape[0]:
         raise DimensionError("incompatible dimensions")
     M, K = shape
@@ -152,17 +263,18 @@ def dsd(shape, data, offsets, row_indices, column_indices, offsets_t, column_ind
     rhs, rhs_colmajor, ld_rhs = _dense_layout(rhs)
     if transpose_a:
         meta = (offsets_t, column_indices_t, block_offsets_t)
-        pairs = _use_pairs("cols", row_indices, column_indices, M // BLOCK)
+        pairs = _use_pairs("cols", offsets, row_indices, column_indices, M // BLOCK, offsets_t, column_indices_t)
     else:
         meta = (offsets, column_indices, None)
-        pairs = _use_pairs("rows", row_indices, column_indices, K // BLOCK)
+        pairs = _use_pairs("rows", offsets, row_indices, column_indices, K // BLOCK, offsets_t, column_indices_t)
     if pairs == 0 and N >= 2 * BLOCK and PAIR_MODE in ROW_KERNEL_MODES:
         pairs = 3            # one block row x 256 dense columns per CTA
+    plan = pair_plan(meta[0], meta[1]) if pairs == 1 else None
     with _lib.on_device(out.device):
         rc = _lib.load().stk_b200_dsd(
             _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),
             _lib.ptr(rhs), _lib.ptr(out), M, N, K, data.shape[0], int(bool(transpose_a)),
-            rhs_colmajor, ld_rhs, out.stride(0), _lib.dtype_code(rhs.dtype), pairs,
+            rhs_colmajor, ld_rhs, out.stride(0), _lib.dtype_code(rhs.dtype), pairs, _lib.ptr(plan),
             _lib.stream_ptr(out.device))
     _lib.check(rc, "stk_b200_dsd")
 
@@ -171,6 +283,7 @@ def dds(lhs, shape, data, offsets, row_indices, column_indices, offsets_t, colum
         block_offsets_t, transpose_b, out):
     """out = lhs @ op(S); `shape` is op(S)'s shape."""
     _require_cuda(lhs, data, out)
+    _same_dtype("dds", lhs, data, out)
     if lhs.shape[1] != shape[0]:
         raise DimensionError("incompatible dimensions")
     M, K = lhs.shape
@@ -180,17 +293,18 @@ def dds(lhs, shape, data, offsets, row_indices, column_indices, offsets_t, colum
     lhs, lhs_colmajor, ld_lhs = _dense_layout(lhs)
     if transpose_b:
         meta = (offsets, column_indices, None)
-        pairs = _use_pairs("rows", row_indices, column_indices, K // BLOCK)
+        pairs = _use_pairs("rows", offsets, row_indices, column_indices, K // BLOCK, offsets_t, column_indices_t)
     else:
         meta = (offsets_t, column_indices_t, block_offsets_t)
-        pairs = _use_pairs("cols", row_indices, column_indices, N // BLOCK)
+        pairs = _use_pairs("cols", offsets, row_indices, column_indices, N // BLOCK, offsets_t, column_indices_t)
     if pairs == 0 and M >= 2 * BLOCK and PAIR_MODE in ROW_KERNEL_MODES:
         pairs = 3            # 256 dense rows x one block column per CTA
+    plan = pair_plan(meta[0], meta[1]) if pairs == 1 else None
     with _lib.on_device(out.device):
         rc = _lib.load().stk_b200_dds(
             _lib.ptr(lhs), _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),
             _lib.ptr(out), M, N, K, data.shape[0], lhs_colmajor, ld_lhs, int(bool(transpose_b)),
-            out.stride(0), _lib.dtype_code(lhs.dtype), pairs, _lib.stream_ptr(out.device))
+            out.stride(0), _lib.dtype_code(lhs.dtype), pairs, _lib.ptr(plan), _lib.stream_ptr(out.device))
     _lib.check(rc, "stk_b200_dds")
 
 
@@ -200,6 +314,7 @@ def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices, epilogue=0, 
     stores the product in out and its GeLU in aux; epilogue=3 stores product * GeLU'(aux)
     (stk_b200.dmoe.expert_mlp).  aux has out's shape and dtype."""
     _require_cuda(lhs, rhs, out)
+    _same_dtype("sdd", lhs, rhs, out, aux)
     if (epilogue in (2, 3)) != (aux is not None):
         raise ValueError("epilogues 2 and 3 take an auxiliary tensor, the others do not")
     if aux is not None:
@@ -214,14 +329,16 @@ def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices, epilogue=0, 
     _check_blocks(out)
     lhs, lhs_colmajor, ld_lhs = _dense_layout(lhs)
     rhs, rhs_colmajor, ld_rhs = _dense_layout(rhs)
-    pairs = _use_pairs("tiles", row_indices, column_indices, N // BLOCK)
+    pairs = _use_pairs("tiles", offsets, row_indices, column_indices, N // BLOCK)
     if pairs == 0 and (PAIR_MODE == "3" or (PAIR_MODE == "auto" and out.shape[0] >= SDD_ROW_MIN_BLOCKS)):
         pairs = 3            # two blocks of a block row per 128x256 tile
+    plan = pair_plan(offsets, column_indices) if pairs == 1 else None
     with _lib.on_device(out.device):
         rc = _lib.load().stk_b200_sdd(
             _lib.ptr(lhs), _lib.ptr(rhs), _lib.ptr(out), _lib.ptr(offsets), _lib.ptr(row_indices),
             _lib.ptr(column_indices), M, N, K, out.shape[0], lhs_colmajor, ld_lhs, rhs_colmajor,
-            ld_rhs, _lib.dtype_code(out.dtype), pairs, epilogue, _lib.ptr(aux), _lib.stream_ptr(out.device))
+            ld_rhs, _lib.dtype_code(out.dtype), pairs, epilogue, _lib.ptr(aux), _lib.ptr(plan),
+            _lib.stream_ptr(out.device))
     _lib.check(rc, "stk_b200_sdd")
 
 
@@ -248,9 +365,10 @@ def transpose_meta(row_indices, column_indices, block_cols):
     lib = _lib.load()
     ws_bytes = lib.stk_b200_transpose_meta_workspace_bytes(nnz, block_cols)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
+    row_indices, column_indices = row_indices.contiguous(), column_indices.contiguous()
     with _lib.on_device(dev):
         rc = lib.stk_b200_transpose_meta(
-            _lib.ptr(row_indices.contiguous()), _lib.ptr(column_indices.contiguous()), nnz,
+            _lib.ptr(row_indices), _lib.ptr(column_indices), nnz,
             block_cols, _lib.ptr(column_indices_t), _lib.ptr(offsets_t), _lib.ptr(block_offsets_t),
             _lib.ptr(ws), ws_bytes, _lib.stream_ptr(dev))
     _lib.check(rc, "stk_b200_transpose_meta")
@@ -330,9 +448,10 @@ def to_dense(data, offsets, column_indices, block_rows, block_cols, blocking):
                       device=data.device)
     if out.numel() == 0:
         return out
+    data = data.contiguous()
     with _lib.on_device(data.device):
         rc = _lib.load().stk_b200_to_dense(
-            _lib.ptr(data.contiguous()) if data.numel() else None, _lib.ptr(offsets),
+            _lib.ptr(data) if data.numel() else None, _lib.ptr(offsets),
             _lib.ptr(column_indices) if column_indices.numel() else None, block_rows, block_cols,
             blocking, _elem_bytes(data), _lib.ptr(out), out.stride(0), _lib.stream_ptr(data.device))
     _lib.check(rc, "stk_b200_to_dense")

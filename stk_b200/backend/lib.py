@@ -9,8 +9,7 @@ import os
 import torch
 
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-# STK_B200_LIB points at an alternative build of the same library (kernel experiments).
-LIB_PATH = os.environ.get("STK_B200_LIB") or os.path.join(_PKG, "libstk_b200.so")
+LIB_PATH = os.path.join(_PKG, "libstk_b200.so")
 
 STK_F16 = 0
 STK_BF16 = 1
@@ -26,11 +25,15 @@ SIGNATURES = {
     "stk_b200_error_string": (ctypes.c_char_p, [_c_int]),
     "stk_b200_device_status": (_c_int, [ctypes.POINTER(_c_int)]),
     "stk_b200_sdd": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64,
-                              _c_i64, _c_int, _c_i64, _c_int, _c_i64, _c_int, _c_int, _c_int, _c_ptr, _c_ptr]),
+                              _c_i64, _c_int, _c_i64, _c_int, _c_i64, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr]),
     "stk_b200_dsd": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64,
-                              _c_i64, _c_int, _c_int, _c_i64, _c_i64, _c_int, _c_int, _c_ptr]),
+                              _c_i64, _c_int, _c_int, _c_i64, _c_i64, _c_int, _c_int, _c_ptr, _c_ptr]),
     "stk_b200_dds": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64,
-                              _c_i64, _c_int, _c_i64, _c_int, _c_i64, _c_int, _c_int, _c_ptr]),
+                              _c_i64, _c_int, _c_i64, _c_int, _c_i64, _c_int, _c_int, _c_ptr, _c_ptr]),
+    "stk_b200_pair_stats": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr,
+                                     _c_ptr]),
+    "stk_b200_pair_plan_bytes": (_c_size, [_c_i64]),
+    "stk_b200_pair_plan": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_ptr, _c_size, _c_ptr]),
     "stk_b200_row_indices": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_ptr]),
     "stk_b200_transpose_meta_workspace_bytes": (_c_size, [_c_i64, _c_i64]),
     "stk_b200_transpose_meta": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr,

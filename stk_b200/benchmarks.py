@@ -91,7 +91,8 @@ def config4(dev="cuda"):
         nd = max(128, int(round(N * density / 128)) * 128)     # dense GEMM with the same FLOPs: 8192 x 8192 x nd
         bd = torch.randn(K, nd, device=dev).to(dtype)
         an, bn = a[:, :nd].contiguous(), b[:nd].contiguous()
-        rows, cols, tiles, _ = kernels.pair_hints(topo.row_indices, topo.column_indices, N // 128)
+        rows, cols, tiles, _, _ = kernels.pair_hints(topo.offsets, topo.row_indices, topo.column_indices, N // 128,
+                                                     topo.offsets_t, topo.column_indices_t, need_t=True, wait=True)
         print(f"\nrandom topology 8192^2, density {density}: {nnz} blocks; useful share of the pair kernel's work: "
               f"row pairs {rows:.2f}, column pairs {cols:.2f}, 2x2 tiles {tiles:.2f}")
         print(_HEADER)

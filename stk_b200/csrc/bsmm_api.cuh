@@ -1,16 +1,17 @@
 // C entry points of the three block-sparse products: argument checks, tensor-map encoding and
-// the choice between the single-CTA 128x128 kernel and the CTA-pair 256x256 kernel.
+// the dispatch to the 128x128 kernel, the CTA-pair 256x256 kernel or the 128x256 row kernel.
 #pragma once
 #include "bsmm_pair_sm100.cuh"
-#include "bsmm_wide_sm100.cuh"
 #include "bsmm_row_sm100.cuh"
 #include "bsmm_sm100.cuh"
 
 namespace stk {
 
-static int check_dtype_dims(int dtype, int64_t M, int64_t N, int64_t K, int64_t nnz, int64_t k_mult) {
+static int check_dtype_dims(int dtype, int64_t M, int64_t N, int64_t K, int64_t nnz, int64_t k_mult,
+                            int pair_mode) {
   if (dtype != STK_F16 && dtype != STK_BF16) return STK_ERR_BAD_DTYPE;
   if (M <= 0 || N <= 0 || K <= 0 || nnz < 0 || M % kBlk || N % kBlk || K % k_mult) return STK_ERR_BAD_DIMS;
+  if (pair_mode != 0 && pair_mode != 1 && pair_mode != 3) return STK_ERR_BAD_DIMS;
   if (nnz * kBlk > INT32_MAX - 2 * kBlk || M > INT32_MAX / 2 || N > INT32_MAX / 2 || K > INT32_MAX / 2 ||
       (M / kBlk) * (N / kBlk) > INT32_MAX)
     return STK_ERR_TOO_LARGE;
@@ -30,8 +31,8 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
                             const int16_t* row_indices, const int16_t* column_indices, int64_t M,
                             int64_t N, int64_t K, int64_t nnz, int lhs_colmajor, int64_t ld_lhs,
                             int rhs_colmajor, int64_t ld_rhs, int dtype, int pair_mode,
-                            int epilogue, void* aux, void* stream) {
-  int rc = check_dtype_dims(dtype, M, N, K, nnz, 32);
+                            int epilogue, void* aux, const int32_t* pair_plan, void* stream) {
+  int rc = check_dtype_dims(dtype, M, N, K, nnz, 32, pair_mode);
   if (rc != STK_OK) return rc;
   if (epilogue < kEpilogueNone || epilogue > kEpilogueGeluGrad) return STK_ERR_BAD_DIMS;
   const bool has_aux = epilogue == kEpilogueGeluKeep || epilogue == kEpilogueGeluGrad;
@@ -103,6 +104,7 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
     p.out = out;
     p.ldc = kBlk;
     p.aux = aux;
+    p.plan = pair_plan;
     return launch_pair(tmA, tmB, tmC, tmX, p, s);
   }
 
@@ -126,8 +128,9 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
 extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int16_t* column_indices,
                             const int32_t* block_offsets, const void* rhs, void* out, int64_t M,
                             int64_t N, int64_t K, int64_t nnz, int trans_sparse, int rhs_colmajor,
-                            int64_t ld_rhs, int64_t ld_out, int dtype, int pair_mode, void* stream) {
-  int rc = check_dtype_dims(dtype, M, N, K, nnz, kBlk);
+                            int64_t ld_rhs, int64_t ld_out, int dtype, int pair_mode,
+                            const int32_t* pair_plan, void* stream) {
+  int rc = check_dtype_dims(dtype, M, N, K, nnz, kBlk, pair_mode);
   if (rc != STK_OK) return rc;
   if ((rc = check_dense(out, ld_out, N)) != STK_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -172,8 +175,7 @@ extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int1
     p.b_mn = rhs_colmajor ? 0 : 1;
     p.fmt = dtype;
     p.num_lists = static_cast<int>(M / kBlk);
-    const int64_t span = pair_mode == 2 ? 4 * kBlk : 2 * kBlk;  // dense columns per work item
-    p.inner = static_cast<int>((N + span - 1) / span);
+    p.inner = static_cast<int>((N + 2 * kBlk - 1) / (2 * kBlk));  // 256 dense columns per work item
     p.num_items = ((p.num_lists + 1) / 2) * p.inner;
     p.zero_coord = static_cast<int>(nnz * kBlk);
     p.out_rows = static_cast<int>(M);
@@ -183,7 +185,8 @@ extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int1
     p.blk_idx = block_offsets;
     p.out = out;
     p.ldc = ld_out;
-    return pair_mode == 2 ? launch_wide(tmA, tmB, tmC, p, s) : launch_pair(tmA, tmB, tmC, tmC, p, s);
+    p.plan = pair_plan;
+    return launch_pair(tmA, tmB, tmC, tmC, p, s);
   }
 
   BsmmParams p{};
@@ -205,8 +208,8 @@ extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* of
                             const int16_t* column_indices, const int32_t* block_offsets, void* out,
                             int64_t M, int64_t N, int64_t K, int64_t nnz, int lhs_colmajor,
                             int64_t ld_lhs, int trans_sparse, int64_t ld_out, int dtype,
-                            int pair_mode, void* stream) {
-  int rc = check_dtype_dims(dtype, M, N, K, nnz, kBlk);
+                            int pair_mode, const int32_t* pair_plan, void* stream) {
+  int rc = check_dtype_dims(dtype, M, N, K, nnz, kBlk, pair_mode);
   if (rc != STK_OK) return rc;
   if ((rc = check_dense(out, ld_out, N)) != STK_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -250,8 +253,7 @@ extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* of
     p.b_mn = trans_sparse ? 0 : 1;
     p.fmt = dtype;
     p.num_lists = static_cast<int>(N / kBlk);
-    const int64_t span = pair_mode == 2 ? 4 * kBlk : 2 * kBlk;  // dense rows per work item
-    p.inner = static_cast<int>((M + span - 1) / span);
+    p.inner = static_cast<int>((M + 2 * kBlk - 1) / (2 * kBlk));  // 256 dense rows per work item
     p.num_items = ((p.num_lists + 1) / 2) * p.inner;
     p.zero_coord = static_cast<int>(nnz * kBlk);
     p.out_rows = static_cast<int>(M);
@@ -261,7 +263,8 @@ extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* of
     p.blk_idx = block_offsets;
     p.out = out;
     p.ldc = ld_out;
-    return pair_mode == 2 ? launch_wide(tmA, tmB, tmC, p, s) : launch_pair(tmA, tmB, tmC, tmC, p, s);
+    p.plan = pair_plan;
+    return launch_pair(tmA, tmB, tmC, tmC, p, s);
   }
 
   BsmmParams p{};

@@ -49,25 +49,12 @@ constexpr int kPNumBars = 2 * kPStages + 4;
 #define STK_DEPENDENT_LAUNCH 1
 #endif
 constexpr bool kUseDependentLaunch = STK_DEPENDENT_LAUNCH != 0;
-constexpr int kMaxBreaks = 64;  // places where the rows are cut into runs (more: no cuts at all)
 constexpr int kPSmemBytes =
-    kPStages * kStageBytes + 2 * kOutStageBytes + kPNumBars * 8 + kPStages * 4 + 32 + (5 * kMaxBreaks + 12) * 4 + 1024;
+    kPStages * kStageBytes + 2 * kOutStageBytes + kPNumBars * 8 + kPStages * 4 + 32 + 1024;
 constexpr int kNoBlock = 0x7fffffff;
 
 enum : uint32_t { kFlagFirst = 1u, kFlagLast = 2u, kFlagEnd = 4u };
 
-#ifdef STK_EXP_PROFILE  // experiment: where each role of each CTA spends its cycles
-__device__ long long g_prof[160][8];
-#define PROF_DECL long long prof_wait = 0, prof_t0 = clock64(), prof_tmp = 0; (void)prof_tmp
-#define PROF_WAIT_BEGIN prof_tmp = clock64()
-#define PROF_WAIT_END prof_wait += clock64() - prof_tmp
-#define PROF_STORE(slot) do { g_prof[blockIdx.x][slot] = prof_wait; g_prof[blockIdx.x][slot + 1] = clock64() - prof_t0; } while (0)
-#else
-#define PROF_DECL
-#define PROF_WAIT_BEGIN
-#define PROF_WAIT_END
-#define PROF_STORE(slot)
-#endif
 
 struct PairParams {
   int mode;
@@ -85,6 +72,7 @@ struct PairParams {
   void* out;
   long long ldc;
   const void* aux;  // SDD with kEpilogueGeluKeep / kEpilogueGeluGrad: the auxiliary tensor
+  const int32_t* plan;  // work-item table written by pair_plan_kernel (plan_sm100.cuh), or nullptr
 };
 
 // Two-pointer merge of the K lists of a pair of block rows (DSD) / block columns (DDS).
@@ -213,24 +201,25 @@ __device__ __forceinline__ void load_operand_pair(const CUtensorMap* tm, uint32_
 // of the pair computing one of them.  Blind pairs (0,1), (2,3), ... go wrong where two experts of a
 // dMoE topology meet at an odd row: the two rows' block lists cannot overlap (the last column of one
 // lies before the first column of the other), so the pair runs for the sum of both lists with half
-// of every MMA wasted, and every pair behind it may be misaligned as well.  The kernel therefore
-// cuts the rows into runs at those places and pairs inside each run; a run of odd length ends in a
-// single row.  Items of such a topology are then equally long, and dealing them round-robin
-// balances the CTA pairs.  Runs are listed longest block lists first: run_start[k] / run_end[k] = rows of
-// the k-th run in that order, run_cum[k] = groups before it.
+// of every MMA wasted, and every pair behind it may be misaligned as well.  The lists are therefore
+// cut into runs at those places and paired inside each run, a run of odd length ending in a single
+// list; that table is computed once per topology (pair_plan_kernel) and read here, one entry per
+// item.  Without a table the kernel pairs blindly, which is still exact.
 struct PairItem {
-  int r, part, inner;  // first row of the group, 0 = rows r and r + 1 / 1 = row r alone, dense supertile
+  int r, part, inner;  // first list of the group, 0 = lists r and r + 1 / 1 = list r alone, dense supertile
 };
-__device__ __forceinline__ PairItem decode_item(int item, int inner_count, const int* run_start,
-                                                const int* run_end, const int* run_cum,
-                                                int num_runs) {
+__device__ __forceinline__ PairItem decode_item(const PairParams& p, int item) {
   PairItem it;
-  const int g = item / inner_count;
-  it.inner = item - g * inner_count;
-  int k = 0;
-  while (k + 1 < num_runs && run_cum[k + 1] <= g) ++k;
-  it.r = run_start[k] + 2 * (g - run_cum[k]);
-  it.part = it.r + 1 >= run_end[k] ? 1 : 0;
+  const int g = item / p.inner;
+  it.inner = item - g * p.inner;
+  if (p.plan != nullptr) {
+    const int e = __ldg(p.plan + 1 + g);
+    it.r = e & 0x3fffffff;
+    it.part = (e >> 30) & 1;
+  } else {
+    it.r = 2 * g;
+    it.part = it.r + 1 >= p.num_lists ? 1 : 0;
+  }
   return it;
 }
 
@@ -255,15 +244,6 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint32_t* tmem_slot = const_cast<uint32_t*>(stage_flags) + kPStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* epilogue_go = abort_flag + 1;  // [2], one per epilogue group
-  int* break_count = const_cast<int*>(epilogue_go) + 2;
-  int* breaks = break_count + 1;                 // [kMaxBreaks + 2]
-  int* run_start = breaks + kMaxBreaks + 2;      // [kMaxBreaks + 2] first row of each run, in dealing order
-  int* run_end = run_start + kMaxBreaks + 2;     // [kMaxBreaks + 2] one past its last row
-  int* run_cum = run_end + kMaxBreaks + 2;       // [kMaxBreaks + 2] groups before each run
-  int* run_cost = run_cum + kMaxBreaks + 2;      // [kMaxBreaks + 2] blocks in the run's first list
-#ifdef STK_EXP_PROFILE
-  __shared__ long long ts_issue[kPStages], ts_commit[kPStages];
-#endif
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -281,7 +261,6 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(tempty_bar(a), 2 * kPEpilogueWarps);  // leader's copy: the epilogue warps of both CTAs
     }
     *abort_flag = 0;
-    *break_count = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
@@ -291,68 +270,18 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tmem_alloc_pair(smem_u32(tmem_slot), kPTmemCols);
     tmem_relinquish_pair();
   }
-  // Everything above touched only this SM; from here on global memory is read.  With a programmatic
-  // dependent launch this is where the kernel waits for the one before it in the stream, and the
-  // next kernel may be scheduled onto SMs as this grid drains (its set-up then overlaps our tail).
-  pdl_launch_dependents();
-  pdl_wait();
-  __syncthreads();
-  // Every CTA finds the cuts by itself (same metadata, same answer in both CTAs).
-  for (int r = threadIdx.x; r + 1 < p.num_lists; r += kPThreads) {
-    const int a0 = p.offsets[r], a1 = p.offsets[r + 1], b1 = p.offsets[r + 2];
-    if (a0 >= a1 || a1 >= b1) continue;
-    const int a_first = __ldg(p.col_idx + a0), a_last = __ldg(p.col_idx + a1 - 1);
-    const int b_first = __ldg(p.col_idx + a1), b_last = __ldg(p.col_idx + b1 - 1);
-    if (a_last < b_first || b_last < a_first) {
-      const int pos = atomicAdd(break_count, 1);
-      if (pos < kMaxBreaks) breaks[pos] = r;
-    }
-  }
-  __syncthreads();
-  {
-    // The runs, longest block lists first: items are dealt round-robin in this order, so every CTA
-    // pair takes its expensive items first and the cheap ones level the load (experts of a dMoE
-    // layer differ in tokens, i.e. in the K length of the weight-gradient products).  All sorting
-    // is by rank counting, one thread per element.
-    int n = *break_count;
-    if (n > kMaxBreaks) n = 0;  // not a dMoE-like topology: one run, blind pairs
-    const int runs = n + 1, k = threadIdx.x;
-    if (k < n) {
-      int rank_k = 0;
-      for (int j2 = 0; j2 < n; ++j2) rank_k += breaks[j2] < breaks[k] ? 1 : 0;
-      run_cum[rank_k] = breaks[k];  // run_cum doubles as the sorted list of cuts
-    }
-    __syncthreads();
-    int start = 0, end = 0, cost = 0;
-    if (k < runs && p.num_lists > 0) {
-      start = k == 0 ? 0 : run_cum[k - 1] + 1;
-      end = k == n ? p.num_lists : run_cum[k] + 1;
-      cost = p.offsets[start + 1] - p.offsets[start];
-      run_cost[k] = cost;
-    }
-    __syncthreads();
-    if (k < runs && p.num_lists > 0) {
-      int rank_k = 0;
-      for (int j2 = 0; j2 < runs; ++j2)
-        rank_k += (run_cost[j2] > cost || (run_cost[j2] == cost && j2 < k)) ? 1 : 0;
-      run_start[rank_k] = start;
-      run_end[rank_k] = end;
-    }
-    __syncthreads();
-    if (k == 0) {
-      run_cum[0] = 0;
-      for (int i2 = 0; i2 < runs; ++i2)
-        run_cum[i2 + 1] = p.num_lists > 0 ? run_cum[i2] + (run_end[i2] - run_start[i2] + 1) / 2 : 0;
-      *break_count = n;
-    }
-  }
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();  // the peer's barriers exist before anything is sent to them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int num_runs = *break_count + 1;
-  const int num_items = run_cum[num_runs] * p.inner;
+  // Everything above touched only this SM pair; from here on global memory is read.  With a
+  // programmatic dependent launch this is where the kernel waits for the one before it in the stream,
+  // and the next kernel may be scheduled onto SMs as this grid drains (its set-up then overlaps our
+  // tail).
+  pdl_launch_dependents();
+  pdl_wait();
+  const int num_items = p.plan != nullptr ? __ldg(p.plan) * p.inner : p.num_items;
 
   if (warp == 0 || warp == kPProducerBWarp) {
     // ------------------------------------------------------------------ TMA producers (both CTAs)
@@ -368,36 +297,16 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      PROF_DECL;
-#ifdef STK_EXP_PROFILE
-      long long prof_d2 = 0, prof_n2 = 0;
-      if (is_a && rank == 0) for (int i = 0; i < kPStages; ++i) { ts_issue[i] = 0; ts_commit[i] = 0; }
-#endif
       // One pipeline stage of this operand: the tile at (mn_elem, k_elem).
       auto produce = [&](int mn_elem, int k_elem, uint32_t flags) {
-        PROF_WAIT_BEGIN;
         ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
-        PROF_WAIT_END;
         if (!ok) return;
-#ifdef STK_EXP_PROFILE
-        if (is_a && rank == 0) {
-          const long long now = clock64();
-          if (ts_commit[stage] != 0) { prof_d2 += now - ts_commit[stage]; ++prof_n2; }
-          ts_issue[stage] = now;
-        }
-#endif
         if (arms) {
           stage_flags[stage] = flags;
-#ifdef STK_EXP_SKIP_TMA  // experiment: MMA issue rate with the operand fetch taken out
-          mbar_arrive(full_bar(stage));
-#else
           mbar_arrive_expect_tx(full_bar(stage), 2 * kStageBytes);
-#endif
         }
-#ifndef STK_EXP_SKIP_TMA
         load_operand_pair(tm, dst0 + stage * kStageBytes, leader_full0 + 8u * stage, mn_major, mn_elem,
                           k_elem);
-#endif
         if (++stage == kPStages) {
           stage = 0;
           phase ^= 1u;
@@ -405,12 +314,9 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       };
       // Is this thread's operand the sparse one (DSD: A, DDS: B)?
       const bool sparse_side = (p.mode == kModeDSD) == is_a;
-#ifdef STK_EXP_ONE_PRODUCER  // experiment (DSD only): one thread per CTA issues both operands' loads
-      if (p.mode == kModeDSD && !is_a) goto producer_done;
-#endif
       for (int item = pair_id; item < num_items && ok; item += num_pairs) {
         if (p.mode == kModeSDD) {
-          const PairItem it = decode_item(item, p.inner, run_start, run_end, run_cum, num_runs);
+          const PairItem it = decode_item(p, item);
           TileWalker w;
           w.init(p, it.r, it.inner, it.part);
           int u, blk[2][2];
@@ -421,7 +327,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                       (ks == 0 ? kFlagFirst : 0u) | (ks == p.k_steps - 1 ? kFlagLast : 0u));
           }
         } else {
-          const PairItem it = decode_item(item, p.inner, run_start, run_end, run_cum, num_runs);
+          const PairItem it = decode_item(p, item);
           MergeWalker w;
           w.init(p, it.r, it.part);
           uint32_t first = kFlagFirst;
@@ -440,37 +346,12 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               mn_elem = it.inner * 2 * kBlk + rank * kBlk;
               k_elem = kpos * kBlk;
             }
-#ifdef STK_EXP_ONE_PRODUCER
-            if (p.mode == kModeDSD) {
-              const int b_mn_elem = it.inner * 2 * kBlk + rank * kBlk, b_k_elem = kpos * kBlk;
-              for (int ks = 0; ks < 2 && ok; ++ks) {
-                ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
-                if (!ok) break;
-                if (arms) {
-                  stage_flags[stage] = ks == 0 ? first : last;
-                  mbar_arrive_expect_tx(full_bar(stage), 2 * kStageBytes);
-                }
-                load_operand_pair(&tmA, smem_base + stage * kStageBytes, leader_full0 + 8u * stage, p.a_mn, mn_elem, k_elem + ks * kBK);
-                load_operand_pair(&tmB, smem_base + kOperandTileBytes + stage * kStageBytes, leader_full0 + 8u * stage, p.b_mn, b_mn_elem, b_k_elem + ks * kBK);
-                if (++stage == kPStages) { stage = 0; phase ^= 1u; }
-              }
-              first = 0u;
-              continue;
-            }
-#endif
             produce(mn_elem, k_elem, first);
             if (ok) produce(mn_elem, k_elem + kBK, last);
             first = 0u;
           }
         }
       }
-#ifdef STK_EXP_ONE_PRODUCER
-    producer_done:
-#endif
-      PROF_STORE(is_a ? 0 : 6);
-#ifdef STK_EXP_PROFILE
-      if (is_a && rank == 0) { g_prof[blockIdx.x + 1][0] = prof_d2; g_prof[blockIdx.x + 1][1] = prof_n2; }
-#endif
       // The leader tells its MMA issuer that the stream is over.
       if (arms && ok) {
         if (mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
@@ -492,10 +373,6 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
-      PROF_DECL;
-#ifdef STK_EXP_PROFILE
-      long long prof_acc_wait = 0, prof_d1 = 0, prof_n1 = 0, prof_mma = 0;
-#endif
       // The tensor pipe queues only an MMA or two ahead of the one it executes, so whatever this
       // thread does between the last MMA of a stage and the first of the next (a barrier poll costs
       // over a hundred cycles even when the phase is complete) shows up as idle tensor cycles.  The
@@ -505,24 +382,13 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t flags = 0;
       while (true) {
         if (!ready) {
-          PROF_WAIT_BEGIN;
           const bool got = mbar_wait(full_bar(stage), phase, abort_flag);
-          PROF_WAIT_END;
           if (!got) break;
           flags = stage_flags[stage];
         }
-#ifdef STK_EXP_PROFILE
-        { const long long now = clock64(); prof_d1 += now - ts_issue[stage]; ++prof_n1; }
-#endif
         if (flags & kFlagEnd) break;
         if (flags & kFlagFirst) {
-#ifdef STK_EXP_PROFILE
-          const long long t1 = clock64();
-#endif
           if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) break;
-#ifdef STK_EXP_PROFILE
-          prof_acc_wait += clock64() - t1;
-#endif
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kPAccCols);
@@ -530,19 +396,12 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint32_t b_lo = b_lo0 + stage * (kStageBytes >> 4);
         const int next_stage = stage + 1 == kPStages ? 0 : stage + 1;
         const uint32_t next_phase = stage + 1 == kPStages ? phase ^ 1u : phase;
-#ifndef STK_EXP_SKIP_MMA  // experiment: operand fetch rate with the MMAs taken out
         umma_f16_pair(d_tmem, smem_desc_join(a_lo), smem_desc_join(b_lo), idesc, (flags & kFlagFirst) ? 0u : 1u);
         umma_f16_pair(d_tmem, smem_desc_join(a_lo + a_kstep), smem_desc_join(b_lo + b_kstep), idesc, 1u);
-#endif
         ready = mbar_test_wait(full_bar(next_stage), next_phase);
         const uint32_t next_flags = stage_flags[next_stage];  // not waited for here; only used if `ready`
-#ifndef STK_EXP_SKIP_MMA
         umma_f16_pair(d_tmem, smem_desc_join(a_lo + 2 * a_kstep), smem_desc_join(b_lo + 2 * b_kstep), idesc, 1u);
         umma_f16_pair(d_tmem, smem_desc_join(a_lo + 3 * a_kstep), smem_desc_join(b_lo + 3 * b_kstep), idesc, 1u);
-#endif
-#ifdef STK_EXP_PROFILE
-        ts_commit[stage] = clock64();
-#endif
         umma_commit_pair(empty_bar(stage), 3);  // frees the stage in both CTAs
         if (flags & kFlagLast) {
           umma_commit_pair(tfull_bar(acc), 3);  // accumulator halves ready in both CTAs
@@ -553,12 +412,6 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         phase = next_phase;
         flags = next_flags;
       }
-      PROF_STORE(2);
-#ifdef STK_EXP_PROFILE
-      g_prof[blockIdx.x][4] = prof_acc_wait;
-      g_prof[blockIdx.x + 1][2] = prof_d1;
-      g_prof[blockIdx.x + 1][3] = prof_n1;
-#endif
     }
     __syncwarp();
   } else {
@@ -595,7 +448,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint16_t* out = static_cast<uint16_t*>(p.out);
     for (int item = pair_id; item < num_items && ok; item += num_pairs) {
       if (p.mode == kModeSDD) {
-        const PairItem it = decode_item(item, p.inner, run_start, run_end, run_cum, num_runs);
+        const PairItem it = decode_item(p, item);
         TileWalker w;
         w.init(p, it.r, it.inner, it.part);
         int u, blk[2][2];
@@ -603,7 +456,6 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint32_t t_addr;
           acquire(t_addr);
           if (!ok) break;
-#ifndef STK_EXP_SKIP_EPILOGUE
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int pb = blk[rank][h];
@@ -612,11 +464,10 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                       staging, row, group, group, 2, issuer,
                                       EpilogueAux{&tmX, static_cast<const uint16_t*>(p.aux)});
           }
-#endif
           release();
         }
       } else {
-        const PairItem it = decode_item(item, p.inner, run_start, run_end, run_cum, num_runs);
+        const PairItem it = decode_item(p, item);
         MergeWalker w;
         w.init(p, it.r, it.part);
         // This CTA's 128 output rows and the 256 output columns of the supertile.  In a single-row
@@ -639,11 +490,9 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t t_addr;
         acquire(t_addr);
         if (!ok) break;
-#ifndef STK_EXP_SKIP_EPILOGUE  // experiment: the main loop without the drain of the accumulators
         if (rows_valid)
           drain_to_output(t_addr, 0, ncols, p.fmt, p.epilogue, &tmC, tile_col, tile_row, staging, row,
                           group, group, 2, issuer);
-#endif
         release();
       }
     }
@@ -705,9 +554,6 @@ static int pair_device_info(PairDeviceInfo** out) {
       clusters = sms / 2;
     }
     d.max_pairs = clusters < sms / 2 ? clusters : sms / 2;
-#ifdef STK_EXP_MAX_PAIRS  // experiment: how the per-stage time depends on the number of active CTA pairs
-    if (d.max_pairs > STK_EXP_MAX_PAIRS) d.max_pairs = STK_EXP_MAX_PAIRS;
-#endif
   }
   *out = &d;
   return STK_OK;

@@ -187,9 +187,6 @@ __device__ __forceinline__ void drain_to_output_plain(uint32_t t_addr, int col0,
                                                 int epilogue, const CUtensorMap* tmC, int out_x,
                                                 int out_y, uint32_t staging, int row, int group,
                                                 int first, int step, bool issuer) {
-#ifdef STK_EXP_SKIP_EPILOGUE  // experiment: main loop alone, nothing drained or stored
-  return;
-#endif
   for (int c = first * 64; c < ncols; c += step * 64) {
     if (issuer) tma_store_wait_read<0>();  // the group's previous store is done reading the tile
     epilogue_sync(group);
@@ -326,9 +323,6 @@ __device__ __forceinline__ void drain_to_output(uint32_t t_addr, int col0, int n
                                                 int out_y, uint32_t staging, int row, int group,
                                                 int first, int step, bool issuer,
                                                 EpilogueAux aux = EpilogueAux{nullptr, nullptr}) {
-#ifdef STK_EXP_SKIP_EPILOGUE  // experiment: main loop alone, nothing drained or stored
-  return;
-#endif
   // the epilogue kind is a compile-time parameter of the body: the plain and GeLU forms keep their
   // short code whatever the two training forms need
   if constexpr (!kTrain) {
@@ -405,13 +399,9 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           const uint32_t b_dst = a_dst + kOperandTileBytes;
-#ifdef STK_EXP_SKIP_TMA  // experiment: MMA issue rate with the operand fetch taken out
-          mbar_arrive(full_bar(stage));
-#else
           mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
           load_operand(&tmA, a_dst, full_bar(stage), p.a_mn, a_mn_elem, a_k_elem);
           load_operand(&tmB, b_dst, full_bar(stage), p.b_mn, b_mn_elem, b_k_elem);
-#endif
         } else {
           ok = 0;
         }
@@ -496,15 +486,11 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const uint32_t b_lo = b_lo0 + stage * (kStageBytes >> 4);
           const int next_stage = stage + 1 == kStages ? 0 : stage + 1;
           const uint32_t next_phase = stage + 1 == kStages ? phase ^ 1u : phase;
-#ifndef STK_EXP_SKIP_MMA  // experiment: operand fetch rate with the MMAs taken out
           umma_f16(d_tmem, smem_desc_join(a_lo), smem_desc_join(b_lo), idesc, accumulate);
           umma_f16(d_tmem, smem_desc_join(a_lo + a_kstep), smem_desc_join(b_lo + b_kstep), idesc, 1u);
-#endif
           ready = mbar_test_wait(full_bar(next_stage), next_phase);
-#ifndef STK_EXP_SKIP_MMA
           umma_f16(d_tmem, smem_desc_join(a_lo + 2 * a_kstep), smem_desc_join(b_lo + 2 * b_kstep), idesc, 1u);
           umma_f16(d_tmem, smem_desc_join(a_lo + 3 * a_kstep), smem_desc_join(b_lo + 3 * b_kstep), idesc, 1u);
-#endif
           accumulate = 1u;
           umma_commit(empty_bar(stage));  // the stage is free once these MMAs have read it
           stage = next_stage;

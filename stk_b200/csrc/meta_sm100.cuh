@@ -11,6 +11,7 @@
 #include <stdint.h>
 
 #include "../../include/stk_b200.h"
+#include "status.cuh"
 
 namespace stk {
 
@@ -115,18 +116,21 @@ static inline TransposePlan plan_transpose(int64_t nnz, int64_t block_cols,
 
 // Shared by both paths: one warp scatters blocks [begin, end) given per-column start positions
 // `colstart` and its group's rank counters `hist_g` (shared or global memory).
+// A block whose column index lies outside [0, block_cols) is left out (the reference's histc drops
+// such values too) and reported through the status word; it never indexes the counters.
 __device__ __forceinline__ void scatter_group(const int16_t* __restrict__ rows,
                                               const int16_t* __restrict__ cols, int begin, int end,
-                                              const int32_t* colstart, int32_t* hist_g,
+                                              int block_cols, const int32_t* colstart, int32_t* hist_g,
                                               int16_t* __restrict__ column_indices_t,
                                               int32_t* __restrict__ block_offsets_t) {
   const int lane = threadIdx.x & 31;
   const uint32_t lt_mask = (1u << lane) - 1u;
   for (int base = begin; base < end; base += 32) {
     const int i = base + lane;
-    const bool active = i < end;
+    int c = i < end ? static_cast<int>(cols[i]) : -1;
+    const bool active = static_cast<unsigned>(c) < static_cast<unsigned>(block_cols);
     // Inactive lanes get distinct negative keys so that they never match a column.
-    const int key = active ? static_cast<int>(cols[i]) : -1 - lane;
+    const int key = active ? c : -1 - lane;
     const uint32_t peers = __match_any_sync(0xffffffffu, key);
     const int rank = __popc(peers & lt_mask);
     const int leader = __ffs(peers) - 1;
@@ -154,7 +158,11 @@ transpose_fused_kernel(const int16_t* __restrict__ rows, const int16_t* __restri
   for (int i = tid; i < kFusedGroups * block_cols; i += kFusedThreads) hist[i] = 0;
   __syncthreads();
   const int begin = min(nnz, warp * chunk), end = min(nnz, begin + chunk);
-  for (int i = begin + lane; i < end; i += 32) atomicAdd(&hist[warp * block_cols + cols[i]], 1);
+  for (int i = begin + lane; i < end; i += 32) {
+    const int c = cols[i];
+    if (static_cast<unsigned>(c) < static_cast<unsigned>(block_cols)) atomicAdd(&hist[warp * block_cols + c], 1);
+    else report_status(STK_ERR_BAD_DIMS);
+  }
   __syncthreads();
   // prefix over groups; colstart[c] = blocks in column c
   for (int c = tid; c < block_cols; c += kFusedThreads) {
@@ -205,7 +213,7 @@ transpose_fused_kernel(const int16_t* __restrict__ rows, const int16_t* __restri
     }
   }
   __syncthreads();
-  scatter_group(rows, cols, begin, end, colstart, hist + warp * block_cols, column_indices_t,
+  scatter_group(rows, cols, begin, end, block_cols, colstart, hist + warp * block_cols, column_indices_t,
                 block_offsets_t);
 }
 
@@ -217,7 +225,11 @@ __global__ void transpose_count_kernel(const int16_t* __restrict__ cols, int nnz
   if (g >= groups) return;
   const int begin = min(nnz, g * chunk), end = min(nnz, begin + chunk);
   int32_t* hist_g = hist + static_cast<int64_t>(g) * block_cols;
-  for (int i = begin + lane; i < end; i += 32) atomicAdd(&hist_g[cols[i]], 1);
+  for (int i = begin + lane; i < end; i += 32) {
+    const int c = cols[i];
+    if (static_cast<unsigned>(c) < static_cast<unsigned>(block_cols)) atomicAdd(&hist_g[c], 1);
+    else report_status(STK_ERR_BAD_DIMS);
+  }
 }
 
 // General path, kernel 2: per column, exclusive prefix over the groups; column totals to counts[c].
@@ -245,7 +257,7 @@ __global__ void transpose_scatter_kernel(const int16_t* __restrict__ rows,
   const int g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (g >= groups) return;
   const int begin = min(nnz, g * chunk), end = min(nnz, begin + chunk);
-  scatter_group(rows, cols, begin, end, offsets_t, hist + static_cast<int64_t>(g) * block_cols,
+  scatter_group(rows, cols, begin, end, block_cols, offsets_t, hist + static_cast<int64_t>(g) * block_cols,
                 column_indices_t, block_offsets_t);
 }
 

@@ -7,6 +7,7 @@
 #include "status.cuh"
 #include "bsmm_api.cuh"
 #include "meta_sm100.cuh"
+#include "plan_sm100.cuh"
 #include "dmoe_sm100.cuh"
 
 extern "C" int stk_b200_version(void) { return STK_B200_VERSION; }
@@ -40,8 +41,3 @@ extern "C" int stk_b200_device_status(int* status_host) {
   return STK_OK;
 }
 
-#ifdef STK_EXP_PROFILE
-extern "C" int stk_b200_exp_profile(long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, stk::g_prof, sizeof(long long) * 160 * 8) == cudaSuccess ? 0 : -6;
-}
-#endif

@@ -429,8 +429,16 @@ class HostPipeline:
         self.pending = None                  # slot whose inputs are on their way but not yet computed
 
     def _upload(self, slot, host_tensors):
-        if self.inputs[slot] is None:
-            self.inputs[slot] = [torch.empty(t.shape, dtype=t.dtype, device=self.device) for t in host_tensors]
+        bufs = self.inputs[slot]
+        stale = bufs is None or len(bufs) != len(host_tensors) or any(
+            b.shape != t.shape or b.dtype != t.dtype for b, t in zip(bufs, host_tensors))
+        if stale:
+            # New buffers may reuse memory that kernels queued on the current stream still read: the
+            # copy-in stream first catches up with it, and the buffers belong to the copy-in stream.
+            self.copy_in.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self.copy_in):
+                self.inputs[slot] = [torch.empty(t.shape, dtype=t.dtype, device=self.device)
+                                     for t in host_tensors]
         with torch.cuda.stream(self.copy_in):
             if self.in_free[slot] is not None:
                 self.copy_in.wait_event(self.in_free[slot])     # the step that read this buffer is done
