@@ -246,27 +246,35 @@ int stk_b200_to_dense(const void* data, const int32_t* offsets, const int16_t* c
 
 /*
  * dMoE plumbing around the products (the callers' side of stk.Matrix / sdd / dsd in a dropless-MoE
- * layer; the reference is a matmul library and has no counterpart for these four).
+ * layer; the reference is a matmul library and has no counterpart for these).
  *
- * gather_rows : dst[i] = index[i] >= 0 ? src[index[i]] : zeros      (i < n_rows output rows)
+ * gather_rows : dst[i] = index[i] >= 0 ? src[index[i] / index_div] : zeros   (i < n_rows output rows)
+ *   index_div = 1 for plain row indices; index_div = k when index holds top-k slots
+ *   (slot = token * k + choice) and src holds one row per token.
  * scatter_rows: dst[index[i]] = src[i] for index[i] >= 0            (i < n_rows input rows)
  *   Rows are row_bytes long (a multiple of 16), src / dst 16-byte aligned.
+ * weighted_sum_rows: dst[t] = sum_{j<k} weights[t*k+j] * src[pos ? pos[t*k+j] : t*k+j] for t < tokens,
+ *   fp32 accumulation, one rounding to `dtype` (STK_F16 / STK_BF16): the weighted top-k combine.
+ *   pos == NULL: src is slot-ordered; weights == NULL: all ones; a negative pos contributes nothing.
  * bin_index   : gather index that puts the token rows received from `world` peers (each peer's rows
  *   ordered by local expert; counts[p*local_experts+e] rows from peer p for expert e, int64) into
  *   per-expert bins padded to a multiple of `block` rows: rows of expert e ordered by peer, then
  *   padding (index -1).  total_padded = sum of the padded bin sizes (the caller knows the counts).
  *   If `compose` is not NULL the source row s is replaced by compose[s] (e.g. a sort order).
- *   bin_rows[e] (optional) receives padded rows of expert e / block.
+ *   bin_rows[e] (optional) receives padded rows of expert e / block.  inverse (optional, as long as
+ *   the largest index + 1): inverse[index[r]] = r for every row r that is not padding.
  * dmoe_topology: blocked CSR-COO metadata, row- and column-major, of the block-diagonal matrix in
  *   which expert e owns bin_rows[e] block rows and block columns [e*cpb, (e+1)*cpb).
  */
 int stk_b200_gather_rows(const void* src, void* dst, const int32_t* index, int64_t n_rows,
-                         int64_t row_bytes, void* stream);
+                         int64_t row_bytes, int index_div, void* stream);
 int stk_b200_scatter_rows(const void* src, void* dst, const int32_t* index, int64_t n_rows,
                           int64_t row_bytes, void* stream);
+int stk_b200_weighted_sum_rows(const void* src, const int32_t* pos, const float* weights, void* dst,
+                               int64_t tokens, int top_k, int64_t row_bytes, int dtype, void* stream);
 int stk_b200_bin_index(const int64_t* counts, int world, int local_experts, int block,
                        const int32_t* compose, int32_t* index, int64_t total_padded,
-                       int32_t* bin_rows, void* stream);
+                       int32_t* bin_rows, int32_t* inverse, void* stream);
 int stk_b200_dmoe_topology(const int32_t* bin_rows, int experts, int cols_per_expert,
                            int64_t block_rows, int16_t* row_indices, int16_t* column_indices,
                            int32_t* offsets, int16_t* column_indices_t, int32_t* offsets_t,
@@ -280,37 +288,58 @@ int stk_b200_dmoe_topology(const int32_t* bin_rows, int experts, int cols_per_ex
 int stk_b200_copy_bytes(const void* src, void* dst, int64_t nbytes, void* stream);
 
 /*
- * Expert-parallel token exchange over peer memory (NVLink).  No counterpart in the reference, which
- * is single-GPU; these move the rows that stk.ops.sdd / dsd work on between the ranks of an
- * expert-parallel dMoE layer without a host-side collective: every rank pushes its token rows into
- * the padded expert bins of the owning rank and pulls the results back.  `peer_bufs[r]` is rank r's
- * buffer as mapped in THIS process (symmetric memory), `cap_rows` its capacity in rows; the caller
- * puts a barrier between ranks after the count exchange, after dispatch and before combine.
- * A row that would fall outside a buffer is skipped and STK_ERR_WORKSPACE is recorded in the status
- * word (stk_b200_device_status).
+ * Expert-parallel token exchange over peer memory (NVLink), top-k routing.  No counterpart in the
+ * reference, which is single-GPU; these move the rows that stk.ops.sdd / dsd work on between the
+ * ranks of an expert-parallel dMoE layer without a host-side collective.  A rank holds `tokens`
+ * tokens with top_k expert choices each (slot = token * top_k + choice).  It pushes the token row of
+ * every slot into the padded bin of the slot's expert on the rank that owns the expert, with a tag
+ * naming the slot's home; after the experts' MLP the owner pushes every result row into the home
+ * rank's slot-ordered buffer, and stk_b200_weighted_sum_rows combines the top_k rows of a token.
+ * Only stores go to a peer.  `peer_*[r]` is rank r's buffer as mapped in THIS process (symmetric
+ * memory); the caller puts a barrier between ranks after the count exchange, after dispatch and
+ * after return.  A row that would fall outside a buffer is skipped and STK_ERR_WORKSPACE is
+ * recorded in the status word (stk_b200_device_status).
+ * The local experts of every rank can be handled in `chunks` groups of consecutive experts (chunk c =
+ * local experts [c*L/chunks, (c+1)*L/chunks), L = experts / world), so that the exchange of one group
+ * overlaps the products of another; chunks <= STK_EP_MAX_CHUNKS.
+ *   ep_barrier: all ranks meet on the stream.  peer_flags[r] = rank r's flag array (int64 [world],
+ *               zero before the first use); every rank stores `epoch` into slot `rank` of every
+ *               array and waits until its own array holds `epoch` everywhere.  `epoch` starts at 1 and
+ *               grows by one per barrier on the same arrays, identically on all ranks.  The wait gives
+ *               up after timeout_ms and records STK_ERR_DEVICE_TIMEOUT in the status word (nothing
+ *               traps).  One rank per GPU: ranks sharing a GPU must not use it.
  *   ep_share_counts: row `rank` of every rank's count matrix (peer_counts[r], int32
- *               [world*experts]) <- offsets[e+1] - offsets[e], this rank's tokens per expert.
- *   ep_plan:    counts_all[s*experts+e] = tokens of rank s for global expert e (int32, the same
+ *               [world*experts]) <- offsets[e+1] - offsets[e], this rank's slots per expert.
+ *   ep_plan:    counts_all[s*experts+e] = slots of rank s for global expert e (int32, the same
  *               matrix on every rank).  Writes dest_base[e] (row in the owner's buffer where this
  *               rank's rows of expert e start), bin_rows[le] (blocks of this rank's local bins),
- *               totals[0] = padded rows of this rank, totals[1] = rows it receives.
- *   ep_zero_padding: zero rows that close each local bin in `recv`.
- *   ep_dispatch: x[order[q]] -> owner's buffer row dest_base[e] + (q - offsets[e]) for every sorted
- *               position q in expert segment e (order / offsets as produced by a stable sort of
- *               the tokens by expert); dest[t] = owner << 40 | row for token t.
- *   ep_combine: out[t] = row dest[t] of the owner's result buffer (zeros for a skipped token).
+ *               totals[0] = padded rows of this rank, totals[1] = rows it receives, totals[2] = the
+ *               largest padded row count of any rank (identical on all ranks: compare it with the
+ *               capacity and every rank takes the same decision), totals[3+c] = padded rows of this
+ *               rank's chunk c.  totals: int64 [3 + chunks].
+ *   ep_zero_padding: zero rows that close each local bin in `recv`; their tags become -1.
+ *   ep_dispatch: for every sorted position q in expert segment e whose expert lies in chunk `chunk`
+ *               of its owner: x[order[q] / top_k] -> owner's buffer row dest_base[e] + (q - offsets[e]),
+ *               tag rank << 40 | order[q] -> owner's tags (order / offsets as produced by a stable
+ *               sort of the slots by expert).
+ *   ep_return:  rows [row0, row0 + n_rows) of `result` -> row (tag & (2^40 - 1)) of the slot-ordered
+ *               buffer of rank tag >> 40 (peer_slots); rows with a negative tag are padding.
  */
+#define STK_EP_MAX_CHUNKS 8
+int stk_b200_ep_barrier(const uint64_t* peer_flags, int world, int rank, int64_t epoch, int64_t timeout_ms,
+                        void* stream);
 int stk_b200_ep_share_counts(const int32_t* offsets, const uint64_t* peer_counts, int world, int experts,
                              int rank, void* stream);
-int stk_b200_ep_plan(const int32_t* counts_all, int world, int experts, int rank, int block,
+int stk_b200_ep_plan(const int32_t* counts_all, int world, int experts, int rank, int block, int chunks,
                      int64_t* dest_base, int32_t* bin_rows, int64_t* totals, void* stream);
 int stk_b200_ep_zero_padding(const int32_t* counts_all, int world, int experts, int rank, int block,
-                             void* recv, int64_t row_bytes, int64_t cap_rows, void* stream);
+                             void* recv, int64_t* tags, int64_t row_bytes, int64_t cap_rows, void* stream);
 int stk_b200_ep_dispatch(const void* x, const int32_t* order, const int32_t* offsets,
-                         const int64_t* dest_base, const uint64_t* peer_bufs, int64_t tokens, int world,
-                         int experts, int64_t row_bytes, int64_t cap_rows, int64_t* dest, void* stream);
-int stk_b200_ep_combine(const uint64_t* peer_bufs, const int64_t* dest, void* out, int64_t tokens,
-                        int64_t row_bytes, int64_t cap_rows, void* stream);
+                         const int64_t* dest_base, const uint64_t* peer_bufs, const uint64_t* peer_tags,
+                         int64_t slots, int top_k, int world, int experts, int rank, int chunk, int chunks,
+                         int64_t row_bytes, int64_t cap_rows, void* stream);
+int stk_b200_ep_return(const void* result, const int64_t* tags, const uint64_t* peer_slots, int64_t row0,
+                       int64_t n_rows, int world, int64_t row_bytes, int64_t slot_cap, void* stream);
 
 #ifdef __cplusplus
 }

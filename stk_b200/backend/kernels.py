@@ -252,8 +252,8 @@ def _same_dtype(what, *tensors):
 def dsd(shape, data, offsets, row_indices, column_indices, offsets_t, column_indices_t,
         block_offsets_t, transpose_a, rhs, out):
     """out = op(S) @ rhs, S given by its blocked CSR-COO fields; `shape` is op(S)'s shape."""
-    _require_cuda(data, rhs, out)
     _same_dtype("dsd", data, rhs, out)
+    _require_cuda(data, rhs, out)
     if shape[1] != rhs.shape[0]:
         raise DimensionError("incompatible dimensions")
     M, K = shape
@@ -282,8 +282,8 @@ def dsd(shape, data, offsets, row_indices, column_indices, offsets_t, column_ind
 def dds(lhs, shape, data, offsets, row_indices, column_indices, offsets_t, column_indices_t,
         block_offsets_t, transpose_b, out):
     """out = lhs @ op(S); `shape` is op(S)'s shape."""
-    _require_cuda(lhs, data, out)
     _same_dtype("dds", lhs, data, out)
+    _require_cuda(lhs, data, out)
     if lhs.shape[1] != shape[0]:
         raise DimensionError("incompatible dimensions")
     M, K = lhs.shape
@@ -313,8 +313,8 @@ def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices, epilogue=0, 
     Extensions: epilogue=1 stores GeLU of the product instead (stk_b200.ops.sdd_gelu); epilogue=2
     stores the product in out and its GeLU in aux; epilogue=3 stores product * GeLU'(aux)
     (stk_b200.dmoe.expert_mlp).  aux has out's shape and dtype."""
-    _require_cuda(lhs, rhs, out)
     _same_dtype("sdd", lhs, rhs, out, aux)
+    _require_cuda(lhs, rhs, out)
     if (epilogue in (2, 3)) != (aux is not None):
         raise ValueError("epilogues 2 and 3 take an auxiliary tensor, the others do not")
     if aux is not None:

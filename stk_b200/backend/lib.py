@@ -47,20 +47,24 @@ SIGNATURES = {
                                         _c_i64, _c_ptr, _c_ptr]),
     "stk_b200_to_dense": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_int, _c_ptr,
                                    _c_i64, _c_ptr]),
-    "stk_b200_gather_rows": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_ptr]),
+    "stk_b200_gather_rows": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_ptr]),
     "stk_b200_scatter_rows": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_ptr]),
+    "stk_b200_weighted_sum_rows": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_i64, _c_int,
+                                            _c_ptr]),
     "stk_b200_bin_index": (_c_int, [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_i64, _c_ptr,
-                                    _c_ptr]),
+                                    _c_ptr, _c_ptr]),
     "stk_b200_dmoe_topology": (_c_int, [_c_ptr, _c_int, _c_int, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                                         _c_ptr, _c_ptr, _c_ptr]),
     "stk_b200_copy_bytes": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_ptr]),
+    "stk_b200_ep_barrier": (_c_int, [_c_ptr, _c_int, _c_int, _c_i64, _c_i64, _c_ptr]),
     "stk_b200_ep_share_counts": (_c_int, [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr]),
-    "stk_b200_ep_plan": (_c_int, [_c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr]),
-    "stk_b200_ep_zero_padding": (_c_int, [_c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_i64, _c_i64,
-                                          _c_ptr]),
-    "stk_b200_ep_dispatch": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_int,
-                                      _c_i64, _c_i64, _c_ptr, _c_ptr]),
-    "stk_b200_ep_combine": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr]),
+    "stk_b200_ep_plan": (_c_int, [_c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr,
+                                  _c_ptr]),
+    "stk_b200_ep_zero_padding": (_c_int, [_c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_i64,
+                                          _c_i64, _c_ptr]),
+    "stk_b200_ep_dispatch": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_int,
+                                      _c_int, _c_int, _c_int, _c_int, _c_i64, _c_i64, _c_ptr]),
+    "stk_b200_ep_return": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_i64, _c_i64, _c_ptr]),
 }
 
 _lib = None

@@ -1,15 +1,22 @@
-"""Per-product timing on the benchmark shapes other than the headline one:
+"""Per-product and per-kernel timing on the benchmark shapes other than the headline one:
 
-    python -m stk_b200.benchmarks c3     # dMoE forward + backward products, 16 experts with Zipf token counts, bf16
-    python -m stk_b200.benchmarks c4     # random block sparsity on 8192^3, bf16, all op / transpose combinations
+    python -m stk_b200.benchmarks c2     # dMoE forward + backward products, 16 experts with Zipf token counts, bf16
+    python -m stk_b200.benchmarks c3     # random block sparsity on 8192^3, bf16, all op / transpose combinations
+    python -m stk_b200.benchmarks meta   # metadata / conversion / row-movement kernels: achieved GB/s
     python -m stk_b200.benchmarks train  # forward + backward of the experts' MLP, fused against unfused
+    python -m stk_b200.benchmarks ref    # the reference's own Triton kernels on this GPU (needs oracle/_ref)
+    python -m stk_b200.benchmarks single 0.25   # a few launches on one random topology (profiler case)
 
-Every line: nonzero-block TFLOP/s (2 * nnz * 128 * 128 * dense extent / time) with the 128x128 kernel
-forced, the 128x256 row kernel forced (DSD and DDS; SDD runs the 128x128 kernel in that column), the
-CTA-pair kernel forced and the per-topology choice, against a cuBLAS GEMM (torch.matmul)
-of the same useful FLOPs timed in the same run.  CUDA events around 20 back-to-back launches after 5
-warm-up launches; operands (hundreds of MB) exceed the L2, which is not flushed.
+Products: nonzero-block TFLOP/s (2 * nnz * 128 * 128 * dense extent / time) with the 128x128 kernel
+forced, the 128x256 row kernel forced, the CTA-pair kernel forced and the per-topology choice, against
+a cuBLAS GEMM (torch.matmul) of the same useful FLOPs.  The candidates of one line are timed
+INTERLEAVED (A, B, C, A, B, C, ... a few launches each, median over the rounds), so that the clock
+drift of a GPU that warms up during the run hits all of them alike.  Operands (hundreds of MB) exceed
+the L2, which is not flushed.  bench.py calls products_c2 / products_c3 / meta_kernels for the extra
+keys of its JSON line.
 """
+import os
+import statistics
 import sys
 
 import numpy as np
@@ -34,25 +41,71 @@ def _time_ms(fn, iters=20, warm=5):
     return start.elapsed_time(stop) / iters
 
 
-def _report(name, flops, fn, dense_fn):
-    saved, cells = kernels.PAIR_MODE, []
-    try:
-        for mode in ("0", "3", "1", "auto"):
-            kernels.PAIR_MODE = mode
-            cells.append(_time_ms(fn))
-    finally:
-        kernels.PAIR_MODE = saved
-    dense = _time_ms(dense_fn)
-    tf = lambda ms: flops / ms / 1e9
-    print(f"| {name:24s} | {tf(cells[0]):5.0f} | {tf(cells[1]):5.0f} | {tf(cells[2]):5.0f} | {tf(cells[3]):5.0f} | "
-          f"{cells[3] * 1e3:7.1f} | {tf(dense):5.0f} | {dense / cells[3]:4.2f} |", flush=True)
+def time_interleaved(fns, rounds=5, iters=4, warm=2):
+    """{name: median ms per call}: every round times `iters` back-to-back calls of each candidate in
+    turn, so slow clock drift affects all candidates equally."""
+    for fn in fns.values():
+        for _ in range(warm):
+            fn()
+    samples = {name: [] for name in fns}
+    for _ in range(rounds):
+        for name, fn in fns.items():
+            torch.cuda.synchronize()
+            torch.cuda._sleep(2_000_000)
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(iters):
+                fn()
+            stop.record()
+            torch.cuda.synchronize()
+            samples[name].append(start.elapsed_time(stop) / iters)
+    return {name: statistics.median(v) for name, v in samples.items()}
 
 
-_HEADER = ("| product                  | 128x128 | 128x256 | pair | auto TFLOP/s | auto us | cuBLAS TFLOP/s | auto / cuBLAS |\n"
-           "|---|---|---|---|---|---|---|---|")
+def _with_mode(mode, fn):
+    def run():
+        saved = kernels.PAIR_MODE
+        kernels.PAIR_MODE = mode
+        try:
+            return fn()
+        finally:
+            kernels.PAIR_MODE = saved
+    return run
 
 
-def config3(dev="cuda"):
+def _product_line(name, flops, fn, dense_fn, all_modes):
+    """One product against its same-FLOP dense GEMM; all_modes adds the three forced kernels."""
+    fns = {"auto": _with_mode("auto", fn), "cublas": dense_fn}
+    if all_modes:
+        fns.update({"tile128": _with_mode("0", fn), "row256": _with_mode("3", fn), "pair256": _with_mode("1", fn)})
+    fn()                                   # settles the kernel choice of an unknown topology
+    torch.cuda.synchronize()
+    fn()
+    ms = time_interleaved(fns)
+    tf = lambda t: round(flops / t / 1e9, 1)
+    line = {"product": name, "tflops": tf(ms["auto"]), "us": round(ms["auto"] * 1e3, 1),
+            "cublas_tflops": tf(ms["cublas"]), "vs_cublas": round(ms["cublas"] / ms["auto"], 3)}
+    if all_modes:
+        line.update({k: tf(ms[k]) for k in ("tile128", "row256", "pair256")})
+    return line
+
+
+def _print_table(title, lines):
+    print(title)
+    modes = "tile128" in lines[0]
+    head = "| product | " + ("128x128 | 128x256 | pair | " if modes else "") + "auto TFLOP/s | auto us | cuBLAS TFLOP/s | auto / cuBLAS |"
+    print(head)
+    print("|" + "---|" * (head.count("|") - 1))
+    for ln in lines:
+        mid = f"{ln['tile128']:.0f} | {ln['row256']:.0f} | {ln['pair256']:.0f} | " if modes else ""
+        print(f"| {ln['product']} | {mid}{ln['tflops']:.0f} | {ln['us']:.1f} | {ln['cublas_tflops']:.0f} | {ln['vs_cublas']:.2f} |",
+              flush=True)
+
+
+def products_c2(dev="cuda", all_modes=False):
+    """The six products of a dMoE forward + backward pass (T=32768, h=2048, f=8192, E=16, Zipf(1.2)
+    token counts, bf16): sdd NN, dsd N, sdd NT, dsd with S transposed, dsd with the dense operand
+    transposed, dds with the dense operand transposed."""
     T, h, f, E, dtype = 32768, 2048, 8192, 16, torch.bfloat16
     g = torch.Generator().manual_seed(0)
     p = (torch.arange(E) + 1.0) ** -1.2
@@ -60,53 +113,160 @@ def config3(dev="cuda"):
     _, padded, _, total = dmoe.route_top1(ids, E)
     topo = dmoe.block_diagonal_topology(padded, f, dtype, dev)
     nnz = topo.data.shape[0]
-    print(f"dMoE fwd+bwd products, T={T} h={h} f={f} E={E} bf16; padded rows {total}, {nnz} blocks, "
-          f"block rows per expert {(padded // 128).tolist()}")
-    print(_HEADER)
     rand = lambda *shape: torch.empty(*shape, dtype=dtype, device=dev).normal_(0, 0.02)
     x, w1, w2, dy = rand(total, h), rand(h, E * f), rand(E * f, h), rand(total, h)
     hid = stk.ops.sdd(x, w1, topo)
     flops = 2.0 * nnz * 128 * 128 * h
     wa, wb, ha = w1[:, :f].contiguous(), w2[:f].contiguous(), rand(total, f)   # one expert's dense twin
-    _report("fwd sdd   x @ w1", flops, lambda: stk.ops.sdd(x, w1, topo), lambda: x @ wa)
-    _report("fwd dsd   h @ w2", flops, lambda: stk.ops.dsd(hid, w2), lambda: ha @ wb)
-    _report("bwd sdd   dy @ w2^T", flops, lambda: stk.ops.sdd(dy, w2.t(), topo), lambda: dy @ wb.t())
-    _report("bwd dsd   h^T @ dy", flops, lambda: stk.ops.dsd(hid.t(), dy), lambda: ha.t() @ dy)
-    _report("bwd dsd   dh @ w1^T", flops, lambda: stk.ops.dsd(hid, w1.t()), lambda: ha @ wa.t())
-    _report("bwd dds   x^T @ dh", flops, lambda: stk.ops.dds(x.t(), hid), lambda: x.t() @ ha)
+    specs = [("fwd sdd x@w1", lambda: stk.ops.sdd(x, w1, topo), lambda: x @ wa),
+             ("fwd dsd h@w2", lambda: stk.ops.dsd(hid, w2), lambda: ha @ wb),
+             ("bwd sdd dy@w2^T", lambda: stk.ops.sdd(dy, w2.t(), topo), lambda: dy @ wb.t()),
+             ("bwd dsd h^T@dy", lambda: stk.ops.dsd(hid.t(), dy), lambda: ha.t() @ dy),
+             ("bwd dsd dh@w1^T", lambda: stk.ops.dsd(hid, w1.t()), lambda: ha @ wa.t()),
+             ("bwd dds x^T@dh", lambda: stk.ops.dds(x.t(), hid), lambda: x.t() @ ha)]
+    lines = [_product_line(n, flops, fn, dfn, all_modes) for n, fn, dfn in specs]
+    info = {"padded_rows": total, "blocks": nnz, "block_rows_per_expert": (padded // 128).tolist()}
+    return info, lines
 
 
-def config4(dev="cuda"):
+def products_c3(dev="cuda", all_modes=False, densities=(0.05, 0.125, 0.25, 0.5)):
+    """Random block sparsity on 8192^3, bf16: SDD NN / TT, DSD with S and S^T, DDS with S and S^T at
+    every density, each against a dense GEMM of the same useful FLOPs."""
     M = N = K = 8192
     dtype = torch.bfloat16
-    for density in (0.05, 0.125, 0.25, 0.5):
+    out = {}
+    a, b = torch.randn(M, K, device=dev).to(dtype), torch.randn(K, N, device=dev).to(dtype)
+    for density in densities:
         np.random.seed(0)
         topo = stk.random.mask(M, N, 1 - density, 128).to(dev)
         nnz = topo.data.shape[0]
         s = stk.Matrix(topo.size(), torch.randn(nnz, 128, 128, device=dev).to(dtype), topo.row_indices,
                        topo.column_indices, topo.offsets, topo.column_indices_t, topo.offsets_t,
                        topo.block_offsets_t)
-        a, b = torch.randn(M, K, device=dev).to(dtype), torch.randn(K, N, device=dev).to(dtype)
         flops = 2.0 * nnz * 128 * 128 * K
         nd = max(128, int(round(N * density / 128)) * 128)     # dense GEMM with the same FLOPs: 8192 x 8192 x nd
         bd = torch.randn(K, nd, device=dev).to(dtype)
         an, bn = a[:, :nd].contiguous(), b[:nd].contiguous()
-        rows, cols, tiles, _, _ = kernels.pair_hints(topo.offsets, topo.row_indices, topo.column_indices, N // 128,
-                                                     topo.offsets_t, topo.column_indices_t, need_t=True, wait=True)
-        print(f"\nrandom topology 8192^2, density {density}: {nnz} blocks; useful share of the pair kernel's work: "
-              f"row pairs {rows:.2f}, column pairs {cols:.2f}, 2x2 tiles {tiles:.2f}")
-        print(_HEADER)
-        _report("sdd  a @ b", flops, lambda: stk.ops.sdd(a, b, s), lambda: a @ bd)
-        _report("sdd  a^T @ b^T", flops, lambda: stk.ops.sdd(a.t(), b.t(), s), lambda: a @ bd)
-        _report("dsd  s @ b", flops, lambda: stk.ops.dsd(s, b), lambda: an @ bn)
-        _report("dsd  s^T @ b", flops, lambda: stk.ops.dsd(s.t(), b), lambda: an @ bn)
-        _report("dds  a @ s", flops, lambda: stk.ops.dds(a, s), lambda: a @ bd)
-        _report("dds  a @ s^T", flops, lambda: stk.ops.dds(a, s.t()), lambda: a @ bd)
+        specs = [("sdd a@b", lambda: stk.ops.sdd(a, b, s), lambda: a @ bd),
+                 ("sdd a^T@b^T", lambda: stk.ops.sdd(a.t(), b.t(), s), lambda: a @ bd),
+                 ("dsd s@b", lambda: stk.ops.dsd(s, b), lambda: an @ bn),
+                 ("dsd s^T@b", lambda: stk.ops.dsd(s.t(), b), lambda: an @ bn),
+                 ("dds a@s", lambda: stk.ops.dds(a, s), lambda: a @ bd),
+                 ("dds a@s^T", lambda: stk.ops.dds(a, s.t()), lambda: a @ bd)]
+        out[f"{density:g}"] = {"blocks": nnz, "lines": [_product_line(n, flops, fn, dfn, all_modes) for n, fn, dfn in specs]}
+        del s, bd, an, bn
+    return out
+
+
+def meta_kernels(dev="cuda", peak_gbs=None):
+    """Achieved GB/s of the metadata, conversion and row-movement kernels: algorithmic bytes (what the
+    step must read and write at least) over the CUDA-event time of the calls that make it up."""
+    from stk_b200.backend import lib
+    results = []
+
+    def add(name, nbytes, fn, note=""):
+        ms = _time_ms(fn, iters=10, warm=3)
+        gbs = nbytes / ms / 1e6
+        results.append({"kernel": name, "algorithmic_mb": round(nbytes / 1e6, 3), "us": round(ms * 1e3, 1),
+                        "gbs": round(gbs, 1), "frac": None if peak_gbs is None else round(gbs / peak_gbs, 3),
+                        "note": note})
+
+    dtype = torch.bfloat16
+    for blocking in (128, 32, 16):
+        M = N = 8192
+        np.random.seed(1)
+        R = M // blocking
+        pat = torch.from_numpy(np.random.rand(R, R) < 0.5).to(dev)
+        x = torch.randn(M, N, device=dev).to(dtype)
+        x = (x.view(R, blocking, R, blocking) * pat.view(R, 1, R, 1)).reshape(M, N).contiguous()
+        mask = kernels.block_mask(x, blocking)
+        offsets, ri, ci = kernels.mask_to_topology(mask)
+        nnz = ri.numel()
+        data = kernels.gather_blocks(x, blocking, ri, ci)
+        tag = f"8192^2 b={blocking} nnz={nnz}"
+        add(f"block_mask {tag}", 2.0 * M * N, lambda: kernels.block_mask(x, blocking))
+        add(f"gather_blocks {tag}", 4.0 * nnz * blocking * blocking, lambda: kernels.gather_blocks(x, blocking, ri, ci))
+        add(f"to_dense {tag}", 2.0 * M * N + 2.0 * nnz * blocking * blocking,
+            lambda: kernels.to_dense(data, offsets, ci, R, R, blocking))
+        if blocking == 128:
+            add(f"to_sparse (all phases incl. transpose and the count read-back) {tag}",
+                2.0 * M * N + 4.0 * nnz * blocking * blocking, lambda: stk.ops.to_sparse(x, blocking),
+                "one host read-back inside")
+        del x, data
+    for nnz, Cb, R, note in ((16768, 1024, 262, "single-CTA path"), (236000, 7168, 2108, "multi-kernel path")):
+        rows = (torch.arange(nnz, device=dev) // (nnz // R + 1)).to(torch.int16)
+        cols = torch.randint(0, Cb, (nnz,), device=dev).to(torch.int16)
+        add(f"transpose_meta nnz={nnz} Cb={Cb}", 4.0 * nnz + 6.0 * nnz + 4.0 * (Cb + 1),
+            lambda: kernels.transpose_meta(rows, cols, Cb), note + "; latency-bound")
+    R, nnz = 2108, 236096
+    offsets = (torch.arange(R + 1, device=dev) * 112).to(torch.int32)
+    out16 = torch.empty(nnz, dtype=torch.int16, device=dev)
+    add(f"row_indices nnz={nnz}", 4.0 * (R + 1) + 2.0 * nnz,
+        lambda: kernels.row_indices(None, None, offsets, None, out16), "latency-bound")
+    for rows, hidden, E, cpb, tag in ((17024, 1024, 8, 32, "configs[1]"), (33536, 4096, 8, 112, "configs[4] / 8")):
+        bin_rows = torch.full((E,), rows // 128 // E, dtype=torch.int32, device=dev)
+        br = int(bin_rows.sum())
+        add(f"dmoe_topology {tag} nnz={br * cpb}", (2 + 2 + 2 + 4) * br * cpb + 4.0 * (br + 1) + 4.0 * (E * cpb + 1),
+            lambda: dmoe.topology_from_bins(bin_rows, br, cpb * 128, dtype, dev, materialize=False), "latency-bound")
+        src = torch.randn(rows, hidden, device=dev).to(dtype)
+        index = torch.randperm(rows, device=dev).to(torch.int32)
+        add(f"gather_rows {tag} {rows}x{hidden}", 4.0 * rows * hidden, lambda: dmoe.gather_rows(src, index))
+        add(f"scatter_rows {tag} {rows}x{hidden}", 4.0 * rows * hidden, lambda: dmoe.scatter_rows(src, index, rows))
+        w = torch.rand(rows // 2, 2, device=dev)
+        add(f"weighted_sum_rows top-2 {tag}", 2.0 * rows * hidden + 1.0 * rows * hidden,
+            lambda: dmoe.weighted_sum_rows(src, index, w, rows // 2, 2))
+    assert lib.device_status() == 0
+    return results
+
+
+def reference_triton(dev="cuda"):
+    """The reference's own Triton kernels (stk/backend/triton_kernels.py:21-220, staged under
+    oracle/_ref) on this GPU, on the configs[1] forward products and the configs[2] products, next to
+    this library on the same operands."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(root, "oracle"))
+    import stage_reference
+    ref = stage_reference.import_reference()
+    if ref is None:
+        print("reference not staged (run python oracle/stage_reference.py where the reference is present)")
+        return []
+    lines = []
+    for tag, (T, h, f, E, dtype, zipf) in (("configs[1]", (16384, 1024, 4096, 8, torch.float16, False)),
+                                          ("configs[2]", (32768, 2048, 8192, 16, torch.bfloat16, True))):
+        g = torch.Generator().manual_seed(0)
+        p = (torch.arange(E) + 1.0) ** -1.2 if zipf else torch.ones(E)
+        ids = torch.multinomial(p / p.sum(), T, replacement=True, generator=g).to(dev)
+        _, padded, _, total = dmoe.route_top1(ids, E)
+        topo = dmoe.block_diagonal_topology(padded, f, dtype, dev)
+        nnz = topo.data.shape[0]
+        rand = lambda *shape: torch.empty(*shape, dtype=dtype, device=dev).normal_(0, 0.02)
+        x, w1, w2, dy = rand(total, h), rand(h, E * f), rand(E * f, h), rand(total, h)
+        mine = stk.ops.sdd(x, w1, topo)
+        rtopo = ref.Matrix(topo.size(), mine.data, topo.row_indices, topo.column_indices, topo.offsets,
+                           topo.column_indices_t, topo.offsets_t, topo.block_offsets_t)
+        flops = 2.0 * nnz * 128 * 128 * h
+        specs = [("sdd x@w1", lambda: stk.ops.sdd(x, w1, topo), lambda: ref.ops.sdd(x, w1, rtopo)),
+                 ("dsd h@w2", lambda: stk.ops.dsd(mine, w2), lambda: ref.ops.dsd(rtopo, w2)),
+                 ("dsd h^T@dy", lambda: stk.ops.dsd(mine.t(), dy), lambda: ref.ops.dsd(rtopo.t(), dy)),
+                 ("dds x^T@dh", lambda: stk.ops.dds(x.t(), mine), lambda: ref.ops.dds(x.t(), rtopo))]
+        with torch.no_grad():
+            for name, fn, rfn in specs:
+                got, want = fn(), rfn()
+                got = got.data if isinstance(got, stk.Matrix) else got
+                want = want.data if hasattr(want, "row_indices") else want
+                err = (got.float() - want.float()).abs().max().item() / max(want.float().pow(2).mean().sqrt().item(), 1e-30)
+                ms = time_interleaved({"stk_b200": fn, "reference_triton": rfn})
+                lines.append({"config": tag, "product": name, "stk_b200_tflops": round(flops / ms["stk_b200"] / 1e9, 1),
+                              "reference_triton_tflops": round(flops / ms["reference_triton"] / 1e9, 1),
+                              "speedup": round(ms["reference_triton"] / ms["stk_b200"], 2),
+                              "max_abs_diff_over_rms": round(err, 5)})
+                print(lines[-1], flush=True)
+    return lines
 
 
 def single(density=0.25, dev="cuda"):
-    """A few launches of s @ b and a @ s on one random topology, kernel chosen by STK_B200_PAIR_MODE:
-    the small case for a profiler capture (python -m stk_b200.benchmarks single 0.25)."""
+    """A few launches of s @ b, a @ s and sdd on one random topology, kernel chosen by
+    STK_B200_PAIR_MODE: the small case for a profiler capture."""
     M = N = K = 8192
     dtype = torch.bfloat16
     np.random.seed(0)
@@ -123,7 +283,7 @@ def single(density=0.25, dev="cuda"):
 
 
 def train_step(dev="cuda"):
-    """Forward + backward of the experts' MLP on the headline shape (T=16384, h=1024, f=4096, E=8, fp16):
+    """Forward + backward of the experts' MLP on the configs[1] shape (T=16384, h=1024, f=4096, E=8, fp16):
     dmoe.expert_mlp (GeLU and its backward inside the products' epilogues) against
     sdd -> torch gelu -> dsd differentiated by autograd."""
     T, h, f, E, dtype = 16384, 1024, 4096, 8, torch.float16
@@ -151,12 +311,21 @@ def train_step(dev="cuda"):
 
 
 if __name__ == "__main__":
-    which = sys.argv[1] if len(sys.argv) > 1 else "c3"
+    which = sys.argv[1] if len(sys.argv) > 1 else "c2"
     if which == "train":
         train_step()
+    elif which == "ref":
+        reference_triton()
     else:
         with torch.no_grad():
             if which == "single":
                 single(float(sys.argv[2]) if len(sys.argv) > 2 else 0.25)
-            else:
-                {"c3": config3, "c4": config4}[which]()
+            elif which == "meta":
+                for r in meta_kernels(peak_gbs=6549.4):
+                    print(f"| {r['kernel']} | {r['algorithmic_mb']} | {r['us']} | {r['gbs']} | {r['frac']} | {r['note']} |", flush=True)
+            elif which == "c2":
+                info, lines = products_c2(all_modes=True)
+                _print_table(f"dMoE fwd+bwd products, T=32768 h=2048 f=8192 E=16 bf16; {info}", lines)
+            elif which == "c3":
+                for density, res in products_c3(all_modes=True).items():
+                    _print_table(f"\nrandom topology 8192^2, density {density}: {res['blocks']} blocks", res["lines"])

@@ -4,22 +4,28 @@
 // accesses, and tiny integer kernels.  The reference has no counterpart (it is a matmul library);
 // these are the callers' side of stk.Matrix(...) / stk.ops.sdd / stk.ops.dsd.
 #pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #include "../../include/stk_b200.h"
+#include "status.cuh"
 
 namespace stk {
 
-// dst[i] = index[i] >= 0 ? src[index[i]] : 0, rows of `vec_per_row` 16-byte vectors.  One warp per
-// output row; every output row is written exactly once (padding rows as zeros).
+// dst[i] = index[i] >= 0 ? src[index[i] / index_div] : 0, rows of `vec_per_row` 16-byte vectors.  One
+// warp per output row; every output row is written exactly once (padding rows as zeros).  index_div > 1:
+// the index names a (token, choice) slot of top-k routing, slot = token * k + choice, and the row
+// fetched is the token's.
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
-                   const int32_t* __restrict__ index, int64_t n_rows, int vec_per_row) {
+                   const int32_t* __restrict__ index, int64_t n_rows, int vec_per_row, int index_div) {
   const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (row >= n_rows) return;
-  const int32_t s = index[row];
+  int32_t s = index[row];
+  if (s >= 0 && index_div > 1) s /= index_div;
   uint4* out = dst + row * vec_per_row;
   if (s < 0) {
     const uint4 z = make_uint4(0u, 0u, 0u, 0u);
@@ -49,11 +55,11 @@ scatter_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
 // the rows for expert e ordered by peer, then zero padding up to a multiple of `block`.
 // index[r] = source row of padded row r, or -1 for padding; with `compose`, the source row is looked
 // up through it (compose[source]), e.g. the sort order that produced the received rows.
-// bin_rows[e] = padded rows / block.
+// bin_rows[e] = padded rows / block.  inverse (optional): inverse[index[r]] = r for every real row.
 __global__ void __launch_bounds__(256)
 bin_index_kernel(const int64_t* __restrict__ counts, int world, int local, int block,
                  const int32_t* __restrict__ compose, int32_t* __restrict__ index,
-                 int64_t total_padded, int32_t* __restrict__ bin_rows) {
+                 int64_t total_padded, int32_t* __restrict__ bin_rows, int32_t* __restrict__ inverse) {
   extern __shared__ int64_t sm[];
   int64_t* bin_start = sm;              // [local + 1] padded
   int64_t* src_start = sm + local + 1;  // [world * local] position of segment (p, e) in the received rows
@@ -90,7 +96,9 @@ bin_index_kernel(const int64_t* __restrict__ counts, int world, int local, int b
     }
     q -= n;
   }
-  index[r] = (src >= 0 && compose != nullptr) ? compose[src] : src;
+  if (src >= 0 && compose != nullptr) src = compose[src];
+  index[r] = src;
+  if (src >= 0 && inverse != nullptr) inverse[src] = static_cast<int32_t>(r);  // where source row src went
 }
 
 // Block-diagonal topology: expert e owns bin_rows[e] consecutive block rows and the block columns
@@ -142,6 +150,51 @@ dmoe_topology_kernel(const int32_t* __restrict__ bin_rows, int experts, int cpb,
   block_offsets_t[q] = static_cast<int32_t>(p);
 }
 
+// dst[t] = sum over j < k of weights[t*k + j] * src[pos ? pos[t*k + j] : t*k + j], accumulated in fp32
+// and rounded once: the top-k weighted combine of a dMoE layer (k = 1 with weight 1 is the plain
+// un-permute).  A slot whose position is negative (a row that was dropped) contributes nothing.
+// One warp per token, 16-byte accesses; kBf16 selects the 16-bit format.
+template <bool kBf16>
+__global__ void __launch_bounds__(256)
+weighted_sum_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ pos,
+                         const float* __restrict__ weights, uint4* __restrict__ dst, int64_t tokens, int k,
+                         int vec_per_row) {
+  const int64_t t = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  for (int v = lane; v < vec_per_row; v += 32) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < k; ++j) {
+      const int64_t slot = t * k + j;
+      const int64_t row = pos != nullptr ? static_cast<int64_t>(pos[slot]) : slot;
+      if (row < 0) continue;
+      const float w = weights != nullptr ? weights[slot] : 1.0f;
+      const uint4 x = __ldg(src + row * vec_per_row + v);
+      const uint32_t words[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 f;
+        if (kBf16) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&words[i]));
+        else f = __half22float2(*reinterpret_cast<const __half2*>(&words[i]));
+        acc[2 * i] = fmaf(w, f.x, acc[2 * i]);
+        acc[2 * i + 1] = fmaf(w, f.y, acc[2 * i + 1]);
+      }
+    }
+    uint32_t out[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (kBf16) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+        out[i] = *reinterpret_cast<const uint32_t*>(&h);
+      } else {
+        const __half2 h = __floats2half2_rn(acc[2 * i], acc[2 * i + 1]);
+        out[i] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    }
+    dst[t * vec_per_row + v] = make_uint4(out[0], out[1], out[2], out[3]);
+  }
+}
+
 // A few bytes copied by a kernel instead of the copy engine: the destination may be pinned host
 // memory (mapped into the device's address space), so that a small read-back - expert counts, the
 // number of padded rows - does not queue behind a large device-to-host copy on the copy engine.
@@ -158,18 +211,57 @@ copy_bytes_kernel(const unsigned char* __restrict__ src, unsigned char* __restri
 }
 
 // ------------------------------------------------------------------ expert-parallel exchange
-// Token exchange over peer memory (NVLink): every rank PUSHES its token rows straight into the
-// padded expert bins of the rank that owns the expert, and later PULLS its results from there.  The
-// peers' buffers are ordinary device pointers (symmetric memory); the kernels only ever issue plain
-// loads and stores to them.  A barrier between ranks (not part of these kernels) separates the
-// steps.  Every address sent to a peer is checked against the buffer's capacity first; a row that
+// Token exchange over peer memory (NVLink) for top-k routing.  Every rank holds `tokens` tokens with
+// k expert choices each: slot = token * k + choice.  A rank PUSHES the token row of every slot
+// straight into the padded bin of the slot's expert on the rank that owns the expert, together with
+// a tag (home rank, slot); after the experts' MLP the owner PUSHES every result row back into the
+// home rank's slot-ordered buffer, where the k rows of a token are combined with their weights.  The
+// peers' buffers are ordinary device pointers (symmetric memory); only plain stores go to a peer, no
+// load of any kind reads one.  A barrier between ranks (not part of these kernels) separates the
+// phases.  Every address sent to a peer is checked against the buffer's capacity first; a row that
 // would not fit is skipped and reported through the status word.
 //
 // Layout on rank d: bin of local expert le = rows [bin_start[le], bin_start[le] + padded[le]), the
-// rows from rank 0 first, then rank 1, ..., each rank's rows in its own (stable) token order, then
-// zero rows up to a multiple of `block`.
+// rows from rank 0 first, then rank 1, ..., each rank's rows in its own (stable) slot order, then
+// zero rows up to a multiple of `block`.  The local experts are cut into `chunks` groups of
+// consecutive experts so that a caller can overlap the exchange of one group with the products of
+// another: chunk c of every rank holds local experts [c * local / chunks, (c + 1) * local / chunks).
 
-// Row `rank` of every rank's count matrix <- this rank's tokens per expert (offsets[e+1] - offsets[e]).
+constexpr int64_t kTagRowMask = (1ll << 40) - 1;
+
+// Barrier between the ranks of the exchange, on the stream: every rank stores `epoch` into slot
+// `rank` of every rank's flag array (peer stores, released at system scope so that everything this
+// rank wrote before - its own rows in the peers' buffers - is visible to whoever reads the flag), then
+// waits until all `world` slots of its own array have reached `epoch`.  Epochs only grow (one counter
+// per flag array on the host, the same on every rank).  The wait is bounded: after `timeout_ns` the
+// kernel records STK_ERR_DEVICE_TIMEOUT in the status word and returns, it never traps or spins on.
+// One thread per rank.  The ranks must run on different GPUs (a waiting kernel and the kernel it
+// waits for are not guaranteed to run at the same time on one GPU).
+__global__ void __launch_bounds__(64)
+ep_barrier_kernel(const uint64_t* __restrict__ peer_flags, int world, int rank, long long epoch,
+                  unsigned long long timeout_ns) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  long long* remote = reinterpret_cast<long long*>(peer_flags[r]) + rank;
+  asm volatile("st.release.sys.global.s64 [%0], %1;" ::"l"(remote), "l"(epoch) : "memory");
+  const long long* mine = reinterpret_cast<const long long*>(peer_flags[rank]) + r;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  while (true) {
+    long long v;
+    asm volatile("ld.acquire.sys.global.s64 %0, [%1];" : "=l"(v) : "l"(mine) : "memory");
+    if (v >= epoch) break;
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if (now - t0 > timeout_ns) {
+      report_status(STK_ERR_DEVICE_TIMEOUT);
+      break;
+    }
+    __nanosleep(200);
+  }
+}
+
+// Row `rank` of every rank's count matrix <- this rank's slots per expert (offsets[e+1] - offsets[e]).
 __global__ void __launch_bounds__(128)
 ep_share_counts_kernel(const int32_t* __restrict__ offsets, const uint64_t* __restrict__ peer_counts,
                        int world, int experts, int rank) {
@@ -179,18 +271,26 @@ ep_share_counts_kernel(const int32_t* __restrict__ offsets, const uint64_t* __re
   }
 }
 
-// counts_all[s * E + e] = tokens of rank s routed to global expert e.  One CTA, E*world small.
+__device__ __forceinline__ int ep_chunk_of(int le, int local, int chunks) {
+  return static_cast<int>((static_cast<long long>(le) * chunks) / local);
+}
+
+// counts_all[s * E + e] = slots of rank s routed to global expert e (the same matrix on every rank).
+// One CTA, E * world small.
 //   dest_base[e]  = row in the owner's buffer where THIS rank's rows for expert e start
-//   bin_rows[le]  = padded rows / block of this rank's local expert le;  totals[0] = sum of padded rows,
-//   totals[1] = rows this rank receives (unpadded)
+//   bin_rows[le]  = padded rows / block of this rank's local expert le
+//   totals[0] = padded rows of this rank, totals[1] = rows it receives (unpadded),
+//   totals[2] = the largest padded row count over ALL ranks (every rank computes the same value, so a
+//               buffer overflow anywhere is seen everywhere), totals[3 + c] = padded rows of this
+//               rank's chunk c
 __global__ void __launch_bounds__(128)
 ep_plan_kernel(const int32_t* __restrict__ counts_all, int world, int experts, int local, int rank,
-               int block, int64_t* __restrict__ dest_base, int32_t* __restrict__ bin_rows,
+               int block, int chunks, int64_t* __restrict__ dest_base, int32_t* __restrict__ bin_rows,
                int64_t* __restrict__ totals) {
   // column sums first (one round of loads), so that the serial parts below run out of shared memory
   extern __shared__ int32_t ep_sm[];
-  int32_t* col_sum = ep_sm;            // [experts] tokens of all ranks per expert
-  int32_t* before_me = ep_sm + experts;  // [experts] tokens of the ranks before this one
+  int32_t* col_sum = ep_sm;              // [experts] slots of all ranks per expert
+  int32_t* before_me = ep_sm + experts;  // [experts] slots of the ranks before this one
   for (int e = threadIdx.x; e < experts; e += blockDim.x) {
     int32_t n = 0, b = 0;
     for (int s = 0; s < world; ++s) {
@@ -210,24 +310,35 @@ ep_plan_kernel(const int32_t* __restrict__ counts_all, int world, int experts, i
     dest_base[e] = start + before_me[e];
   }
   if (threadIdx.x == 0) {
-    int64_t padded_total = 0, received = 0;
-    for (int le = 0; le < local; ++le) {
-      const int64_t n = col_sum[rank * local + le];
-      const int64_t padded = (n + block - 1) / block * block;
-      bin_rows[le] = static_cast<int32_t>(padded / block);
-      padded_total += padded;
-      received += n;
+    int64_t padded_total = 0, received = 0, worst = 0;
+    for (int c = 0; c < chunks; ++c) totals[3 + c] = 0;
+    for (int g = 0; g < world; ++g) {
+      int64_t sum = 0;
+      for (int le = 0; le < local; ++le) {
+        const int64_t n = col_sum[g * local + le];
+        const int64_t padded = (n + block - 1) / block * block;
+        sum += padded;
+        if (g == rank) {
+          bin_rows[le] = static_cast<int32_t>(padded / block);
+          received += n;
+          totals[3 + ep_chunk_of(le, local, chunks)] += padded;
+        }
+      }
+      if (g == rank) padded_total = sum;
+      if (sum > worst) worst = sum;
     }
     totals[0] = padded_total;
     totals[1] = received;
+    totals[2] = worst;
   }
 }
 
-// Zero rows that close each local bin (nobody writes them).  One warp per padding row.
+// Zero rows that close each local bin (nobody writes them), and mark them in `tags` as belonging to
+// nobody.  One warp per padding row.
 __global__ void __launch_bounds__(256)
 ep_zero_padding_kernel(const int32_t* __restrict__ counts_all, int world, int experts, int local,
-                       int rank, int block, uint4* __restrict__ recv, int vec_per_row,
-                       int64_t cap_rows) {
+                       int rank, int block, uint4* __restrict__ recv, int64_t* __restrict__ tags,
+                       int vec_per_row, int64_t cap_rows) {
   const int le = blockIdx.y;
   int64_t start = 0, n = 0;
   for (int k = 0; k <= le; ++k) {
@@ -243,57 +354,62 @@ ep_zero_padding_kernel(const int32_t* __restrict__ counts_all, int world, int ex
   if (row >= cap_rows) return;
   const uint4 z = make_uint4(0u, 0u, 0u, 0u);
   for (int v = lane; v < vec_per_row; v += 32) recv[row * vec_per_row + v] = z;
+  if (lane == 0 && tags != nullptr) tags[row] = -1;
 }
 
-// Sorted position q (tokens ordered by expert: token order[q], expert segments offsets[e..e+1]) goes
-// to row dest_base[e] + (q - offsets[e]) of the buffer of rank e / local.  One warp per row.
-// dest[t] = owner rank << 40 | row, kept for the way back.
+// Sorted position q (slots ordered by expert: slot order[q], expert segments offsets[e..e+1]) goes to
+// row dest_base[e] + (q - offsets[e]) of the buffer of rank e / local: the row of token order[q] / k,
+// and the tag (this rank << 40 | slot) into the owner's tag array.  Only the slots whose expert lies
+// in chunk `chunk` of its owner are handled (chunks = 1: all).  One warp per slot.
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ order,
                    const int32_t* __restrict__ offsets, const int64_t* __restrict__ dest_base,
-                   const uint64_t* __restrict__ peer_bufs, int64_t tokens, int experts, int local,
-                   int vec_per_row, int64_t cap_rows, int64_t* __restrict__ dest) {
+                   const uint64_t* __restrict__ peer_bufs, const uint64_t* __restrict__ peer_tags,
+                   int64_t slots, int k, int experts, int local, int rank, int chunk, int chunks,
+                   int vec_per_row, int64_t cap_rows) {
   const int64_t q = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (q >= tokens) return;
+  if (q >= slots) return;
   int lo = 0, hi = experts;  // last e with offsets[e] <= q
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
     if (offsets[mid] <= q) lo = mid; else hi = mid;
   }
   const int e = lo, owner = e / local;
+  if (chunks > 1 && ep_chunk_of(e - owner * local, local, chunks) != chunk) return;
   const int64_t row = dest_base[e] + (q - offsets[e]);
-  const int32_t t = order[q];
+  const int32_t slot = order[q];
   if (row < 0 || row >= cap_rows) {
-    if (lane == 0) {
-      dest[t] = -1;
-      report_status(STK_ERR_WORKSPACE);
-    }
+    if (lane == 0) report_status(STK_ERR_WORKSPACE);
     return;
   }
-  if (lane == 0) dest[t] = (static_cast<int64_t>(owner) << 40) | row;
-  const uint4* in = x + static_cast<int64_t>(t) * vec_per_row;
+  if (lane == 0)
+    reinterpret_cast<int64_t*>(peer_tags[owner])[row] = (static_cast<int64_t>(rank) << 40) | slot;
+  const uint4* in = x + static_cast<int64_t>(slot / k) * vec_per_row;
   uint4* out = reinterpret_cast<uint4*>(peer_bufs[owner]) + row * vec_per_row;
   for (int v = lane; v < vec_per_row; v += 32) out[v] = __ldg(in + v);
 }
 
-// out[t] = row dest[t] of the result buffer of the rank that computed it.  One warp per token.
+// The way back: rows [row0, row0 + n_rows) of this rank's result go to the home rank's slot-ordered
+// buffer, row tag & mask of rank tag >> 40; padding rows (tag < 0) go nowhere.  One warp per row.
 __global__ void __launch_bounds__(256)
-ep_combine_kernel(const uint64_t* __restrict__ peer_bufs, const int64_t* __restrict__ dest,
-                  uint4* __restrict__ out, int64_t tokens, int vec_per_row, int64_t cap_rows) {
-  const int64_t t = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+ep_return_kernel(const uint4* __restrict__ result, const int64_t* __restrict__ tags,
+                 const uint64_t* __restrict__ peer_slots, int64_t row0, int64_t n_rows, int world,
+                 int vec_per_row, int64_t slot_cap) {
+  const int64_t w = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (t >= tokens) return;
-  const int64_t d = dest[t];
-  uint4* o = out + t * vec_per_row;
-  const int64_t row = d & ((1ll << 40) - 1);
-  if (d < 0 || row >= cap_rows) {
-    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-    for (int v = lane; v < vec_per_row; v += 32) o[v] = z;
+  if (w >= n_rows) return;
+  const int64_t row = row0 + w;
+  const int64_t tag = tags[row];
+  if (tag < 0) return;
+  const int64_t home = tag >> 40, slot = tag & kTagRowMask;
+  if (home >= world || slot >= slot_cap) {
+    if (lane == 0) report_status(STK_ERR_WORKSPACE);
     return;
   }
-  const uint4* in = reinterpret_cast<const uint4*>(peer_bufs[d >> 40]) + row * vec_per_row;
-  for (int v = lane; v < vec_per_row; v += 32) o[v] = in[v];
+  const uint4* in = result + row * vec_per_row;
+  uint4* out = reinterpret_cast<uint4*>(peer_slots[home]) + slot * vec_per_row;
+  for (int v = lane; v < vec_per_row; v += 32) out[v] = __ldg(in + v);
 }
 
 }  // namespace stk
@@ -311,14 +427,15 @@ static int rows_args_ok(const void* src, const void* dst, const int32_t* index, 
 }
 
 extern "C" int stk_b200_gather_rows(const void* src, void* dst, const int32_t* index, int64_t n_rows,
-                                    int64_t row_bytes, void* stream) {
+                                    int64_t row_bytes, int index_div, void* stream) {
   const int rc = rows_args_ok(src, dst, index, n_rows, row_bytes);
   if (rc != STK_OK || n_rows == 0) return rc;
+  if (index_div < 1) return STK_ERR_BAD_DIMS;
   const int64_t ctas = (n_rows + 7) / 8;
   if (ctas > INT32_MAX) return STK_ERR_TOO_LARGE;
   gather_rows_kernel<<<static_cast<unsigned>(ctas), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src), static_cast<uint4*>(dst), index, n_rows,
-      static_cast<int>(row_bytes / 16));
+      static_cast<int>(row_bytes / 16), index_div);
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 
@@ -336,14 +453,14 @@ extern "C" int stk_b200_scatter_rows(const void* src, void* dst, const int32_t* 
 
 extern "C" int stk_b200_bin_index(const int64_t* counts, int world, int local_experts, int block,
                                   const int32_t* compose, int32_t* index, int64_t total_padded,
-                                  int32_t* bin_rows, void* stream) {
+                                  int32_t* bin_rows, int32_t* inverse, void* stream) {
   if (world <= 0 || local_experts <= 0 || block <= 0 || total_padded < 0) return STK_ERR_BAD_DIMS;
   if (static_cast<int64_t>(world) * local_experts > 4096 || total_padded > INT32_MAX) return STK_ERR_TOO_LARGE;
   if (counts == nullptr || (total_padded > 0 && index == nullptr)) return STK_ERR_NULL_POINTER;
   const size_t smem = (static_cast<size_t>(local_experts) + 1 + static_cast<size_t>(world) * local_experts) * sizeof(int64_t);
   const int64_t ctas = total_padded > 0 ? (total_padded + 255) / 256 : 1;
   bin_index_kernel<<<static_cast<unsigned>(ctas), 256, smem, static_cast<cudaStream_t>(stream)>>>(
-      counts, world, local_experts, block, compose, index, total_padded, bin_rows);
+      counts, world, local_experts, block, compose, index, total_padded, bin_rows, inverse);
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 
@@ -381,20 +498,32 @@ extern "C" int stk_b200_ep_share_counts(const int32_t* offsets, const uint64_t* 
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 
+extern "C" int stk_b200_ep_barrier(const uint64_t* peer_flags, int world, int rank, int64_t epoch,
+                                   int64_t timeout_ms, void* stream) {
+  if (!peer_flags) return STK_ERR_NULL_POINTER;
+  if (world < 1 || world > 64 || rank < 0 || rank >= world || epoch < 1 || timeout_ms < 1) return STK_ERR_BAD_DIMS;
+  stk::ep_barrier_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(
+      peer_flags, world, rank, static_cast<long long>(epoch),
+      static_cast<unsigned long long>(timeout_ms) * 1000000ull);
+  return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
+}
+
 extern "C" int stk_b200_ep_plan(const int32_t* counts_all, int world, int experts, int rank, int block,
-                                int64_t* dest_base, int32_t* bin_rows, int64_t* totals, void* stream) {
+                                int chunks, int64_t* dest_base, int32_t* bin_rows, int64_t* totals,
+                                void* stream) {
   if (!counts_all || !dest_base || !bin_rows || !totals) return STK_ERR_NULL_POINTER;
-  if (world < 1 || experts < 1 || experts % world != 0 || rank < 0 || rank >= world || block < 1)
+  if (world < 1 || experts < 1 || experts % world != 0 || rank < 0 || rank >= world || block < 1 ||
+      chunks < 1 || chunks > experts / world || chunks > STK_EP_MAX_CHUNKS)
     return STK_ERR_BAD_DIMS;
   if (experts > 4096) return STK_ERR_TOO_LARGE;
   stk::ep_plan_kernel<<<1, 128, 2 * experts * sizeof(int32_t), static_cast<cudaStream_t>(stream)>>>(
-      counts_all, world, experts, experts / world, rank, block, dest_base, bin_rows, totals);
+      counts_all, world, experts, experts / world, rank, block, chunks, dest_base, bin_rows, totals);
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 
 extern "C" int stk_b200_ep_zero_padding(const int32_t* counts_all, int world, int experts, int rank,
-                                        int block, void* recv, int64_t row_bytes, int64_t cap_rows,
-                                        void* stream) {
+                                        int block, void* recv, int64_t* tags, int64_t row_bytes,
+                                        int64_t cap_rows, void* stream) {
   if (!counts_all || !recv) return STK_ERR_NULL_POINTER;
   if (world < 1 || experts < 1 || experts % world != 0 || rank < 0 || rank >= world || block < 1 ||
       row_bytes <= 0 || row_bytes % 16 != 0 || cap_rows < 0)
@@ -402,35 +531,64 @@ extern "C" int stk_b200_ep_zero_padding(const int32_t* counts_all, int world, in
   const int local = experts / world;
   const dim3 grid(static_cast<unsigned>((block * 32 + 255) / 256), static_cast<unsigned>(local));
   stk::ep_zero_padding_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      counts_all, world, experts, local, rank, block, static_cast<uint4*>(recv),
+      counts_all, world, experts, local, rank, block, static_cast<uint4*>(recv), tags,
       static_cast<int>(row_bytes / 16), cap_rows);
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 
 extern "C" int stk_b200_ep_dispatch(const void* x, const int32_t* order, const int32_t* offsets,
-                                    const int64_t* dest_base, const uint64_t* peer_bufs, int64_t tokens,
-                                    int world, int experts, int64_t row_bytes, int64_t cap_rows,
-                                    int64_t* dest, void* stream) {
-  if (tokens == 0) return STK_OK;
-  if (!x || !order || !offsets || !dest_base || !peer_bufs || !dest) return STK_ERR_NULL_POINTER;
-  if (tokens < 0 || world < 1 || experts < 1 || experts % world != 0 || row_bytes <= 0 ||
+                                    const int64_t* dest_base, const uint64_t* peer_bufs,
+                                    const uint64_t* peer_tags, int64_t slots, int top_k, int world,
+                                    int experts, int rank, int chunk, int chunks, int64_t row_bytes,
+                                    int64_t cap_rows, void* stream) {
+  if (slots == 0) return STK_OK;
+  if (!x || !order || !offsets || !dest_base || !peer_bufs || !peer_tags) return STK_ERR_NULL_POINTER;
+  if (slots < 0 || top_k < 1 || world < 1 || experts < 1 || experts % world != 0 || rank < 0 ||
+      rank >= world || chunks < 1 || chunk < 0 || chunk >= chunks || row_bytes <= 0 ||
       row_bytes % 16 != 0 || cap_rows < 0)
     return STK_ERR_BAD_DIMS;
-  const int64_t blocks = (tokens * 32 + 255) / 256;
+  if (slots > INT32_MAX) return STK_ERR_TOO_LARGE;
+  const int64_t blocks = (slots * 32 + 255) / 256;
   stk::ep_dispatch_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(x), order, offsets, dest_base, peer_bufs, tokens, experts,
-      experts / world, static_cast<int>(row_bytes / 16), cap_rows, dest);
+      static_cast<const uint4*>(x), order, offsets, dest_base, peer_bufs, peer_tags, slots, top_k, experts,
+      experts / world, rank, chunk, chunks, static_cast<int>(row_bytes / 16), cap_rows);
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 
-extern "C" int stk_b200_ep_combine(const uint64_t* peer_bufs, const int64_t* dest, void* out,
-                                   int64_t tokens, int64_t row_bytes, int64_t cap_rows, void* stream) {
+extern "C" int stk_b200_ep_return(const void* result, const int64_t* tags, const uint64_t* peer_slots,
+                                  int64_t row0, int64_t n_rows, int world, int64_t row_bytes,
+                                  int64_t slot_cap, void* stream) {
+  if (n_rows == 0) return STK_OK;
+  if (!result || !tags || !peer_slots) return STK_ERR_NULL_POINTER;
+  if (row0 < 0 || n_rows < 0 || world < 1 || row_bytes <= 0 || row_bytes % 16 != 0 || slot_cap < 0)
+    return STK_ERR_BAD_DIMS;
+  const int64_t blocks = (n_rows * 32 + 255) / 256;
+  if (blocks > INT32_MAX) return STK_ERR_TOO_LARGE;
+  stk::ep_return_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(result), tags, peer_slots, row0, n_rows, world,
+      static_cast<int>(row_bytes / 16), slot_cap);
+  return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
+}
+
+extern "C" int stk_b200_weighted_sum_rows(const void* src, const int32_t* pos, const float* weights,
+                                          void* dst, int64_t tokens, int top_k, int64_t row_bytes,
+                                          int dtype, void* stream) {
   if (tokens == 0) return STK_OK;
-  if (!peer_bufs || !dest || !out) return STK_ERR_NULL_POINTER;
-  if (tokens < 0 || row_bytes <= 0 || row_bytes % 16 != 0 || cap_rows < 0) return STK_ERR_BAD_DIMS;
+  if (dtype != STK_F16 && dtype != STK_BF16) return STK_ERR_BAD_DTYPE;
+  if (tokens < 0 || top_k < 1 || row_bytes <= 0 || row_bytes % 16 != 0) return STK_ERR_BAD_DIMS;
+  if (!src || !dst) return STK_ERR_NULL_POINTER;
+  if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) return STK_ERR_BAD_LAYOUT;
   const int64_t blocks = (tokens * 32 + 255) / 256;
-  stk::ep_combine_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      peer_bufs, dest, static_cast<uint4*>(out), tokens, static_cast<int>(row_bytes / 16), cap_rows);
+  if (blocks > INT32_MAX || row_bytes / 16 > INT32_MAX) return STK_ERR_TOO_LARGE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == STK_BF16)
+    stk::weighted_sum_rows_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+        static_cast<const uint4*>(src), pos, weights, static_cast<uint4*>(dst), tokens, top_k,
+        static_cast<int>(row_bytes / 16));
+  else
+    stk::weighted_sum_rows_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+        static_cast<const uint4*>(src), pos, weights, static_cast<uint4*>(dst), tokens, top_k,
+        static_cast<int>(row_bytes / 16));
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 

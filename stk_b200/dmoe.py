@@ -25,7 +25,7 @@ BLOCK = 128
 
 # ------------------------------------------------------------------------------ building blocks
 def sort_by_expert(expert_ids, num_experts):
-    """Stable sort of token indices by expert: (order int32 [T], offsets int32 [E+1])."""
+    """Stable sort of token (or slot) indices by expert: (order int32 [T], offsets int32 [E+1])."""
     if expert_ids.is_cuda:
         ids16 = expert_ids.to(torch.int16)
         _, offsets, order = _kernels.transpose_meta(ids16, ids16, num_experts)
@@ -36,8 +36,9 @@ def sort_by_expert(expert_ids, num_experts):
     return order, offsets
 
 
-def gather_rows(src, index, n_out=None):
-    """out[i] = src[index[i]], or a zero row where index[i] < 0."""
+def gather_rows(src, index, n_out=None, index_div=1):
+    """out[i] = src[index[i] // index_div], or a zero row where index[i] < 0.  index_div = k when
+    `index` holds top-k slots (slot = token * k + choice) and `src` one row per token."""
     n_out = index.numel() if n_out is None else n_out
     if src.is_cuda:
         src = src.contiguous()
@@ -45,13 +46,36 @@ def gather_rows(src, index, n_out=None):
         with _lib.on_device(src.device):
             rc = _lib.load().stk_b200_gather_rows(
                 _lib.ptr(src), _lib.ptr(out), _lib.ptr(index), n_out,
-                src.shape[1] * src.element_size(), _lib.stream_ptr(src.device))
+                src.shape[1] * src.element_size(), index_div, _lib.stream_ptr(src.device))
         _lib.check(rc, "stk_b200_gather_rows")
         return out
     out = src.new_zeros((n_out, src.shape[1]))
     valid = index >= 0
-    out[valid] = src[index[valid].long()]
+    out[valid] = src[torch.div(index[valid].long(), index_div, rounding_mode="floor")]
     return out
+
+
+def weighted_sum_rows(src, position, weights, tokens, top_k):
+    """out[t] = sum_j weights[t, j] * src[position[t*k + j]] (fp32 accumulation, one rounding): the
+    top-k combine.  position None: src is slot-ordered; weights None: all ones (float32 [T, k] or
+    [T*k] otherwise); a negative position contributes nothing."""
+    if src.is_cuda:
+        src = src.contiguous()
+        out = torch.empty((tokens, src.shape[1]), dtype=src.dtype, device=src.device)
+        if weights is not None:
+            weights = weights.to(torch.float32).contiguous()
+        with _lib.on_device(src.device):
+            rc = _lib.load().stk_b200_weighted_sum_rows(
+                _lib.ptr(src), _lib.ptr(position), _lib.ptr(weights), _lib.ptr(out), tokens, top_k,
+                src.shape[1] * src.element_size(), _lib.dtype_code(src.dtype), _lib.stream_ptr(src.device))
+        _lib.check(rc, "stk_b200_weighted_sum_rows")
+        return out
+    slots = tokens * top_k
+    pos = torch.arange(slots) if position is None else position.long()
+    rows = src.float()[pos.clamp(min=0)] * (pos >= 0).float()[:, None]
+    if weights is not None:
+        rows = rows * weights.reshape(-1, 1).float()
+    return rows.view(tokens, top_k, -1).sum(1).to(src.dtype)
 
 
 def scatter_rows(src, index, n_out):
@@ -72,23 +96,27 @@ def scatter_rows(src, index, n_out):
     return out
 
 
-def bin_index(counts, total_padded, block=BLOCK, compose=None):
+def bin_index(counts, total_padded, block=BLOCK, compose=None, inverse_size=None):
     """Gather index of the padded expert bins.
 
     counts: int64 [world, local_experts], rows received from each peer for each local expert (the
     received rows are ordered by peer, then expert).  Returns (index int32 [total_padded],
-    bin_rows int32 [local_experts]); see stk_b200_bin_index in include/stk_b200.h."""
+    bin_rows int32 [local_experts]); see stk_b200_bin_index in include/stk_b200.h.  With
+    inverse_size = n a third result, position int32 [n], says where source row s went
+    (index[position[s]] == s)."""
     world, local = counts.shape
     if counts.is_cuda:
         dev = counts.device
         index = torch.empty(total_padded, dtype=torch.int32, device=dev)
         bin_rows = torch.empty(local, dtype=torch.int32, device=dev)
+        inverse = None if inverse_size is None else torch.full((inverse_size,), -1, dtype=torch.int32, device=dev)
+        counts = counts.contiguous()
         with _lib.on_device(dev):
             rc = _lib.load().stk_b200_bin_index(
-                _lib.ptr(counts.contiguous()), world, local, block, _lib.ptr(compose),
-                _lib.ptr(index), total_padded, _lib.ptr(bin_rows), _lib.stream_ptr(dev))
+                _lib.ptr(counts), world, local, block, _lib.ptr(compose),
+                _lib.ptr(index), total_padded, _lib.ptr(bin_rows), _lib.ptr(inverse), _lib.stream_ptr(dev))
         _lib.check(rc, "stk_b200_bin_index")
-        return index, bin_rows
+        return (index, bin_rows) if inverse_size is None else (index, bin_rows, inverse)
     per_expert = counts.sum(0)
     padded = ((per_expert + block - 1) // block) * block
     index = torch.full((total_padded,), -1, dtype=torch.int32)
@@ -105,7 +133,13 @@ def bin_index(counts, total_padded, block=BLOCK, compose=None):
     if compose is not None:
         valid = index >= 0
         index[valid] = compose[index[valid].long()]
-    return index, (padded // block).to(torch.int32)
+    bin_rows = (padded // block).to(torch.int32)
+    if inverse_size is None:
+        return index, bin_rows
+    inverse = torch.full((inverse_size,), -1, dtype=torch.int32)
+    valid = index >= 0
+    inverse[index[valid].long()] = torch.nonzero(valid).view(-1).to(torch.int32)
+    return index, bin_rows, inverse
 
 
 def padded_bins(counts, block=BLOCK):
@@ -115,11 +149,12 @@ def padded_bins(counts, block=BLOCK):
     return padded, starts, int(padded.sum().item())
 
 
-def topology_from_bins(bin_rows, block_rows, ffn, dtype, device, block=BLOCK, data=None):
+def topology_from_bins(bin_rows, block_rows, ffn, dtype, device, block=BLOCK, data=None, materialize=True):
     """stk.Matrix [block_rows*128, E*ffn]: expert e owns bin_rows[e] consecutive block rows and its
     own ffn/128 block columns.  bin_rows: int32 [E] on `device`; block_rows: their sum, known to the
     host.  All seven metadata arrays are written by one kernel (the transposed ones in closed
-    form, nothing is sorted)."""
+    form, nothing is sorted).  materialize=False: the values are a stride-0 placeholder of the right
+    shape that occupies no memory - enough for stk.ops.sdd, which only takes the shape from it."""
     experts = bin_rows.numel()
     cpb = ffn // block
     nnz = block_rows * cpb
@@ -135,7 +170,8 @@ def topology_from_bins(bin_rows, block_rows, ffn, dtype, device, block=BLOCK, da
             _lib.stream_ptr(device))
     _lib.check(rc, "stk_b200_dmoe_topology")
     if data is None:
-        data = torch.empty((nnz, block, block), dtype=dtype, device=device)
+        data = (torch.empty((nnz, block, block), dtype=dtype, device=device) if materialize
+                else torch.empty((), dtype=dtype, device=device).expand(nnz, block, block))
     if cpb % 2 == 0:
         # Known by construction: all block rows of an expert share one column list and column
         # pairs never straddle experts; only row pairs at expert boundaries fail to pair.
@@ -174,41 +210,63 @@ def read_back(t):
 
 
 # ------------------------------------------------------------------------------ one GPU
-def route_top1(expert_ids, num_experts, block=BLOCK):
-    """Placement of tokens in padded expert order for top-1 routing on one device.
+def _flat_slots(expert_ids):
+    """(flat expert id per slot, k): expert_ids is [T] (top-1) or [T, k]; slot = token * k + choice."""
+    if expert_ids.dim() == 1:
+        return expert_ids, 1
+    return expert_ids.reshape(-1), expert_ids.shape[1]
 
-    Returns (index, padded, bin_rows, total): padded row r holds token index[r] (or is zero
-    padding where index[r] < 0); padded = rows per expert bin (host int64 [E]); bin_rows = the same
-    in blocks, on the device."""
-    order, offsets = sort_by_expert(expert_ids, num_experts)
+
+def route_topk(expert_ids, num_experts, block=BLOCK):
+    """Placement of the (token, choice) slots of top-k routing in padded expert order on one device.
+
+    expert_ids: [T] or [T, k].  Returns (index, position, padded, bin_rows, total): padded row r
+    holds slot index[r] (zero padding where index[r] < 0); slot s sits in padded row position[s];
+    padded = rows per expert bin (host int64 [E]); bin_rows = the same in blocks, on the device."""
+    flat, _ = _flat_slots(expert_ids)
+    order, offsets = sort_by_expert(flat, num_experts)
     counts = (offsets[1:] - offsets[:-1]).to(torch.int64).view(1, num_experts)
     host_counts = read_back(counts).view(-1)               # the one synchronisation
     padded = ((host_counts + block - 1) // block) * block
     total = int(padded.sum())
-    index, bin_rows = bin_index(counts, total, block, compose=order)
+    index, bin_rows, position = bin_index(counts, total, block, compose=order, inverse_size=flat.numel())
+    return index, position, padded, bin_rows, total
+
+
+def route_top1(expert_ids, num_experts, block=BLOCK):
+    """route_topk for one choice per token, without the inverse: (index, padded, bin_rows, total)."""
+    index, _, padded, bin_rows, total = route_topk(expert_ids, num_experts, block)
     return index, padded, bin_rows, total
 
 
-def permute_tokens(x, index, total_rows=None):
-    """Padded, expert-ordered copy of the token matrix x [T, h] (padding rows are zero)."""
-    return gather_rows(x, index, total_rows)
+def permute_tokens(x, index, total_rows=None, top_k=1):
+    """Padded, expert-ordered copy of the token matrix x [T, h] (padding rows are zero); with top_k > 1
+    `index` holds slots and every token's row is copied to each of its k places."""
+    return gather_rows(x, index, total_rows, index_div=top_k)
 
 
 def unpermute_tokens(y, index, tokens):
-    """Inverse of permute_tokens: token t gets the padded row that held it."""
+    """Inverse of permute_tokens for top-1 routing: token t gets the padded row that held it."""
     return scatter_rows(y, index, tokens)
+
+
+def combine_tokens(y, position, weights, tokens, top_k):
+    """Inverse of permute_tokens for top-k routing: out[t] = sum_j weights[t, j] * y[position[t*k + j]]."""
+    return weighted_sum_rows(y, position, weights, tokens, top_k)
 
 
 # ------------------------------------------------------------------------------ expert parallel
 class ExpertParallelExchange:
     """Token exchange of an expert-parallel dMoE layer: rank g owns experts
-    [g*E/n, (g+1)*E/n); every rank starts with its own tokens and their expert ids.
+    [g*E/n, (g+1)*E/n); every rank starts with its own tokens and their expert ids ([T] or, for
+    top-k routing, [T, k]).
 
-    dispatch(): tokens are sorted by expert (hence by destination rank), the per-expert counts are
-    exchanged, and the rows travel with all_to_all_single; the receiver gathers them into
-    per-expert bins padded to a multiple of 128 rows.  combine(): the inverse.  One host read-back
-    per dispatch (the counts: NCCL needs the split sizes on the host).  Works with any
-    torch.distributed backend: NCCL over NVLink on the GPUs, gloo on the host for tests.
+    dispatch(): the (token, choice) slots are sorted by expert (hence by destination rank), the
+    per-expert counts are exchanged, and the rows travel with all_to_all_single; the receiver gathers
+    them into per-expert bins padded to a multiple of 128 rows.  combine(): the inverse, with the k
+    rows of a token summed under their weights.  One host read-back per dispatch (the counts: NCCL
+    needs the split sizes on the host).  Works with any torch.distributed backend: NCCL over NVLink
+    on the GPUs, gloo on the host for tests.
     """
 
     def __init__(self, num_experts, group=None, block=BLOCK):
@@ -226,7 +284,8 @@ class ExpertParallelExchange:
         state["block_rows"] is the number of padded block rows (host int)."""
         dev = x.device
         world, local = self.world, self.local_experts
-        order, offsets = sort_by_expert(expert_ids, self.num_experts)
+        flat, top_k = _flat_slots(expert_ids)
+        order, offsets = sort_by_expert(flat, self.num_experts)
         counts = torch.empty((2, self.num_experts), dtype=torch.int64, device=dev)
         counts[0] = offsets[1:] - offsets[:-1]
         # counts[0][e] for the experts of rank g go to rank g: one row of E/n counts per peer
@@ -238,22 +297,26 @@ class ExpertParallelExchange:
         per_expert = recv_by_peer.sum(0)
         total = int((((per_expert + self.block - 1) // self.block) * self.block).sum())
         recv = torch.empty((sum(recv_splits), x.shape[1]), dtype=x.dtype, device=dev)
-        dist.all_to_all_single(recv, gather_rows(x, order), recv_splits, send_splits,
+        dist.all_to_all_single(recv, gather_rows(x, order, index_div=top_k), recv_splits, send_splits,
                                group=self.group)
         index, bin_rows = bin_index(counts[1].view(world, local), total, self.block)
         x_padded = gather_rows(recv, index, total)
         state = dict(order=order, send_splits=send_splits, recv_splits=recv_splits, index=index,
-                     received=recv.shape[0], tokens=x.shape[0], block_rows=total // self.block)
+                     received=recv.shape[0], tokens=x.shape[0], top_k=top_k, block_rows=total // self.block)
         return x_padded, bin_rows, state
 
-    def combine(self, y_padded, state):
-        """Inverse of dispatch for the per-token results y_padded [T'_local, h_out]."""
+    def combine(self, y_padded, state, weights=None):
+        """Inverse of dispatch for the per-slot results y_padded [T'_local, h_out]: token t gets
+        sum_j weights[t, j] * (result of its j-th slot); weights None = ones."""
+        slots = state["tokens"] * state["top_k"]
         back = scatter_rows(y_padded, state["index"], state["received"])
-        out_sorted = torch.empty((state["tokens"], y_padded.shape[1]), dtype=y_padded.dtype,
-                                 device=y_padded.device)
+        out_sorted = torch.empty((slots, y_padded.shape[1]), dtype=y_padded.dtype, device=y_padded.device)
         dist.all_to_all_single(out_sorted, back, state["send_splits"], state["recv_splits"],
                                group=self.group)
-        return scatter_rows(out_sorted, state["order"], state["tokens"])
+        by_slot = scatter_rows(out_sorted, state["order"], slots)
+        if state["top_k"] == 1 and weights is None:
+            return by_slot
+        return weighted_sum_rows(by_slot, None, weights, state["tokens"], state["top_k"])
 
 
 # ------------------------------------------------------------------------------ exchange over peer memory
@@ -264,140 +327,242 @@ def _ep_call(name, device, *args):
 
 
 class PeerExchangeBuffers:
-    """One rank's share of the exchange state: the count matrix, the padded bins the peers push token
-    rows into, and the result rows the peers pull from.  `peer_*` are int64 device arrays with the
-    address of the same region on every rank, as mapped in this process."""
+    """One rank's share of the exchange state.  Written by the peers: the count matrix, the padded
+    bins (token rows and their tags), the slot-ordered rows that come back, and two flag arrays for
+    the barriers.  `peer_*` are int64 device arrays with the address of the same region on every
+    rank, as mapped in this process."""
 
-    def __init__(self, counts, recv, result, peer_counts, peer_recv, peer_result):
-        self.counts, self.recv, self.result = counts, recv, result
-        self.peer_counts, self.peer_recv, self.peer_result = peer_counts, peer_recv, peer_result
+    def __init__(self, counts, recv, tags, slots, peer_counts, peer_recv, peer_tags, peer_slots,
+                 peer_flags=(None, None)):
+        self.counts, self.recv, self.tags, self.slots = counts, recv, tags, slots
+        self.peer_counts, self.peer_recv, self.peer_tags, self.peer_slots = peer_counts, peer_recv, peer_tags, peer_slots
+        self.peer_flags = peer_flags
 
 
 class PeerExchange:
     """ExpertParallelExchange with this library's own kernels moving the rows over NVLink.
 
-    Every rank pushes its token rows straight into the padded expert bins of the rank that owns
-    the expert (peer stores) and pulls its results from that rank's result buffer (peer loads); the
-    buffers live in torch symmetric memory, allocated once for `capacity_rows` padded rows.  There
-    is no NCCL call in a step: the per-expert counts travel the same way, and the steps are
-    separated by the symmetric-memory barrier.  One host read-back per dispatch (the number of
-    padded rows, which sizes the topology).  Same results, row for row, as ExpertParallelExchange.
+    Every rank pushes the token row of each of its (token, choice) slots straight into the padded bin
+    of the slot's expert on the rank that owns it, tagged with where it came from; after the
+    experts' MLP the owner pushes every result row back into the home rank's slot-ordered buffer,
+    where the k rows of a token are summed under their weights.  Only stores cross NVLink.  The
+    buffers live in torch symmetric memory, allocated once for `capacity_rows` padded rows; there is
+    no NCCL call in a step: the per-expert counts travel the same way, and the phases are separated by
+    the library's own barrier kernel (bounded wait).  One host read-back per dispatch (the padded row
+    counts, which size the topology).  Same results as ExpertParallelExchange.
+
+    chunks > 1 cuts every rank's local experts into that many groups; forward() then overlaps the
+    exchange of one group with the products of another on a second stream.
 
     `buffers` / `barrier` can be given to run several ranks of this logic inside one process on one
-    GPU (tests): then nothing is allocated here and `barrier()` is called where ranks must meet.
+    GPU (tests): then nothing is allocated here and `barrier(channel)` is called where ranks meet.
     """
 
+    BARRIER_TIMEOUT_MS = 20000
+
     def __init__(self, num_experts, tokens, hidden, out_hidden, dtype, device, group=None,
-                 block=BLOCK, capacity_rows=None, world=None, rank=None, buffers=None, barrier=None):
+                 block=BLOCK, capacity_rows=None, world=None, rank=None, buffers=None, barrier=None,
+                 top_k=1, chunks=1):
         self.world = dist.get_world_size(group) if world is None else world
         self.rank = dist.get_rank(group) if rank is None else rank
         if num_experts % self.world != 0:
             raise ValueError(f"{num_experts} experts do not divide over {self.world} ranks")
         self.num_experts, self.local_experts = num_experts, num_experts // self.world
+        if not 1 <= chunks <= min(self.local_experts, 8):
+            raise ValueError(f"chunks must lie in 1..min(local experts, 8), got {chunks}")
         self.block, self.device, self.dtype = block, torch.device(device), dtype
-        self.hidden, self.out_hidden = hidden, out_hidden
+        self.hidden, self.out_hidden, self.top_k, self.chunks = hidden, out_hidden, top_k, chunks
+        self.slot_rows = tokens * top_k
         if capacity_rows is None:
-            capacity_rows = 2 * tokens + self.local_experts * block
+            capacity_rows = 2 * self.slot_rows + self.local_experts * block
         self.capacity_rows = (capacity_rows + block - 1) // block * block
         if buffers is None:
             # symmetric allocations have the same size on every rank
-            cap = torch.tensor([self.capacity_rows], dtype=torch.int64, device=self.device)
+            cap = torch.tensor([self.capacity_rows, self.slot_rows], dtype=torch.int64, device=self.device)
             dist.all_reduce(cap, op=dist.ReduceOp.MAX, group=group)
-            self.capacity_rows = int(cap.item())
-            buffers, barrier = self._allocate(group)
+            self.capacity_rows, self.slot_rows = int(cap[0]), int(cap[1])
+            buffers = self._allocate(group)
+        if barrier is None:
+            barrier = self._barrier
         self.buf, self.barrier = buffers, barrier
-        self._totals_host = torch.empty(2, dtype=torch.int64).pin_memory()
+        self.result = torch.empty((self.capacity_rows, out_hidden), dtype=dtype, device=self.device)
+        self._totals_host = torch.zeros(3 + chunks, dtype=torch.int64).pin_memory()
+        self._epoch = [0, 0]
+        self._side = None
 
     def _allocate(self, group):
         import torch.distributed._symmetric_memory as symm_mem
         elem = torch.empty((), dtype=self.dtype).element_size()
         align = lambda n: (n + 255) // 256 * 256
-        n_counts = align(4 * self.world * self.num_experts)
-        n_recv = align(self.capacity_rows * self.hidden * elem)
-        n_result = align(self.capacity_rows * self.out_hidden * elem)
-        raw = symm_mem.empty(n_counts + n_recv + n_result, dtype=torch.uint8, device=self.device)
+        sizes = [2 * 8 * 64,                                           # two flag arrays of 64 int64
+                 4 * self.world * self.num_experts,                    # counts
+                 self.capacity_rows * self.hidden * elem,              # recv
+                 8 * self.capacity_rows,                               # tags
+                 self.slot_rows * self.out_hidden * elem]              # slots
+        offs = [0]
+        for n in sizes:
+            offs.append(offs[-1] + align(n))
+        raw = symm_mem.empty(offs[-1], dtype=torch.uint8, device=self.device)
+        raw[:offs[1]].zero_()
+        torch.cuda.synchronize(self.device)
         handle = symm_mem.rendezvous(raw, group if group is not None else dist.group.WORLD)
+        dist.barrier(group=group)                                     # everyone's flags are zero before anyone signals
         ptrs = [int(p) for p in handle.buffer_ptrs]
         dev_ptrs = lambda off: torch.tensor([p + off for p in ptrs], dtype=torch.int64, device=self.device)
-        counts = raw[:4 * self.world * self.num_experts].view(torch.int32).view(self.world, self.num_experts)
-        recv = raw[n_counts:n_counts + self.capacity_rows * self.hidden * elem].view(self.dtype)
-        result = raw[n_counts + n_recv:n_counts + n_recv + self.capacity_rows * self.out_hidden * elem].view(self.dtype)
-        buffers = PeerExchangeBuffers(counts, recv.view(self.capacity_rows, self.hidden),
-                                      result.view(self.capacity_rows, self.out_hidden),
-                                      dev_ptrs(0), dev_ptrs(n_counts), dev_ptrs(n_counts + n_recv))
+        view = lambda i: raw[offs[i]:offs[i] + sizes[i]]
+        counts = view(1).view(torch.int32).view(self.world, self.num_experts)
+        recv = view(2).view(self.dtype).view(self.capacity_rows, self.hidden)
+        tags = view(3).view(torch.int64)
+        slots = view(4).view(self.dtype).view(self.slot_rows, self.out_hidden)
         self._raw, self._handle = raw, handle
-        return buffers, handle.barrier
+        return PeerExchangeBuffers(counts, recv, tags, slots, dev_ptrs(offs[1]), dev_ptrs(offs[2]),
+                                   dev_ptrs(offs[3]), dev_ptrs(offs[4]), (dev_ptrs(0), dev_ptrs(8 * 64)))
 
-    # The three phases of dispatch are separate so that a single-process emulation can interleave
-    # the ranks; dispatch() runs them back to back with the barriers in between.
+    def _barrier(self, channel):
+        """All ranks meet on the current stream (channel 0: main stream, 1: the exchange stream)."""
+        self._epoch[channel] += 1
+        _ep_call("stk_b200_ep_barrier", self.device, _lib.ptr(self.buf.peer_flags[channel]), self.world,
+                 self.rank, self._epoch[channel], self.BARRIER_TIMEOUT_MS)
+
+    # The phases are separate methods so that a single-process emulation can interleave the ranks;
+    # dispatch() / combine() / forward() run them in order with the barriers in between.
     def share_counts(self, expert_ids):
-        order, offsets = sort_by_expert(expert_ids, self.num_experts)
+        flat, top_k = _flat_slots(expert_ids)
+        if top_k != self.top_k:
+            raise ValueError(f"exchange built for top-{self.top_k} routing, got {top_k} choices per token")
+        order, offsets = sort_by_expert(flat, self.num_experts)
         _ep_call("stk_b200_ep_share_counts", self.device, _lib.ptr(offsets), _lib.ptr(self.buf.peer_counts),
                  self.world, self.num_experts, self.rank)
         return order, offsets
 
-    def push(self, x, order, offsets):
-        dev, tokens = self.device, x.shape[0]
-        x = x.contiguous()
+    def plan(self):
+        """After the counts of all ranks have arrived: where this rank's rows go, this rank's bins,
+        the padded row counts (copied to pinned host memory by a kernel), zeroed padding rows."""
+        dev = self.device
         dest_base = torch.empty(self.num_experts, dtype=torch.int64, device=dev)
         bin_rows = torch.empty(self.local_experts, dtype=torch.int32, device=dev)
-        totals = torch.empty(2, dtype=torch.int64, device=dev)
+        totals = torch.empty(3 + self.chunks, dtype=torch.int64, device=dev)
         _ep_call("stk_b200_ep_plan", dev, _lib.ptr(self.buf.counts), self.world, self.num_experts, self.rank,
-                 self.block, _lib.ptr(dest_base), _lib.ptr(bin_rows), _lib.ptr(totals))
+                 self.block, self.chunks, _lib.ptr(dest_base), _lib.ptr(bin_rows), _lib.ptr(totals))
         with _lib.on_device(dev):        # by a kernel, not the copy engine (see read_back)
-            rc = _lib.load().stk_b200_copy_bytes(_lib.ptr(totals), self._totals_host.data_ptr(), 16,
-                                                 _lib.stream_ptr(dev))
+            rc = _lib.load().stk_b200_copy_bytes(_lib.ptr(totals), self._totals_host.data_ptr(),
+                                                 8 * (3 + self.chunks), _lib.stream_ptr(dev))
         _lib.check(rc, "stk_b200_copy_bytes")
-        row_bytes = self.hidden * x.element_size()
+        elem = self.buf.recv.element_size()
         _ep_call("stk_b200_ep_zero_padding", dev, _lib.ptr(self.buf.counts), self.world, self.num_experts,
-                 self.rank, self.block, _lib.ptr(self.buf.recv), row_bytes, self.capacity_rows)
-        dest = torch.empty(tokens, dtype=torch.int64, device=dev)
-        _ep_call("stk_b200_ep_dispatch", dev, _lib.ptr(x), _lib.ptr(order), _lib.ptr(offsets),
-                 _lib.ptr(dest_base), _lib.ptr(self.buf.peer_recv), tokens, self.world, self.num_experts,
-                 row_bytes, self.capacity_rows, _lib.ptr(dest))
-        return dest, bin_rows
+                 self.rank, self.block, _lib.ptr(self.buf.recv), _lib.ptr(self.buf.tags), self.hidden * elem,
+                 self.capacity_rows)
+        self._planned = torch.cuda.Event()
+        self._planned.record(torch.cuda.current_stream(dev))
+        return dest_base, bin_rows
+
+    def push(self, x, order, offsets, dest_base, chunk=0, chunks=1):
+        """This rank's rows (of the experts in `chunk` of every owner) into the owners' bins."""
+        x = x.contiguous()
+        _ep_call("stk_b200_ep_dispatch", self.device, _lib.ptr(x), _lib.ptr(order), _lib.ptr(offsets),
+                 _lib.ptr(dest_base), _lib.ptr(self.buf.peer_recv), _lib.ptr(self.buf.peer_tags),
+                 order.numel(), self.top_k, self.world, self.num_experts, self.rank, chunk, chunks,
+                 self.hidden * x.element_size(), self.capacity_rows)
+        return x
+
+    def totals(self):
+        """Host values (padded rows of this rank, rows received, largest padded row count of any
+        rank, padded rows per chunk); waits for plan() only.  Every rank sees the same largest count,
+        so if the buffers of ANY rank are too small every rank raises here, before the next barrier."""
+        self._planned.synchronize()                                    # the one synchronisation
+        t = [int(v) for v in self._totals_host]
+        if t[2] > self.capacity_rows:
+            raise RuntimeError(f"{t[2]} padded rows arrive at one rank but the exchange buffers hold "
+                               f"{self.capacity_rows}: construct PeerExchange with a larger capacity_rows")
+        return t
 
     def padded_rows(self):
-        """Host value of this rank's padded row count (waits for the stream)."""
-        torch.cuda.current_stream(self.device).synchronize()       # the one synchronisation
-        total = int(self._totals_host[0])
-        if total > self.capacity_rows:
-            raise RuntimeError(f"{total} padded rows arrive at rank {self.rank} but the exchange buffers hold "
-                               f"{self.capacity_rows}: construct PeerExchange with a larger capacity_rows")
-        return total
+        return self.totals()[0]
 
     def dispatch(self, x, expert_ids):
         """Returns (x_padded [T'_local, h] - a view of the receive buffer, valid until the next
         dispatch -, bin_rows int32 [local_experts], state)."""
         order, offsets = self.share_counts(expert_ids)
         self.barrier(0)
-        dest, bin_rows = self.push(x, order, offsets)
-        self.barrier(1)                  # enqueued before the read-back: it runs while the host wakes up
-        total = self.padded_rows()
-        state = dict(dest=dest, tokens=x.shape[0], block_rows=total // self.block, total=total)
-        return self.buf.recv[:total], bin_rows, state
+        dest_base, bin_rows = self.plan()
+        keep = self.push(x, order, offsets, dest_base)
+        self.barrier(0)                  # enqueued before the read-back: it runs while the host wakes up
+        t = self.totals()
+        state = dict(tokens=x.shape[0], block_rows=t[0] // self.block, total=t[0], keep=keep)
+        return self.buf.recv[:t[0]], bin_rows, state
 
     def result_rows(self, state):
-        """The rows of the result buffer for this dispatch: write the expert outputs here (e.g.
+        """Where the experts' output rows of this dispatch belong: write them here (e.g.
         stk.ops.dsd(h, w2, out=...)) and combine() has nothing to copy."""
-        return self.buf.result[:state["total"]]
+        return self.result[:state["total"]]
 
-    def publish(self, y_padded, state):
+    def give_back(self, row0, n_rows):
+        """Result rows [row0, row0 + n_rows) travel to the slot-ordered buffers of their home ranks."""
+        _ep_call("stk_b200_ep_return", self.device, _lib.ptr(self.result), _lib.ptr(self.buf.tags),
+                 _lib.ptr(self.buf.peer_slots), row0, n_rows, self.world,
+                 self.out_hidden * self.result.element_size(), self.slot_rows)
+
+    def gather_slots(self, tokens, weights=None):
+        """out[t] = sum_j weights[t, j] * (row that came back for slot t*k + j)."""
+        return weighted_sum_rows(self.buf.slots, None, weights, tokens, self.top_k)
+
+    def combine(self, y_padded, state, weights=None):
+        """Inverse of dispatch for the per-slot results y_padded [T'_local, out_hidden]."""
         target = self.result_rows(state)
         if y_padded.data_ptr() != target.data_ptr():
             target.copy_(y_padded)
+        self.give_back(0, state["total"])
+        self.barrier(0)
+        return self.gather_slots(state["tokens"], weights)
 
-    def pull(self, state):
-        out = torch.empty((state["tokens"], self.out_hidden), dtype=self.dtype, device=self.device)
-        _ep_call("stk_b200_ep_combine", self.device, _lib.ptr(self.buf.peer_result), _lib.ptr(state["dest"]),
-                 _lib.ptr(out), state["tokens"], self.out_hidden * out.element_size(), self.capacity_rows)
-        return out
+    def forward(self, x, expert_ids, weights, expert_fn):
+        """One expert-parallel step with the exchange overlapped chunk by chunk.
 
-    def combine(self, y_padded, state):
-        """Inverse of dispatch for the per-token results y_padded [T'_local, out_hidden]."""
-        self.publish(y_padded, state)
-        self.barrier(2)
-        return self.pull(state)
+        expert_fn(chunk, x_rows, bin_rows, block_rows, out_rows) runs the experts' MLP of one chunk:
+        x_rows [rows, hidden] are the padded bins of the chunk's experts (bin_rows int32 on the
+        device, one entry per expert of the chunk; block_rows their sum, a host int) and the result
+        goes into out_rows [rows, out_hidden].  While chunk c is computed on the current stream, the
+        rows of chunk c + 1 arrive and the results of chunk c - 1 travel home on a second stream."""
+        dev, chunks = self.device, self.chunks
+        if self._side is None:
+            self._side = torch.cuda.Stream(dev)
+        main, side = torch.cuda.current_stream(dev), self._side
+        order, offsets = self.share_counts(expert_ids)
+        self.barrier(0)
+        dest_base, bin_rows = self.plan()
+        side.wait_event(self._planned)
+        pushed = []
+        with torch.cuda.stream(side):
+            for c in range(chunks):
+                keep = self.push(x, order, offsets, dest_base, c, chunks)
+                self.barrier(1)
+                ev = torch.cuda.Event()
+                ev.record(side)
+                pushed.append(ev)
+        for used_on_side in (keep, order, offsets, dest_base):
+            used_on_side.record_stream(side)
+        t = self.totals()
+        per = self.local_experts
+        row0 = 0
+        for c in range(chunks):
+            rows = t[3 + c]
+            e0, e1 = -(-c * per // chunks), -(-(c + 1) * per // chunks)     # experts with le*chunks//per == c
+            main.wait_event(pushed[c])
+            if rows:
+                expert_fn(c, self.buf.recv[row0:row0 + rows], bin_rows[e0:e1], rows // self.block,
+                          self.result[row0:row0 + rows])
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(side):
+                side.wait_event(done)
+                self.give_back(row0, rows)
+            row0 += rows
+        with torch.cuda.stream(side):
+            self.barrier(1)
+            home = torch.cuda.Event()
+            home.record(side)
+        main.wait_event(home)
+        return self.gather_slots(x.shape[0], weights)
 
 
 # ------------------------------------------------------------------------------ batches from host memory

@@ -29,6 +29,34 @@ def test_route_top1_and_padding():
     check_routing(dmoe, torch.randn(300, 8), torch.randint(0, 2, (300,)) * 3, 5)   # empty experts
 
 
+def check_topk(dmoe, x, ids, weights, experts, tol=1e-5):
+    """Top-k routing: every (token, choice) slot lands in its expert's bin, and the weighted combine
+    of per-slot results gives sum_j w[t, j] * f(x[t])."""
+    tokens, k = ids.shape
+    index, position, padded, bin_rows, total = dmoe.route_topk(ids, experts)
+    assert total == int(padded.sum()) and index.numel() == total and position.numel() == tokens * k
+    xp = dmoe.permute_tokens(x, index, total, top_k=k)
+    idx, pos = index.cpu().long(), position.cpu().long()
+    assert torch.equal(idx[pos], torch.arange(tokens * k))               # position inverts index
+    flat = ids.cpu().reshape(-1)
+    starts = torch.cumsum(padded, 0) - padded
+    for e in range(experts):
+        rows = xp[starts[e]:starts[e] + padded[e]].cpu()
+        slots = torch.nonzero(flat == e).view(-1)
+        assert torch.equal(rows[:slots.numel()], x.cpu()[slots // k])    # stable slot order inside an expert
+        assert torch.count_nonzero(rows[slots.numel():]).item() == 0
+    out = dmoe.combine_tokens(xp * 2, position, weights, tokens, k)
+    expect = 2 * x.float() * weights.float().sum(1, keepdim=True)
+    assert torch.allclose(out.float().cpu(), expect.cpu(), rtol=tol, atol=tol)
+
+
+def test_route_topk_and_weighted_combine():
+    from stk_b200 import dmoe
+    torch.manual_seed(1)
+    check_topk(dmoe, torch.randn(500, 8), torch.randint(0, 6, (500, 2)), torch.rand(500, 2), 6)
+    check_topk(dmoe, torch.randn(77, 8), torch.randint(0, 3, (77, 3)) * 2, torch.rand(77, 3), 7)
+
+
 def _exchange_worker(rank, world, port, tmp):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -58,6 +86,20 @@ def _exchange_worker(rank, world, port, tmp):
         y = xp * 2 + tag[:, None].float() * (xp.abs().sum(1, keepdim=True) > 0)
         out = ex.combine(y, state)
         assert torch.allclose(out, x * 2 + ids[:, None].float())
+        # top-2 routing with weights through the same exchange
+        ids2 = torch.randint(0, E, (T, 2))
+        w2 = torch.rand(T, 2)
+        xp2, bins2, st2 = ex.dispatch(x, ids2)
+        assert xp2.shape[0] == int(bins2.sum()) * 128
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (x, ids2))
+        starts2 = torch.cumsum(bins2.long() * 128, 0) - bins2.long() * 128
+        for le in range(ex.local_experts):
+            e = rank * ex.local_experts + le
+            expect = torch.cat([gx[torch.nonzero(gi.reshape(-1) == e).view(-1) // 2] for gx, gi in gathered])
+            assert torch.equal(xp2[starts2[le]:starts2[le] + expect.shape[0]], expect)
+        out2 = ex.combine(xp2 * 3, st2, w2)
+        assert torch.allclose(out2, 3 * x * w2.sum(1, keepdim=True), rtol=1e-5, atol=1e-5)
         # mismatched expert count is a host-side error, raised before any collective
         try:
             dmoe.ExpertParallelExchange(7)

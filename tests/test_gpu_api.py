@@ -1,0 +1,221 @@
+"""GPU tests of the API surface around the products: element-wise mul (the reference's
+stk/ops/eltwise_ops_test.py), autocast behaviour (stk/backend/autocast.py), externally supplied
+transposed metadata in the reference's tie order, the kernel-choice statistics, the pair kernel's
+work-item table, top-k routing against the host logic, and bad metadata handed to the transpose."""
+import itertools
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import stk_oracle as oracle
+from tests.parity import assert_product_close
+
+pytestmark = pytest.mark.gpu
+
+_ELTWISE_SIZES = (
+    (128, 128, 0.0), (256, 256, 0.5), (2048, 1024, 0.8), (512, 128, 0.0), (128, 512, 0.0),
+    (1024, 512, 0.0), (1024, 512, 0.5), (1024, 512, 0.75), (512, 1024, 0.0), (512, 1024, 0.5),
+    (512, 1024, 0.75), (1024, 1024, 0.0), (1024, 1024, 0.5), (1024, 1024, 0.75),
+)
+_DTYPE = (torch.float16, torch.bfloat16)
+
+
+@pytest.fixture(scope="module")
+def stk():
+    import stk_b200
+    from stk_b200.backend import lib
+    yield stk_b200
+    assert lib.device_status() == 0
+
+
+def _dense_and_sparse(stk, rows, cols, sparsity, dtype, std=0.1):
+    mask = stk.random.dense_mask(rows, cols, sparsity, 128)
+    dense = (torch.randn(rows, cols) * std * mask).type(dtype).cuda()
+    sparse = stk.ops.to_sparse(dense, 128)
+    return dense.requires_grad_(True), sparse.requires_grad_(True)
+
+
+@pytest.mark.parametrize("m,n,sparsity,dtype", [(*s, d) for s, d in itertools.product(_ELTWISE_SIZES, _DTYPE)])
+def test_eltwise_mul(stk, m, n, sparsity, dtype):
+    """stk.ops.mul forward and both gradients against torch.mul on the dense twins
+    (stk/ops/eltwise_ops_test.py:53-83).  Element-wise products of 16-bit values: one rounding."""
+    torch.manual_seed(m + n)
+    a_dense, a = _dense_and_sparse(stk, m, n, sparsity, dtype)
+    b_vals = (torch.randn_like(a.data) * 0.1).detach()
+    b = stk.Matrix(a.size(), b_vals, a.row_indices, a.column_indices, a.offsets)
+    b_dense = stk.ops.to_dense(b).requires_grad_(True)
+    b.requires_grad_(True)
+    out = stk.ops.mul(a, b)
+    expected = torch.mul(a_dense, b_dense)
+    expected.sum().backward()
+    stk.ops.sum(out).backward()
+    dense_out = stk.ops.to_dense(out)
+    assert dense_out.dim() == 2 and dense_out.size() == expected.size() and dense_out.dtype == dtype
+    assert torch.equal(dense_out, expected.detach())
+    assert torch.equal(stk.ops.to_dense(a.grad), a_dense.grad)
+    assert torch.equal(stk.ops.to_dense(b.grad), b_dense.grad)
+
+
+@pytest.mark.parametrize("op", ["sdd", "dsd", "dds"])
+def test_ops_under_autocast(stk, op):
+    """Under torch.autocast(bfloat16) the products cast their fp32 operands to bfloat16, run with
+    autocast off, and return bfloat16 (stk/backend/autocast.py:19-37); gradients flow back in fp32."""
+    np.random.seed(5)
+    torch.manual_seed(5)
+    topo = stk.random.mask(384, 256, 0.5, 128).to("cuda")
+    a32 = (torch.randn(384, 192, device="cuda") * 0.1).requires_grad_(True)
+    b32 = (torch.randn(192, 256, device="cuda") * 0.1).requires_grad_(True)
+    sp_vals = (torch.randn(topo.data.shape, device="cuda") * 0.1)
+    bf = torch.bfloat16
+    r, c = topo.row_indices.cpu().numpy(), topo.column_indices.cpu().numpy()
+    with torch.autocast(device_type="cuda", dtype=bf):
+        if op == "sdd":
+            out = stk.ops.sdd(a32, b32, topo)
+            got, ref = out.data, oracle.sdd(a32.detach().cpu().to(bf), b32.detach().cpu().to(bf), r, c, bf)
+            leaves = (a32, b32)
+        else:
+            s = stk.Matrix(topo.size(), sp_vals.clone().requires_grad_(True), topo.row_indices,
+                           topo.column_indices, topo.offsets, topo.column_indices_t, topo.offsets_t,
+                           topo.block_offsets_t)
+            s_dense = oracle.to_dense(sp_vals.cpu().to(bf), r, c, (384, 256))
+            if op == "dsd":
+                d32 = (torch.randn(256, 128, device="cuda") * 0.1).requires_grad_(True)
+                got, ref = stk.ops.dsd(s, d32), oracle.dsd(s_dense, d32.detach().cpu().to(bf), bf)
+            else:
+                d32 = (torch.randn(128, 384, device="cuda") * 0.1).requires_grad_(True)
+                got, ref = stk.ops.dds(d32, s), oracle.dds(d32.detach().cpu().to(bf), s_dense, bf)
+            leaves = (s.data, d32)
+        assert torch.is_autocast_enabled()
+    assert got.dtype == bf
+    assert_product_close(got, ref, f"{op} under autocast")
+    got.float().sum().backward()
+    for leaf in leaves:
+        assert leaf.grad is not None and leaf.grad.dtype == torch.float32 and leaf.grad.shape == leaf.shape
+
+
+@pytest.mark.parametrize("mode", ["auto", "1"])
+def test_external_transposed_metadata_in_reference_tie_order(stk, golden, mode):
+    """A Matrix built from all seven fields as the reference produces them: its unstable argsort leaves
+    the rows inside a block column unordered (stk/matrix.py:110; fixture sq205).  The products through
+    the transposed metadata must still be right - the pair kernel's merge needs ascending lists, so
+    such a topology must end up on a kernel that does not."""
+    from stk_b200.backend import kernels
+    g = golden["metadata"]
+    t = lambda k, dt: torch.from_numpy(g[f"sq205/{k}"].astype(dt)).cuda()
+    cit, bot, ot = g["sq205/column_indices_t"], g["sq205/block_offsets_t"], g["sq205/offsets_t"]
+    unsorted_cols = sum(1 for c in range(len(ot) - 1) if np.any(np.diff(cit[ot[c]:ot[c + 1]].astype(np.int64)) < 0))
+    assert unsorted_cols > 0, "the fixture must hold the reference's non-stable order"
+    nnz = len(cit)
+    torch.manual_seed(2)
+    data = (torch.randn(nnz, 128, 128) * 0.1).half()
+    m = stk.Matrix(torch.Size((2048, 2048)), data.cuda(), t("row_indices", np.int16), t("column_indices", np.int16),
+                   t("offsets", np.int32), t("column_indices_t", np.int16), t("offsets_t", np.int32),
+                   t("block_offsets_t", np.int32))
+    dense = oracle.to_dense(data, g["sq205/row_indices"], g["sq205/column_indices"], (2048, 2048))
+    b = (torch.randn(2048, 256) * 0.1).half()
+    a = (torch.randn(256, 2048) * 0.1).half()
+    saved = kernels.PAIR_MODE
+    kernels.PAIR_MODE = mode
+    try:
+        for _ in range(3):          # the statistics arrive asynchronously: every call must be right
+            assert_product_close(stk.ops.dsd(m.t(), b.cuda()), oracle.dsd(dense.t(), b, torch.float16), "dsd S^T")
+            assert_product_close(stk.ops.dds(a.cuda(), m), oracle.dds(a, dense, torch.float16), "dds S")
+            torch.cuda.synchronize()
+        hints = kernels.pair_hints(m.offsets, m.row_indices, m.column_indices, 16, m.offsets_t, m.column_indices_t,
+                                   need_t=True, wait=True)
+        assert hints[3] is True and hints[4] is False
+    finally:
+        kernels.PAIR_MODE = saved
+
+
+def _stats_by_hand(rows, cols):
+    rp = len({(r >> 1, c) for r, c in zip(rows, cols)})
+    cp = len({(r, c >> 1) for r, c in zip(rows, cols)})
+    tl = len({(r >> 1, c >> 1) for r, c in zip(rows, cols)})
+    return rp, cp, tl
+
+
+def test_pair_stats_and_plan_match_host_logic(stk):
+    from stk_b200 import dmoe
+    from stk_b200.backend import kernels, lib
+    L = lib.load()
+    dev = torch.device("cuda", 0)
+    np.random.seed(17)
+    cases = [stk.random.mask(1024, 2048, 0.6, 128).to("cuda"), stk.random.mask(2048, 1024, 0.0, 128).to("cuda"),
+             dmoe.block_diagonal_topology(torch.tensor([3, 0, 1, 4, 2, 5]) * 128, 512, torch.float16, "cuda")]
+    for m in cases:
+        rows, cols = m.row_indices.cpu().tolist(), m.column_indices.cpu().tolist()
+        R, Cb = m.size()[0] // 128, m.size()[1] // 128
+        stats = torch.zeros(8, dtype=torch.int32, device=dev)
+        lib.check(L.stk_b200_pair_stats(lib.ptr(m.offsets), lib.ptr(m.row_indices), lib.ptr(m.column_indices),
+                                        lib.ptr(m.offsets_t), lib.ptr(m.column_indices_t), R, Cb, len(rows),
+                                        lib.ptr(stats), lib.stream_ptr(dev)), "stk_b200_pair_stats")
+        assert stats.cpu().tolist()[:6] == [*_stats_by_hand(rows, cols), 1, 1, 1]
+        # the work-item table: every list exactly once, pairs only inside runs, longest lists first
+        for offsets, idx, n in ((m.offsets, m.column_indices, R), (m.offsets_t, m.column_indices_t, Cb)):
+            plan = kernels.pair_plan(offsets, idx).cpu().tolist()
+            off, lst = offsets.cpu().tolist(), idx.cpu().tolist()
+            G, seen, costs = plan[0], [], []
+            for e in plan[1:1 + G]:
+                r, single = e & 0x3fffffff, (e >> 30) & 1
+                seen += [r] if single else [r, r + 1]
+                costs.append(off[r + 1] - off[r])
+                if not single:
+                    a, b = lst[off[r]:off[r + 1]], lst[off[r + 1]:off[r + 2]]
+                    assert not (a and b and (a[-1] < b[0] or b[-1] < a[0])), "a pair straddles a cut"
+            assert sorted(seen) == list(range(n))
+            assert costs == sorted(costs, reverse=True)
+    # blocks out of order are reported as such (and the counts then mean nothing)
+    m = cases[0]
+    perm = torch.arange(m.row_indices.numel() - 1, -1, -1, device=dev)
+    stats = torch.zeros(8, dtype=torch.int32, device=dev)
+    ri, ci = m.row_indices[perm].contiguous(), m.column_indices[perm].contiguous()
+    lib.check(L.stk_b200_pair_stats(lib.ptr(m.offsets), lib.ptr(ri), lib.ptr(ci), None, None, 8, 16, ri.numel(),
+                                    lib.ptr(stats), lib.stream_ptr(dev)), "stk_b200_pair_stats")
+    assert stats.cpu().tolist()[3:6] == [0, -1, 1]
+
+
+def test_topk_routing_kernels_match_host_logic(stk):
+    from stk_b200 import dmoe
+    from tests.test_dmoe_host import check_topk
+    g = torch.Generator().manual_seed(4)
+    for tokens, experts, k, hidden in [(3000, 8, 2, 64), (16384, 64, 2, 128), (500, 5, 3, 8)]:
+        ids = torch.randint(0, experts, (tokens, k), generator=g)
+        if experts == 64:
+            ids[ids == 9] = 10         # an expert without tokens
+        x = torch.randn(tokens, hidden, generator=g)
+        w = torch.rand(tokens, k, generator=g)
+        check_topk(dmoe, x.half().cuda(), ids.cuda().to(torch.int32), w.cuda(), experts, tol=4e-3)
+        dev_res = dmoe.route_topk(ids.cuda().to(torch.int32), experts)
+        host_res = dmoe.route_topk(ids, experts)
+        for a, b in zip(dev_res, host_res):
+            if torch.is_tensor(a):
+                assert torch.equal(a.cpu(), b.cpu())
+            else:
+                assert a == b
+        # 16-bit rows: the device kernel (fp32 accumulate, one rounding) against the host formula
+        xh = x.half()
+        index, position = dev_res[0], dev_res[1]
+        yp = dmoe.permute_tokens(xh.cuda(), index, dev_res[4], top_k=k)
+        got = dmoe.combine_tokens(yp, position, w.cuda(), tokens, k)
+        expect = (xh.float() * w.sum(1, keepdim=True))
+        assert torch.allclose(got.float().cpu(), expect, rtol=2e-3, atol=2e-3)
+
+
+def test_transpose_skips_and_reports_bad_column_indices(stk):
+    """A column index outside [0, block_cols) never reaches the counters: the block is left out (as
+    the reference's histc drops out-of-range values) and STK_ERR_BAD_DIMS is recorded."""
+    from stk_b200.backend import kernels, lib
+    for nnz, block_cols in ((64, 8), (40000, 2048)):       # single-CTA path and multi-kernel path
+        rows = torch.arange(nnz, dtype=torch.int16, device="cuda") % 7
+        cols = (torch.arange(nnz, device="cuda") % block_cols).to(torch.int16)
+        cols[nnz // 2] = block_cols + 5
+        cols[nnz // 3] = -3
+        cit, ot, bot = kernels.transpose_meta(rows, cols, block_cols)
+        torch.cuda.synchronize()
+        assert lib.device_status() == -2
+        good = (cols >= 0) & (cols < block_cols)
+        counts = torch.bincount(cols[good].long(), minlength=block_cols)
+        assert torch.equal(ot.cpu()[1:].long(), torch.cumsum(counts, 0).cpu())
+        assert int(ot[-1]) == nnz - 2

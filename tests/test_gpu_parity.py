@@ -262,8 +262,7 @@ def test_strided_views_and_errors(stk):
 @pytest.mark.parametrize("experts,cols_per_expert", [(5, 3), (9, 2), (80, 1)])
 def test_block_diagonal_topologies_with_odd_runs(stk, experts, cols_per_expert):
     """Expert bins of 1 to 3 block rows: runs of odd length (a single row closes them), runs of one
-    row, and - with 80 experts - more cuts than the pair kernel tracks (it then pairs blindly).
-    All six products against the dense path."""
+    row, and - with 80 experts - a long work-item table.  All six products against the dense path."""
     from stk_b200 import dmoe
     g = torch.Generator().manual_seed(experts)
     bin_rows = torch.randint(1, 4, (experts,), generator=g)

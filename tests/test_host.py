@@ -259,3 +259,31 @@ def test_autograd_wiring_matches_dense_calculus(monkeypatch):
             torch.testing.assert_close(oracle.to_dense(out.data.detach(), r, c, (12, 8)), ref.detach())
             torch.testing.assert_close(a1.grad, a2.grad)
             torch.testing.assert_close(b1.grad, b2.grad)
+
+
+def test_products_reject_mixed_dtypes_and_unknown_kernel_modes():
+    """float16 and bfloat16 operands in one product would be reinterpreted bit for bit: the launchers
+    refuse them before anything else (no GPU needed).  pair_mode values other than 0, 1, 3 are
+    rejected by the C entry points."""
+    from stk_b200.backend import kernels, lib
+    h = lambda *shape: torch.zeros(*shape, dtype=torch.float16)
+    b = lambda *shape: torch.zeros(*shape, dtype=torch.bfloat16)
+    idx = torch.zeros(1, dtype=torch.int16)
+    off = torch.zeros(2, dtype=torch.int32)
+    blk = torch.zeros(1, dtype=torch.int32)
+    with pytest.raises(ValueError, match="share one dtype"):
+        kernels.dsd((128, 128), h(1, 128, 128), off, idx, idx, off, idx, blk, False, b(128, 128), b(128, 128))
+    with pytest.raises(ValueError, match="share one dtype"):
+        kernels.dds(h(128, 128), (128, 128), b(1, 128, 128), off, idx, idx, off, idx, blk, False, h(128, 128))
+    with pytest.raises(ValueError, match="share one dtype"):
+        kernels.sdd(h(128, 128), b(128, 128), (128, 128), h(1, 128, 128), off, idx, idx)
+    l = lib.load()
+    null = ctypes.c_void_p(0)
+    assert l.stk_b200_sdd(null, null, null, null, null, null, 128, 128, 128, 1, 0, 128, 0, 128, 0, 2, 0, null, null, null) == -2
+    assert l.stk_b200_dsd(null, null, null, null, null, null, 128, 128, 128, 1, 0, 0, 128, 128, 0, 7, null, null) == -2
+    assert l.stk_b200_pair_plan(null, null, 0, null, 0, null) == -2
+    assert l.stk_b200_pair_plan(null, null, 4, null, 0, null) == -1
+    assert l.stk_b200_pair_plan_bytes(100) == 4 * 204
+    assert l.stk_b200_ep_barrier(null, 2, 0, 1, 100, null) == -1
+    assert l.stk_b200_ep_plan(null, 2, 8, 0, 128, 1, null, null, null, null) == -1
+    assert l.stk_b200_weighted_sum_rows(null, null, null, null, 4, 2, 24, 0, null) == -2
