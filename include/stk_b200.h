@@ -221,7 +221,9 @@ int stk_b200_transpose_meta_static(const int16_t* row_indices, const int16_t* co
  * 2. mask_to_offsets: offsets[0]=0, offsets[r+1] = number of set bytes in mask rows 0..r.
  *    The caller reads offsets[R] back to size data / row_indices / column_indices.
  * 3. mask_to_indices: row-major list of the set positions as int16 row / column indices.
- * 4. gather_blocks: data[p] = x[r_p*b:+b, c_p*b:+b], copied bit-exactly.
+ * 4. gather_blocks: data[p] = x[r_p*b:+b, c_p*b:+b], copied bit-exactly.  `offsets` (the CSR offsets of
+ *    step 2; may be NULL) lets blocks smaller than 64 be copied by block-row strips instead of one
+ *    CTA per block.
  */
 int stk_b200_block_mask(const void* x, int64_t rows, int64_t cols, int64_t ld,
                         int blocking, int elem_bytes, uint8_t* mask, void* stream);
@@ -231,7 +233,7 @@ int stk_b200_mask_to_indices(const uint8_t* mask, int64_t block_rows, int64_t bl
                              const int32_t* offsets, int16_t* row_indices, int16_t* column_indices,
                              void* stream);
 int stk_b200_gather_blocks(const void* x, int64_t rows, int64_t cols, int64_t ld,
-                           int blocking, int elem_bytes,
+                           int blocking, int elem_bytes, const int32_t* offsets,
                            const int16_t* row_indices, const int16_t* column_indices, int64_t nnz,
                            void* data, void* stream);
 

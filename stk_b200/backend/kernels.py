@@ -424,8 +424,9 @@ def mask_to_topology(mask):
     return offsets, row_idx, col_idx
 
 
-def gather_blocks(x, blocking, row_idx, col_idx):
-    """data [nnz, b, b]: the listed blocks of x, copied bit-exactly."""
+def gather_blocks(x, blocking, row_idx, col_idx, offsets=None):
+    """data [nnz, b, b]: the listed blocks of x, copied bit-exactly (offsets: the CSR offsets of the
+    list, which let small blocks be copied strip by strip)."""
     _require_cuda(x, row_idx, col_idx)
     rows, cols = x.shape
     if x.stride(1) != 1:
@@ -435,7 +436,7 @@ def gather_blocks(x, blocking, row_idx, col_idx):
     with _lib.on_device(x.device):
         rc = _lib.load().stk_b200_gather_blocks(
             _lib.ptr(x), rows, cols, x.stride(0) if rows > 1 else max(cols, 1), blocking,
-            _elem_bytes(x), _lib.ptr(row_idx), _lib.ptr(col_idx), nnz, _lib.ptr(data),
+            _elem_bytes(x), _lib.ptr(offsets), _lib.ptr(row_idx), _lib.ptr(col_idx), nnz, _lib.ptr(data),
             _lib.stream_ptr(x.device))
     _lib.check(rc, "stk_b200_gather_blocks")
     return data

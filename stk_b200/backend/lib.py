@@ -43,7 +43,7 @@ SIGNATURES = {
     "stk_b200_block_mask": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_ptr, _c_ptr]),
     "stk_b200_mask_to_offsets": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr]),
     "stk_b200_mask_to_indices": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr]),
-    "stk_b200_gather_blocks": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_ptr, _c_ptr,
+    "stk_b200_gather_blocks": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr,
                                         _c_i64, _c_ptr, _c_ptr]),
     "stk_b200_to_dense": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_int, _c_ptr,
                                    _c_i64, _c_ptr]),

@@ -182,10 +182,10 @@ def meta_kernels(dev="cuda", peak_gbs=None):
         mask = kernels.block_mask(x, blocking)
         offsets, ri, ci = kernels.mask_to_topology(mask)
         nnz = ri.numel()
-        data = kernels.gather_blocks(x, blocking, ri, ci)
+        data = kernels.gather_blocks(x, blocking, ri, ci, offsets)
         tag = f"8192^2 b={blocking} nnz={nnz}"
         add(f"block_mask {tag}", 2.0 * M * N, lambda: kernels.block_mask(x, blocking))
-        add(f"gather_blocks {tag}", 4.0 * nnz * blocking * blocking, lambda: kernels.gather_blocks(x, blocking, ri, ci))
+        add(f"gather_blocks {tag}", 4.0 * nnz * blocking * blocking, lambda: kernels.gather_blocks(x, blocking, ri, ci, offsets))
         add(f"to_dense {tag}", 2.0 * M * N + 2.0 * nnz * blocking * blocking,
             lambda: kernels.to_dense(data, offsets, ci, R, R, blocking))
         if blocking == 128:

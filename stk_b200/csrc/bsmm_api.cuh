@@ -18,10 +18,16 @@ static int check_dtype_dims(int dtype, int64_t M, int64_t N, int64_t K, int64_t 
   return STK_OK;
 }
 
-// SDD work items (row pair x column segment) aimed at per CTA pair: enough of them for the static
-// round-robin schedule to balance (measured: 16 beats 5 on the dMoE shapes although every item
-// starts with a short chain of dependent metadata loads).
-constexpr int kItemsPerPairTarget = 16;
+// Lists (block rows / columns) per tile-order group of the row kernel: as many as keep the group's
+// sparse blocks (32 KiB each) within a share of the L2 that leaves room for the dense panels in use.
+static int row_raster_group(int64_t nnz, int64_t num_lists) {
+  const int64_t budget_blocks = (48ll << 20) / (kBlk * kBlk * 2);
+  const int64_t per_list = (nnz + num_lists - 1) / num_lists;
+  int64_t g = budget_blocks / (per_list > 0 ? per_list : 1);
+  if (g < 1) g = 1;
+  if (g > num_lists) g = num_lists;
+  return static_cast<int>(g);
+}
 
 }  // namespace stk
 
@@ -81,14 +87,26 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
     if ((rc = pair_device_info(&d)) != STK_OK) return rc;
     const int block_rows = static_cast<int>(M / kBlk), block_cols = static_cast<int>(N / kBlk);
     const int row_pairs = (block_rows + 1) / 2;
-    // Split every row pair's column range into segments until there is enough parallel slack.
-    int segments = (kItemsPerPairTarget * d->max_pairs + row_pairs - 1) / row_pairs;
-    // No finer than one 2x2 tile per segment on average (a row pair that shares its columns has
-    // about half as many tiles as a row has blocks): finer segments come out unequal.
-    int max_segments = static_cast<int>(nnz / block_rows / 2);
-    if (max_segments > (block_cols + 1) / 2) max_segments = (block_cols + 1) / 2;
-    if (segments > max_segments) segments = max_segments;
-    if (segments < 1) segments = 1;
+    // Every row pair's column range is split into `segments` items.  The items are dealt round-robin,
+    // so a launch lasts (rounds of items) x (tiles per item): the split is chosen to minimise that
+    // product for a topology whose row pairs have about nnz / block_rows / 2 tiles each (dMoE: all
+    // alike), among the splits that cut a row pair's tiles into equal parts, preferring fewer,
+    // longer items on a tie (every item starts with a short chain of dependent metadata loads).
+    int tiles_per_group = static_cast<int>(((nnz + block_rows - 1) / block_rows + 1) / 2);
+    if (tiles_per_group > (block_cols + 1) / 2) tiles_per_group = (block_cols + 1) / 2;
+    if (tiles_per_group < 1) tiles_per_group = 1;
+    int segments = 1;
+    long long best = -1;
+    for (int cand = 1; cand <= tiles_per_group; ++cand) {
+      if (tiles_per_group % cand != 0) continue;
+      const long long items = static_cast<long long>(row_pairs) * cand;
+      const long long rounds = (items + d->max_pairs - 1) / d->max_pairs;
+      const long long cost = rounds * (tiles_per_group / cand) * 64 + rounds;  // + a little per item start
+      if (best < 0 || cost < best) {
+        best = cost;
+        segments = cand;
+      }
+    }
     PairParams p{};
     p.mode = kModeSDD;
     p.a_mn = lhs_colmajor ? 1 : 0;
@@ -166,6 +184,7 @@ extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int1
     p.out = out;
     p.ldc = ld_out;
     p.out_cols = static_cast<int>(N);
+    p.raster_group = row_raster_group(nnz, M / kBlk);
     return launch_row(tmA, tmB, tmC, tmC, p, s);
   }
   if (pair_mode) {
@@ -244,6 +263,7 @@ extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* of
     p.out = out;
     p.ldc = ld_out;
     p.out_rows = static_cast<int>(M);
+    p.raster_group = row_raster_group(nnz, N / kBlk);
     return launch_row(tmA, tmB, tmC, tmC, p, s);
   }
   if (pair_mode) {

@@ -10,7 +10,7 @@
 // topology.  DDS runs as the transposed product: the sparse tile is the MMA's A operand (its 128
 // block columns are the accumulator's lanes), the 256 dense rows are the N side, and the epilogue
 // writes the accumulator transposed (for one dense row a warp's 32 lanes hold 32 neighbouring
-// output columns: 64-byte stores).  Structure (roles, barriers, probe-ahead MMA loop, staged
+// output columns; staged through shared memory and stored by TMA).  Structure (roles, barriers, probe-ahead MMA loop, staged
 // TMA-store epilogue for DSD) is that of bsmm_sm100.cuh; the reference semantics are those of
 // _dsd_kernel / _dds_kernel, stk/backend/triton_kernels.py:83-145, 160-220.
 #pragma once
@@ -22,7 +22,26 @@ constexpr int kRStages = 4;
 constexpr int kRStageBytes = 3 * kOperandTileBytes;  // sparse tile, two dense tiles (contiguous: N = 256)
 constexpr int kRTmemCols = 512;                      // two 256-column fp32 accumulators
 constexpr int kRNumBars = 2 * kRStages + 4;
-constexpr int kRSmemBytes = kRStages * kRStageBytes + kOutStageBytes + kRNumBars * 8 + 32 + 1024;
+constexpr int kRSmemBytes = kRStages * kRStageBytes + 2 * kOutStageBytes + kRNumBars * 8 + 32 + 1024;
+
+// Tile order of the DSD / DDS row kernel.  A tile is (list, panel): one block row of op(S) (DSD) or
+// block column (DDS) against 256 dense columns / rows.  With the panel running fastest, the CTAs
+// resident at one time cover a few lists times ALL panels, i.e. they sweep the whole dense operand,
+// and so does every later wave: at 8192^3 and half the blocks present the dense operand was read
+// from DRAM 14 times.  The lists are therefore taken in groups of `raster_group`; inside a group the
+// panel is the OUTER index and the list the inner one, so that the CTAs resident at one time share one
+// or two panels of the dense operand while the group's sparse blocks (chosen to fit in the L2) are
+// re-read from the L2 panel after panel.  (The reference gets a similar effect from tl.swizzle2d,
+// stk/backend/triton_kernels.py:94-99.)
+__device__ __forceinline__ void row_tile(const BsmmParams& p, int tile, int& list, int& panel) {
+  const int num_lists = p.num_tiles / p.tiles_inner;
+  const int per_group = p.raster_group * p.tiles_inner;
+  const int g = tile / per_group, rem = tile - g * per_group;
+  const int first = g * p.raster_group;
+  const int lists_here = min(p.raster_group, num_lists - first);
+  panel = rem / lists_here;
+  list = first + (rem - panel * lists_here);
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
 bsmm_row_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -32,9 +51,9 @@ bsmm_row_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
   const uint32_t smem_base = smem_u32(smem);
 
-  const uint32_t staging = smem_base + kRStages * kRStageBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kRStages * kRStageBytes + kOutStageBytes);
-  const uint32_t bars_base = staging + kOutStageBytes;
+  const uint32_t staging = smem_base + kRStages * kRStageBytes;  // two 16 KiB output staging tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kRStages * kRStageBytes + 2 * kOutStageBytes);
+  const uint32_t bars_base = staging + 2 * kOutStageBytes;
   auto full_bar = [&](int s) { return bars_base + 8u * s; };
   auto empty_bar = [&](int s) { return bars_base + 8u * (kRStages + s); };
   auto tfull_bar = [&](int a) { return bars_base + 8u * (2 * kRStages + a); };
@@ -86,7 +105,8 @@ bsmm_row_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     uint32_t phase = 0;
     int ok = 1;
     for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-      const int tm = tile / p.tiles_inner, tn = tile - tm * p.tiles_inner;
+      int tm, tn;
+      row_tile(p, tile, tm, tn);
       const int j0 = p.offsets[tm], j1 = p.offsets[tm + 1];
       for (int jb = j0; jb < j1 && ok; jb += 32) {
         // The warp fetches the metadata of up to 32 blocks at once, then replays it.
@@ -145,13 +165,15 @@ bsmm_row_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       bool ready = false;  // the next stage's barrier is probed between the MMAs of the current one
       int nk_next = 0;
       if (static_cast<int>(blockIdx.x) < p.num_tiles) {
-        const int tm = blockIdx.x / p.tiles_inner;
+        int tm, tn;
+        row_tile(p, blockIdx.x, tm, tn);
         nk_next = 2 * (p.offsets[tm + 1] - p.offsets[tm]);
       }
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
         const int nk = nk_next;
         if (tile + static_cast<int>(gridDim.x) < p.num_tiles) {  // fetched while this tile's MMAs are issued
-          const int tm = (tile + gridDim.x) / p.tiles_inner;
+          int tm, tn;
+          row_tile(p, tile + gridDim.x, tm, tn);
           nk_next = 2 * (p.offsets[tm + 1] - p.offsets[tm]);
         }
         if (nk == 0) continue;  // the epilogue writes zeros; no accumulator is used
@@ -195,7 +217,8 @@ bsmm_row_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-      const int tm = tile / p.tiles_inner, tn = tile - tm * p.tiles_inner;
+      int tm, tn;
+      row_tile(p, tile, tm, tn);
       const int nk = 2 * (p.offsets[tm + 1] - p.offsets[tm]);
       const int col0 = tn * 2 * kBlk;  // DSD: first dense column; DDS: first dense row
       const int ncols = min(2 * kBlk, (dds ? p.out_rows : p.out_cols) - col0);
@@ -228,18 +251,37 @@ bsmm_row_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         drain_to_output(t_addr, 0, ncols, p.fmt, p.epilogue, &tmC, col0, tm * kBlk, staging, row, 0, 0,
                         1, issuer);
       } else {
-        // accumulator lane = output column tm*128 + row, accumulator column = dense row col0 + c
-        uint16_t* out_col = out + static_cast<long long>(col0) * p.ldc + tm * kBlk + row;
-        for (int c = 0; c < ncols; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(t_addr + c, v);
-          tmem_ld_wait();
+        // Accumulator lane = output column tm*128 + row, accumulator column = dense row col0 + c: the
+        // tile is written transposed.  128 dense rows at a time go through two staging tiles of
+        // [128 dense rows][64 output columns] in the 128-byte-swizzle layout (warps of TMEM lane
+        // quarters 0-1 fill the first, 2-3 the second; for one dense row a warp's lanes write 64
+        // contiguous bytes), and leave with one TMA store each; rows past the matrix are clipped.
+        const uint32_t my_stage = staging + (quarter >> 1) * kOutStageBytes;
+        const int col_in_half = (quarter & 1) * 32 + lane;  // this thread's column inside the 64-column half
+        for (int c0 = 0; c0 < ncols; c0 += kBlk) {
+          if (issuer) tma_store_wait_read<0>();  // the previous stores are done reading the tiles
+          epilogue_sync(0);
+#pragma unroll 1
+          for (int c = 0; c < kBlk; c += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(t_addr + c0 + c, v);
+            tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float f = __uint_as_float(v[i]);
-            const uint16_t h = p.fmt == STK_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(f))
-                                                 : __half_as_ushort(__float2half_rn(f));
-            out_col[static_cast<long long>(c + i) * p.ldc] = h;
+            for (int i = 0; i < 32; ++i) {
+              const float f = __uint_as_float(v[i]);
+              const uint16_t h = p.fmt == STK_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(f))
+                                                   : __half_as_ushort(__float2half_rn(f));
+              const int r = c + i;  // dense row inside the 128-row chunk = row of the staging tile
+              const uint32_t addr = my_stage + r * 128 + ((((col_in_half >> 3) ^ (r & 7))) << 4) + (col_in_half & 7) * 2;
+              asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(h) : "memory");
+            }
+          }
+          fence_proxy_async_smem();
+          epilogue_sync(0);
+          if (issuer) {
+            tma_store_2d(&tmC, staging, tm * kBlk, col0 + c0);
+            tma_store_2d(&tmC, staging + kOutStageBytes, tm * kBlk + 64, col0 + c0);
+            tma_store_commit();
           }
         }
       }

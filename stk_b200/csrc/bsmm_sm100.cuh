@@ -121,6 +121,7 @@ struct BsmmParams {
   int out_cols;             // row kernel (bsmm_row_sm100.cuh), DSD: dense columns of the output
   int out_rows;             // row kernel, DDS: dense rows of the output
   int nnz;                  // row kernel, SDD: number of blocks
+  int raster_group;         // row kernel, DSD / DDS: lists per tile-order group (see row_tile)
   const void* aux;          // SDD with kEpilogueGeluKeep / kEpilogueGeluGrad: the auxiliary tensor
 };
 

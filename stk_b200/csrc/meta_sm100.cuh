@@ -87,7 +87,7 @@ struct TransposePlan {
 constexpr int kFusedThreads = 1024;
 constexpr int kFusedGroups = 32;
 constexpr int64_t kFusedMaxCols = 1536;    // 32*Cb*4 + (Cb+1)*4 bytes of shared memory <= ~200 KiB
-constexpr int64_t kFusedMaxNnz = 32768;
+constexpr int64_t kFusedMaxNnz = 8192;     // beyond this one CTA is slower than the multi-kernel path
 constexpr int64_t kHistEntriesCap = 1 << 20;  // 4 MiB of workspace at most
 
 static inline TransposePlan plan_transpose(int64_t nnz, int64_t block_cols,
@@ -417,6 +417,48 @@ to_dense_vec_kernel(const uint16_t* __restrict__ data, const int32_t* __restrict
   }
 }
 
+// Small blocks (blocking < 64): a CTA per block would move 128 B - 2 KiB.  Instead a CTA covers one
+// block row and 2048 columns; a thread owns one 16-byte column strip (8 elements, inside one block
+// because blocking % 8 == 0), finds its block once (binary search in the row's column list) and walks
+// down the block's rows: output rows are written as contiguous 4 KiB runs by the CTA.
+__global__ void __launch_bounds__(256)
+to_dense_strip_kernel(const uint16_t* __restrict__ data, const int32_t* __restrict__ offsets,
+                      const int16_t* __restrict__ column_indices, int blocking, int cols,
+                      uint16_t* __restrict__ out, int64_t ld_out) {
+  const int col0 = (blockIdx.x * 256 + threadIdx.x) * 8;
+  if (col0 >= cols) return;
+  const int br = blockIdx.y, bc = col0 / blocking;
+  const int p = find_block(offsets, column_indices, br, bc);
+  uint16_t* dst = out + static_cast<int64_t>(br) * blocking * ld_out + col0;
+  if (p < 0) {
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll 4
+    for (int r = 0; r < blocking; ++r, dst += ld_out) *reinterpret_cast<uint4*>(dst) = z;
+    return;
+  }
+  const uint16_t* src = data + static_cast<int64_t>(p) * blocking * blocking + (col0 - bc * blocking);
+#pragma unroll 4
+  for (int r = 0; r < blocking; ++r, dst += ld_out, src += blocking)
+    *reinterpret_cast<uint4*>(dst) = __ldg(reinterpret_cast<const uint4*>(src));
+}
+
+// The same geometry for gather_blocks: threads whose block is absent have nothing to do.
+__global__ void __launch_bounds__(256)
+gather_blocks_strip_kernel(const uint16_t* __restrict__ x, int64_t ld, int blocking, int cols,
+                           const int32_t* __restrict__ offsets,
+                           const int16_t* __restrict__ column_indices, uint16_t* __restrict__ data) {
+  const int col0 = (blockIdx.x * 256 + threadIdx.x) * 8;
+  if (col0 >= cols) return;
+  const int br = blockIdx.y, bc = col0 / blocking;
+  const int p = find_block(offsets, column_indices, br, bc);
+  if (p < 0) return;
+  const uint16_t* src = x + static_cast<int64_t>(br) * blocking * ld + col0;
+  uint16_t* dst = data + static_cast<int64_t>(p) * blocking * blocking + (col0 - bc * blocking);
+#pragma unroll 4
+  for (int r = 0; r < blocking; ++r, src += ld, dst += blocking)
+    *reinterpret_cast<uint4*>(dst) = __ldg(reinterpret_cast<const uint4*>(src));
+}
+
 template <typename T>
 __global__ void to_dense_generic_kernel(const T* __restrict__ data,
                                         const int32_t* __restrict__ offsets,
@@ -593,9 +635,9 @@ extern "C" int stk_b200_mask_to_indices(const uint8_t* mask, int64_t block_rows,
 }
 
 extern "C" int stk_b200_gather_blocks(const void* x, int64_t rows, int64_t cols, int64_t ld,
-                                      int blocking, int elem_bytes, const int16_t* row_indices,
-                                      const int16_t* column_indices, int64_t nnz, void* data,
-                                      void* stream) {
+                                      int blocking, int elem_bytes, const int32_t* offsets,
+                                      const int16_t* row_indices, const int16_t* column_indices,
+                                      int64_t nnz, void* data, void* stream) {
   if (blocking <= 0 || rows < 0 || cols < 0 || nnz < 0 || rows % blocking || cols % blocking ||
       ld < cols)
     return STK_ERR_BAD_DIMS;
@@ -607,7 +649,12 @@ extern "C" int stk_b200_gather_blocks(const void* x, int64_t rows, int64_t cols,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool vec = elem_bytes == 2 && blocking % 8 == 0 && ld % 8 == 0 && ptr_aligned16(x) &&
                    ptr_aligned16(data);
-  if (vec) {
+  if (vec && blocking < 64 && offsets != nullptr && rows / blocking <= 65535) {
+    const dim3 grid(static_cast<unsigned>((cols / 8 + 255) / 256), static_cast<unsigned>(rows / blocking));
+    gather_blocks_strip_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(x), ld, blocking,
+                                                    static_cast<int>(cols), offsets, column_indices,
+                                                    static_cast<uint16_t*>(data));
+  } else if (vec) {
     gather_blocks_vec_kernel<<<static_cast<unsigned>(nnz), 256, 0, s>>>(
         static_cast<const uint16_t*>(x), ld, blocking, row_indices, column_indices,
         static_cast<uint16_t*>(data));
@@ -641,12 +688,17 @@ extern "C" int stk_b200_to_dense(const void* data, const int32_t* offsets,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool vec = elem_bytes == 2 && blocking % 8 == 0 && ld_out % 8 == 0 && ptr_aligned16(out) &&
                    ptr_aligned16(data);
-  if (vec) {
+  if (vec && blocking < 64) {
+    const int64_t cols = block_cols * blocking;
+    const dim3 grid(static_cast<unsigned>((cols / 8 + 255) / 256), static_cast<unsigned>(block_rows));
+    to_dense_strip_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(data), offsets, column_indices,
+                                               blocking, static_cast<int>(cols),
+                                               static_cast<uint16_t*>(out), ld_out);
+  } else if (vec) {
     const dim3 grid(static_cast<unsigned>(block_cols), static_cast<unsigned>(block_rows));
-    const int threads = blocking >= 64 ? 256 : 64;
-    to_dense_vec_kernel<<<grid, threads, 0, s>>>(static_cast<const uint16_t*>(data), offsets,
-                                                 column_indices, blocking,
-                                                 static_cast<uint16_t*>(out), ld_out);
+    to_dense_vec_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(data), offsets,
+                                             column_indices, blocking,
+                                             static_cast<uint16_t*>(out), ld_out);
   } else {
     const int64_t rows = block_rows * blocking, cols = block_cols * blocking;
     const int64_t blocks = (rows * cols + 255) / 256;

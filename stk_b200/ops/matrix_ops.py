@@ -59,7 +59,7 @@ def to_sparse(x, blocking=1):
     xd = x.to(dev)
     mask = _kernels.block_mask(xd, blocking)
     offsets, row_idx, col_idx = _kernels.mask_to_topology(mask)
-    data = _kernels.gather_blocks(xd, blocking, row_idx, col_idx)
+    data = _kernels.gather_blocks(xd, blocking, row_idx, col_idx, offsets)
     col_t, off_t, blk_t = _kernels.transpose_meta(row_idx, col_idx, x.size()[1] // blocking)
     fields = [t.to(home) for t in (data, row_idx, col_idx, offsets, col_t, off_t, blk_t)]
     return Matrix(x.size(), *fields)

@@ -64,8 +64,8 @@ def test_ops_under_autocast(stk, op):
     np.random.seed(5)
     torch.manual_seed(5)
     topo = stk.random.mask(384, 256, 0.5, 128).to("cuda")
-    a32 = (torch.randn(384, 192, device="cuda") * 0.1).requires_grad_(True)
-    b32 = (torch.randn(192, 256, device="cuda") * 0.1).requires_grad_(True)
+    a32 = (torch.randn(384, 256, device="cuda") * 0.1).requires_grad_(True)
+    b32 = (torch.randn(256, 256, device="cuda") * 0.1).requires_grad_(True)
     sp_vals = (torch.randn(topo.data.shape, device="cuda") * 0.1)
     bf = torch.bfloat16
     r, c = topo.row_indices.cpu().numpy(), topo.column_indices.cpu().numpy()
