@@ -343,6 +343,57 @@ int stk_b200_ep_dispatch(const void* x, const int32_t* order, const int32_t* off
 int stk_b200_ep_return(const void* result, const int64_t* tags, const uint64_t* peer_slots, int64_t row0,
                        int64_t n_rows, int world, int64_t row_bytes, int64_t slot_cap, void* stream);
 
+/*
+ * 32-bit block indices.  The reference stores block row / column indices as int16 and rejects matrices
+ * with more than 32767 blocks per side (stk/matrix.py:161-167, dtype handling left as a TODO at
+ * :178-181).  Every entry point above that takes or produces int16 index arrays (row_indices,
+ * column_indices, column_indices_t) has a twin with the suffix _i32 that takes int32 arrays instead;
+ * all other arguments, the results and the error codes are the same.  offsets, offsets_t and
+ * block_offsets_t are int32 in both.
+ */
+int stk_b200_sdd_i32(const void* lhs, const void* rhs, void* out, const int32_t* offsets,
+                     const int32_t* row_indices, const int32_t* column_indices,
+                     int64_t M, int64_t N, int64_t K, int64_t nnz,
+                     int lhs_colmajor, int64_t ld_lhs, int rhs_colmajor, int64_t ld_rhs,
+                     int dtype, int pair_mode, int epilogue, void* aux, const int32_t* pair_plan,
+                     void* stream);
+int stk_b200_dsd_i32(const void* data, const int32_t* offsets, const int32_t* column_indices,
+                     const int32_t* block_offsets, const void* rhs, void* out,
+                     int64_t M, int64_t N, int64_t K, int64_t nnz,
+                     int trans_sparse, int rhs_colmajor, int64_t ld_rhs, int64_t ld_out,
+                     int dtype, int pair_mode, const int32_t* pair_plan, void* stream);
+int stk_b200_dds_i32(const void* lhs, const void* data, const int32_t* offsets,
+                     const int32_t* column_indices, const int32_t* block_offsets, void* out,
+                     int64_t M, int64_t N, int64_t K, int64_t nnz,
+                     int lhs_colmajor, int64_t ld_lhs, int trans_sparse, int64_t ld_out,
+                     int dtype, int pair_mode, const int32_t* pair_plan, void* stream);
+int stk_b200_pair_stats_i32(const int32_t* offsets, const int32_t* row_indices,
+                            const int32_t* column_indices, const int32_t* offsets_t,
+                            const int32_t* column_indices_t, int64_t block_rows, int64_t block_cols,
+                            int64_t nnz, int32_t* stats, void* stream);
+int stk_b200_pair_plan_i32(const int32_t* offsets, const int32_t* column_indices, int64_t num_lists,
+                           int32_t* plan, size_t plan_bytes, void* stream);
+int stk_b200_row_indices_i32(const int32_t* offsets, int32_t* out, int64_t block_rows, int64_t nnz,
+                             void* stream);
+int stk_b200_transpose_meta_i32(const int32_t* row_indices, const int32_t* column_indices,
+                                int64_t nnz, int64_t block_cols,
+                                int32_t* column_indices_t, int32_t* offsets_t, int32_t* block_offsets_t,
+                                void* workspace, size_t workspace_bytes, void* stream);
+int stk_b200_mask_to_indices_i32(const uint8_t* mask, int64_t block_rows, int64_t block_cols,
+                                 const int32_t* offsets, int32_t* row_indices, int32_t* column_indices,
+                                 void* stream);
+int stk_b200_gather_blocks_i32(const void* x, int64_t rows, int64_t cols, int64_t ld,
+                               int blocking, int elem_bytes, const int32_t* offsets,
+                               const int32_t* row_indices, const int32_t* column_indices, int64_t nnz,
+                               void* data, void* stream);
+int stk_b200_to_dense_i32(const void* data, const int32_t* offsets, const int32_t* column_indices,
+                          int64_t block_rows, int64_t block_cols, int blocking, int elem_bytes,
+                          void* out, int64_t ld_out, void* stream);
+int stk_b200_dmoe_topology_i32(const int32_t* bin_rows, int experts, int cols_per_expert,
+                               int64_t block_rows, int32_t* row_indices, int32_t* column_indices,
+                               int32_t* offsets, int32_t* column_indices_t, int32_t* offsets_t,
+                               int32_t* block_offsets_t, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

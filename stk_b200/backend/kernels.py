@@ -97,7 +97,7 @@ def _launch_stats(h, offsets, row_indices, column_indices, offsets_t, column_ind
     dev = column_indices.device
     row_indices, column_indices = row_indices.contiguous(), column_indices.contiguous()
     with _lib.on_device(dev):
-        rc = _lib.load().stk_b200_pair_stats(
+        rc = _lib.entry("stk_b200_pair_stats", column_indices)(
             _lib.ptr(offsets), _lib.ptr(row_indices), _lib.ptr(column_indices), _lib.ptr(offsets_t),
             _lib.ptr(column_indices_t), offsets.numel() - 1, block_cols, column_indices.numel(),
             slot.data_ptr(), _lib.stream_ptr(dev))
@@ -183,7 +183,7 @@ def pair_plan(offsets, indices):
     nbytes = lib.stk_b200_pair_plan_bytes(num_lists)
     plan = torch.empty(nbytes // 4, dtype=torch.int32, device=indices.device)
     with _lib.on_device(indices.device):
-        rc = lib.stk_b200_pair_plan(_lib.ptr(offsets), _lib.ptr(indices), num_lists, _lib.ptr(plan), nbytes,
+        rc = _lib.entry("stk_b200_pair_plan", indices)(_lib.ptr(offsets), _lib.ptr(indices), num_lists, _lib.ptr(plan), nbytes,
                                     _lib.stream_ptr(indices.device))
     _lib.check(rc, "stk_b200_pair_plan")
     setattr(indices, _PLAN_ATTR, ((indices._version, offsets.data_ptr(), offsets._version), plan))
@@ -271,7 +271,7 @@ def dsd(shape, data, offsets, row_indices, column_indices, offsets_t, column_ind
         pairs = 3            # one block row x 256 dense columns per CTA
     plan = pair_plan(meta[0], meta[1]) if pairs == 1 else None
     with _lib.on_device(out.device):
-        rc = _lib.load().stk_b200_dsd(
+        rc = _lib.entry("stk_b200_dsd", meta[1])(
             _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),
             _lib.ptr(rhs), _lib.ptr(out), M, N, K, data.shape[0], int(bool(transpose_a)),
             rhs_colmajor, ld_rhs, out.stride(0), _lib.dtype_code(rhs.dtype), pairs, _lib.ptr(plan),
@@ -301,7 +301,7 @@ def dds(lhs, shape, data, offsets, row_indices, column_indices, offsets_t, colum
         pairs = 3            # 256 dense rows x one block column per CTA
     plan = pair_plan(meta[0], meta[1]) if pairs == 1 else None
     with _lib.on_device(out.device):
-        rc = _lib.load().stk_b200_dds(
+        rc = _lib.entry("stk_b200_dds", meta[1])(
             _lib.ptr(lhs), _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),
             _lib.ptr(out), M, N, K, data.shape[0], lhs_colmajor, ld_lhs, int(bool(transpose_b)),
             out.stride(0), _lib.dtype_code(lhs.dtype), pairs, _lib.ptr(plan), _lib.stream_ptr(out.device))
@@ -334,7 +334,7 @@ def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices, epilogue=0, 
         pairs = 3            # two blocks of a block row per 128x256 tile
     plan = pair_plan(offsets, column_indices) if pairs == 1 else None
     with _lib.on_device(out.device):
-        rc = _lib.load().stk_b200_sdd(
+        rc = _lib.entry("stk_b200_sdd", column_indices)(
             _lib.ptr(lhs), _lib.ptr(rhs), _lib.ptr(out), _lib.ptr(offsets), _lib.ptr(row_indices),
             _lib.ptr(column_indices), M, N, K, out.shape[0], lhs_colmajor, ld_lhs, rhs_colmajor,
             ld_rhs, _lib.dtype_code(out.dtype), pairs, epilogue, _lib.ptr(aux), _lib.ptr(plan),
@@ -345,11 +345,11 @@ def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices, epilogue=0, 
 def row_indices(shape, data, offsets, column_indices, out):
     """out[p] = block row of block p (CSR offsets -> COO)."""
     _require_cuda(offsets, out)
-    if out.dtype != torch.int16:
-        raise ValueError(f"row indices are int16, got an output of {out.dtype}")
+    if out.dtype not in (torch.int16, torch.int32):
+        raise ValueError(f"row indices are int16 or int32, got an output of {out.dtype}")
     block_rows = offsets.numel() - 1
     with _lib.on_device(out.device):
-        rc = _lib.load().stk_b200_row_indices(
+        rc = _lib.entry("stk_b200_row_indices", out)(
             _lib.ptr(offsets), _lib.ptr(out), block_rows, out.numel(), _lib.stream_ptr(out.device))
     _lib.check(rc, "stk_b200_row_indices")
 
@@ -359,7 +359,9 @@ def transpose_meta(row_indices, column_indices, block_cols):
     _require_cuda(row_indices, column_indices)
     dev = column_indices.device
     nnz = column_indices.numel()
-    column_indices_t = torch.empty(nnz, dtype=torch.int16, device=dev)
+    if row_indices.dtype != column_indices.dtype:
+        raise ValueError("row and column indices must share one integer type")
+    column_indices_t = torch.empty(nnz, dtype=column_indices.dtype, device=dev)
     offsets_t = torch.empty(block_cols + 1, dtype=torch.int32, device=dev)
     block_offsets_t = torch.empty(nnz, dtype=torch.int32, device=dev)
     lib = _lib.load()
@@ -367,7 +369,7 @@ def transpose_meta(row_indices, column_indices, block_cols):
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
     row_indices, column_indices = row_indices.contiguous(), column_indices.contiguous()
     with _lib.on_device(dev):
-        rc = lib.stk_b200_transpose_meta(
+        rc = _lib.entry("stk_b200_transpose_meta", column_indices)(
             _lib.ptr(row_indices), _lib.ptr(column_indices), nnz,
             block_cols, _lib.ptr(column_indices_t), _lib.ptr(offsets_t), _lib.ptr(block_offsets_t),
             _lib.ptr(ws), ws_bytes, _lib.stream_ptr(dev))
@@ -397,11 +399,20 @@ def block_mask(x, blocking):
     return mask
 
 
-def mask_to_topology(mask):
+INT16_BLOCKS = 32767   # most blocks per side that int16 indices can name
+
+
+def index_dtype_for(block_rows, block_cols):
+    """int16 as in the reference (stk/ops/matrix_ops.py:74-75) while it can name every block row and
+    column, int32 beyond (the reference raises there, stk/matrix.py:161-167)."""
+    return torch.int16 if max(block_rows, block_cols) <= INT16_BLOCKS else torch.int32
+
+
+def mask_to_topology(mask, index_dtype=None):
     """(offsets, row_indices, column_indices) of a uint8 [R, Cb] block mask (row-major order).
 
     Reads the block count back to the host to size the index tensors, like torch.nonzero does in
-    the reference's to_sparse.
+    the reference's to_sparse.  index_dtype: torch.int16 / torch.int32 (default: the narrowest that fits).
     """
     _require_cuda(mask)
     dev = mask.device
@@ -414,11 +425,13 @@ def mask_to_topology(mask):
                                           _lib.stream_ptr(dev))
         _lib.check(rc, "stk_b200_mask_to_offsets")
         nnz = int(offsets[-1].item())
-        row_idx = torch.empty(nnz, dtype=torch.int16, device=dev)
-        col_idx = torch.empty(nnz, dtype=torch.int16, device=dev)
+        if index_dtype is None:
+            index_dtype = index_dtype_for(block_rows, block_cols)
+        row_idx = torch.empty(nnz, dtype=index_dtype, device=dev)
+        col_idx = torch.empty(nnz, dtype=index_dtype, device=dev)
         if nnz == 0:
             return offsets, row_idx, col_idx
-        rc = lib.stk_b200_mask_to_indices(_lib.ptr(mask), block_rows, block_cols, _lib.ptr(offsets),
+        rc = _lib.entry("stk_b200_mask_to_indices", col_idx)(_lib.ptr(mask), block_rows, block_cols, _lib.ptr(offsets),
                                           _lib.ptr(row_idx), _lib.ptr(col_idx), _lib.stream_ptr(dev))
         _lib.check(rc, "stk_b200_mask_to_indices")
     return offsets, row_idx, col_idx
@@ -434,7 +447,7 @@ def gather_blocks(x, blocking, row_idx, col_idx, offsets=None):
     nnz = row_idx.numel()
     data = torch.empty((nnz, blocking, blocking), dtype=x.dtype, device=x.device)
     with _lib.on_device(x.device):
-        rc = _lib.load().stk_b200_gather_blocks(
+        rc = _lib.entry("stk_b200_gather_blocks", col_idx)(
             _lib.ptr(x), rows, cols, x.stride(0) if rows > 1 else max(cols, 1), blocking,
             _elem_bytes(x), _lib.ptr(offsets), _lib.ptr(row_idx), _lib.ptr(col_idx), nnz, _lib.ptr(data),
             _lib.stream_ptr(x.device))
@@ -451,7 +464,7 @@ def to_dense(data, offsets, column_indices, block_rows, block_cols, blocking):
         return out
     data = data.contiguous()
     with _lib.on_device(data.device):
-        rc = _lib.load().stk_b200_to_dense(
+        rc = _lib.entry("stk_b200_to_dense", column_indices)(
             _lib.ptr(data) if data.numel() else None, _lib.ptr(offsets),
             _lib.ptr(column_indices) if column_indices.numel() else None, block_rows, block_cols,
             blocking, _elem_bytes(data), _lib.ptr(out), out.stride(0), _lib.stream_ptr(data.device))

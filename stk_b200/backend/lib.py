@@ -66,6 +66,10 @@ SIGNATURES = {
                                       _c_int, _c_int, _c_int, _c_int, _c_i64, _c_i64, _c_ptr]),
     "stk_b200_ep_return": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_i64, _c_i64, _c_ptr]),
 }
+# every routine that takes or produces int16 block indices has an _i32 twin with the same signature
+for _name in ("sdd", "dsd", "dds", "pair_stats", "pair_plan", "row_indices", "transpose_meta",
+              "mask_to_indices", "gather_blocks", "to_dense", "dmoe_topology"):
+    SIGNATURES[f"stk_b200_{_name}_i32"] = SIGNATURES[f"stk_b200_{_name}"]
 
 _lib = None
 
@@ -146,6 +150,16 @@ class on_device:
         if self.prev is not None:
             torch.cuda.set_device(self.prev)
         return False
+
+
+def entry(name, index_tensor):
+    """The entry point `name` for the width of `index_tensor`'s block indices (int16 / int32)."""
+    lib = load()
+    if index_tensor is not None and index_tensor.dtype == torch.int32:
+        return getattr(lib, name + "_i32")
+    if index_tensor is not None and index_tensor.dtype != torch.int16:
+        raise ValueError(f"block indices are int16 or int32, got {index_tensor.dtype}")
+    return getattr(lib, name)
 
 
 def dtype_code(dtype):

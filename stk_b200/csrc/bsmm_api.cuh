@@ -33,11 +33,11 @@ static int row_raster_group(int64_t nnz, int64_t num_lists) {
 
 using namespace stk;
 
-extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const int32_t* offsets,
-                            const int16_t* row_indices, const int16_t* column_indices, int64_t M,
-                            int64_t N, int64_t K, int64_t nnz, int lhs_colmajor, int64_t ld_lhs,
-                            int rhs_colmajor, int64_t ld_rhs, int dtype, int pair_mode,
-                            int epilogue, void* aux, const int32_t* pair_plan, void* stream) {
+static int sdd_impl(const void* lhs, const void* rhs, void* out, const int32_t* offsets,
+                    IndexArray row_indices, IndexArray column_indices, int64_t M, int64_t N, int64_t K,
+                    int64_t nnz, int lhs_colmajor, int64_t ld_lhs, int rhs_colmajor, int64_t ld_rhs,
+                    int dtype, int pair_mode, int epilogue, void* aux, const int32_t* pair_plan,
+                    void* stream) {
   int rc = check_dtype_dims(dtype, M, N, K, nnz, 32, pair_mode);
   if (rc != STK_OK) return rc;
   if (epilogue < kEpilogueNone || epilogue > kEpilogueGeluGrad) return STK_ERR_BAD_DIMS;
@@ -45,8 +45,7 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
   if (has_aux && nnz != 0 && aux == nullptr) return STK_ERR_NULL_POINTER;
   if (has_aux && !aligned16(aux)) return STK_ERR_BAD_LAYOUT;
   if (nnz == 0) return STK_OK;
-  if (out == nullptr || row_indices == nullptr || column_indices == nullptr)
-    return STK_ERR_NULL_POINTER;
+  if (out == nullptr || row_indices.null() || column_indices.null()) return STK_ERR_NULL_POINTER;
   if (pair_mode && pair_mode != 3 && offsets == nullptr) return STK_ERR_NULL_POINTER;
   if (!aligned16(out)) return STK_ERR_BAD_LAYOUT;
   if ((rc = check_dense(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) return rc;
@@ -143,11 +142,10 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
   return launch(tmA, tmB, tmC, tmX, p, s);
 }
 
-extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int16_t* column_indices,
-                            const int32_t* block_offsets, const void* rhs, void* out, int64_t M,
-                            int64_t N, int64_t K, int64_t nnz, int trans_sparse, int rhs_colmajor,
-                            int64_t ld_rhs, int64_t ld_out, int dtype, int pair_mode,
-                            const int32_t* pair_plan, void* stream) {
+static int dsd_impl(const void* data, const int32_t* offsets, IndexArray column_indices,
+                    const int32_t* block_offsets, const void* rhs, void* out, int64_t M, int64_t N,
+                    int64_t K, int64_t nnz, int trans_sparse, int rhs_colmajor, int64_t ld_rhs,
+                    int64_t ld_out, int dtype, int pair_mode, const int32_t* pair_plan, void* stream) {
   int rc = check_dtype_dims(dtype, M, N, K, nnz, kBlk, pair_mode);
   if (rc != STK_OK) return rc;
   if ((rc = check_dense(out, ld_out, N)) != STK_OK) return rc;
@@ -157,7 +155,7 @@ extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int1
     return cudaMemset2DAsync(out, ld_out * 2, 0, N * 2, M, s) == cudaSuccess ? STK_OK
                                                                              : STK_ERR_LAUNCH;
   }
-  if (data == nullptr || offsets == nullptr || column_indices == nullptr) return STK_ERR_NULL_POINTER;
+  if (data == nullptr || offsets == nullptr || column_indices.null()) return STK_ERR_NULL_POINTER;
   if (trans_sparse && block_offsets == nullptr) return STK_ERR_NULL_POINTER;
   if (!aligned16(data)) return STK_ERR_BAD_LAYOUT;
   if ((rc = check_dense(rhs, ld_rhs, rhs_colmajor ? K : N)) != STK_OK) return rc;
@@ -223,11 +221,10 @@ extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int1
   return launch(tmA, tmB, tmC, tmC, p, s);
 }
 
-extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* offsets,
-                            const int16_t* column_indices, const int32_t* block_offsets, void* out,
-                            int64_t M, int64_t N, int64_t K, int64_t nnz, int lhs_colmajor,
-                            int64_t ld_lhs, int trans_sparse, int64_t ld_out, int dtype,
-                            int pair_mode, const int32_t* pair_plan, void* stream) {
+static int dds_impl(const void* lhs, const void* data, const int32_t* offsets, IndexArray column_indices,
+                    const int32_t* block_offsets, void* out, int64_t M, int64_t N, int64_t K, int64_t nnz,
+                    int lhs_colmajor, int64_t ld_lhs, int trans_sparse, int64_t ld_out, int dtype,
+                    int pair_mode, const int32_t* pair_plan, void* stream) {
   int rc = check_dtype_dims(dtype, M, N, K, nnz, kBlk, pair_mode);
   if (rc != STK_OK) return rc;
   if ((rc = check_dense(out, ld_out, N)) != STK_OK) return rc;
@@ -236,7 +233,7 @@ extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* of
     return cudaMemset2DAsync(out, ld_out * 2, 0, N * 2, M, s) == cudaSuccess ? STK_OK
                                                                              : STK_ERR_LAUNCH;
   }
-  if (data == nullptr || offsets == nullptr || column_indices == nullptr) return STK_ERR_NULL_POINTER;
+  if (data == nullptr || offsets == nullptr || column_indices.null()) return STK_ERR_NULL_POINTER;
   if (!trans_sparse && block_offsets == nullptr) return STK_ERR_NULL_POINTER;
   if (!aligned16(data)) return STK_ERR_BAD_LAYOUT;
   if ((rc = check_dense(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) return rc;
@@ -300,4 +297,57 @@ extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* of
   p.out = out;
   p.ldc = ld_out;
   return launch(tmA, tmB, tmC, tmC, p, s);
+}
+
+// The exported entry points: block indices as int16 (the reference's format) or, with the _i32
+// suffix, as int32.
+extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const int32_t* offsets,
+                            const int16_t* row_indices, const int16_t* column_indices, int64_t M,
+                            int64_t N, int64_t K, int64_t nnz, int lhs_colmajor, int64_t ld_lhs,
+                            int rhs_colmajor, int64_t ld_rhs, int dtype, int pair_mode,
+                            int epilogue, void* aux, const int32_t* pair_plan, void* stream) {
+  return sdd_impl(lhs, rhs, out, offsets, IndexArray{row_indices, 0}, IndexArray{column_indices, 0}, M, N, K,
+                  nnz, lhs_colmajor, ld_lhs, rhs_colmajor, ld_rhs, dtype, pair_mode, epilogue, aux, pair_plan,
+                  stream);
+}
+extern "C" int stk_b200_sdd_i32(const void* lhs, const void* rhs, void* out, const int32_t* offsets,
+                                const int32_t* row_indices, const int32_t* column_indices, int64_t M,
+                                int64_t N, int64_t K, int64_t nnz, int lhs_colmajor, int64_t ld_lhs,
+                                int rhs_colmajor, int64_t ld_rhs, int dtype, int pair_mode,
+                                int epilogue, void* aux, const int32_t* pair_plan, void* stream) {
+  return sdd_impl(lhs, rhs, out, offsets, IndexArray{row_indices, 1}, IndexArray{column_indices, 1}, M, N, K,
+                  nnz, lhs_colmajor, ld_lhs, rhs_colmajor, ld_rhs, dtype, pair_mode, epilogue, aux, pair_plan,
+                  stream);
+}
+extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int16_t* column_indices,
+                            const int32_t* block_offsets, const void* rhs, void* out, int64_t M,
+                            int64_t N, int64_t K, int64_t nnz, int trans_sparse, int rhs_colmajor,
+                            int64_t ld_rhs, int64_t ld_out, int dtype, int pair_mode,
+                            const int32_t* pair_plan, void* stream) {
+  return dsd_impl(data, offsets, IndexArray{column_indices, 0}, block_offsets, rhs, out, M, N, K, nnz,
+                  trans_sparse, rhs_colmajor, ld_rhs, ld_out, dtype, pair_mode, pair_plan, stream);
+}
+extern "C" int stk_b200_dsd_i32(const void* data, const int32_t* offsets, const int32_t* column_indices,
+                                const int32_t* block_offsets, const void* rhs, void* out, int64_t M,
+                                int64_t N, int64_t K, int64_t nnz, int trans_sparse, int rhs_colmajor,
+                                int64_t ld_rhs, int64_t ld_out, int dtype, int pair_mode,
+                                const int32_t* pair_plan, void* stream) {
+  return dsd_impl(data, offsets, IndexArray{column_indices, 1}, block_offsets, rhs, out, M, N, K, nnz,
+                  trans_sparse, rhs_colmajor, ld_rhs, ld_out, dtype, pair_mode, pair_plan, stream);
+}
+extern "C" int stk_b200_dds(const void* lhs, const void* data, const int32_t* offsets,
+                            const int16_t* column_indices, const int32_t* block_offsets, void* out,
+                            int64_t M, int64_t N, int64_t K, int64_t nnz, int lhs_colmajor,
+                            int64_t ld_lhs, int trans_sparse, int64_t ld_out, int dtype,
+                            int pair_mode, const int32_t* pair_plan, void* stream) {
+  return dds_impl(lhs, data, offsets, IndexArray{column_indices, 0}, block_offsets, out, M, N, K, nnz,
+                  lhs_colmajor, ld_lhs, trans_sparse, ld_out, dtype, pair_mode, pair_plan, stream);
+}
+extern "C" int stk_b200_dds_i32(const void* lhs, const void* data, const int32_t* offsets,
+                                const int32_t* column_indices, const int32_t* block_offsets, void* out,
+                                int64_t M, int64_t N, int64_t K, int64_t nnz, int lhs_colmajor,
+                                int64_t ld_lhs, int trans_sparse, int64_t ld_out, int dtype,
+                                int pair_mode, const int32_t* pair_plan, void* stream) {
+  return dds_impl(lhs, data, offsets, IndexArray{column_indices, 1}, block_offsets, out, M, N, K, nnz,
+                  lhs_colmajor, ld_lhs, trans_sparse, ld_out, dtype, pair_mode, pair_plan, stream);
 }

@@ -66,7 +66,7 @@ struct PairParams {
   int num_lists;    // DSD: block rows of op(S); DDS: block columns of op(S); SDD: block rows of the topology
   int zero_coord;   // an out-of-range row of the sparse tensor map (nnz * 128): reads as zeros
   int out_rows, out_cols;  // DSD/DDS: extent of the dense output in elements
-  const int16_t* col_idx;
+  IndexArray col_idx;
   const int32_t* offsets;
   const int32_t* blk_idx;  // nullptr: block j is data[j]
   void* out;
@@ -77,7 +77,7 @@ struct PairParams {
 
 // Two-pointer merge of the K lists of a pair of block rows (DSD) / block columns (DDS).
 struct MergeWalker {
-  const int16_t* col;
+  IndexArray col;
   const int32_t* blk;
   int ia, a1, ib, b1;
   // Lists la and la + 1 (part 0), or list la alone (part 1).
@@ -97,8 +97,8 @@ struct MergeWalker {
   __device__ __forceinline__ bool empty() const { return ia >= a1 && ib >= b1; }
   // Next K position; blk_a / blk_b = index into data of the block each list has there, or kNoBlock.
   __device__ __forceinline__ void next(int& kpos, int& blk_a, int& blk_b) {
-    const int ca = ia < a1 ? static_cast<int>(__ldg(col + ia)) : kNoBlock;
-    const int cb = ib < b1 ? static_cast<int>(__ldg(col + ib)) : kNoBlock;
+    const int ca = ia < a1 ? col[ia] : kNoBlock;
+    const int cb = ib < b1 ? col[ib] : kNoBlock;
     kpos = min(ca, cb);
     blk_a = blk_b = kNoBlock;
     if (ca == kpos) {
@@ -114,12 +114,12 @@ struct MergeWalker {
 
 // Walks the 2x2 block tiles of one row pair of an SDD topology inside one column segment.
 struct TileWalker {
-  const int16_t* col;
+  IndexArray col;
   int ia, a1, ib, b1, u_end;
   __device__ __forceinline__ int lower_bound(int lo, int hi, int c_min) const {
     while (lo < hi) {
       const int mid = (lo + hi) >> 1;
-      if (static_cast<int>(__ldg(col + mid)) < c_min) lo = mid + 1; else hi = mid;
+      if (col[mid] < c_min) lo = mid + 1; else hi = mid;
     }
     return lo;
   }
@@ -128,11 +128,11 @@ struct TileWalker {
   // only a wrong guess pays for the binary search (a chain of dependent loads).
   __device__ __forceinline__ int seek(int lo, int hi, int c_min) const {
     if (lo >= hi) return lo;
-    const int first = static_cast<int>(__ldg(col + lo));
+    const int first = col[lo];
     if (first >= c_min) return lo;
     const int guess = lo + (c_min - first);
-    if (guess < hi && static_cast<int>(__ldg(col + guess)) >= c_min &&
-        static_cast<int>(__ldg(col + guess - 1)) < c_min)
+    if (guess < hi && col[guess] >= c_min &&
+        col[guess - 1] < c_min)
       return guess;
     return lower_bound(lo, hi, c_min);
   }
@@ -151,12 +151,12 @@ struct TileWalker {
     if (a0 >= a1 && b0 >= b1) return;  // no block in either row
     int c_min = kNoBlock, c_max = -1;
     if (a0 < a1) {
-      c_min = min(c_min, static_cast<int>(__ldg(col + a0)));
-      c_max = max(c_max, static_cast<int>(__ldg(col + a1 - 1)));
+      c_min = min(c_min, col[a0]);
+      c_max = max(c_max, col[a1 - 1]);
     }
     if (b0 < b1) {
-      c_min = min(c_min, static_cast<int>(__ldg(col + b0)));
-      c_max = max(c_max, static_cast<int>(__ldg(col + b1 - 1)));
+      c_min = min(c_min, col[b0]);
+      c_max = max(c_max, col[b1 - 1]);
     }
     const int u_min = c_min >> 1, n_u = (c_max >> 1) - u_min + 1;
     const int u_lo = u_min + static_cast<int>((static_cast<long long>(seg) * n_u) / p.inner);
@@ -166,8 +166,8 @@ struct TileWalker {
   }
   // Next tile: u = column pair; p[r][h] = block index of (row ra+r, column 2u+h) or kNoBlock.
   __device__ __forceinline__ bool next(int& u, int (&p)[2][2]) {
-    const int ca = ia < a1 ? static_cast<int>(__ldg(col + ia)) : kNoBlock;
-    const int cb = ib < b1 ? static_cast<int>(__ldg(col + ib)) : kNoBlock;
+    const int ca = ia < a1 ? col[ia] : kNoBlock;
+    const int cb = ib < b1 ? col[ib] : kNoBlock;
     const int c = min(ca, cb);
     if (c == kNoBlock || (c >> 1) >= u_end) return false;
     u = c >> 1;
@@ -175,11 +175,11 @@ struct TileWalker {
 #pragma unroll
     for (int rep = 0; rep < 2; ++rep) {
       if (ia < a1) {
-        const int cc = static_cast<int>(__ldg(col + ia));
+        const int cc = col[ia];
         if ((cc >> 1) == u) { p[0][cc & 1] = ia; ++ia; }
       }
       if (ib < b1) {
-        const int cc = static_cast<int>(__ldg(col + ib));
+        const int cc = col[ib];
         if ((cc >> 1) == u) { p[1][cc & 1] = ib; ++ib; }
       }
     }

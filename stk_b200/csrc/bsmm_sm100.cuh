@@ -31,6 +31,7 @@
 #include <stdint.h>
 
 #include "../../include/stk_b200.h"
+#include "index.cuh"
 #include "sm100_ptx.cuh"
 #include "status.cuh"
 
@@ -112,8 +113,8 @@ struct BsmmParams {
   int num_tiles;
   int tiles_inner; // DSD: number of N tiles (n runs fastest); DDS: number of M tiles (m runs fastest)
   int k_steps;     // SDD: ceil(K / 64)
-  const int16_t* row_idx;   // SDD
-  const int16_t* col_idx;   // SDD: block column; DSD/DDS: position of block j along K, in blocks
+  IndexArray row_idx;       // SDD
+  IndexArray col_idx;       // SDD: block column; DSD/DDS: position of block j along K, in blocks
   const int32_t* offsets;   // DSD/DDS: K-loop segment of every block-row / block-column
   const int32_t* blk_idx;   // DSD/DDS: index into data of block j, or nullptr for the identity
   void* out;

@@ -10,6 +10,7 @@
 #include <stdint.h>
 
 #include "../../include/stk_b200.h"
+#include "index.cuh"
 #include "status.cuh"
 
 namespace stk {
@@ -106,9 +107,9 @@ bin_index_kernel(const int64_t* __restrict__ counts, int world, int local, int b
 // metadata; nothing is sorted.
 __global__ void __launch_bounds__(256)
 dmoe_topology_kernel(const int32_t* __restrict__ bin_rows, int experts, int cpb, int64_t nnz,
-                     int block_rows, int16_t* __restrict__ row_indices,
-                     int16_t* __restrict__ column_indices, int32_t* __restrict__ offsets,
-                     int16_t* __restrict__ column_indices_t, int32_t* __restrict__ offsets_t,
+                     int block_rows, IndexArray row_indices, IndexArray column_indices,
+                     int32_t* __restrict__ offsets, IndexArray column_indices_t,
+                     int32_t* __restrict__ offsets_t,
                      int32_t* __restrict__ block_offsets_t) {
   extern __shared__ int32_t row_start[];  // [experts + 1] first block row of every expert
   if (threadIdx.x == 0) {
@@ -141,12 +142,12 @@ dmoe_topology_kernel(const int32_t* __restrict__ bin_rows, int experts, int cpb,
     if (row_start[mid] <= r) lo = mid; else hi = mid - 1;
   }
   const int e = lo;
-  row_indices[p] = static_cast<int16_t>(r);
-  column_indices[p] = static_cast<int16_t>(e * cpb + j);
+  row_indices.store(p, r);
+  column_indices.store(p, e * cpb + j);
   // the same block in column-major order: column e*cpb + j, k-th block row of the expert
   const int k = r - row_start[e];
   const int64_t q = static_cast<int64_t>(row_start[e]) * cpb + static_cast<int64_t>(j) * bin_rows[e] + k;
-  column_indices_t[q] = static_cast<int16_t>(r);
+  column_indices_t.store(q, r);
   block_offsets_t[q] = static_cast<int32_t>(p);
 }
 
@@ -464,19 +465,19 @@ extern "C" int stk_b200_bin_index(const int64_t* counts, int world, int local_ex
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 
-extern "C" int stk_b200_dmoe_topology(const int32_t* bin_rows, int experts, int cols_per_expert,
-                                      int64_t block_rows, int16_t* row_indices,
-                                      int16_t* column_indices, int32_t* offsets,
-                                      int16_t* column_indices_t, int32_t* offsets_t,
-                                      int32_t* block_offsets_t, void* stream) {
+static int dmoe_topology_impl(const int32_t* bin_rows, int experts, int cols_per_expert,
+                              int64_t block_rows, IndexArray row_indices, IndexArray column_indices,
+                              int32_t* offsets, IndexArray column_indices_t, int32_t* offsets_t,
+                              int32_t* block_offsets_t, void* stream) {
   if (experts <= 0 || cols_per_expert <= 0 || block_rows < 0) return STK_ERR_BAD_DIMS;
   const int64_t block_cols = static_cast<int64_t>(experts) * cols_per_expert;
-  if (experts > 8192 || block_rows > 32767 || block_cols > 32767) return STK_ERR_TOO_LARGE;
+  const long long limit = index_limit(row_indices.wide);
+  if (experts > 8192 || block_rows > limit || block_cols > limit) return STK_ERR_TOO_LARGE;
   if (bin_rows == nullptr || offsets == nullptr || offsets_t == nullptr) return STK_ERR_NULL_POINTER;
   const int64_t nnz = block_rows * cols_per_expert;
   if (nnz > INT32_MAX) return STK_ERR_TOO_LARGE;
-  if (nnz > 0 && (row_indices == nullptr || column_indices == nullptr ||
-                  column_indices_t == nullptr || block_offsets_t == nullptr))
+  if (nnz > 0 && (row_indices.null() || column_indices.null() || column_indices_t.null() ||
+                  block_offsets_t == nullptr))
     return STK_ERR_NULL_POINTER;
   int64_t threads = nnz;
   if (threads < block_cols + 1) threads = block_cols + 1;
@@ -487,6 +488,25 @@ extern "C" int stk_b200_dmoe_topology(const int32_t* bin_rows, int experts, int 
       bin_rows, experts, cols_per_expert, nnz, static_cast<int>(block_rows), row_indices,
       column_indices, offsets, column_indices_t, offsets_t, block_offsets_t);
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
+}
+
+extern "C" int stk_b200_dmoe_topology(const int32_t* bin_rows, int experts, int cols_per_expert,
+                                      int64_t block_rows, int16_t* row_indices,
+                                      int16_t* column_indices, int32_t* offsets,
+                                      int16_t* column_indices_t, int32_t* offsets_t,
+                                      int32_t* block_offsets_t, void* stream) {
+  return dmoe_topology_impl(bin_rows, experts, cols_per_expert, block_rows, IndexArray{row_indices, 0},
+                            IndexArray{column_indices, 0}, offsets, IndexArray{column_indices_t, 0}, offsets_t,
+                            block_offsets_t, stream);
+}
+extern "C" int stk_b200_dmoe_topology_i32(const int32_t* bin_rows, int experts, int cols_per_expert,
+                                          int64_t block_rows, int32_t* row_indices,
+                                          int32_t* column_indices, int32_t* offsets,
+                                          int32_t* column_indices_t, int32_t* offsets_t,
+                                          int32_t* block_offsets_t, void* stream) {
+  return dmoe_topology_impl(bin_rows, experts, cols_per_expert, block_rows, IndexArray{row_indices, 1},
+                            IndexArray{column_indices, 1}, offsets, IndexArray{column_indices_t, 1}, offsets_t,
+                            block_offsets_t, stream);
 }
 
 extern "C" int stk_b200_ep_share_counts(const int32_t* offsets, const uint64_t* peer_counts, int world,

@@ -11,6 +11,7 @@
 #include <stdint.h>
 
 #include "../../include/stk_b200.h"
+#include "index.cuh"
 #include "status.cuh"
 
 namespace stk {
@@ -18,8 +19,8 @@ namespace stk {
 // ------------------------------------------------------------------------------------------
 // row_indices: block p belongs to the block row r with offsets[r] <= p < offsets[r+1].
 // One thread per block, binary search, fully coalesced stores.
-__global__ void row_indices_kernel(const int32_t* __restrict__ offsets, int16_t* __restrict__ out,
-                                   int block_rows, int nnz) {
+__global__ void row_indices_kernel(const int32_t* __restrict__ offsets, IndexArray out, int block_rows,
+                                   int nnz) {
   const int p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= nnz) return;
   int lo = 0, hi = block_rows - 1;  // smallest r with offsets[r+1] > p
@@ -27,7 +28,7 @@ __global__ void row_indices_kernel(const int32_t* __restrict__ offsets, int16_t*
     const int mid = (lo + hi) >> 1;
     if (offsets[mid + 1] > p) hi = mid; else lo = mid + 1;
   }
-  out[p] = static_cast<int16_t>(lo);
+  out.store(p, lo);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -118,16 +119,15 @@ static inline TransposePlan plan_transpose(int64_t nnz, int64_t block_cols,
 // `colstart` and its group's rank counters `hist_g` (shared or global memory).
 // A block whose column index lies outside [0, block_cols) is left out (the reference's histc drops
 // such values too) and reported through the status word; it never indexes the counters.
-__device__ __forceinline__ void scatter_group(const int16_t* __restrict__ rows,
-                                              const int16_t* __restrict__ cols, int begin, int end,
+__device__ __forceinline__ void scatter_group(IndexArray rows, IndexArray cols, int begin, int end,
                                               int block_cols, const int32_t* colstart, int32_t* hist_g,
-                                              int16_t* __restrict__ column_indices_t,
+                                              IndexArray column_indices_t,
                                               int32_t* __restrict__ block_offsets_t) {
   const int lane = threadIdx.x & 31;
   const uint32_t lt_mask = (1u << lane) - 1u;
   for (int base = begin; base < end; base += 32) {
     const int i = base + lane;
-    int c = i < end ? static_cast<int>(cols[i]) : -1;
+    int c = i < end ? cols[i] : -1;
     const bool active = static_cast<unsigned>(c) < static_cast<unsigned>(block_cols);
     // Inactive lanes get distinct negative keys so that they never match a column.
     const int key = active ? c : -1 - lane;
@@ -139,7 +139,7 @@ __device__ __forceinline__ void scatter_group(const int16_t* __restrict__ rows,
     first = __shfl_sync(0xffffffffu, first, leader);
     if (active) {
       const int dst = colstart[key] + first + rank;
-      column_indices_t[dst] = rows[i];
+      column_indices_t.store(dst, rows[i]);
       block_offsets_t[dst] = i;
     }
     __syncwarp();
@@ -147,8 +147,8 @@ __device__ __forceinline__ void scatter_group(const int16_t* __restrict__ rows,
 }
 
 __global__ void __launch_bounds__(kFusedThreads, 1)
-transpose_fused_kernel(const int16_t* __restrict__ rows, const int16_t* __restrict__ cols, int nnz,
-                       int block_cols, int chunk, int16_t* __restrict__ column_indices_t,
+transpose_fused_kernel(IndexArray rows, IndexArray cols, int nnz, int block_cols, int chunk,
+                       IndexArray column_indices_t,
                        int32_t* __restrict__ offsets_t, int32_t* __restrict__ block_offsets_t) {
   extern __shared__ int32_t tsm[];
   int32_t* hist = tsm;                                  // [32][block_cols]
@@ -218,7 +218,7 @@ transpose_fused_kernel(const int16_t* __restrict__ rows, const int16_t* __restri
 }
 
 // General path, kernel 1: hist[g][c] = number of blocks of group g in column c (hist pre-zeroed).
-__global__ void transpose_count_kernel(const int16_t* __restrict__ cols, int nnz, int block_cols,
+__global__ void transpose_count_kernel(IndexArray cols, int nnz, int block_cols,
                                        int chunk, int groups, int32_t* __restrict__ hist) {
   const int g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -248,11 +248,10 @@ __global__ void transpose_group_prefix_kernel(int32_t* __restrict__ hist, int bl
 }
 
 // General path, kernel 4 (kernel 3 is exclusive_scan_kernel on offsets_t).
-__global__ void transpose_scatter_kernel(const int16_t* __restrict__ rows,
-                                         const int16_t* __restrict__ cols, int nnz, int block_cols,
+__global__ void transpose_scatter_kernel(IndexArray rows, IndexArray cols, int nnz, int block_cols,
                                          int chunk, int groups, int32_t* __restrict__ hist,
                                          const int32_t* __restrict__ offsets_t,
-                                         int16_t* __restrict__ column_indices_t,
+                                         IndexArray column_indices_t,
                                          int32_t* __restrict__ block_offsets_t) {
   const int g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (g >= groups) return;
@@ -268,9 +267,9 @@ __global__ void transpose_scatter_kernel(const int16_t* __restrict__ rows,
 // row, 2048 columns and 1/gridDim.z of the block's rows; a thread ORs one 16-byte column strip.
 __global__ void __launch_bounds__(256)
 block_mask_vec_kernel(const uint16_t* __restrict__ x, int64_t ld, int cols, int blocking,
-                      int block_cols, uint8_t* __restrict__ mask) {
+                      int block_cols, int br0, uint8_t* __restrict__ mask) {
   const int col0 = (blockIdx.x * 256 + threadIdx.x) * 8;
-  const int br = blockIdx.y;
+  const int br = br0 + blockIdx.y;  // the grid's y extent is limited: tall matrices take several launches
   const int rows_per_split = (blocking + gridDim.z - 1) / gridDim.z;
   const int r0 = blockIdx.z * rows_per_split;
   const int r1 = min(blocking, r0 + rows_per_split);
@@ -326,8 +325,7 @@ __global__ void mask_row_count_kernel(const uint8_t* __restrict__ mask, int bloc
 // Ordered compaction of one mask row per warp.
 __global__ void mask_to_indices_kernel(const uint8_t* __restrict__ mask, int block_rows,
                                        int block_cols, const int32_t* __restrict__ offsets,
-                                       int16_t* __restrict__ row_indices,
-                                       int16_t* __restrict__ column_indices) {
+                                       IndexArray row_indices, IndexArray column_indices) {
   const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (r >= block_rows) return;
@@ -339,8 +337,8 @@ __global__ void mask_to_indices_kernel(const uint8_t* __restrict__ mask, int blo
     const uint32_t bal = __ballot_sync(0xffffffffu, set);
     if (set) {
       const int dst = pos + __popc(bal & ((1u << lane) - 1u));
-      row_indices[dst] = static_cast<int16_t>(r);
-      column_indices[dst] = static_cast<int16_t>(c);
+      row_indices.store(dst, r);
+      column_indices.store(dst, c);
     }
     pos += __popc(bal);
   }
@@ -352,8 +350,8 @@ __global__ void mask_to_indices_kernel(const uint8_t* __restrict__ mask, int blo
 // Vector path: one CTA per block, 16-byte copies, rows of the block are contiguous in `data`.
 __global__ void __launch_bounds__(256)
 gather_blocks_vec_kernel(const uint16_t* __restrict__ x, int64_t ld, int blocking,
-                         const int16_t* __restrict__ row_indices,
-                         const int16_t* __restrict__ column_indices, uint16_t* __restrict__ data) {
+                         IndexArray row_indices, IndexArray column_indices,
+                         uint16_t* __restrict__ data) {
   const int64_t p = blockIdx.x;
   const int vec_per_row = blocking / 8;
   const int nvec = blocking * vec_per_row;
@@ -368,8 +366,7 @@ gather_blocks_vec_kernel(const uint16_t* __restrict__ x, int64_t ld, int blockin
 
 template <typename T>
 __global__ void gather_blocks_generic_kernel(const T* __restrict__ x, int64_t ld, int blocking,
-                                             const int16_t* __restrict__ row_indices,
-                                             const int16_t* __restrict__ column_indices,
+                                             IndexArray row_indices, IndexArray column_indices,
                                              int64_t total, T* __restrict__ data) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= total) return;
@@ -385,7 +382,7 @@ __global__ void gather_blocks_generic_kernel(const T* __restrict__ x, int64_t ld
 // to_dense: every output tile is either a copy of its block or zeros; found by binary search in
 // the block row's (sorted) column list.
 __device__ __forceinline__ int find_block(const int32_t* __restrict__ offsets,
-                                          const int16_t* __restrict__ column_indices, int br,
+                                          IndexArray column_indices, int br,
                                           int bc) {
   int lo = offsets[br], hi = offsets[br + 1];
   while (lo < hi) {
@@ -399,9 +396,9 @@ __device__ __forceinline__ int find_block(const int32_t* __restrict__ offsets,
 
 __global__ void __launch_bounds__(256)
 to_dense_vec_kernel(const uint16_t* __restrict__ data, const int32_t* __restrict__ offsets,
-                    const int16_t* __restrict__ column_indices, int blocking,
+                    IndexArray column_indices, int blocking, int br0,
                     uint16_t* __restrict__ out, int64_t ld_out) {
-  const int bc = blockIdx.x, br = blockIdx.y;
+  const int bc = blockIdx.x, br = br0 + blockIdx.y;
   const int p = find_block(offsets, column_indices, br, bc);
   const int vec_per_row = blocking / 8;
   const int nvec = blocking * vec_per_row;
@@ -423,11 +420,11 @@ to_dense_vec_kernel(const uint16_t* __restrict__ data, const int32_t* __restrict
 // down the block's rows: output rows are written as contiguous 4 KiB runs by the CTA.
 __global__ void __launch_bounds__(256)
 to_dense_strip_kernel(const uint16_t* __restrict__ data, const int32_t* __restrict__ offsets,
-                      const int16_t* __restrict__ column_indices, int blocking, int cols,
+                      IndexArray column_indices, int blocking, int cols, int br0,
                       uint16_t* __restrict__ out, int64_t ld_out) {
   const int col0 = (blockIdx.x * 256 + threadIdx.x) * 8;
   if (col0 >= cols) return;
-  const int br = blockIdx.y, bc = col0 / blocking;
+  const int br = br0 + blockIdx.y, bc = col0 / blocking;
   const int p = find_block(offsets, column_indices, br, bc);
   uint16_t* dst = out + static_cast<int64_t>(br) * blocking * ld_out + col0;
   if (p < 0) {
@@ -446,10 +443,10 @@ to_dense_strip_kernel(const uint16_t* __restrict__ data, const int32_t* __restri
 __global__ void __launch_bounds__(256)
 gather_blocks_strip_kernel(const uint16_t* __restrict__ x, int64_t ld, int blocking, int cols,
                            const int32_t* __restrict__ offsets,
-                           const int16_t* __restrict__ column_indices, uint16_t* __restrict__ data) {
+                           IndexArray column_indices, int br0, uint16_t* __restrict__ data) {
   const int col0 = (blockIdx.x * 256 + threadIdx.x) * 8;
   if (col0 >= cols) return;
-  const int br = blockIdx.y, bc = col0 / blocking;
+  const int br = br0 + blockIdx.y, bc = col0 / blocking;
   const int p = find_block(offsets, column_indices, br, bc);
   if (p < 0) return;
   const uint16_t* src = x + static_cast<int64_t>(br) * blocking * ld + col0;
@@ -462,7 +459,7 @@ gather_blocks_strip_kernel(const uint16_t* __restrict__ x, int64_t ld, int block
 template <typename T>
 __global__ void to_dense_generic_kernel(const T* __restrict__ data,
                                         const int32_t* __restrict__ offsets,
-                                        const int16_t* __restrict__ column_indices, int blocking,
+                                        IndexArray column_indices, int blocking,
                                         int64_t rows, int64_t cols, T* __restrict__ out,
                                         int64_t ld_out) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -484,12 +481,20 @@ static inline int launch_status() { return cudaGetLastError() == cudaSuccess ? S
 
 using namespace stk;
 
-extern "C" int stk_b200_row_indices(const int32_t* offsets, int16_t* out, int64_t block_rows,
-                                    int64_t nnz, void* stream) {
+// ====================================================================== host side
+// Every routine that takes or produces block indices exists twice in the C ABI: with int16 indices
+// (the reference's format) and, suffixed _i32, with int32 indices.  Both are thin wrappers of the
+// *_impl functions below, which see the indices through IndexArray.
+namespace stk {
+
+constexpr int kMaxGridY = 65535;
+
+static int row_indices_impl(const int32_t* offsets, IndexArray out, int64_t block_rows, int64_t nnz,
+                            void* stream) {
   if (block_rows < 0 || nnz < 0) return STK_ERR_BAD_DIMS;
-  if (block_rows > 32767 || nnz > INT32_MAX) return STK_ERR_TOO_LARGE;
+  if (block_rows > index_limit(out.wide) || nnz > INT32_MAX) return STK_ERR_TOO_LARGE;
   if (nnz == 0) return STK_OK;
-  if (offsets == nullptr || out == nullptr) return STK_ERR_NULL_POINTER;
+  if (offsets == nullptr || out.null()) return STK_ERR_NULL_POINTER;
   if (block_rows == 0) return STK_ERR_BAD_DIMS;
   const int threads = 256;
   const int blocks = static_cast<int>((nnz + threads - 1) / threads);
@@ -498,19 +503,11 @@ extern "C" int stk_b200_row_indices(const int32_t* offsets, int16_t* out, int64_
   return launch_status();
 }
 
-extern "C" size_t stk_b200_transpose_meta_workspace_bytes(int64_t nnz, int64_t block_cols) {
-  if (nnz <= 0 || block_cols <= 0) return 0;
-  const TransposePlan pl = plan_transpose(nnz, block_cols);
-  if (pl.fused) return 0;
-  return static_cast<size_t>(pl.groups) * static_cast<size_t>(block_cols) * sizeof(int32_t);
-}
-
-namespace stk {
 // Shared by the caller-workspace entry point and the variant with built-in scratch.
-static int transpose_meta_impl(const int16_t* row_indices, const int16_t* column_indices,
-                               int64_t nnz, int64_t block_cols, int16_t* column_indices_t,
-                               int32_t* offsets_t, int32_t* block_offsets_t, void* workspace,
-                               cudaStream_t s, int64_t hist_entries_cap = kHistEntriesCap) {
+static int transpose_meta_launch(IndexArray row_indices, IndexArray column_indices, int64_t nnz,
+                                 int64_t block_cols, IndexArray column_indices_t, int32_t* offsets_t,
+                                 int32_t* block_offsets_t, void* workspace, cudaStream_t s,
+                                 int64_t hist_entries_cap = kHistEntriesCap) {
   const TransposePlan pl = plan_transpose(nnz, block_cols, hist_entries_cap);
   const int n = static_cast<int>(nnz), cb = static_cast<int>(block_cols);
   if (pl.fused) {
@@ -546,14 +543,22 @@ static int transpose_meta_impl(const int16_t* row_indices, const int16_t* column
       block_offsets_t);
   return launch_status();
 }
-}  // namespace stk
 
-extern "C" int stk_b200_transpose_meta(const int16_t* row_indices, const int16_t* column_indices,
-                                       int64_t nnz, int64_t block_cols, int16_t* column_indices_t,
-                                       int32_t* offsets_t, int32_t* block_offsets_t, void* workspace,
-                                       size_t workspace_bytes, void* stream) {
+static size_t transpose_workspace_bytes(int64_t nnz, int64_t block_cols) {
+  if (nnz <= 0 || block_cols <= 0) return 0;
+  const TransposePlan pl = plan_transpose(nnz, block_cols);
+  if (pl.fused) return 0;
+  return static_cast<size_t>(pl.groups) * static_cast<size_t>(block_cols) * sizeof(int32_t);
+}
+
+static int transpose_meta_impl(IndexArray row_indices, IndexArray column_indices, int64_t nnz,
+                               int64_t block_cols, IndexArray column_indices_t, int32_t* offsets_t,
+                               int32_t* block_offsets_t, void* workspace, size_t workspace_bytes,
+                               void* stream) {
   if (nnz < 0 || block_cols <= 0) return STK_ERR_BAD_DIMS;
-  if (block_cols > 32767 || nnz > INT32_MAX) return STK_ERR_TOO_LARGE;
+  // the per-group counters are indexed [group][column]: keep their number within int range
+  if (block_cols > index_limit(column_indices.wide) || block_cols > (1 << 24) || nnz > INT32_MAX)
+    return STK_ERR_TOO_LARGE;
   if (offsets_t == nullptr) return STK_ERR_NULL_POINTER;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (nnz == 0) {
@@ -561,72 +566,24 @@ extern "C" int stk_b200_transpose_meta(const int16_t* row_indices, const int16_t
                ? STK_OK
                : STK_ERR_LAUNCH;
   }
-  if (row_indices == nullptr || column_indices == nullptr || column_indices_t == nullptr ||
+  if (row_indices.null() || column_indices.null() || column_indices_t.null() ||
       block_offsets_t == nullptr)
     return STK_ERR_NULL_POINTER;
-  const size_t need = stk_b200_transpose_meta_workspace_bytes(nnz, block_cols);
+  const size_t need = transpose_workspace_bytes(nnz, block_cols);
   if (need > 0 && (workspace == nullptr || workspace_bytes < need || !ptr_aligned16(workspace)))
     return STK_ERR_WORKSPACE;
-  return transpose_meta_impl(row_indices, column_indices, nnz, block_cols, column_indices_t,
-                             offsets_t, block_offsets_t, workspace, s);
+  return transpose_meta_launch(row_indices, column_indices, nnz, block_cols, column_indices_t,
+                               offsets_t, block_offsets_t, workspace, s);
 }
 
-extern "C" int stk_b200_block_mask(const void* x, int64_t rows, int64_t cols, int64_t ld,
-                                   int blocking, int elem_bytes, uint8_t* mask, void* stream) {
-  if (blocking <= 0 || rows < 0 || cols < 0 || rows % blocking || cols % blocking || ld < cols)
-    return STK_ERR_BAD_DIMS;
-  if (elem_bytes != 2 && elem_bytes != 4) return STK_ERR_BAD_DTYPE;
-  if (rows == 0 || cols == 0) return STK_OK;
-  if (x == nullptr || mask == nullptr) return STK_ERR_NULL_POINTER;
-  const int64_t R = rows / blocking, Cb = cols / blocking;
-  if (R > 32767 || Cb > 32767) return STK_ERR_TOO_LARGE;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool vec = elem_bytes == 2 && blocking % 8 == 0 && ld % 8 == 0 && ptr_aligned16(x);
-  if (vec) {
-    if (cudaMemsetAsync(mask, 0, R * Cb, s) != cudaSuccess) return STK_ERR_LAUNCH;
-    const int splits = blocking >= 128 ? 4 : (blocking >= 32 ? 2 : 1);
-    const dim3 grid(static_cast<unsigned>((cols / 8 + 255) / 256), static_cast<unsigned>(R), splits);
-    block_mask_vec_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(x), ld,
-                                               static_cast<int>(cols), blocking,
-                                               static_cast<int>(Cb), mask);
-  } else {
-    const int64_t nb = R * Cb;
-    const unsigned blocks = static_cast<unsigned>((nb + 255) / 256);
-    if (elem_bytes == 2)
-      block_mask_generic_kernel<uint16_t, 0x7fff><<<blocks, 256, 0, s>>>(
-          static_cast<const uint16_t*>(x), ld, blocking, static_cast<int>(R), static_cast<int>(Cb), mask);
-    else
-      block_mask_generic_kernel<uint32_t, 0x7fffffffu><<<blocks, 256, 0, s>>>(
-          static_cast<const uint32_t*>(x), ld, blocking, static_cast<int>(R), static_cast<int>(Cb), mask);
-  }
-  return launch_status();
-}
-
-extern "C" int stk_b200_mask_to_offsets(const uint8_t* mask, int64_t block_rows, int64_t block_cols,
-                                        int32_t* offsets, void* stream) {
+static int mask_to_indices_impl(const uint8_t* mask, int64_t block_rows, int64_t block_cols,
+                                const int32_t* offsets, IndexArray row_indices,
+                                IndexArray column_indices, void* stream) {
   if (block_rows < 0 || block_cols < 0) return STK_ERR_BAD_DIMS;
-  if (block_rows > 32767 || block_cols > 32767) return STK_ERR_TOO_LARGE;
-  if (offsets == nullptr) return STK_ERR_NULL_POINTER;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (block_rows == 0 || block_cols == 0) {
-    return cudaMemsetAsync(offsets, 0, (block_rows + 1) * sizeof(int32_t), s) == cudaSuccess
-               ? STK_OK
-               : STK_ERR_LAUNCH;
-  }
-  if (mask == nullptr) return STK_ERR_NULL_POINTER;
-  const int R = static_cast<int>(block_rows), Cb = static_cast<int>(block_cols);
-  mask_row_count_kernel<<<(R + 7) / 8, 256, 0, s>>>(mask, R, Cb, offsets);
-  exclusive_scan_kernel<<<1, 1024, 0, s>>>(offsets, R);
-  return launch_status();
-}
-
-extern "C" int stk_b200_mask_to_indices(const uint8_t* mask, int64_t block_rows, int64_t block_cols,
-                                        const int32_t* offsets, int16_t* row_indices,
-                                        int16_t* column_indices, void* stream) {
-  if (block_rows < 0 || block_cols < 0) return STK_ERR_BAD_DIMS;
-  if (block_rows > 32767 || block_cols > 32767) return STK_ERR_TOO_LARGE;
+  const long long limit = index_limit(row_indices.wide);
+  if (block_rows > limit || block_cols > limit || block_rows > (1 << 28)) return STK_ERR_TOO_LARGE;
   if (block_rows == 0 || block_cols == 0) return STK_OK;
-  if (mask == nullptr || offsets == nullptr || row_indices == nullptr || column_indices == nullptr)
+  if (mask == nullptr || offsets == nullptr || row_indices.null() || column_indices.null())
     return STK_ERR_NULL_POINTER;
   const int R = static_cast<int>(block_rows), Cb = static_cast<int>(block_cols);
   mask_to_indices_kernel<<<(R + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -634,26 +591,29 @@ extern "C" int stk_b200_mask_to_indices(const uint8_t* mask, int64_t block_rows,
   return launch_status();
 }
 
-extern "C" int stk_b200_gather_blocks(const void* x, int64_t rows, int64_t cols, int64_t ld,
-                                      int blocking, int elem_bytes, const int32_t* offsets,
-                                      const int16_t* row_indices, const int16_t* column_indices,
-                                      int64_t nnz, void* data, void* stream) {
+static int gather_blocks_impl(const void* x, int64_t rows, int64_t cols, int64_t ld, int blocking,
+                              int elem_bytes, const int32_t* offsets, IndexArray row_indices,
+                              IndexArray column_indices, int64_t nnz, void* data, void* stream) {
   if (blocking <= 0 || rows < 0 || cols < 0 || nnz < 0 || rows % blocking || cols % blocking ||
       ld < cols)
     return STK_ERR_BAD_DIMS;
   if (elem_bytes != 2 && elem_bytes != 4) return STK_ERR_BAD_DTYPE;
   if (nnz == 0) return STK_OK;
-  if (nnz > INT32_MAX) return STK_ERR_TOO_LARGE;
-  if (x == nullptr || data == nullptr || row_indices == nullptr || column_indices == nullptr)
+  if (nnz > INT32_MAX || cols > INT32_MAX) return STK_ERR_TOO_LARGE;
+  if (x == nullptr || data == nullptr || row_indices.null() || column_indices.null())
     return STK_ERR_NULL_POINTER;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool vec = elem_bytes == 2 && blocking % 8 == 0 && ld % 8 == 0 && ptr_aligned16(x) &&
                    ptr_aligned16(data);
-  if (vec && blocking < 64 && offsets != nullptr && rows / blocking <= 65535) {
-    const dim3 grid(static_cast<unsigned>((cols / 8 + 255) / 256), static_cast<unsigned>(rows / blocking));
-    gather_blocks_strip_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(x), ld, blocking,
-                                                    static_cast<int>(cols), offsets, column_indices,
-                                                    static_cast<uint16_t*>(data));
+  if (vec && blocking < 64 && offsets != nullptr) {
+    const int64_t R = rows / blocking;
+    for (int64_t br0 = 0; br0 < R; br0 += kMaxGridY) {
+      const dim3 grid(static_cast<unsigned>((cols / 8 + 255) / 256),
+                      static_cast<unsigned>(R - br0 < kMaxGridY ? R - br0 : kMaxGridY));
+      gather_blocks_strip_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(x), ld, blocking,
+                                                      static_cast<int>(cols), offsets, column_indices,
+                                                      static_cast<int>(br0), static_cast<uint16_t*>(data));
+    }
   } else if (vec) {
     gather_blocks_vec_kernel<<<static_cast<unsigned>(nnz), 256, 0, s>>>(
         static_cast<const uint16_t*>(x), ld, blocking, row_indices, column_indices,
@@ -674,31 +634,38 @@ extern "C" int stk_b200_gather_blocks(const void* x, int64_t rows, int64_t cols,
   return launch_status();
 }
 
-extern "C" int stk_b200_to_dense(const void* data, const int32_t* offsets,
-                                 const int16_t* column_indices, int64_t block_rows,
-                                 int64_t block_cols, int blocking, int elem_bytes, void* out,
-                                 int64_t ld_out, void* stream) {
+static int to_dense_impl(const void* data, const int32_t* offsets, IndexArray column_indices,
+                         int64_t block_rows, int64_t block_cols, int blocking, int elem_bytes,
+                         void* out, int64_t ld_out, void* stream) {
   if (blocking <= 0 || block_rows < 0 || block_cols < 0 || ld_out < block_cols * blocking)
     return STK_ERR_BAD_DIMS;
   if (elem_bytes != 2 && elem_bytes != 4) return STK_ERR_BAD_DTYPE;
-  if (block_rows > 32767 || block_cols > 32767) return STK_ERR_TOO_LARGE;
+  const long long limit = index_limit(column_indices.wide);
+  if (block_rows > limit || block_cols > limit || block_cols * blocking > INT32_MAX ||
+      block_rows > (1 << 28))
+    return STK_ERR_TOO_LARGE;
   if (block_rows == 0 || block_cols == 0) return STK_OK;
   // `data` and `column_indices` may be NULL when there is no block at all.
   if (offsets == nullptr || out == nullptr) return STK_ERR_NULL_POINTER;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool vec = elem_bytes == 2 && blocking % 8 == 0 && ld_out % 8 == 0 && ptr_aligned16(out) &&
                    ptr_aligned16(data);
-  if (vec && blocking < 64) {
+  if (vec) {
     const int64_t cols = block_cols * blocking;
-    const dim3 grid(static_cast<unsigned>((cols / 8 + 255) / 256), static_cast<unsigned>(block_rows));
-    to_dense_strip_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(data), offsets, column_indices,
-                                               blocking, static_cast<int>(cols),
-                                               static_cast<uint16_t*>(out), ld_out);
-  } else if (vec) {
-    const dim3 grid(static_cast<unsigned>(block_cols), static_cast<unsigned>(block_rows));
-    to_dense_vec_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(data), offsets,
-                                             column_indices, blocking,
-                                             static_cast<uint16_t*>(out), ld_out);
+    for (int64_t br0 = 0; br0 < block_rows; br0 += kMaxGridY) {
+      const unsigned gy = static_cast<unsigned>(block_rows - br0 < kMaxGridY ? block_rows - br0 : kMaxGridY);
+      if (blocking < 64) {
+        const dim3 grid(static_cast<unsigned>((cols / 8 + 255) / 256), gy);
+        to_dense_strip_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(data), offsets,
+                                                   column_indices, blocking, static_cast<int>(cols),
+                                                   static_cast<int>(br0), static_cast<uint16_t*>(out), ld_out);
+      } else {
+        const dim3 grid(static_cast<unsigned>(block_cols), gy);
+        to_dense_vec_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(data), offsets,
+                                                 column_indices, blocking, static_cast<int>(br0),
+                                                 static_cast<uint16_t*>(out), ld_out);
+      }
+    }
   } else {
     const int64_t rows = block_rows * blocking, cols = block_cols * blocking;
     const int64_t blocks = (rows * cols + 255) / 256;
@@ -715,17 +682,143 @@ extern "C" int stk_b200_to_dense(const void* data, const int32_t* offsets,
   return launch_status();
 }
 
-// ------------------------------------------------------------------------------------------
 // transpose_meta with built-in scratch, for callers that cannot allocate device memory.
-
-namespace stk {
 constexpr int64_t kStaticScratchEntries = 1 << 18;        // 1 MiB of int32 counters
 constexpr int64_t kStaticMaxBlockCols = 8192;             // leaves >= 32 groups of counters
 constexpr int64_t kStaticMaxNnz = 1 << 20;
 // The group-by-column counters of the multi-kernel transpose path.  In host code this name is only
 // a handle for cudaGetSymbolAddress; the device address is looked up once per device below.
 static __device__ __align__(256) int32_t g_transpose_scratch[kStaticScratchEntries];
+
 }  // namespace stk
+
+using namespace stk;
+
+extern "C" int stk_b200_row_indices(const int32_t* offsets, int16_t* out, int64_t block_rows,
+                                    int64_t nnz, void* stream) {
+  return row_indices_impl(offsets, IndexArray{out, 0}, block_rows, nnz, stream);
+}
+extern "C" int stk_b200_row_indices_i32(const int32_t* offsets, int32_t* out, int64_t block_rows,
+                                        int64_t nnz, void* stream) {
+  return row_indices_impl(offsets, IndexArray{out, 1}, block_rows, nnz, stream);
+}
+
+extern "C" size_t stk_b200_transpose_meta_workspace_bytes(int64_t nnz, int64_t block_cols) {
+  return transpose_workspace_bytes(nnz, block_cols);
+}
+extern "C" int stk_b200_transpose_meta(const int16_t* row_indices, const int16_t* column_indices,
+                                       int64_t nnz, int64_t block_cols, int16_t* column_indices_t,
+                                       int32_t* offsets_t, int32_t* block_offsets_t, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
+  return transpose_meta_impl(IndexArray{row_indices, 0}, IndexArray{column_indices, 0}, nnz, block_cols,
+                             IndexArray{column_indices_t, 0}, offsets_t, block_offsets_t, workspace,
+                             workspace_bytes, stream);
+}
+extern "C" int stk_b200_transpose_meta_i32(const int32_t* row_indices, const int32_t* column_indices,
+                                           int64_t nnz, int64_t block_cols, int32_t* column_indices_t,
+                                           int32_t* offsets_t, int32_t* block_offsets_t,
+                                           void* workspace, size_t workspace_bytes, void* stream) {
+  return transpose_meta_impl(IndexArray{row_indices, 1}, IndexArray{column_indices, 1}, nnz, block_cols,
+                             IndexArray{column_indices_t, 1}, offsets_t, block_offsets_t, workspace,
+                             workspace_bytes, stream);
+}
+
+extern "C" int stk_b200_block_mask(const void* x, int64_t rows, int64_t cols, int64_t ld,
+                                   int blocking, int elem_bytes, uint8_t* mask, void* stream) {
+  if (blocking <= 0 || rows < 0 || cols < 0 || rows % blocking || cols % blocking || ld < cols)
+    return STK_ERR_BAD_DIMS;
+  if (elem_bytes != 2 && elem_bytes != 4) return STK_ERR_BAD_DTYPE;
+  if (rows == 0 || cols == 0) return STK_OK;
+  if (x == nullptr || mask == nullptr) return STK_ERR_NULL_POINTER;
+  const int64_t R = rows / blocking, Cb = cols / blocking;
+  if (R > (1 << 28) || Cb > (1 << 28) || cols > INT32_MAX) return STK_ERR_TOO_LARGE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool vec = elem_bytes == 2 && blocking % 8 == 0 && ld % 8 == 0 && ptr_aligned16(x);
+  if (vec) {
+    if (cudaMemsetAsync(mask, 0, R * Cb, s) != cudaSuccess) return STK_ERR_LAUNCH;
+    const int splits = blocking >= 128 ? 4 : (blocking >= 32 ? 2 : 1);
+    for (int64_t br0 = 0; br0 < R; br0 += kMaxGridY) {
+      const dim3 grid(static_cast<unsigned>((cols / 8 + 255) / 256),
+                      static_cast<unsigned>(R - br0 < kMaxGridY ? R - br0 : kMaxGridY), splits);
+      block_mask_vec_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(x), ld,
+                                                 static_cast<int>(cols), blocking,
+                                                 static_cast<int>(Cb), static_cast<int>(br0), mask);
+    }
+  } else {
+    const int64_t nb = R * Cb;
+    if ((nb + 255) / 256 > INT32_MAX) return STK_ERR_TOO_LARGE;
+    const unsigned blocks = static_cast<unsigned>((nb + 255) / 256);
+    if (elem_bytes == 2)
+      block_mask_generic_kernel<uint16_t, 0x7fff><<<blocks, 256, 0, s>>>(
+          static_cast<const uint16_t*>(x), ld, blocking, static_cast<int>(R), static_cast<int>(Cb), mask);
+    else
+      block_mask_generic_kernel<uint32_t, 0x7fffffffu><<<blocks, 256, 0, s>>>(
+          static_cast<const uint32_t*>(x), ld, blocking, static_cast<int>(R), static_cast<int>(Cb), mask);
+  }
+  return launch_status();
+}
+
+extern "C" int stk_b200_mask_to_offsets(const uint8_t* mask, int64_t block_rows, int64_t block_cols,
+                                        int32_t* offsets, void* stream) {
+  if (block_rows < 0 || block_cols < 0) return STK_ERR_BAD_DIMS;
+  if (block_rows > (1 << 28) || block_cols > (1 << 28)) return STK_ERR_TOO_LARGE;
+  if (offsets == nullptr) return STK_ERR_NULL_POINTER;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (block_rows == 0 || block_cols == 0) {
+    return cudaMemsetAsync(offsets, 0, (block_rows + 1) * sizeof(int32_t), s) == cudaSuccess
+               ? STK_OK
+               : STK_ERR_LAUNCH;
+  }
+  if (mask == nullptr) return STK_ERR_NULL_POINTER;
+  const int R = static_cast<int>(block_rows), Cb = static_cast<int>(block_cols);
+  mask_row_count_kernel<<<(R + 7) / 8, 256, 0, s>>>(mask, R, Cb, offsets);
+  exclusive_scan_kernel<<<1, 1024, 0, s>>>(offsets, R);
+  return launch_status();
+}
+
+extern "C" int stk_b200_mask_to_indices(const uint8_t* mask, int64_t block_rows, int64_t block_cols,
+                                        const int32_t* offsets, int16_t* row_indices,
+                                        int16_t* column_indices, void* stream) {
+  return mask_to_indices_impl(mask, block_rows, block_cols, offsets, IndexArray{row_indices, 0},
+                              IndexArray{column_indices, 0}, stream);
+}
+extern "C" int stk_b200_mask_to_indices_i32(const uint8_t* mask, int64_t block_rows,
+                                            int64_t block_cols, const int32_t* offsets,
+                                            int32_t* row_indices, int32_t* column_indices,
+                                            void* stream) {
+  return mask_to_indices_impl(mask, block_rows, block_cols, offsets, IndexArray{row_indices, 1},
+                              IndexArray{column_indices, 1}, stream);
+}
+
+extern "C" int stk_b200_gather_blocks(const void* x, int64_t rows, int64_t cols, int64_t ld,
+                                      int blocking, int elem_bytes, const int32_t* offsets,
+                                      const int16_t* row_indices, const int16_t* column_indices,
+                                      int64_t nnz, void* data, void* stream) {
+  return gather_blocks_impl(x, rows, cols, ld, blocking, elem_bytes, offsets, IndexArray{row_indices, 0},
+                            IndexArray{column_indices, 0}, nnz, data, stream);
+}
+extern "C" int stk_b200_gather_blocks_i32(const void* x, int64_t rows, int64_t cols, int64_t ld,
+                                          int blocking, int elem_bytes, const int32_t* offsets,
+                                          const int32_t* row_indices, const int32_t* column_indices,
+                                          int64_t nnz, void* data, void* stream) {
+  return gather_blocks_impl(x, rows, cols, ld, blocking, elem_bytes, offsets, IndexArray{row_indices, 1},
+                            IndexArray{column_indices, 1}, nnz, data, stream);
+}
+
+extern "C" int stk_b200_to_dense(const void* data, const int32_t* offsets,
+                                 const int16_t* column_indices, int64_t block_rows,
+                                 int64_t block_cols, int blocking, int elem_bytes, void* out,
+                                 int64_t ld_out, void* stream) {
+  return to_dense_impl(data, offsets, IndexArray{column_indices, 0}, block_rows, block_cols, blocking,
+                       elem_bytes, out, ld_out, stream);
+}
+extern "C" int stk_b200_to_dense_i32(const void* data, const int32_t* offsets,
+                                     const int32_t* column_indices, int64_t block_rows,
+                                     int64_t block_cols, int blocking, int elem_bytes, void* out,
+                                     int64_t ld_out, void* stream) {
+  return to_dense_impl(data, offsets, IndexArray{column_indices, 1}, block_rows, block_cols, blocking,
+                       elem_bytes, out, ld_out, stream);
+}
 
 extern "C" int stk_b200_transpose_meta_static(const int16_t* row_indices,
                                               const int16_t* column_indices, int64_t nnz,
@@ -759,7 +852,7 @@ extern "C" int stk_b200_transpose_meta_static(const int16_t* row_indices,
   }
   // The counters are cleared inside (cudaMemsetAsync on the part this call uses); the array
   // keeps whatever the previous call left elsewhere.
-  return transpose_meta_impl(row_indices, column_indices, nnz, block_cols, column_indices_t,
-                             offsets_t, block_offsets_t, scratch_addr[dev], s,
-                             kStaticScratchEntries);
+  return transpose_meta_launch(IndexArray{row_indices, 0}, IndexArray{column_indices, 0}, nnz, block_cols,
+                               IndexArray{column_indices_t, 0}, offsets_t, block_offsets_t,
+                               scratch_addr[dev], s, kStaticScratchEntries);
 }

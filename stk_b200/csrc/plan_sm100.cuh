@@ -15,6 +15,7 @@
 #include <stdint.h>
 
 #include "../../include/stk_b200.h"
+#include "index.cuh"
 
 namespace stk {
 
@@ -23,7 +24,7 @@ constexpr int kPlanSortMaxGroups = 4096;  // beyond this the groups stay in row 
 
 // Position of column `c` in block row `r` (lists ascending), or -1.
 __device__ __forceinline__ int plan_find(const int32_t* __restrict__ offsets,
-                                         const int16_t* __restrict__ cols, int r, int c) {
+                                         IndexArray cols, int r, int c) {
   int lo = offsets[r], hi = offsets[r + 1];
   while (lo < hi) {
     const int mid = (lo + hi) >> 1;
@@ -43,9 +44,8 @@ __device__ __forceinline__ int plan_find(const int32_t* __restrict__ offsets,
 //            not, -1 if the transposed metadata was not given
 // stats[5] = 1, written last (a completion mark for a host that polls the memory)
 __global__ void __launch_bounds__(kPlanThreads, 1)
-pair_stats_kernel(const int32_t* __restrict__ offsets, const int16_t* __restrict__ rows,
-                  const int16_t* __restrict__ cols, const int32_t* __restrict__ offsets_t,
-                  const int16_t* __restrict__ cols_t, int block_rows, int block_cols, int nnz,
+pair_stats_kernel(const int32_t* __restrict__ offsets, IndexArray rows, IndexArray cols,
+                  const int32_t* __restrict__ offsets_t, IndexArray cols_t, int block_rows, int block_cols, int nnz,
                   volatile int32_t* stats) {
   __shared__ int acc[5];
   if (threadIdx.x < 5) acc[threadIdx.x] = threadIdx.x >= 3 ? 1 : 0;
@@ -87,7 +87,7 @@ pair_stats_kernel(const int32_t* __restrict__ offsets, const int16_t* __restrict
     atomicAdd(&acc[1], n_cp);
     atomicAdd(&acc[2], n_t);
   }
-  if (offsets_t != nullptr && cols_t != nullptr) {
+  if (offsets_t != nullptr && !cols_t.null()) {
     int ok = 1;
     for (int c = threadIdx.x; c < block_cols; c += kPlanThreads) {
       const int a = offsets_t[c], b = offsets_t[c + 1];
@@ -102,7 +102,7 @@ pair_stats_kernel(const int32_t* __restrict__ offsets, const int16_t* __restrict
   __syncthreads();
   if (threadIdx.x < 5) {
     int v = acc[threadIdx.x];
-    if (threadIdx.x == 4 && (offsets_t == nullptr || cols_t == nullptr)) v = -1;
+    if (threadIdx.x == 4 && (offsets_t == nullptr || cols_t.null())) v = -1;
     stats[threadIdx.x] = v;
   }
   __threadfence_system();
@@ -164,8 +164,7 @@ __device__ __forceinline__ int plan_block_scan_max(int v, int* warp_tmp) {
 }
 
 // Lists r and r + 1 cannot share a K position: both non-empty and their column ranges disjoint.
-__device__ __forceinline__ bool plan_is_cut(const int32_t* __restrict__ offsets,
-                                            const int16_t* __restrict__ cols, int r) {
+__device__ __forceinline__ bool plan_is_cut(const int32_t* __restrict__ offsets, IndexArray cols, int r) {
   const int a0 = offsets[r], a1 = offsets[r + 1], b1 = offsets[r + 2];
   if (a0 >= a1 || a1 >= b1) return false;
   const int a_first = cols[a0], a_last = cols[a1 - 1], b_first = cols[a1], b_last = cols[b1 - 1];
@@ -178,7 +177,7 @@ __device__ __forceinline__ bool plan_is_cut(const int32_t* __restrict__ offsets,
 // expensive items first; beyond kPlanSortMaxGroups they stay in list order.  plan[1 + num_lists ..]
 // is scratch of the same size.
 __global__ void __launch_bounds__(kPlanThreads, 1)
-pair_plan_kernel(const int32_t* __restrict__ offsets, const int16_t* __restrict__ cols, int num_lists,
+pair_plan_kernel(const int32_t* __restrict__ offsets, IndexArray cols, int num_lists,
                  int32_t* __restrict__ plan) {
   __shared__ int warp_tmp[32];
   __shared__ int total_groups;
@@ -225,31 +224,56 @@ pair_plan_kernel(const int32_t* __restrict__ offsets, const int16_t* __restrict_
 
 }  // namespace stk
 
-extern "C" int stk_b200_pair_stats(const int32_t* offsets, const int16_t* row_indices,
-                                   const int16_t* column_indices, const int32_t* offsets_t,
-                                   const int16_t* column_indices_t, int64_t block_rows,
-                                   int64_t block_cols, int64_t nnz, int32_t* stats, void* stream) {
+namespace stk {
+static int pair_stats_impl(const int32_t* offsets, IndexArray row_indices, IndexArray column_indices,
+                           const int32_t* offsets_t, IndexArray column_indices_t, int64_t block_rows,
+                           int64_t block_cols, int64_t nnz, int32_t* stats, void* stream) {
   if (block_rows <= 0 || block_cols <= 0 || nnz < 0) return STK_ERR_BAD_DIMS;
-  if (block_rows > 32767 || block_cols > 32767 || nnz > INT32_MAX) return STK_ERR_TOO_LARGE;
+  const long long limit = index_limit(column_indices.wide);
+  if (block_rows > limit || block_cols > limit || nnz > INT32_MAX) return STK_ERR_TOO_LARGE;
   if (stats == nullptr || offsets == nullptr) return STK_ERR_NULL_POINTER;
-  if (nnz > 0 && (row_indices == nullptr || column_indices == nullptr)) return STK_ERR_NULL_POINTER;
-  stk::pair_stats_kernel<<<1, stk::kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  if (nnz > 0 && (row_indices.null() || column_indices.null())) return STK_ERR_NULL_POINTER;
+  pair_stats_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       offsets, row_indices, column_indices, offsets_t, column_indices_t, static_cast<int>(block_rows),
       static_cast<int>(block_cols), static_cast<int>(nnz), stats);
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
+static int pair_plan_impl(const int32_t* offsets, IndexArray column_indices, int64_t num_lists,
+                          int32_t* plan, size_t plan_bytes, void* stream) {
+  if (num_lists <= 0) return STK_ERR_BAD_DIMS;
+  if (num_lists > (1 << 29)) return STK_ERR_TOO_LARGE;
+  if (offsets == nullptr || plan == nullptr) return STK_ERR_NULL_POINTER;
+  if (plan_bytes < stk_b200_pair_plan_bytes(num_lists)) return STK_ERR_WORKSPACE;
+  pair_plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      offsets, column_indices, static_cast<int>(num_lists), plan);
+  return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
+}
+}  // namespace stk
 
 extern "C" size_t stk_b200_pair_plan_bytes(int64_t num_lists) {
   return num_lists < 0 ? 0 : static_cast<size_t>(2 * num_lists + 4) * sizeof(int32_t);
 }
-
+extern "C" int stk_b200_pair_stats(const int32_t* offsets, const int16_t* row_indices,
+                                   const int16_t* column_indices, const int32_t* offsets_t,
+                                   const int16_t* column_indices_t, int64_t block_rows,
+                                   int64_t block_cols, int64_t nnz, int32_t* stats, void* stream) {
+  return stk::pair_stats_impl(offsets, stk::IndexArray{row_indices, 0}, stk::IndexArray{column_indices, 0},
+                              offsets_t, stk::IndexArray{column_indices_t, 0}, block_rows, block_cols, nnz, stats,
+                              stream);
+}
+extern "C" int stk_b200_pair_stats_i32(const int32_t* offsets, const int32_t* row_indices,
+                                       const int32_t* column_indices, const int32_t* offsets_t,
+                                       const int32_t* column_indices_t, int64_t block_rows,
+                                       int64_t block_cols, int64_t nnz, int32_t* stats, void* stream) {
+  return stk::pair_stats_impl(offsets, stk::IndexArray{row_indices, 1}, stk::IndexArray{column_indices, 1},
+                              offsets_t, stk::IndexArray{column_indices_t, 1}, block_rows, block_cols, nnz, stats,
+                              stream);
+}
 extern "C" int stk_b200_pair_plan(const int32_t* offsets, const int16_t* column_indices,
                                   int64_t num_lists, int32_t* plan, size_t plan_bytes, void* stream) {
-  if (num_lists <= 0) return STK_ERR_BAD_DIMS;
-  if (num_lists > 32767) return STK_ERR_TOO_LARGE;
-  if (offsets == nullptr || plan == nullptr) return STK_ERR_NULL_POINTER;
-  if (plan_bytes < stk_b200_pair_plan_bytes(num_lists)) return STK_ERR_WORKSPACE;
-  stk::pair_plan_kernel<<<1, stk::kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      offsets, column_indices, static_cast<int>(num_lists), plan);
-  return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
+  return stk::pair_plan_impl(offsets, stk::IndexArray{column_indices, 0}, num_lists, plan, plan_bytes, stream);
+}
+extern "C" int stk_b200_pair_plan_i32(const int32_t* offsets, const int32_t* column_indices,
+                                      int64_t num_lists, int32_t* plan, size_t plan_bytes, void* stream) {
+  return stk::pair_plan_impl(offsets, stk::IndexArray{column_indices, 1}, num_lists, plan, plan_bytes, stream);
 }

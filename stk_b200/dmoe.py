@@ -158,13 +158,13 @@ def topology_from_bins(bin_rows, block_rows, ffn, dtype, device, block=BLOCK, da
     experts = bin_rows.numel()
     cpb = ffn // block
     nnz = block_rows * cpb
-    meta16 = torch.empty((3, max(nnz, 1)), dtype=torch.int16, device=device)
+    meta16 = torch.empty((3, max(nnz, 1)), dtype=_kernels.index_dtype_for(block_rows, experts * cpb), device=device)
     offsets = torch.empty(block_rows + 1, dtype=torch.int32, device=device)
     offsets_t = torch.empty(experts * cpb + 1, dtype=torch.int32, device=device)
     block_offsets_t = torch.empty(nnz, dtype=torch.int32, device=device)
     row_idx, col_idx, col_idx_t = (meta16[i, :nnz] for i in range(3))
     with _lib.on_device(device):
-        rc = _lib.load().stk_b200_dmoe_topology(
+        rc = _lib.entry("stk_b200_dmoe_topology", meta16)(
             _lib.ptr(bin_rows), experts, cpb, block_rows, _lib.ptr(row_idx), _lib.ptr(col_idx),
             _lib.ptr(offsets), _lib.ptr(col_idx_t), _lib.ptr(offsets_t), _lib.ptr(block_offsets_t),
             _lib.stream_ptr(device))

@@ -33,7 +33,8 @@ def _validate_matrix(shape, data, row_indices, column_indices, offsets):
     """Shape / dtype / device checks of the five defining fields (stk/matrix.py:14-102).
 
     Returns `data` viewed as [nnz, block, block].  Unlike the reference, bfloat16 values are
-    accepted next to float16 (its matmuls are tested with both).
+    accepted next to float16 (its matmuls are tested with both), and the block indices may be int32
+    instead of int16 (needed beyond 32767 blocks per side).
     """
     if data.dim() == 1:
         data = data.reshape(data.numel(), 1, 1)
@@ -69,8 +70,11 @@ def _validate_matrix(shape, data, row_indices, column_indices, offsets):
     if data.dtype not in (torch.float16, torch.bfloat16):
         raise ValueError(f"Expected float16 or bfloat16 data. Got {data.dtype} data.")
     for name, t in (("row_indices", row_indices), ("column_indices", column_indices)):
-        if t.dtype != torch.int16:
-            raise ValueError(f"Expected int16 {name}. Got {t.dtype} {name}.")
+        if t.dtype not in (torch.int16, torch.int32):
+            raise ValueError(f"Expected int16 or int32 {name}. Got {t.dtype} {name}.")
+    if row_indices.dtype != column_indices.dtype:
+        raise ValueError("Expected row_indices and column_indices of one integer type. "
+                         f"Got {row_indices.dtype} and {column_indices.dtype}.")
     if offsets.dtype != torch.int32:
         raise ValueError(f"Expected int32 offsets. Got {offsets.dtype} offsets.")
     return data
@@ -91,7 +95,9 @@ class Matrix(torch.nn.Module):
     Fields (dtypes as produced by stk.ops.to_sparse): data [nnz, b, b]; row_indices and
     column_indices int16 [nnz]; offsets int32 [block_rows + 1]; and the same topology in
     column-major order: column_indices_t int16 [nnz] (block rows), offsets_t int32
-    [block_cols + 1], block_offsets_t int32 [nnz] (positions in data).
+    [block_cols + 1], block_offsets_t int32 [nnz] (positions in data).  A matrix with more than 32767
+    blocks per side carries int32 row_indices / column_indices / column_indices_t instead (the
+    reference rejects such sizes, stk/matrix.py:161-167).
     """
 
     def __init__(self, size, data, row_indices, column_indices, offsets, column_indices_t=None,

@@ -49,8 +49,10 @@ def _mask(x, blocking=1):
 
 
 @torch.no_grad()
-def to_sparse(x, blocking=1):
-    """Blocked CSR-COO form of the 2-D tensor x; blocks that are entirely +-0 are dropped."""
+def to_sparse(x, blocking=1, index_dtype=None):
+    """Blocked CSR-COO form of the 2-D tensor x; blocks that are entirely +-0 are dropped.
+    index_dtype (not in the reference): torch.int16 or torch.int32 for the block indices; by default
+    int16 as in the reference, int32 when x has more than 32767 blocks per side."""
     assert x.dim() == 2
     assert x.size()[0] % blocking == 0
     assert x.size()[1] % blocking == 0
@@ -58,7 +60,7 @@ def to_sparse(x, blocking=1):
     dev = compute_device(x)
     xd = x.to(dev)
     mask = _kernels.block_mask(xd, blocking)
-    offsets, row_idx, col_idx = _kernels.mask_to_topology(mask)
+    offsets, row_idx, col_idx = _kernels.mask_to_topology(mask, index_dtype)
     data = _kernels.gather_blocks(xd, blocking, row_idx, col_idx, offsets)
     col_t, off_t, blk_t = _kernels.transpose_meta(row_idx, col_idx, x.size()[1] // blocking)
     fields = [t.to(home) for t in (data, row_idx, col_idx, offsets, col_t, off_t, blk_t)]

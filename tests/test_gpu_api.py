@@ -219,3 +219,76 @@ def test_transpose_skips_and_reports_bad_column_indices(stk):
         counts = torch.bincount(cols[good].long(), minlength=block_cols)
         assert torch.equal(ot.cpu()[1:].long(), torch.cumsum(counts, 0).cpu())
         assert int(ot[-1]) == nnz - 2
+
+
+def _as_int32(stk, m):
+    i32 = lambda t: t.to(torch.int32)
+    return stk.Matrix(m.size(), m.data, i32(m.row_indices), i32(m.column_indices), m.offsets)
+
+
+@pytest.mark.parametrize("mode", ["0", "1", "3", "auto"])
+def test_int32_block_indices_give_identical_results(stk, mode):
+    """The same topology with int32 instead of int16 block indices: transposed metadata equal value for
+    value, every product bit-identical, conversions bit-identical (the reference leaves the index
+    dtype as a TODO, stk/matrix.py:178-181)."""
+    from stk_b200 import dmoe
+    from stk_b200.backend import kernels
+    np.random.seed(23)
+    torch.manual_seed(23)
+    cases = [stk.random.randn((512, 768), 0.5, 128).to("cuda"),
+             dmoe.block_diagonal_topology(torch.tensor([2, 1, 0, 3]) * 128, 256, torch.float16, "cuda")]
+    cases[1].data.normal_(0, 0.1)
+    saved = kernels.PAIR_MODE
+    kernels.PAIR_MODE = mode
+    try:
+        for m16 in cases:
+            m32 = _as_int32(stk, m16)
+            m32.validate()
+            assert m32.column_indices_t.dtype == torch.int32 and m32.row_indices.dtype == torch.int32
+            assert torch.equal(m32.column_indices_t.to(torch.int16), m16.column_indices_t)
+            assert torch.equal(m32.offsets_t, m16.offsets_t) and torch.equal(m32.block_offsets_t, m16.block_offsets_t)
+            rows, cols = m16.size()
+            a = (torch.randn(rows, 256, device="cuda") * 0.1).half()
+            b = (torch.randn(256, cols, device="cuda") * 0.1).half()
+            right = (torch.randn(cols, 256, device="cuda") * 0.1).half()
+            left = (torch.randn(256, rows, device="cuda") * 0.1).half()
+            for _ in range(2):         # the second round runs with the kernel-choice statistics known
+                assert torch.equal(stk.ops.sdd(a, b, m32).data, stk.ops.sdd(a, b, m16).data)
+                assert torch.equal(stk.ops.dsd(m32, right), stk.ops.dsd(m16, right))
+                assert torch.equal(stk.ops.dsd(m32.t(), left.t()), stk.ops.dsd(m16.t(), left.t()))
+                assert torch.equal(stk.ops.dds(left, m32), stk.ops.dds(left, m16))
+                assert torch.equal(stk.ops.dds(right.t(), m32.t()), stk.ops.dds(right.t(), m16.t()))
+                torch.cuda.synchronize()
+            assert torch.equal(stk.ops.to_dense(m32), stk.ops.to_dense(m16))
+            ri = stk.ops.row_indices(m32.size(), m32.data, m32.offsets, m32.column_indices)
+            assert ri.dtype == torch.int32 and torch.equal(ri, m32.row_indices)
+            again = stk.ops.to_sparse(stk.ops.to_dense(m16), 128, index_dtype=torch.int32)
+            assert again.column_indices.dtype == torch.int32
+            keep = (m16.data.view(m16.data.shape[0], -1) != 0).any(1)
+            assert torch.equal(again.data, m16.data[keep])
+    finally:
+        kernels.PAIR_MODE = saved
+
+
+def test_more_than_32767_blocks_per_side(stk):
+    """40000 block rows (blocking 1): beyond what int16 indices can name.  The reference raises
+    (stk/matrix.py:161-167); here the conversion switches to int32 indices and round-trips exactly."""
+    torch.manual_seed(3)
+    x = torch.randn(40000, 16).half() * (torch.rand(40000, 16) < 0.3)
+    m = stk.ops.to_sparse(x.cuda(), 1)
+    m.validate()
+    assert m.row_indices.dtype == torch.int32 and m.column_indices.dtype == torch.int32
+    nz = torch.nonzero(x != 0)
+    assert torch.equal(m.row_indices.cpu().long(), nz[:, 0]) and torch.equal(m.column_indices.cpu().long(), nz[:, 1])
+    assert torch.equal(stk.ops.to_dense(m).cpu(), x)
+    order = torch.argsort(nz[:, 1], stable=True)
+    assert torch.equal(m.block_offsets_t.cpu().long(), order)
+    assert torch.equal(m.column_indices_t.cpu().long(), nz[:, 0][order])
+    # blocks of 8 x 8 on a matrix with 40000 block rows: the strip kernels take several launches
+    y = (torch.randn(40000 * 8, 16) * (torch.rand(40000, 1, 2, 1) < 0.5).expand(40000, 8, 2, 8).reshape(320000, 16)).half()
+    m8 = stk.ops.to_sparse(y.cuda(), 8)
+    assert m8.row_indices.dtype == torch.int32
+    assert torch.equal(stk.ops.to_dense(m8).cpu(), y)
+    with pytest.raises(ValueError):
+        stk.Matrix(m.size(), m.data, m.row_indices.to(torch.int16), m.column_indices.to(torch.int16), m.offsets,
+                   m.column_indices_t, m.offsets_t, m.block_offsets_t)

@@ -287,3 +287,18 @@ def test_products_reject_mixed_dtypes_and_unknown_kernel_modes():
     assert l.stk_b200_ep_barrier(null, 2, 0, 1, 100, null) == -1
     assert l.stk_b200_ep_plan(null, 2, 8, 0, 128, 1, null, null, null, null) == -1
     assert l.stk_b200_weighted_sum_rows(null, null, null, null, 4, 2, 24, 0, null) == -2
+
+
+def test_matrix_accepts_int32_block_indices():
+    """validate() takes int16 or int32 block indices, but not a mix of the two."""
+    import stk_b200 as stk
+    data = torch.zeros((1, 8, 8), dtype=torch.float16)
+    off = torch.tensor([0, 1], dtype=torch.int32)
+    i16, i32 = torch.zeros(1, dtype=torch.int16), torch.zeros(1, dtype=torch.int32)
+    full = lambda r, c: stk.Matrix(torch.Size((8, 8)), data, r, c, off, r, off, torch.zeros(1, dtype=torch.int32))
+    full(i16, i16).validate()
+    full(i32, i32).validate()
+    with pytest.raises(ValueError, match="one integer type"):
+        full(i16, i32).validate()
+    with pytest.raises(ValueError, match="int16 or int32"):
+        full(i32.long(), i32.long()).validate()
