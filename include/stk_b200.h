@@ -100,20 +100,14 @@ int stk_b200_device_status(int* status_host);
  *   aux: [nnz,128,128] contiguous like out, written (2) or read (3); NULL for epilogue 0 / 1.
  *   pair_plan: work-item table from stk_b200_pair_plan(offsets, column_indices, M/128, ...) for
  *        pair_mode = 1, or NULL (block rows are then paired blindly; see stk_b200_pair_plan).
- *   workspace: scratch of stk_b200_sdd_workspace_bytes(nnz, K, pair_mode, epilogue) bytes (16-byte
- *        aligned; contents on entry do not matter), or NULL.  With few blocks pair_mode 3 cuts the K
- *        loop into parts so that all SMs have work, keeps the parts' fp32 partial products there and
- *        adds them in a fixed order; without the workspace it does not split (same results up to fp32
- *        summation order, fewer SMs busy).  The size is 0 whenever no split would be made.
  * nnz == 0 is a no-op.
  */
-size_t stk_b200_sdd_workspace_bytes(int64_t nnz, int64_t K, int pair_mode, int epilogue);
 int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const int32_t* offsets,
                  const int16_t* row_indices, const int16_t* column_indices,
                  int64_t M, int64_t N, int64_t K, int64_t nnz,
                  int lhs_colmajor, int64_t ld_lhs, int rhs_colmajor, int64_t ld_rhs,
                  int dtype, int pair_mode, int epilogue, void* aux, const int32_t* pair_plan,
-                 void* workspace, size_t workspace_bytes, void* stream);
+                 void* stream);
 
 /*
  * DSD: out[M,N] = op(S)[M,K] @ rhs[K,N].
@@ -362,7 +356,7 @@ int stk_b200_sdd_i32(const void* lhs, const void* rhs, void* out, const int32_t*
                      int64_t M, int64_t N, int64_t K, int64_t nnz,
                      int lhs_colmajor, int64_t ld_lhs, int rhs_colmajor, int64_t ld_rhs,
                      int dtype, int pair_mode, int epilogue, void* aux, const int32_t* pair_plan,
-                     void* workspace, size_t workspace_bytes, void* stream);
+                     void* stream);
 int stk_b200_dsd_i32(const void* data, const int32_t* offsets, const int32_t* column_indices,
                      const int32_t* block_offsets, const void* rhs, void* out,
                      int64_t M, int64_t N, int64_t K, int64_t nnz,

@@ -27,7 +27,7 @@ ROW_KERNEL_MODES = ("3", "auto")
 # SDD with the row kernel (two blocks of a block row per tile) has half as many, twice as long work
 # items: on 8192^3 it is ahead of the 128x128 kernel from about 1000 blocks (level at 1024, 1190 vs
 # 920 TFLOP/s at 2048) and behind at 512 (685 vs 750), where 256 items leave the 148 SMs unevenly loaded.
-SDD_ROW_MIN_BLOCKS = 64
+SDD_ROW_MIN_BLOCKS = 1536
 # Fraction of the pair kernel's MMA work that must be useful for it to be chosen (measured with
 # python -m stk_b200.benchmarks).  DSD / DDS ("rows", "cols"): the alternative is the 128x256 row
 # kernel, which needs no pairing and is within 5 % of the pair kernel even on dMoE topologies
@@ -334,14 +334,11 @@ def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices, epilogue=0, 
         pairs = 3            # two blocks of a block row per 128x256 tile
     plan = pair_plan(offsets, column_indices) if pairs == 1 else None
     with _lib.on_device(out.device):
-        # few blocks: the row kernel splits K and needs room for the parts' fp32 partial products
-        ws_bytes = _lib.load().stk_b200_sdd_workspace_bytes(out.shape[0], K, pairs, epilogue) if pairs == 3 else 0
-        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=out.device) if ws_bytes else None
         rc = _lib.entry("stk_b200_sdd", column_indices)(
             _lib.ptr(lhs), _lib.ptr(rhs), _lib.ptr(out), _lib.ptr(offsets), _lib.ptr(row_indices),
             _lib.ptr(column_indices), M, N, K, out.shape[0], lhs_colmajor, ld_lhs, rhs_colmajor,
             ld_rhs, _lib.dtype_code(out.dtype), pairs, epilogue, _lib.ptr(aux), _lib.ptr(plan),
-            _lib.ptr(ws), ws_bytes, _lib.stream_ptr(out.device))
+            _lib.stream_ptr(out.device))
     _lib.check(rc, "stk_b200_sdd")
 
 

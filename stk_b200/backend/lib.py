@@ -25,9 +25,7 @@ SIGNATURES = {
     "stk_b200_error_string": (ctypes.c_char_p, [_c_int]),
     "stk_b200_device_status": (_c_int, [ctypes.POINTER(_c_int)]),
     "stk_b200_sdd": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64,
-                              _c_i64, _c_int, _c_i64, _c_int, _c_i64, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr,
-                              _c_size, _c_ptr]),
-    "stk_b200_sdd_workspace_bytes": (_c_size, [_c_i64, _c_i64, _c_int, _c_int]),
+                              _c_i64, _c_int, _c_i64, _c_int, _c_i64, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr]),
     "stk_b200_dsd": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64,
                               _c_i64, _c_int, _c_int, _c_i64, _c_i64, _c_int, _c_int, _c_ptr, _c_ptr]),
     "stk_b200_dds": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64,

@@ -46,7 +46,7 @@ static int sdd_impl(const void* lhs, const void* rhs, void* out, const int32_t* 
                     IndexArray row_indices, IndexArray column_indices, int64_t M, int64_t N, int64_t K,
                     int64_t nnz, int lhs_colmajor, int64_t ld_lhs, int rhs_colmajor, int64_t ld_rhs,
                     int dtype, int pair_mode, int epilogue, void* aux, const int32_t* pair_plan,
-                    void* workspace, size_t workspace_bytes, void* stream) {
+                    void* stream) {
   int rc = check_dtype_dims(dtype, M, N, K, nnz, 32, pair_mode);
   if (rc != STK_OK) return rc;
   if (epilogue < kEpilogueNone || epilogue > kEpilogueGeluGrad) return STK_ERR_BAD_DIMS;
@@ -88,15 +88,6 @@ static int sdd_impl(const void* lhs, const void* rhs, void* out, const int32_t* 
     p.ldc = kBlk;
     p.nnz = static_cast<int>(nnz);
     p.aux = aux;
-    DeviceInfo* d = nullptr;
-    if ((rc = device_info(&d)) != STK_OK) return rc;
-    // with few blocks the K loop is cut into parts (needs the caller's fp32 workspace; without it: no split)
-    p.k_split = row_sdd_k_split(nnz, k_steps, d->sms, epilogue);
-    if (p.k_split > 1) {
-      const size_t need = static_cast<size_t>(p.k_split) * nnz * kBlk * kBlk * sizeof(float);
-      if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) p.k_split = 1;
-    }
-    p.partials = static_cast<float*>(workspace);
     return launch_row(tmA, tmB, tmC, tmX, p, s);
   }
   if (pair_mode) {
@@ -326,30 +317,21 @@ extern "C" int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const i
                             const int16_t* row_indices, const int16_t* column_indices, int64_t M,
                             int64_t N, int64_t K, int64_t nnz, int lhs_colmajor, int64_t ld_lhs,
                             int rhs_colmajor, int64_t ld_rhs, int dtype, int pair_mode,
-                            int epilogue, void* aux, const int32_t* pair_plan, void* workspace,
-                            size_t workspace_bytes, void* stream) {
+                            int epilogue, void* aux, const int32_t* pair_plan, void* stream) {
   return sdd_impl(lhs, rhs, out, offsets, IndexArray{row_indices, 0}, IndexArray{column_indices, 0}, M, N, K,
                   nnz, lhs_colmajor, ld_lhs, rhs_colmajor, ld_rhs, dtype, pair_mode, epilogue, aux, pair_plan,
-                  workspace, workspace_bytes, stream);
+                  stream);
 }
 extern "C" int stk_b200_sdd_i32(const void* lhs, const void* rhs, void* out, const int32_t* offsets,
                                 const int32_t* row_indices, const int32_t* column_indices, int64_t M,
                                 int64_t N, int64_t K, int64_t nnz, int lhs_colmajor, int64_t ld_lhs,
                                 int rhs_colmajor, int64_t ld_rhs, int dtype, int pair_mode,
-                                int epilogue, void* aux, const int32_t* pair_plan, void* workspace,
-                                size_t workspace_bytes, void* stream) {
+                                int epilogue, void* aux, const int32_t* pair_plan, void* stream) {
   return sdd_impl(lhs, rhs, out, offsets, IndexArray{row_indices, 1}, IndexArray{column_indices, 1}, M, N, K,
                   nnz, lhs_colmajor, ld_lhs, rhs_colmajor, ld_rhs, dtype, pair_mode, epilogue, aux, pair_plan,
-                  workspace, workspace_bytes, stream);
+                  stream);
 }
 
-extern "C" size_t stk_b200_sdd_workspace_bytes(int64_t nnz, int64_t K, int pair_mode, int epilogue) {
-  if (pair_mode != 3 || nnz <= 0 || K <= 0) return 0;
-  DeviceInfo* d = nullptr;
-  if (device_info(&d) != STK_OK) return 0;
-  const int split = row_sdd_k_split(nnz, static_cast<int>((K + kBK - 1) / kBK), d->sms, epilogue);
-  return split > 1 ? static_cast<size_t>(split) * nnz * kBlk * kBlk * sizeof(float) : 0;
-}
 extern "C" int stk_b200_dsd(const void* data, const int32_t* offsets, const int16_t* column_indices,
                             const int32_t* block_offsets, const void* rhs, void* out, int64_t M,
                             int64_t N, int64_t K, int64_t nnz, int trans_sparse, int rhs_colmajor,

@@ -314,10 +314,6 @@ bsmm_row_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 // the same block row, else one half-used tile for each (a static enumeration, no prefix sums; a block
 // row of L blocks wastes at most one half tile).  Reference semantics: _sdd_kernel,
 // stk/backend/triton_kernels.py:34-68.
-// With few blocks (fewer work items than two or three per SM) the K loop is cut into `k_split`
-// parts, each an item of its own: part s of an item covers K steps [s * per, (s + 1) * per) and leaves
-// its fp32 partial products in slab s of a workspace [k_split][nnz][128][128]; sdd_splitk_finish_kernel
-// then adds the slabs in order (deterministic, unlike atomics) and rounds once.
 struct RowSddItem {
   int tiles;       // 1 or 2
   int row[2];      // block row of each tile
@@ -401,8 +397,6 @@ bsmm_row_sdd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int ks_per = (p.k_steps + p.k_split - 1) / p.k_split;  // K steps per part
-  const int num_work = p.num_tiles * p.k_split;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -410,13 +404,11 @@ bsmm_row_sdd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
-        const int item = work / p.k_split, part = work - item * p.k_split;
-        const int ks0 = part * ks_per, ks1 = min(p.k_steps, ks0 + ks_per);
+      for (int item = blockIdx.x; item < p.num_tiles && ok; item += gridDim.x) {
         const RowSddItem it = row_sdd_item(p, item);
         for (int t = 0; t < it.tiles && ok; ++t) {
           const bool both = it.col[t][1] >= 0;
-          for (int ks = ks0; ks < ks1 && ok; ++ks) {
+          for (int ks = 0; ks < p.k_steps && ok; ++ks) {
             ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
             if (!ok) break;
             const uint32_t a_dst = smem_base + stage * kRStageBytes;
@@ -456,18 +448,16 @@ bsmm_row_sdd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const int j1 = 2 * item + 1;
         return (j1 < p.nnz && p.row_idx[j1] != p.row_idx[j1 - 1]) ? 2 : 1;
       };
-      int tiles_next = static_cast<int>(blockIdx.x) < num_work ? tiles_of(blockIdx.x / p.k_split) : 0;
-      for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
-        const int part = work % p.k_split;
-        const int ks0 = part * ks_per, ks1 = min(p.k_steps, ks0 + ks_per);
+      int tiles_next = static_cast<int>(blockIdx.x) < p.num_tiles ? tiles_of(blockIdx.x) : 0;
+      for (int item = blockIdx.x; item < p.num_tiles && ok; item += gridDim.x) {
         const int tiles = tiles_next;
-        if (work + static_cast<int>(gridDim.x) < num_work) tiles_next = tiles_of((work + gridDim.x) / p.k_split);
+        if (item + static_cast<int>(gridDim.x) < p.num_tiles) tiles_next = tiles_of(item + gridDim.x);
         for (int t = 0; t < tiles && ok; ++t) {
           ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag);
           if (!ok) break;
           const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * 2 * kBlk);
           uint32_t accumulate = 0;
-          for (int ks = ks0; ks < ks1; ++ks) {
+          for (int ks = 0; ks < p.k_steps; ++ks) {
             if (!ready) {
               ok = mbar_wait(full_bar(stage), phase, abort_flag);
               if (!ok) break;
@@ -503,8 +493,7 @@ bsmm_row_sdd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
-      const int item = work / p.k_split, part = work - item * p.k_split;
+    for (int item = blockIdx.x; item < p.num_tiles && ok; item += gridDim.x) {
       const RowSddItem it = row_sdd_item(p, item);
       for (int t = 0; t < it.tiles && ok; ++t) {
         mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
@@ -518,24 +507,10 @@ bsmm_row_sdd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                 static_cast<uint32_t>(acc * 2 * kBlk);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          if (it.blk[t][h] < 0) continue;
-          if (p.k_split > 1) {
-            // this part's fp32 partial products of the block: 512 contiguous bytes per thread
-            float* dst = p.partials + ((static_cast<long long>(part) * p.nnz + it.blk[t][h]) * kBlk + row) * kBlk;
-#pragma unroll 1
-            for (int c = 0; c < kBlk; c += 32) {
-              uint32_t v[32];
-              tmem_ld_32x32(t_addr + h * kBlk + c, v);
-              tmem_ld_wait();
-#pragma unroll
-              for (int i = 0; i < 32; i += 4)
-                *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-            }
-          } else {
+          if (it.blk[t][h] >= 0)
             drain_to_output<kTrain>(t_addr, h * kBlk, kBlk, p.fmt, p.epilogue, &tmC, 0,
                                     it.blk[t][h] * kBlk, staging, row, 0, 0, 1, issuer,
                                     EpilogueAux{&tmX, static_cast<const uint16_t*>(p.aux)});
-          }
         }
         tc_fence_before();
         __syncwarp();
@@ -561,55 +536,6 @@ bsmm_row_sdd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (threadIdx.x == 0 && *abort_flag != 0) report_status(STK_ERR_DEVICE_TIMEOUT);
 }
 
-// Adds the k_split fp32 slabs of partial products in slab order and rounds to the 16-bit output.
-template <bool kBf16>
-__global__ void __launch_bounds__(256)
-sdd_splitk_finish_kernel(const float4* __restrict__ partials, uint2* __restrict__ out, long long quads,
-                         int k_split) {
-  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= quads) return;
-  float4 acc = partials[i];
-  for (int s = 1; s < k_split; ++s) {
-    const float4 v = partials[s * quads + i];
-    acc.x += v.x;
-    acc.y += v.y;
-    acc.z += v.z;
-    acc.w += v.w;
-  }
-  uint2 r;
-  if (kBf16) {
-    const __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y), b = __floats2bfloat162_rn(acc.z, acc.w);
-    r.x = *reinterpret_cast<const uint32_t*>(&a);
-    r.y = *reinterpret_cast<const uint32_t*>(&b);
-  } else {
-    const __half2 a = __floats2half2_rn(acc.x, acc.y), b = __floats2half2_rn(acc.z, acc.w);
-    r.x = *reinterpret_cast<const uint32_t*>(&a);
-    r.y = *reinterpret_cast<const uint32_t*>(&b);
-  }
-  out[i] = r;
-}
-
-// Parts to cut the K loop of the row SDD kernel into: the split that minimises
-// (rounds of work items over the SMs) x (K steps per item, plus a few for the item's start), never
-// leaving a part shorter than 8 K steps.  1 when there are items enough without a split.
-static int row_sdd_k_split(int64_t nnz, int k_steps, int sms, int epilogue) {
-  if (epilogue != kEpilogueNone || nnz <= 0) return 1;
-  const long long items = (nnz + 1) / 2;
-  int best_s = 1;
-  long long best = -1;
-  for (int s = 1; s <= 8; ++s) {
-    const int per = (k_steps + s - 1) / s;
-    if (s > 1 && per < 8) break;
-    const long long rounds = (items * s + sms - 1) / sms;
-    const long long cost = rounds * (per + 4) + (s > 1 ? per / 4 : 0);  // + the pass that adds the slabs
-    if (best < 0 || cost < best) {
-      best = cost;
-      best_s = s;
-    }
-  }
-  return best_s;
-}
-
 static int launch_row(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                       const CUtensorMap& tmX, const BsmmParams& p, cudaStream_t stream) {
   DeviceInfo* d = nullptr;
@@ -630,8 +556,7 @@ static int launch_row(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUte
     }
     opted_in[dev] = true;
   }
-  const long long work = static_cast<long long>(p.num_tiles) * (p.mode == kModeSDD ? p.k_split : 1);
-  const int grid = work < d->sms ? static_cast<int>(work) : d->sms;
+  const int grid = p.num_tiles < d->sms ? p.num_tiles : d->sms;
   cudaError_t err;
   if (p.mode != kModeSDD)
     err = launch_dependent(bsmm_row_kernel, grid, kThreads, kRSmemBytes, stream, tmA, tmB, tmC, p);
@@ -639,19 +564,7 @@ static int launch_row(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUte
     err = launch_dependent(bsmm_row_sdd_kernel<true>, grid, kThreads, kRSmemBytes, stream, tmA, tmB, tmC, tmX, p);
   else
     err = launch_dependent(bsmm_row_sdd_kernel<false>, grid, kThreads, kRSmemBytes, stream, tmA, tmB, tmC, tmX, p);
-  if (err != cudaSuccess) return STK_ERR_LAUNCH;
-  if (p.mode == kModeSDD && p.k_split > 1) {
-    const long long quads = static_cast<long long>(p.nnz) * kBlk * kBlk / 4;
-    const unsigned blocks = static_cast<unsigned>((quads + 255) / 256);
-    if (p.fmt == STK_BF16)
-      sdd_splitk_finish_kernel<true><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float4*>(p.partials),
-                                                                 static_cast<uint2*>(p.out), quads, p.k_split);
-    else
-      sdd_splitk_finish_kernel<false><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float4*>(p.partials),
-                                                                  static_cast<uint2*>(p.out), quads, p.k_split);
-    if (cudaGetLastError() != cudaSuccess) return STK_ERR_LAUNCH;
-  }
-  return STK_OK;
+  return err == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 
 }  // namespace stk

@@ -123,8 +123,6 @@ struct BsmmParams {
   int out_rows;             // row kernel, DDS: dense rows of the output
   int nnz;                  // row kernel, SDD: number of blocks
   int raster_group;         // row kernel, DSD / DDS: lists per tile-order group (see row_tile)
-  int k_split;              // row kernel, SDD: parts the K loop is cut into (>= 1)
-  float* partials;          // row kernel, SDD with k_split > 1: [k_split][nnz][128][128] fp32
   const void* aux;          // SDD with kEpilogueGeluKeep / kEpilogueGeluGrad: the auxiliary tensor
 };
 

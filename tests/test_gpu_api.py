@@ -293,34 +293,3 @@ def test_more_than_32767_blocks_per_side(stk):
         stk.Matrix(m.size(), m.data, m.row_indices.to(torch.int16), m.column_indices.to(torch.int16), m.offsets,
                    m.column_indices_t, m.offsets_t, m.block_offsets_t)
 
-
-@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-def test_sdd_with_few_blocks_splits_k_deterministically(stk, dtype):
-    """Few blocks and a long K loop: the row kernel cuts K into parts (fp32 partial products in a
-    workspace, added in a fixed order).  Same values as the dense path, bit-identical from run to run,
-    and within rounding of the unsplit kernel."""
-    from stk_b200.backend import kernels, lib
-    np.random.seed(31)
-    torch.manual_seed(31)
-    topo = stk.random.mask(1024, 1280, 0.6, 128).to("cuda")
-    nnz, K = topo.data.shape[0], 4096
-    assert lib.load().stk_b200_sdd_workspace_bytes(nnz, K, 3, 0) >= 2 * nnz * 128 * 128 * 4   # a split is made
-    assert lib.load().stk_b200_sdd_workspace_bytes(nnz, K, 3, 1) == 0                          # not with an epilogue
-    a = (torch.randn(1024, K) * 0.05).to(dtype)
-    b = (torch.randn(K, 1280) * 0.05).to(dtype)
-    r, c = topo.row_indices.cpu().numpy(), topo.column_indices.cpu().numpy()
-    saved = kernels.PAIR_MODE
-    try:
-        kernels.PAIR_MODE = "3"
-        first = stk.ops.sdd(a.cuda(), b.cuda(), topo).data
-        again = stk.ops.sdd(a.cuda(), b.cuda(), topo).data
-        transposed = stk.ops.sdd(a.t().contiguous().cuda().t(), b.t().contiguous().cuda().t(), topo).data
-        kernels.PAIR_MODE = "0"
-        unsplit = stk.ops.sdd(a.cuda(), b.cuda(), topo).data
-    finally:
-        kernels.PAIR_MODE = saved
-    assert torch.equal(first, again)
-    ref = oracle.sdd(a, b, r, c, dtype)
-    assert_product_close(first, ref, "split-K sdd")
-    assert_product_close(transposed, ref, "split-K sdd, transposed operands")
-    assert_product_close(first, unsplit.float(), "split against unsplit", roundings=2)

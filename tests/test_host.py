@@ -39,16 +39,16 @@ def test_argument_validation_happens_before_any_launch():
     l = lib.load()
     null = ctypes.c_void_p(0)
     # M not a multiple of 128 / K not a multiple of 32 / bad dtype
-    assert l.stk_b200_sdd(null, null, null, null, null, null, 100, 128, 128, 1, 0, 128, 0, 128, 0, 0, 0, null, null, null, 0, null) == -2
-    assert l.stk_b200_sdd(null, null, null, null, null, null, 128, 128, 48, 1, 0, 128, 0, 128, 0, 0, 0, null, null, null, 0, null) == -2
-    assert l.stk_b200_sdd(null, null, null, null, null, null, 128, 128, 128, 1, 0, 128, 0, 128, 7, 0, 0, null, null, null, 0, null) == -3
+    assert l.stk_b200_sdd(null, null, null, null, null, null, 100, 128, 128, 1, 0, 128, 0, 128, 0, 0, 0, null, null, null) == -2
+    assert l.stk_b200_sdd(null, null, null, null, null, null, 128, 128, 48, 1, 0, 128, 0, 128, 0, 0, 0, null, null, null) == -2
+    assert l.stk_b200_sdd(null, null, null, null, null, null, 128, 128, 128, 1, 0, 128, 0, 128, 7, 0, 0, null, null, null) == -3
     # nnz == 0 is a no-op for SDD even with NULL pointers
-    assert l.stk_b200_sdd(null, null, null, null, null, null, 128, 128, 128, 0, 0, 128, 0, 128, 0, 1, 0, null, null, null, 0, null) == 0
+    assert l.stk_b200_sdd(null, null, null, null, null, null, 128, 128, 128, 0, 0, 128, 0, 128, 0, 1, 0, null, null, null) == 0
     # NULL operands
-    assert l.stk_b200_sdd(null, null, null, null, null, null, 128, 128, 128, 1, 0, 128, 0, 128, 0, 0, 0, null, null, null, 0, null) == -1
+    assert l.stk_b200_sdd(null, null, null, null, null, null, 128, 128, 128, 1, 0, 128, 0, 128, 0, 0, 0, null, null, null) == -1
     # an epilogue with an auxiliary tensor needs one; unknown epilogue codes are rejected
-    assert l.stk_b200_sdd(null, null, null, null, null, null, 128, 128, 128, 1, 0, 128, 0, 128, 0, 0, 2, null, null, null, 0, null) == -1
-    assert l.stk_b200_sdd(null, null, null, null, null, null, 128, 128, 128, 1, 0, 128, 0, 128, 0, 0, 4, null, null, null, 0, null) == -2
+    assert l.stk_b200_sdd(null, null, null, null, null, null, 128, 128, 128, 1, 0, 128, 0, 128, 0, 0, 2, null, null, null) == -1
+    assert l.stk_b200_sdd(null, null, null, null, null, null, 128, 128, 128, 1, 0, 128, 0, 128, 0, 0, 4, null, null, null) == -2
     assert l.stk_b200_dsd(null, null, null, null, null, null, 128, 128, 100, 1, 0, 0, 128, 128, 0, 0, null, null) == -2
     assert l.stk_b200_transpose_meta(null, null, -1, 4, null, null, null, null, 0, null) == -2
     assert l.stk_b200_transpose_meta(null, null, 4, 40000, null, null, null, null, 0, null) == -9
@@ -279,7 +279,7 @@ def test_products_reject_mixed_dtypes_and_unknown_kernel_modes():
         kernels.sdd(h(128, 128), b(128, 128), (128, 128), h(1, 128, 128), off, idx, idx)
     l = lib.load()
     null = ctypes.c_void_p(0)
-    assert l.stk_b200_sdd(null, null, null, null, null, null, 128, 128, 128, 1, 0, 128, 0, 128, 0, 2, 0, null, null, null, 0, null) == -2
+    assert l.stk_b200_sdd(null, null, null, null, null, null, 128, 128, 128, 1, 0, 128, 0, 128, 0, 2, 0, null, null, null) == -2
     assert l.stk_b200_dsd(null, null, null, null, null, null, 128, 128, 128, 1, 0, 0, 128, 128, 0, 7, null, null) == -2
     assert l.stk_b200_pair_plan(null, null, 0, null, 0, null) == -2
     assert l.stk_b200_pair_plan(null, null, 4, null, 0, null) == -1
