@@ -291,8 +291,11 @@ def run_ours(args):
     tokens_total, experts_total = T_TOKENS // args.shrink, EXPERTS // args.shrink
     if experts_total % world or tokens_total % (world * TOKEN_BLOCK):
         raise SystemExit(f"{experts_total} experts / {tokens_total} tokens do not divide over {world} ranks")
-    chunks = int(os.environ.get("STK_B200_EP_CHUNKS", "2"))
-    layer = Layer(rank, world, dev, tokens_total, experts_total, min(chunks, experts_total // world))
+    # expert chunks of the overlapped exchange: at least four experts per chunk (shorter products lose
+    # more to their last, partly filled round of work items than the overlap gains), at most four chunks
+    local_experts = experts_total // world
+    chunks = int(os.environ.get("STK_B200_EP_CHUNKS", str(min(4, max(1, local_experts // 4)))))
+    layer = Layer(rank, world, dev, tokens_total, experts_total, min(chunks, local_experts))
     tokens = layer.tokens
     ids_all, probs_all = routing(tokens_total, experts_total)
     sl = slice(rank * tokens, (rank + 1) * tokens)
