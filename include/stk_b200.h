@@ -70,16 +70,13 @@ int stk_b200_device_status(int* status_host);
  * CTA pairs (tcgen05 cta_group::2): two neighbouring block rows / columns of the sparse operand are
  * processed together over the merge of their block lists, which halves the operand traffic per
  * FLOP when the neighbours' lists mostly coincide (dMoE topologies) and wastes MMA work when they
- * do not.  2 is the same kernel with a dynamic schedule: instead of dealing the work items
- * round-robin, every CTA pair draws its next item from a ticket counter when it is ready for one
- * (balanced whatever the items cost; the counters are part of the library image and reset
- * themselves).  3 runs 128x256 tiles on one CTA with one N = 256 MMA per K step: one block row of op(S) x
+ * do not.  3 runs 128x256 tiles on one CTA with one N = 256 MMA per K step: one block row of op(S) x
  * 256 dense columns (dsd), 256 dense rows x one block column (dds, computed transposed), or two
  * blocks of one block row (sdd: blocks 2i and 2i+1 of the list; row_indices / column_indices in
  * row-major order).  Three quarters of mode 0's operand traffic for any topology, no pairing
  * needed - the choice for topologies that do not pair up.  Any other value is STK_ERR_BAD_DIMS.
- * All modes give the same results; modes 1 and 2 need every block row's column_indices (and every
- * block column's column_indices_t) in ascending order.
+ * All modes give the same results; mode 1 needs every block row's column_indices (and every block
+ * column's column_indices_t) in ascending order.
  */
 
 /*
@@ -90,7 +87,7 @@ int stk_b200_device_status(int* status_host);
  *        column-major (lhs_colmajor=1, element (m,k) at k*ld_lhs+m - an exact .t() view).
  *   rhs: logical [K,N]; same convention with ld_rhs.
  *   out: [nnz,128,128] contiguous.
- *   offsets: CSR offsets [M/128+1]; only read when pair_mode = 1 or 2 (may be NULL otherwise).
+ *   offsets: CSR offsets [M/128+1]; only read when pair_mode = 1 (may be NULL otherwise).
  *   epilogue: 0 stores the product; 1 (STK_EPILOGUE_GELU) stores GeLU(product), the exact erf form
  *             applied to the fp32 accumulator before rounding - the step between SDD and DSD in a
  *             dMoE layer, fused so that the hidden activations are written once.  The reference
@@ -102,7 +99,7 @@ int stk_b200_device_status(int* status_host);
  *             the activations.
  *   aux: [nnz,128,128] contiguous like out, written (2) or read (3); NULL for epilogue 0 / 1.
  *   pair_plan: work-item table from stk_b200_pair_plan(offsets, column_indices, M/128, ...) for
- *        pair_mode = 1 / 2, or NULL (block rows are then paired blindly; see stk_b200_pair_plan).
+ *        pair_mode = 1, or NULL (block rows are then paired blindly; see stk_b200_pair_plan).
  * nnz == 0 is a no-op.
  */
 int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const int32_t* offsets,
@@ -122,7 +119,7 @@ int stk_b200_sdd(const void* lhs, const void* rhs, void* out, const int32_t* off
  *   M,K: logical (already transposed) shape of op(S).  Block rows without blocks give zeros.
  *   rhs: row-major or column-major as for stk_b200_sdd.  out: row-major, leading dimension ld_out.
  *   pair_plan: table from stk_b200_pair_plan over the SAME offsets / column_indices arrays that are
- *        passed here (M/128 lists), for pair_mode = 1 / 2; or NULL.
+ *        passed here (M/128 lists), for pair_mode = 1; or NULL.
  */
 int stk_b200_dsd(const void* data, const int32_t* offsets, const int16_t* column_indices,
                  const int32_t* block_offsets, const void* rhs, void* out,
@@ -139,7 +136,7 @@ int stk_b200_dsd(const void* data, const int32_t* offsets, const int16_t* column
  *                     (block column n of S^T is block row n of S, blocks used transposed).
  *   K,N: logical shape of op(S).
  *   pair_plan: table from stk_b200_pair_plan over the offsets / column_indices arrays passed here
- *        (N/128 lists), for pair_mode = 1 / 2; or NULL.
+ *        (N/128 lists), for pair_mode = 1; or NULL.
  */
 int stk_b200_dds(const void* lhs, const void* data, const int32_t* offsets,
                  const int16_t* column_indices, const int32_t* block_offsets, void* out,

@@ -17,13 +17,10 @@ from stk_b200.backend import lib as _lib
 BLOCK = 128  # the matmul kernels are built for 128x128 blocks
 
 # Which matmul kernel runs: "0" = one 128x128 tile per CTA, "1" = 256x256 supertiles on CTA pairs
-# wherever the metadata allows it, work items dealt round-robin, "2" = the same kernel with the items
-# drawn from a ticket counter as pairs become free, "3" = 128x256 tiles on one CTA (two blocks of a
-# block row for SDD, one block row / column x 256 dense columns / rows for DSD / DDS), "auto" = per
-# topology, from how well neighbouring block rows / columns pair up (see pair_hints).
+# wherever the metadata allows it, "3" = 128x256 tiles on one CTA (two blocks of a block row for SDD,
+# one block row / column x 256 dense columns / rows for DSD / DDS), "auto" = per topology, from how
+# well neighbouring block rows / columns pair up (see pair_hints).
 PAIR_MODE = os.environ.get("STK_B200_PAIR_MODE", "auto")
-# The pair kernel's schedule when "auto" picks that kernel: 2 = dynamic (ticket counter), 1 = static.
-AUTO_PAIR_SCHEDULE = int(os.environ.get("STK_B200_PAIR_SCHEDULE", "2"))
 # DSD / DDS products that do not take the pair kernel run the 128x256 row kernel in these modes when
 # the dense operand has at least 256 columns (DSD) / rows (DDS); "3" never takes the pair kernel.
 ROW_KERNEL_MODES = ("3", "auto")
@@ -159,7 +156,7 @@ def _use_pairs(kind, offsets, row_indices, column_indices, block_cols, offsets_t
     """kind: "rows", "cols" or "tiles" - which neighbours the product would pair.  1 = pair kernel."""
     if PAIR_MODE in ("0", "3"):
         return 0
-    forced = PAIR_MODE in ("1", "2")
+    forced = PAIR_MODE == "1"
     hints = pair_hints(offsets, row_indices, column_indices, block_cols, offsets_t, column_indices_t,
                        need_t=kind == "cols", wait=forced)
     if hints is None:
@@ -170,8 +167,8 @@ def _use_pairs(kind, offsets, row_indices, column_indices, block_cols, offsets_t
     if not in_order or (kind == "cols" and not t_order):
         return 0
     if forced:
-        return int(PAIR_MODE)
-    return AUTO_PAIR_SCHEDULE if {"rows": rows, "cols": cols, "tiles": tiles}[kind] >= PAIR_THRESHOLD[kind] else 0
+        return 1
+    return int({"rows": rows, "cols": cols, "tiles": tiles}[kind] >= PAIR_THRESHOLD[kind])
 
 
 def pair_plan(offsets, indices):
@@ -272,7 +269,7 @@ def dsd(shape, data, offsets, row_indices, column_indices, offsets_t, column_ind
         pairs = _use_pairs("rows", offsets, row_indices, column_indices, K // BLOCK, offsets_t, column_indices_t)
     if pairs == 0 and N >= 2 * BLOCK and PAIR_MODE in ROW_KERNEL_MODES:
         pairs = 3            # one block row x 256 dense columns per CTA
-    plan = pair_plan(meta[0], meta[1]) if pairs in (1, 2) else None
+    plan = pair_plan(meta[0], meta[1]) if pairs == 1 else None
     with _lib.on_device(out.device):
         rc = _lib.entry("stk_b200_dsd", meta[1])(
             _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),
@@ -302,7 +299,7 @@ def dds(lhs, shape, data, offsets, row_indices, column_indices, offsets_t, colum
         pairs = _use_pairs("cols", offsets, row_indices, column_indices, N // BLOCK, offsets_t, column_indices_t)
     if pairs == 0 and M >= 2 * BLOCK and PAIR_MODE in ROW_KERNEL_MODES:
         pairs = 3            # 256 dense rows x one block column per CTA
-    plan = pair_plan(meta[0], meta[1]) if pairs in (1, 2) else None
+    plan = pair_plan(meta[0], meta[1]) if pairs == 1 else None
     with _lib.on_device(out.device):
         rc = _lib.entry("stk_b200_dds", meta[1])(
             _lib.ptr(lhs), _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),
@@ -335,7 +332,7 @@ def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices, epilogue=0, 
     pairs = _use_pairs("tiles", offsets, row_indices, column_indices, N // BLOCK)
     if pairs == 0 and (PAIR_MODE == "3" or (PAIR_MODE == "auto" and out.shape[0] >= SDD_ROW_MIN_BLOCKS)):
         pairs = 3            # two blocks of a block row per 128x256 tile
-    plan = pair_plan(offsets, column_indices) if pairs in (1, 2) else None
+    plan = pair_plan(offsets, column_indices) if pairs == 1 else None
     with _lib.on_device(out.device):
         rc = _lib.entry("stk_b200_sdd", column_indices)(
             _lib.ptr(lhs), _lib.ptr(rhs), _lib.ptr(out), _lib.ptr(offsets), _lib.ptr(row_indices),

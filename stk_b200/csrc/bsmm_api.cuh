@@ -11,7 +11,7 @@ static int check_dtype_dims(int dtype, int64_t M, int64_t N, int64_t K, int64_t 
                             int pair_mode) {
   if (dtype != STK_F16 && dtype != STK_BF16) return STK_ERR_BAD_DTYPE;
   if (M <= 0 || N <= 0 || K <= 0 || nnz < 0 || M % kBlk || N % kBlk || K % k_mult) return STK_ERR_BAD_DIMS;
-  if (pair_mode < 0 || pair_mode > 3) return STK_ERR_BAD_DIMS;
+  if (pair_mode != 0 && pair_mode != 1 && pair_mode != 3) return STK_ERR_BAD_DIMS;
   if (nnz * kBlk > INT32_MAX - 2 * kBlk || M > INT32_MAX / 2 || N > INT32_MAX / 2 || K > INT32_MAX / 2 ||
       (M / kBlk) * (N / kBlk) > INT32_MAX)
     return STK_ERR_TOO_LARGE;
@@ -20,6 +20,15 @@ static int check_dtype_dims(int dtype, int64_t M, int64_t N, int64_t K, int64_t 
 
 // Lists (block rows / columns) per tile-order group of the row kernel: as many as keep the group's
 // sparse blocks (32 KiB each) within a share of the L2 that leaves room for the dense panels in use.
+// Groups (pairs of lists) per band of the pair kernel's item order: as many as keep the band's own
+// operand - `bytes_per_group` of dense rows (SDD) or sparse blocks (DSD / DDS) - within 64 MiB, half the L2.
+static int pair_band(int64_t bytes_per_group) {
+  int64_t g = (64ll << 20) / (bytes_per_group > 0 ? bytes_per_group : 1);
+  if (g < 1) g = 1;
+  if (g > (1 << 20)) g = 1 << 20;
+  return static_cast<int>(g);
+}
+
 static int row_raster_group(int64_t nnz, int64_t num_lists) {
   const int64_t budget_blocks = (48ll << 20) / (kBlk * kBlk * 2);
   const int64_t per_list = (nnz + num_lists - 1) / num_lists;
@@ -46,7 +55,7 @@ static int sdd_impl(const void* lhs, const void* rhs, void* out, const int32_t* 
   if (has_aux && !aligned16(aux)) return STK_ERR_BAD_LAYOUT;
   if (nnz == 0) return STK_OK;
   if (out == nullptr || row_indices.null() || column_indices.null()) return STK_ERR_NULL_POINTER;
-  if ((pair_mode == 1 || pair_mode == 2) && offsets == nullptr) return STK_ERR_NULL_POINTER;
+  if (pair_mode && pair_mode != 3 && offsets == nullptr) return STK_ERR_NULL_POINTER;
   if (!aligned16(out)) return STK_ERR_BAD_LAYOUT;
   if ((rc = check_dense(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) return rc;
   if ((rc = check_dense(rhs, ld_rhs, rhs_colmajor ? K : N)) != STK_OK) return rc;
@@ -122,7 +131,8 @@ static int sdd_impl(const void* lhs, const void* rhs, void* out, const int32_t* 
     p.ldc = kBlk;
     p.aux = aux;
     p.plan = pair_plan;
-    return launch_pair(tmA, tmB, tmC, tmX, p, pair_mode == 2, s);
+    p.band = pair_band(2 * kBlk * K * 2);  // a row group's lhs panel
+    return launch_pair(tmA, tmB, tmC, tmX, p, s);
   }
 
   BsmmParams p{};
@@ -203,7 +213,8 @@ static int dsd_impl(const void* data, const int32_t* offsets, IndexArray column_
     p.out = out;
     p.ldc = ld_out;
     p.plan = pair_plan;
-    return launch_pair(tmA, tmB, tmC, tmC, p, pair_mode == 2, s);
+    p.band = pair_band(2 * ((nnz + p.num_lists - 1) / p.num_lists) * kBlk * kBlk * 2);  // a group's blocks
+    return launch_pair(tmA, tmB, tmC, tmC, p, s);
   }
 
   BsmmParams p{};
@@ -281,7 +292,8 @@ static int dds_impl(const void* lhs, const void* data, const int32_t* offsets, I
     p.out = out;
     p.ldc = ld_out;
     p.plan = pair_plan;
-    return launch_pair(tmA, tmB, tmC, tmC, p, pair_mode == 2, s);
+    p.band = pair_band(2 * ((nnz + p.num_lists - 1) / p.num_lists) * kBlk * kBlk * 2);  // a group's blocks
+    return launch_pair(tmA, tmB, tmC, tmC, p, s);
   }
 
   BsmmParams p{};

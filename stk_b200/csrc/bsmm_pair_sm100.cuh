@@ -44,14 +44,13 @@ constexpr int kPProducerBWarp = 6;
 constexpr int kPStages = 6;
 constexpr int kPAccCols = 256;   // one accumulator: 128 lanes x 256 fp32 columns per CTA
 constexpr int kPTmemCols = 512;  // two accumulators
-constexpr int kPSched = 4;       // depth of the work-item ring (dynamic schedule)
-constexpr int kPNumBars = 2 * kPStages + 4 + 2 * kPSched;
+constexpr int kPNumBars = 2 * kPStages + 4;
 #ifndef STK_DEPENDENT_LAUNCH
 #define STK_DEPENDENT_LAUNCH 1
 #endif
 constexpr bool kUseDependentLaunch = STK_DEPENDENT_LAUNCH != 0;
 constexpr int kPSmemBytes =
-    kPStages * kStageBytes + 2 * kOutStageBytes + kPNumBars * 8 + kPStages * 4 + 32 + kPSched * 4 + 8 + 1024;
+    kPStages * kStageBytes + 2 * kOutStageBytes + kPNumBars * 8 + kPStages * 4 + 32 + 1024;
 constexpr int kNoBlock = 0x7fffffff;
 
 enum : uint32_t { kFlagFirst = 1u, kFlagLast = 2u, kFlagEnd = 4u };
@@ -74,7 +73,7 @@ struct PairParams {
   long long ldc;
   const void* aux;  // SDD with kEpilogueGeluKeep / kEpilogueGeluGrad: the auxiliary tensor
   const int32_t* plan;  // work-item table written by pair_plan_kernel (plan_sm100.cuh), or nullptr
-  unsigned int* ticket; // dynamic schedule: a counter that is 0 at launch (see ItemFeed), or nullptr
+  int band;             // groups per band of the item order (see decode_item); >= 1
 };
 
 // Two-pointer merge of the K lists of a pair of block rows (DSD) / block columns (DDS).
@@ -210,15 +209,22 @@ __device__ __forceinline__ void load_operand_pair(const CUtensorMap* tm, uint32_
 struct PairItem {
   int r, part, inner;  // first list of the group, 0 = lists r and r + 1 / 1 = list r alone, dense supertile
 };
-// Item order: item = group * inner + inner position, the inner position (dense supertile of a
-// DSD / DDS group, column segment of an SDD row group) running fastest, dealt round-robin to the CTA
-// pairs.  (Taking the groups in L2-sized bands with the group running fastest inside a band was
-// measured too: DRAM traffic did not drop - pairs that share an operand tile drift apart in time, and
-// the re-reads come from that, not from the footprint of one wave.)
-__device__ __forceinline__ PairItem decode_item(const PairParams& p, int item) {
+// Item order.  An item is (group of lists, inner position): the dense supertile of a DSD / DDS group
+// or the column segment of an SDD row group.  The items running at one time should share operands
+// that then stay in the L2: with the inner position running fastest, 74 CTA pairs cover a few groups
+// times ALL inner positions, i.e. one operand's whole expert slice (117 MB on the dMoE-XL shape), and
+// every wave streams it from DRAM again (measured 5x the compulsory reads).  The groups are therefore
+// taken in bands of `band` groups - as many as keep the band's own operand rows within a share of the
+// L2 - and inside a band the GROUP runs fastest: the pairs running at one time hold one band's rows
+// (resident in the L2 across the band) times a few inner positions (each fetched once per band).
+__device__ __forceinline__ PairItem decode_item(const PairParams& p, int item, int num_groups) {
   PairItem it;
-  const int g = item / p.inner;
-  it.inner = item - g * p.inner;
+  const int per_band = p.band * p.inner;
+  const int band = item / per_band, rem = item - band * per_band;
+  const int first = band * p.band;
+  const int here = min(p.band, num_groups - first);
+  it.inner = rem / here;
+  const int g = first + (rem - it.inner * here);
   if (p.plan != nullptr) {
     const int e = __ldg(p.plan + 1 + g);
     it.r = e & 0x3fffffff;
@@ -229,68 +235,6 @@ __device__ __forceinline__ PairItem decode_item(const PairParams& p, int item) {
   }
   return it;
 }
-
-// Where a role gets its work items from.
-//
-// Static schedule (no ticket counter): pair q takes items q, q + pairs, q + 2 pairs, ...
-//
-// Dynamic schedule: the A producer of the pair's leader CTA draws the next item from a global ticket
-// counter whenever the pair is ready for one and hands it to the other roles of both CTAs through a
-// small ring in shared memory: slot s holds an item, `ready[s]` (one arrival: the writer's, local or
-// remote) says it is there, `taken[s]` (in the leader; seven arrivals: the B producer and the two
-// epilogue groups of the leader, both producers and the two epilogue groups of its peer) says every
-// role has read it.  A pair that finishes early simply draws again, so the pairs stay balanced
-// whatever the items cost, and the items in flight at any time are consecutive ones - which share
-// operands - started within a short time of each other.  Every pair draws exactly one ticket past the
-// end; the pair that draws the very last one resets the counter for the next launch.
-struct ItemFeed {
-  bool dynamic, writer;
-  int next_static, num_pairs, num_items;
-  int slot;
-  uint32_t phase;
-  uint32_t ready0, taken0_leader;      // barrier addresses: own `ready`, the leader's `taken` (cluster-mapped)
-  uint32_t taken0_local;               // writer only: the same `taken` barriers as a local address
-  uint32_t peer_ready0, peer_items;    // writer only: the peer CTA's `ready` barriers and item slots
-  volatile int* items;                 // own ring
-  unsigned int* ticket;
-  volatile int* abort_flag;
-
-  __device__ __forceinline__ void advance() {
-    if (++slot == kPSched) {
-      slot = 0;
-      phase ^= 1u;
-    }
-  }
-  // Reader side: the next item, or -1 at the end.  In a role of several threads all of them call
-  // peek(), then ONE calls done() once all have read (a single-thread role calls both).
-  __device__ __forceinline__ int peek() {
-    if (!dynamic) return next_static < num_items ? next_static : -1;
-    if (!mbar_wait_cluster(ready0 + 8u * slot, phase, abort_flag)) return -1;
-    return items[slot];
-  }
-  __device__ __forceinline__ void done(bool arrive) {
-    if (!dynamic) {
-      next_static += num_pairs;
-      return;
-    }
-    if (arrive) mbar_arrive_cluster(taken0_leader + 8u * slot);
-    advance();
-  }
-  // Writer side (one thread): draw a ticket and publish it in both CTAs; returns the item or -1.
-  __device__ __forceinline__ int publish() {
-    if (!mbar_wait_cluster(taken0_local + 8u * slot, phase ^ 1u, abort_flag)) return -1;
-    const unsigned int t = atomicAdd(ticket, 1u);
-    const unsigned int total = static_cast<unsigned int>(num_items) + static_cast<unsigned int>(num_pairs);
-    if (t + 1u == total) atomicExch(ticket, 0u);   // the last ticket of the launch: ready for the next one
-    const int item = t < static_cast<unsigned int>(num_items) ? static_cast<int>(t) : -1;
-    items[slot] = item;
-    st_shared_cluster_u32(peer_items + 4u * slot, static_cast<uint32_t>(item));
-    mbar_arrive(ready0 + 8u * slot);
-    mbar_arrive_cluster(peer_ready0 + 8u * slot);
-    advance();
-    return item;
-  }
-};
 
 template <bool kTrain>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1)
@@ -309,14 +253,10 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   auto empty_bar = [&](int s) { return bars_base + 8u * (kPStages + s); };
   auto tfull_bar = [&](int a) { return bars_base + 8u * (2 * kPStages + a); };
   auto tempty_bar = [&](int a) { return bars_base + 8u * (2 * kPStages + 2 + a); };
-  auto ready_bar = [&](int s) { return bars_base + 8u * (2 * kPStages + 4 + s); };
-  auto taken_bar = [&](int s) { return bars_base + 8u * (2 * kPStages + 4 + kPSched + s); };
   volatile uint32_t* stage_flags = reinterpret_cast<volatile uint32_t*>(bars + kPNumBars);
   uint32_t* tmem_slot = const_cast<uint32_t*>(stage_flags) + kPStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* epilogue_go = abort_flag + 1;  // [2], one per epilogue group
-  volatile int* sched_items = epilogue_go + 2;  // [kPSched] work-item ring of the dynamic schedule
-  volatile int* sched_pick = sched_items + kPSched;  // [2] the item an epilogue group works on
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -332,10 +272,6 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);   // one multicast commit per tile
       mbar_init(tempty_bar(a), 2 * kPEpilogueWarps);  // leader's copy: the epilogue warps of both CTAs
-    }
-    for (int s = 0; s < kPSched; ++s) {
-      mbar_init(ready_bar(s), 1);  // the writer's arrival (remote for the peer CTA's copy)
-      mbar_init(taken_bar(s), 7);  // leader's copy: every reading role of both CTAs
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -358,23 +294,8 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // tail).
   pdl_launch_dependents();
   pdl_wait();
-  const int num_items = p.plan != nullptr ? __ldg(p.plan) * p.inner : p.num_items;
-  ItemFeed feed;
-  feed.dynamic = p.ticket != nullptr;
-  feed.writer = false;
-  feed.next_static = pair_id;
-  feed.num_pairs = num_pairs;
-  feed.num_items = num_items;
-  feed.slot = 0;
-  feed.phase = 0;
-  feed.ready0 = ready_bar(0);
-  feed.taken0_leader = map_to_cta(taken_bar(0), 0);
-  feed.taken0_local = taken_bar(0);
-  feed.peer_ready0 = map_to_cta(ready_bar(0), 1);
-  feed.peer_items = map_to_cta(smem_u32(const_cast<int*>(sched_items)), 1);
-  feed.items = sched_items;
-  feed.ticket = p.ticket;
-  feed.abort_flag = abort_flag;
+  const int num_groups = p.plan != nullptr ? __ldg(p.plan) : p.num_items / p.inner;
+  const int num_items = num_groups * p.inner;
 
   if (warp == 0 || warp == kPProducerBWarp) {
     // ------------------------------------------------------------------ TMA producers (both CTAs)
@@ -407,22 +328,9 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       };
       // Is this thread's operand the sparse one (DSD: A, DDS: B)?
       const bool sparse_side = (p.mode == kModeDSD) == is_a;
-      // The leader's A producer writes the dynamic schedule: it publishes one item ahead of the one it
-      // works on, so that the other roles never wait for it.
-      const bool publishes = feed.dynamic && arms;
-      int ahead = publishes ? feed.publish() : -1;
-      while (ok) {
-        int item;
-        if (publishes) {
-          item = ahead;
-          if (item >= 0) ahead = feed.publish();
-        } else {
-          item = feed.peek();
-          feed.done(true);
-        }
-        if (item < 0) break;
+      for (int item = pair_id; item < num_items && ok; item += num_pairs) {
         if (p.mode == kModeSDD) {
-          const PairItem it = decode_item(p, item);
+          const PairItem it = decode_item(p, item, num_groups);
           TileWalker w;
           w.init(p, it.r, it.inner, it.part);
           int u, blk[2][2];
@@ -433,7 +341,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                       (ks == 0 ? kFlagFirst : 0u) | (ks == p.k_steps - 1 ? kFlagLast : 0u));
           }
         } else {
-          const PairItem it = decode_item(p, item);
+          const PairItem it = decode_item(p, item, num_groups);
           MergeWalker w;
           w.init(p, it.r, it.part);
           uint32_t first = kFlagFirst;
@@ -552,24 +460,9 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (acc == 0) acc_phase ^= 1u;
     };
     uint16_t* out = static_cast<uint16_t*>(p.out);
-    while (ok) {
-      int item;
-      if (feed.dynamic) {
-        // one thread of the group waits for the slot; the group follows what it read (or gives up with it)
-        if (issuer) {
-          const int v = feed.peek();
-          sched_pick[group] = (*abort_flag != 0) ? -1 : v;
-        }
-        epilogue_sync(group);
-        item = sched_pick[group];
-        epilogue_sync(group);
-      } else {
-        item = feed.peek();
-      }
-      feed.done(issuer);
-      if (item < 0) break;
+    for (int item = pair_id; item < num_items && ok; item += num_pairs) {
       if (p.mode == kModeSDD) {
-        const PairItem it = decode_item(p, item);
+        const PairItem it = decode_item(p, item, num_groups);
         TileWalker w;
         w.init(p, it.r, it.inner, it.part);
         int u, blk[2][2];
@@ -588,7 +481,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           release();
         }
       } else {
-        const PairItem it = decode_item(p, item);
+        const PairItem it = decode_item(p, item, num_groups);
         MergeWalker w;
         w.init(p, it.r, it.part);
         // This CTA's 128 output rows and the 256 output columns of the supertile.  In a single-row
@@ -680,35 +573,11 @@ static int pair_device_info(PairDeviceInfo** out) {
   return STK_OK;
 }
 
-// Ticket counters of the dynamic schedule: zero between launches (the kernel resets the one it used),
-// one per launch in flight, handed out in turn.  A pair kernel occupies every SM, so no more than two
-// or three launches ever overlap on a device; 32 counters are never all in use.
-constexpr int kTicketSlots = 32;
-static __device__ unsigned int g_pair_tickets[kTicketSlots];
-
 static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
-                       const CUtensorMap& tmX, const PairParams& params, bool dynamic,
-                       cudaStream_t stream) {
+                       const CUtensorMap& tmX, const PairParams& p, cudaStream_t stream) {
   PairDeviceInfo* d = nullptr;
   const int rc = pair_device_info(&d);
   if (rc != STK_OK) return rc;
-  PairParams p = params;
-  p.ticket = nullptr;
-  if (dynamic) {
-    static unsigned int* base[64] = {};
-    static unsigned int turn[64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return STK_ERR_LAUNCH;
-    if (base[dev] == nullptr) {
-      void* ptr = nullptr;
-      if (cudaGetSymbolAddress(&ptr, g_pair_tickets) != cudaSuccess || ptr == nullptr) {
-        cudaGetLastError();
-        return STK_ERR_LAUNCH;
-      }
-      base[dev] = static_cast<unsigned int*>(ptr);
-    }
-    p.ticket = base[dev] + (__atomic_fetch_add(&turn[dev], 1u, __ATOMIC_RELAXED) % kTicketSlots);
-  }
   const int pairs = p.num_items < d->max_pairs ? p.num_items : d->max_pairs;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));

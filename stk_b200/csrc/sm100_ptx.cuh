@@ -86,38 +86,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
-// The same bounded wait with cluster-scope acquire: the data guarded by the barrier was written by a
-// thread of the OTHER CTA of the cluster (a store into this CTA's shared memory followed by a remote
-// arrive with release at cluster scope).
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-#pragma unroll 1
-  for (int i = 0; i < 4096; ++i)
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  uint32_t spins = 0;
-  while (true) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    if ((++spins & 63u) == 0u) {
-      if (*abort_flag != 0) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
-        *abort_flag = 1;
-        return false;
-      }
-    }
-  }
-}
-
 // ---------------------------------------------------------------- programmatic dependent launch
 // A kernel launched with the programmatic-stream-serialization attribute may start while the kernel
 // before it in the stream still runs; it must not touch global memory before pdl_wait(), which
@@ -269,10 +237,6 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
                : "memory");
-}
-// 32-bit store into the shared memory of another CTA of the cluster (cluster-mapped address).
-__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t value) {
-  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(value) : "memory");
 }
 // TMA load into this CTA's shared memory whose completion bytes are counted on a barrier of the
 // pair's leader CTA (cluster-mapped address).  No multicast: each CTA fetches its own tile.

@@ -94,7 +94,7 @@ def test_ops_under_autocast(stk, op):
         assert leaf.grad is not None and leaf.grad.dtype == torch.float32 and leaf.grad.shape == leaf.shape
 
 
-@pytest.mark.parametrize("mode", ["auto", "1", "2"])
+@pytest.mark.parametrize("mode", ["auto", "1"])
 def test_external_transposed_metadata_in_reference_tie_order(stk, golden, mode):
     """A Matrix built from all seven fields as the reference produces them: its unstable argsort leaves
     the rows inside a block column unordered (stk/matrix.py:110; fixture sq205).  The products through
@@ -226,7 +226,7 @@ def _as_int32(stk, m):
     return stk.Matrix(m.size(), m.data, i32(m.row_indices), i32(m.column_indices), m.offsets)
 
 
-@pytest.mark.parametrize("mode", ["0", "1", "2", "3", "auto"])
+@pytest.mark.parametrize("mode", ["0", "1", "3", "auto"])
 def test_int32_block_indices_give_identical_results(stk, mode):
     """The same topology with int32 instead of int16 block indices: transposed metadata equal value for
     value, every product bit-identical, conversions bit-identical (the reference leaves the index
