@@ -77,8 +77,7 @@ def _product_line(name, flops, fn, dense_fn, all_modes):
     """One product against its same-FLOP dense GEMM; all_modes adds the three forced kernels."""
     fns = {"auto": _with_mode("auto", fn), "cublas": dense_fn}
     if all_modes:
-        fns.update({"tile128": _with_mode("0", fn), "row256": _with_mode("3", fn), "pair256": _with_mode("1", fn),
-                    "pair256dyn": _with_mode("2", fn)})
+        fns.update({"tile128": _with_mode("0", fn), "row256": _with_mode("3", fn), "pair256": _with_mode("1", fn)})
     fn()                                   # settles the kernel choice of an unknown topology
     torch.cuda.synchronize()
     fn()
@@ -87,18 +86,18 @@ def _product_line(name, flops, fn, dense_fn, all_modes):
     line = {"product": name, "tflops": tf(ms["auto"]), "us": round(ms["auto"] * 1e3, 1),
             "cublas_tflops": tf(ms["cublas"]), "vs_cublas": round(ms["cublas"] / ms["auto"], 3)}
     if all_modes:
-        line.update({k: tf(ms[k]) for k in ("tile128", "row256", "pair256", "pair256dyn")})
+        line.update({k: tf(ms[k]) for k in ("tile128", "row256", "pair256")})
     return line
 
 
 def _print_table(title, lines):
     print(title)
     modes = "tile128" in lines[0]
-    head = "| product | " + ("128x128 | 128x256 | pair | pair, dynamic | " if modes else "") + "auto TFLOP/s | auto us | cuBLAS TFLOP/s | auto / cuBLAS |"
+    head = "| product | " + ("128x128 | 128x256 | pair | " if modes else "") + "auto TFLOP/s | auto us | cuBLAS TFLOP/s | auto / cuBLAS |"
     print(head)
     print("|" + "---|" * (head.count("|") - 1))
     for ln in lines:
-        mid = f"{ln['tile128']:.0f} | {ln['row256']:.0f} | {ln['pair256']:.0f} | {ln['pair256dyn']:.0f} | " if modes else ""
+        mid = f"{ln['tile128']:.0f} | {ln['row256']:.0f} | {ln['pair256']:.0f} | " if modes else ""
         print(f"| {ln['product']} | {mid}{ln['tflops']:.0f} | {ln['us']:.1f} | {ln['cublas_tflops']:.0f} | {ln['vs_cublas']:.2f} |",
               flush=True)
 
