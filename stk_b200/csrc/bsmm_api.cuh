@@ -20,15 +20,6 @@ static int check_dtype_dims(int dtype, int64_t M, int64_t N, int64_t K, int64_t 
 
 // Lists (block rows / columns) per tile-order group of the row kernel: as many as keep the group's
 // sparse blocks (32 KiB each) within a share of the L2 that leaves room for the dense panels in use.
-// Groups (pairs of lists) per band of the pair kernel's item order: as many as keep the band's own
-// operand - `bytes_per_group` of dense rows (SDD) or sparse blocks (DSD / DDS) - within 64 MiB, half the L2.
-static int pair_band(int64_t bytes_per_group) {
-  int64_t g = (64ll << 20) / (bytes_per_group > 0 ? bytes_per_group : 1);
-  if (g < 1) g = 1;
-  if (g > (1 << 20)) g = 1 << 20;
-  return static_cast<int>(g);
-}
-
 static int row_raster_group(int64_t nnz, int64_t num_lists) {
   const int64_t budget_blocks = (48ll << 20) / (kBlk * kBlk * 2);
   const int64_t per_list = (nnz + num_lists - 1) / num_lists;
@@ -131,7 +122,6 @@ static int sdd_impl(const void* lhs, const void* rhs, void* out, const int32_t* 
     p.ldc = kBlk;
     p.aux = aux;
     p.plan = pair_plan;
-    p.band = pair_band(2 * kBlk * K * 2);  // a row group's lhs panel
     return launch_pair(tmA, tmB, tmC, tmX, p, s);
   }
 
@@ -213,7 +203,6 @@ static int dsd_impl(const void* data, const int32_t* offsets, IndexArray column_
     p.out = out;
     p.ldc = ld_out;
     p.plan = pair_plan;
-    p.band = pair_band(2 * ((nnz + p.num_lists - 1) / p.num_lists) * kBlk * kBlk * 2);  // a group's blocks
     return launch_pair(tmA, tmB, tmC, tmC, p, s);
   }
 
@@ -292,7 +281,6 @@ static int dds_impl(const void* lhs, const void* data, const int32_t* offsets, I
     p.out = out;
     p.ldc = ld_out;
     p.plan = pair_plan;
-    p.band = pair_band(2 * ((nnz + p.num_lists - 1) / p.num_lists) * kBlk * kBlk * 2);  // a group's blocks
     return launch_pair(tmA, tmB, tmC, tmC, p, s);
   }
 

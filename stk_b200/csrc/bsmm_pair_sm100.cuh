@@ -73,7 +73,6 @@ struct PairParams {
   long long ldc;
   const void* aux;  // SDD with kEpilogueGeluKeep / kEpilogueGeluGrad: the auxiliary tensor
   const int32_t* plan;  // work-item table written by pair_plan_kernel (plan_sm100.cuh), or nullptr
-  int band;             // groups per band of the item order (see decode_item); >= 1
 };
 
 // Two-pointer merge of the K lists of a pair of block rows (DSD) / block columns (DDS).
@@ -209,22 +208,13 @@ __device__ __forceinline__ void load_operand_pair(const CUtensorMap* tm, uint32_
 struct PairItem {
   int r, part, inner;  // first list of the group, 0 = lists r and r + 1 / 1 = list r alone, dense supertile
 };
-// Item order.  An item is (group of lists, inner position): the dense supertile of a DSD / DDS group
-// or the column segment of an SDD row group.  The items running at one time should share operands
-// that then stay in the L2: with the inner position running fastest, 74 CTA pairs cover a few groups
-// times ALL inner positions, i.e. one operand's whole expert slice (117 MB on the dMoE-XL shape), and
-// every wave streams it from DRAM again (measured 5x the compulsory reads).  The groups are therefore
-// taken in bands of `band` groups - as many as keep the band's own operand rows within a share of the
-// L2 - and inside a band the GROUP runs fastest: the pairs running at one time hold one band's rows
-// (resident in the L2 across the band) times a few inner positions (each fetched once per band).
-__device__ __forceinline__ PairItem decode_item(const PairParams& p, int item, int num_groups) {
+// Item order: item = group * inner + inner position, the inner position (dense supertile of a
+// DSD / DDS group, column segment of an SDD row group) running fastest, dealt round-robin to the CTA
+// pairs.
+__device__ __forceinline__ PairItem decode_item(const PairParams& p, int item) {
   PairItem it;
-  const int per_band = p.band * p.inner;
-  const int band = item / per_band, rem = item - band * per_band;
-  const int first = band * p.band;
-  const int here = min(p.band, num_groups - first);
-  it.inner = rem / here;
-  const int g = first + (rem - it.inner * here);
+  const int g = item / p.inner;
+  it.inner = item - g * p.inner;
   if (p.plan != nullptr) {
     const int e = __ldg(p.plan + 1 + g);
     it.r = e & 0x3fffffff;
@@ -294,8 +284,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // tail).
   pdl_launch_dependents();
   pdl_wait();
-  const int num_groups = p.plan != nullptr ? __ldg(p.plan) : p.num_items / p.inner;
-  const int num_items = num_groups * p.inner;
+  const int num_items = p.plan != nullptr ? __ldg(p.plan) * p.inner : p.num_items;
 
   if (warp == 0 || warp == kPProducerBWarp) {
     // ------------------------------------------------------------------ TMA producers (both CTAs)
@@ -330,7 +319,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const bool sparse_side = (p.mode == kModeDSD) == is_a;
       for (int item = pair_id; item < num_items && ok; item += num_pairs) {
         if (p.mode == kModeSDD) {
-          const PairItem it = decode_item(p, item, num_groups);
+          const PairItem it = decode_item(p, item);
           TileWalker w;
           w.init(p, it.r, it.inner, it.part);
           int u, blk[2][2];
@@ -341,7 +330,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                       (ks == 0 ? kFlagFirst : 0u) | (ks == p.k_steps - 1 ? kFlagLast : 0u));
           }
         } else {
-          const PairItem it = decode_item(p, item, num_groups);
+          const PairItem it = decode_item(p, item);
           MergeWalker w;
           w.init(p, it.r, it.part);
           uint32_t first = kFlagFirst;
@@ -462,7 +451,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint16_t* out = static_cast<uint16_t*>(p.out);
     for (int item = pair_id; item < num_items && ok; item += num_pairs) {
       if (p.mode == kModeSDD) {
-        const PairItem it = decode_item(p, item, num_groups);
+        const PairItem it = decode_item(p, item);
         TileWalker w;
         w.init(p, it.r, it.inner, it.part);
         int u, blk[2][2];
@@ -481,7 +470,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           release();
         }
       } else {
-        const PairItem it = decode_item(p, item, num_groups);
+        const PairItem it = decode_item(p, item);
         MergeWalker w;
         w.init(p, it.r, it.part);
         // This CTA's 128 output rows and the 256 output columns of the supertile.  In a single-row
