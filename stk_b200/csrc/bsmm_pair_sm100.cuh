@@ -73,6 +73,7 @@ struct PairParams {
   long long ldc;
   const void* aux;  // SDD with kEpilogueGeluKeep / kEpilogueGeluGrad: the auxiliary tensor
   const int32_t* plan;  // work-item table written by pair_plan_kernel (plan_sm100.cuh), or nullptr
+  unsigned int* pace;   // counter of finished items that keeps the CTA pairs in step (see pace_gate), or nullptr
 };
 
 // Two-pointer merge of the K lists of a pair of block rows (DSD) / block columns (DDS).
@@ -226,6 +227,32 @@ __device__ __forceinline__ PairItem decode_item(const PairParams& p, int item) {
   return it;
 }
 
+// Keeping the CTA pairs in step.  The items are dealt round-robin, so in round k the 74 pairs work on 74
+// consecutive items, which share operand tiles (the supertiles of one row group share its sparse
+// blocks, the same supertile of neighbouring groups shares the dense panel).  A shared tile comes out
+// of the L2 for every pair after the first only while the pairs stay within the L2's turnover time of
+// each other (~20 us at the fill rate of these kernels); left alone they drift apart by a few per
+// cent per round (SMs differ in their distance to the L2 slices) and most sharing is lost - measured:
+// 4x the compulsory DRAM reads.  So the leader's A producer counts finished items in a global counter
+// and starts its k-th item only when (almost) all pairs have finished k items - a barrier with slack
+// and a short time limit, never a hard wait: a pair that would wait longer goes on (pairs that were
+// scheduled late, behind the tail of the previous kernel, are caught up with a few microseconds per
+// round).  The static schedule ends with its slowest pair anyway, so the waiting costs no time.  The
+// pair that finishes the very last item resets the counter for the next launch.
+#ifndef STK_PACE_PAIRS
+#define STK_PACE_PAIRS 1
+#endif
+constexpr bool kPacePairs = STK_PACE_PAIRS != 0;
+constexpr unsigned int kPaceSlack = 3;          // pairs that may still be busy when a round starts
+constexpr unsigned long long kPaceLimitNs = 12000;
+__device__ __forceinline__ void pace_gate(const unsigned int* pace, unsigned int target) {
+  const unsigned long long t0 = globaltimer_ns();
+  while (*reinterpret_cast<const volatile unsigned int*>(pace) < target) {
+    if (globaltimer_ns() - t0 > kPaceLimitNs) return;
+    __nanosleep(100);
+  }
+}
+
 template <bool kTrain>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1)
 bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -317,7 +344,11 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       };
       // Is this thread's operand the sparse one (DSD: A, DDS: B)?
       const bool sparse_side = (p.mode == kModeDSD) == is_a;
-      for (int item = pair_id; item < num_items && ok; item += num_pairs) {
+      const bool paced = arms && p.pace != nullptr;  // this thread keeps the pair in step with the others
+      unsigned int round = 0;
+      for (int item = pair_id; item < num_items && ok; item += num_pairs, ++round) {
+        if (paced && round > 0 && round * static_cast<unsigned int>(num_pairs) > kPaceSlack)
+          pace_gate(p.pace, round * static_cast<unsigned int>(num_pairs) - kPaceSlack);
         if (p.mode == kModeSDD) {
           const PairItem it = decode_item(p, item);
           TileWalker w;
@@ -353,6 +384,10 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (ok) produce(mn_elem, k_elem + kBK, last);
             first = 0u;
           }
+        }
+        if (paced) {
+          const unsigned int done = atomicAdd(p.pace, 1u) + 1u;
+          if (done == static_cast<unsigned int>(num_items)) atomicExch(p.pace, 0u);  // ready for the next launch
         }
       }
       // The leader tells its MMA issuer that the stream is over.
@@ -562,11 +597,34 @@ static int pair_device_info(PairDeviceInfo** out) {
   return STK_OK;
 }
 
+// Pace counters: zero between launches (the kernel resets the one it used), one per launch in flight,
+// handed out in turn.  A pair kernel occupies every SM, so no more than two or three launches ever
+// overlap on a device; 32 counters are never all in use.
+constexpr int kPaceSlots = 32;
+static __device__ unsigned int g_pair_pace[kPaceSlots];
+
 static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
-                       const CUtensorMap& tmX, const PairParams& p, cudaStream_t stream) {
+                       const CUtensorMap& tmX, const PairParams& params, cudaStream_t stream) {
   PairDeviceInfo* d = nullptr;
   const int rc = pair_device_info(&d);
   if (rc != STK_OK) return rc;
+  PairParams p = params;
+  p.pace = nullptr;
+  if (kPacePairs) {
+    static unsigned int* base[64] = {};
+    static unsigned int turn[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return STK_ERR_LAUNCH;
+    if (base[dev] == nullptr) {
+      void* ptr = nullptr;
+      if (cudaGetSymbolAddress(&ptr, g_pair_pace) != cudaSuccess || ptr == nullptr) {
+        cudaGetLastError();
+        return STK_ERR_LAUNCH;
+      }
+      base[dev] = static_cast<unsigned int*>(ptr);
+    }
+    p.pace = base[dev] + (__atomic_fetch_add(&turn[dev], 1u, __ATOMIC_RELAXED) % kPaceSlots);
+  }
   const int pairs = p.num_items < d->max_pairs ? p.num_items : d->max_pairs;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
