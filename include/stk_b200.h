@@ -74,9 +74,13 @@ int stk_b200_device_status(int* status_host);
  * 256 dense columns (dsd), 256 dense rows x one block column (dds, computed transposed), or two
  * blocks of one block row (sdd: blocks 2i and 2i+1 of the list; row_indices / column_indices in
  * row-major order).  Three quarters of mode 0's operand traffic for any topology, no pairing
- * needed - the choice for topologies that do not pair up.  Any other value is STK_ERR_BAD_DIMS.
- * All modes give the same results; mode 1 needs every block row's column_indices (and every block
- * column's column_indices_t) in ascending order.
+ * needed - the choice for topologies that do not pair up.  2 (dsd / dds; sdd treats it as 1) is mode 1
+ * with work items of 256x512 (dsd) / 512x256 (dds): every sparse tile is fetched once for two dense
+ * tiles and feeds both accumulators of tensor memory - a quarter less operand traffic per FLOP than
+ * mode 1, but the epilogue of an item no longer overlaps the next item's MMAs, so it pays when the
+ * block lists are long.  Any other value is STK_ERR_BAD_DIMS.
+ * All modes give the same results; modes 1 and 2 need every block row's column_indices (and every
+ * block column's column_indices_t) in ascending order, and take the same pair_plan.
  */
 
 /*
@@ -266,7 +270,10 @@ int stk_b200_to_dense(const void* data, const int32_t* offsets, const int16_t* c
  *   bin_rows[e] (optional) receives padded rows of expert e / block.  inverse (optional, as long as
  *   the largest index + 1): inverse[index[r]] = r for every row r that is not padding.
  * dmoe_topology: blocked CSR-COO metadata, row- and column-major, of the block-diagonal matrix in
- *   which expert e owns bin_rows[e] block rows and block columns [e*cpb, (e+1)*cpb).
+ *   which expert e owns bin_rows[e] block rows and block columns [e*cpb, (e+1)*cpb).  bin_rows lives on
+ *   the device, so its sum is checked there: bins that are negative or do not add up to block_rows
+ *   (the number the arrays were sized for) leave the arrays unwritten and record STK_ERR_BAD_DIMS in
+ *   the device status word.
  */
 int stk_b200_gather_rows(const void* src, void* dst, const int32_t* index, int64_t n_rows,
                          int64_t row_bytes, int index_div, void* stream);

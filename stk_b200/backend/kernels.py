@@ -17,10 +17,19 @@ from stk_b200.backend import lib as _lib
 BLOCK = 128  # the matmul kernels are built for 128x128 blocks
 
 # Which matmul kernel runs: "0" = one 128x128 tile per CTA, "1" = 256x256 supertiles on CTA pairs
-# wherever the metadata allows it, "3" = 128x256 tiles on one CTA (two blocks of a block row for SDD,
+# wherever the metadata allows it, "2" = the same with 256x512 items for DSD / DDS, "3" = 128x256 tiles on one CTA (two blocks of a block row for SDD,
 # one block row / column x 256 dense columns / rows for DSD / DDS), "auto" = per topology, from how
 # well neighbouring block rows / columns pair up (see pair_hints).
 PAIR_MODE = os.environ.get("STK_B200_PAIR_MODE", "auto")
+# DSD / DDS on CTA pairs come in two tile shapes: 256x256 (two accumulators alternate, so the epilogue
+# of one tile hides under the next tile's MMAs) and, mode "2", 256x512 (both accumulators belong to one
+# tile: a quarter less operand traffic per FLOP, but the epilogue is exposed), which pays once the
+# lists are long.  "auto" takes the wide shape from this many blocks per list on average.  Measured on
+# dMoE topologies (8 experts x 4096 rows, 4096 dense columns) in loops of a second or more, i.e. under
+# the power cap, wide against 256x256: 0.96 at 16 blocks per list, 0.99 - 1.02 at 32, 1.04 at 64, 1.06
+# at 112 (in bursts of a few launches, where nothing is power-limited: 0.91 at 8, 0.98 at 16, 0.98 - 1.02
+# from 32 on).
+WIDE_MIN_LIST_BLOCKS = int(os.environ.get("STK_B200_WIDE_MIN_LIST_BLOCKS", "48"))
 # DSD / DDS products that do not take the pair kernel run the 128x256 row kernel in these modes when
 # the dense operand has at least 256 columns (DSD) / rows (DDS); "3" never takes the pair kernel.
 ROW_KERNEL_MODES = ("3", "auto")
@@ -156,7 +165,7 @@ def _use_pairs(kind, offsets, row_indices, column_indices, block_cols, offsets_t
     """kind: "rows", "cols" or "tiles" - which neighbours the product would pair.  1 = pair kernel."""
     if PAIR_MODE in ("0", "3"):
         return 0
-    forced = PAIR_MODE == "1"
+    forced = PAIR_MODE in ("1", "2")
     hints = pair_hints(offsets, row_indices, column_indices, block_cols, offsets_t, column_indices_t,
                        need_t=kind == "cols", wait=forced)
     if hints is None:
@@ -169,6 +178,17 @@ def _use_pairs(kind, offsets, row_indices, column_indices, block_cols, offsets_t
     if forced:
         return 1
     return int({"rows": rows, "cols": cols, "tiles": tiles}[kind] >= PAIR_THRESHOLD[kind])
+
+
+def _pair_shape(pairs, nnz, num_lists, dense_extent):
+    """pair_mode of a DSD / DDS product that takes the pair kernel: 1 = 256x256 tiles, 2 = 256x512."""
+    if pairs != 1:
+        return pairs
+    if PAIR_MODE == "2":
+        return 2
+    if PAIR_MODE == "auto" and dense_extent >= 4 * BLOCK and nnz >= WIDE_MIN_LIST_BLOCKS * num_lists:
+        return 2
+    return 1
 
 
 def pair_plan(offsets, indices):
@@ -270,6 +290,7 @@ def dsd(shape, data, offsets, row_indices, column_indices, offsets_t, column_ind
     if pairs == 0 and N >= 2 * BLOCK and PAIR_MODE in ROW_KERNEL_MODES:
         pairs = 3            # one block row x 256 dense columns per CTA
     plan = pair_plan(meta[0], meta[1]) if pairs == 1 else None
+    pairs = _pair_shape(pairs, data.shape[0], M // BLOCK, N)
     with _lib.on_device(out.device):
         rc = _lib.entry("stk_b200_dsd", meta[1])(
             _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),
@@ -300,6 +321,7 @@ def dds(lhs, shape, data, offsets, row_indices, column_indices, offsets_t, colum
     if pairs == 0 and M >= 2 * BLOCK and PAIR_MODE in ROW_KERNEL_MODES:
         pairs = 3            # 256 dense rows x one block column per CTA
     plan = pair_plan(meta[0], meta[1]) if pairs == 1 else None
+    pairs = _pair_shape(pairs, data.shape[0], N // BLOCK, M)
     with _lib.on_device(out.device):
         rc = _lib.entry("stk_b200_dds", meta[1])(
             _lib.ptr(lhs), _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),

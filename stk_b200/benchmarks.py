@@ -74,10 +74,11 @@ def _with_mode(mode, fn):
 
 
 def _product_line(name, flops, fn, dense_fn, all_modes):
-    """One product against its same-FLOP dense GEMM; all_modes adds the three forced kernels."""
+    """One product against its same-FLOP dense GEMM; all_modes adds the four forced kernels."""
     fns = {"auto": _with_mode("auto", fn), "cublas": dense_fn}
     if all_modes:
-        fns.update({"tile128": _with_mode("0", fn), "row256": _with_mode("3", fn), "pair256": _with_mode("1", fn)})
+        fns.update({"tile128": _with_mode("0", fn), "row256": _with_mode("3", fn), "pair256": _with_mode("1", fn),
+                    "wide512": _with_mode("2", fn)})
     fn()                                   # settles the kernel choice of an unknown topology
     torch.cuda.synchronize()
     fn()
@@ -86,18 +87,18 @@ def _product_line(name, flops, fn, dense_fn, all_modes):
     line = {"product": name, "tflops": tf(ms["auto"]), "us": round(ms["auto"] * 1e3, 1),
             "cublas_tflops": tf(ms["cublas"]), "vs_cublas": round(ms["cublas"] / ms["auto"], 3)}
     if all_modes:
-        line.update({k: tf(ms[k]) for k in ("tile128", "row256", "pair256")})
+        line.update({k: tf(ms[k]) for k in ("tile128", "row256", "pair256", "wide512")})
     return line
 
 
 def _print_table(title, lines):
     print(title)
     modes = "tile128" in lines[0]
-    head = "| product | " + ("128x128 | 128x256 | pair | " if modes else "") + "auto TFLOP/s | auto us | cuBLAS TFLOP/s | auto / cuBLAS |"
+    head = "| product | " + ("128x128 | 128x256 | pair 256x256 | pair 256x512 (sdd: 256x256) | " if modes else "") + "auto TFLOP/s | auto us | cuBLAS TFLOP/s | auto / cuBLAS |"
     print(head)
     print("|" + "---|" * (head.count("|") - 1))
     for ln in lines:
-        mid = f"{ln['tile128']:.0f} | {ln['row256']:.0f} | {ln['pair256']:.0f} | " if modes else ""
+        mid = f"{ln['tile128']:.0f} | {ln['row256']:.0f} | {ln['pair256']:.0f} | {ln['wide512']:.0f} | " if modes else ""
         print(f"| {ln['product']} | {mid}{ln['tflops']:.0f} | {ln['us']:.1f} | {ln['cublas_tflops']:.0f} | {ln['vs_cublas']:.2f} |",
               flush=True)
 

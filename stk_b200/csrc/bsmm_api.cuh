@@ -2,6 +2,7 @@
 // the dispatch to the 128x128 kernel, the CTA-pair 256x256 kernel or the 128x256 row kernel.
 #pragma once
 #include "bsmm_pair_sm100.cuh"
+#include "bsmm_wide_sm100.cuh"
 #include "bsmm_row_sm100.cuh"
 #include "bsmm_sm100.cuh"
 
@@ -11,7 +12,7 @@ static int check_dtype_dims(int dtype, int64_t M, int64_t N, int64_t K, int64_t 
                             int pair_mode) {
   if (dtype != STK_F16 && dtype != STK_BF16) return STK_ERR_BAD_DTYPE;
   if (M <= 0 || N <= 0 || K <= 0 || nnz < 0 || M % kBlk || N % kBlk || K % k_mult) return STK_ERR_BAD_DIMS;
-  if (pair_mode != 0 && pair_mode != 1 && pair_mode != 3) return STK_ERR_BAD_DIMS;
+  if (pair_mode < 0 || pair_mode > 3) return STK_ERR_BAD_DIMS;
   if (nnz * kBlk > INT32_MAX - 2 * kBlk || M > INT32_MAX / 2 || N > INT32_MAX / 2 || K > INT32_MAX / 2 ||
       (M / kBlk) * (N / kBlk) > INT32_MAX)
     return STK_ERR_TOO_LARGE;
@@ -192,7 +193,9 @@ static int dsd_impl(const void* data, const int32_t* offsets, IndexArray column_
     p.b_mn = rhs_colmajor ? 0 : 1;
     p.fmt = dtype;
     p.num_lists = static_cast<int>(M / kBlk);
-    p.inner = static_cast<int>((N + 2 * kBlk - 1) / (2 * kBlk));  // 256 dense columns per work item
+    // dense columns per work item: 256, or 512 (two accumulators fed by one sparse tile)
+    const int64_t panel = pair_mode == 2 ? 4 * kBlk : 2 * kBlk;
+    p.inner = static_cast<int>((N + panel - 1) / panel);
     p.num_items = ((p.num_lists + 1) / 2) * p.inner;
     p.zero_coord = static_cast<int>(nnz * kBlk);
     p.out_rows = static_cast<int>(M);
@@ -203,7 +206,7 @@ static int dsd_impl(const void* data, const int32_t* offsets, IndexArray column_
     p.out = out;
     p.ldc = ld_out;
     p.plan = pair_plan;
-    return launch_pair(tmA, tmB, tmC, tmC, p, s);
+    return pair_mode == 2 ? launch_wide(tmA, tmB, p, s) : launch_pair(tmA, tmB, tmC, tmC, p, s);
   }
 
   BsmmParams p{};
@@ -270,7 +273,9 @@ static int dds_impl(const void* lhs, const void* data, const int32_t* offsets, I
     p.b_mn = trans_sparse ? 0 : 1;
     p.fmt = dtype;
     p.num_lists = static_cast<int>(N / kBlk);
-    p.inner = static_cast<int>((M + 2 * kBlk - 1) / (2 * kBlk));  // 256 dense rows per work item
+    // dense rows per work item: 256, or 512 (two accumulators fed by one sparse tile)
+    const int64_t panel = pair_mode == 2 ? 4 * kBlk : 2 * kBlk;
+    p.inner = static_cast<int>((M + panel - 1) / panel);
     p.num_items = ((p.num_lists + 1) / 2) * p.inner;
     p.zero_coord = static_cast<int>(nnz * kBlk);
     p.out_rows = static_cast<int>(M);
@@ -281,7 +286,7 @@ static int dds_impl(const void* lhs, const void* data, const int32_t* offsets, I
     p.out = out;
     p.ldc = ld_out;
     p.plan = pair_plan;
-    return launch_pair(tmA, tmB, tmC, tmC, p, s);
+    return pair_mode == 2 ? launch_wide(tmA, tmB, p, s) : launch_pair(tmA, tmB, tmC, tmC, p, s);
   }
 
   BsmmParams p{};

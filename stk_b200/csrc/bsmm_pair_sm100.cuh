@@ -220,6 +220,12 @@ __device__ __forceinline__ PairItem decode_item(const PairParams& p, int item) {
     const int e = __ldg(p.plan + 1 + g);
     it.r = e & 0x3fffffff;
     it.part = (e >> 30) & 1;
+    // a table that does not belong to this topology must not send anyone out of bounds
+    if (it.r + (it.part ? 0 : 1) >= p.num_lists) {
+      report_status(STK_ERR_BAD_DIMS);
+      it.r = p.num_lists - 1;
+      it.part = 1;
+    }
   } else {
     it.r = 2 * g;
     it.part = it.r + 1 >= p.num_lists ? 1 : 0;
@@ -603,28 +609,33 @@ static int pair_device_info(PairDeviceInfo** out) {
 constexpr int kPaceSlots = 32;
 static __device__ unsigned int g_pair_pace[kPaceSlots];
 
+// The counter of the next launch on the current device (nullptr when pacing is compiled out).
+static int next_pace_counter(unsigned int** out) {
+  *out = nullptr;
+  if (!kPacePairs) return STK_OK;
+  static unsigned int* base[64] = {};
+  static unsigned int turn[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return STK_ERR_LAUNCH;
+  if (base[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_pair_pace) != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();
+      return STK_ERR_LAUNCH;
+    }
+    base[dev] = static_cast<unsigned int*>(ptr);
+  }
+  *out = base[dev] + (__atomic_fetch_add(&turn[dev], 1u, __ATOMIC_RELAXED) % kPaceSlots);
+  return STK_OK;
+}
+
 static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                        const CUtensorMap& tmX, const PairParams& params, cudaStream_t stream) {
   PairDeviceInfo* d = nullptr;
-  const int rc = pair_device_info(&d);
+  int rc = pair_device_info(&d);
   if (rc != STK_OK) return rc;
   PairParams p = params;
-  p.pace = nullptr;
-  if (kPacePairs) {
-    static unsigned int* base[64] = {};
-    static unsigned int turn[64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return STK_ERR_LAUNCH;
-    if (base[dev] == nullptr) {
-      void* ptr = nullptr;
-      if (cudaGetSymbolAddress(&ptr, g_pair_pace) != cudaSuccess || ptr == nullptr) {
-        cudaGetLastError();
-        return STK_ERR_LAUNCH;
-      }
-      base[dev] = static_cast<unsigned int*>(ptr);
-    }
-    p.pace = base[dev] + (__atomic_fetch_add(&turn[dev], 1u, __ATOMIC_RELAXED) % kPaceSlots);
-  }
+  if ((rc = next_pace_counter(&p.pace)) != STK_OK) return rc;
   const int pairs = p.num_items < d->max_pairs ? p.num_items : d->max_pairs;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));

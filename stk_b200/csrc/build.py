@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 LIB_PATH = os.path.join(PKG, "libstk_b200.so")
 SOURCES = ["stk_b200.cu"]
-HEADERS = ["bsmm_sm100.cuh", "bsmm_pair_sm100.cuh", "bsmm_row_sm100.cuh", "bsmm_api.cuh", "meta_sm100.cuh", "plan_sm100.cuh", "index.cuh", "dmoe_sm100.cuh", "sm100_ptx.cuh", "status.cuh",
+HEADERS = ["bsmm_sm100.cuh", "bsmm_pair_sm100.cuh", "bsmm_wide_sm100.cuh", "bsmm_row_sm100.cuh", "bsmm_api.cuh", "meta_sm100.cuh", "plan_sm100.cuh", "index.cuh", "dmoe_sm100.cuh", "sm100_ptx.cuh", "status.cuh",
            os.path.join("..", "..", "include", "stk_b200.h")]
 
 

@@ -113,14 +113,26 @@ dmoe_topology_kernel(const int32_t* __restrict__ bin_rows, int experts, int cpb,
                      int32_t* __restrict__ block_offsets_t) {
   extern __shared__ int32_t row_start[];  // [experts + 1] first block row of every expert
   if (threadIdx.x == 0) {
-    int32_t run = 0;
+    int64_t run = 0;
+    bool bad = false;
     for (int e = 0; e < experts; ++e) {
-      row_start[e] = run;
-      run += bin_rows[e];
+      row_start[e] = static_cast<int32_t>(run);
+      bad |= bin_rows[e] < 0;
+      run += max(bin_rows[e], 0);
+      if (run > block_rows) {  // keeps the prefix inside int32 whatever the bins hold
+        bad = true;
+        run = block_rows;
+      }
     }
-    row_start[experts] = run;
+    // Every position written below is in range only if the bins add up to the block rows the
+    // arrays were sized for: anything else writes nothing and is reported.
+    row_start[experts] = (bad || run != block_rows) ? -1 : static_cast<int32_t>(run);
   }
   __syncthreads();
+  if (row_start[experts] < 0) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) report_status(STK_ERR_BAD_DIMS);
+    return;
+  }
   const int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   // column-major offsets: one entry per block column (plus the end), written by the first threads
   const int64_t block_cols = static_cast<int64_t>(experts) * cpb;

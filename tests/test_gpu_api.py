@@ -221,12 +221,30 @@ def test_transpose_skips_and_reports_bad_column_indices(stk):
         assert int(ot[-1]) == nnz - 2
 
 
+def test_topology_kernel_refuses_bins_that_do_not_add_up(stk):
+    """The dMoE topology kernel sizes nothing itself: bins that are negative or whose sum is not the
+    number of block rows the arrays were allocated for must leave the arrays untouched and record
+    STK_ERR_BAD_DIMS (they used to be trusted, and positions computed from them were written)."""
+    from stk_b200 import dmoe
+    from stk_b200.backend import lib
+    good = dmoe.topology_from_bins(torch.tensor([2, 0, 3], dtype=torch.int32, device="cuda"), 5, 256,
+                                   torch.float16, "cuda")
+    torch.cuda.synchronize()
+    assert lib.device_status() == 0
+    assert good.offsets_t.tolist() == [0, 2, 4, 4, 4, 7, 10]
+    for bins, block_rows in (([4096, 4096], 64), ([2, -1, 4], 5), ([1, 1, 1], 5)):
+        dmoe.topology_from_bins(torch.tensor(bins, dtype=torch.int32, device="cuda"), block_rows, 256,
+                                torch.float16, "cuda")
+        torch.cuda.synchronize()
+        assert lib.device_status() == -2
+
+
 def _as_int32(stk, m):
     i32 = lambda t: t.to(torch.int32)
     return stk.Matrix(m.size(), m.data, i32(m.row_indices), i32(m.column_indices), m.offsets)
 
 
-@pytest.mark.parametrize("mode", ["0", "1", "3", "auto"])
+@pytest.mark.parametrize("mode", ["0", "1", "2", "3", "auto"])
 def test_int32_block_indices_give_identical_results(stk, mode):
     """The same topology with int32 instead of int16 block indices: transposed metadata equal value for
     value, every product bit-identical, conversions bit-identical (the reference leaves the index

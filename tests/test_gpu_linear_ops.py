@@ -27,7 +27,7 @@ _IDS = [f"{m}x{k}x{n}-s{s}-{'t' if ta else 'n'}{'t' if tb else 'n'}-{str(dt)[6:]
         for m, k, n, s, ta, tb, dt in _CASES]
 
 
-@pytest.fixture(scope="module", params=["0", "1", "3"], ids=["tile128", "pair256", "row256"])
+@pytest.fixture(scope="module", params=["0", "1", "2", "3"], ids=["tile128", "pair256", "wide512", "row256"])
 def stk(request):
     """The package with the matmul kernel choice forced: one 128x128 tile per CTA, or 256x256
     supertiles on CTA pairs (both must give the same results on every topology)."""

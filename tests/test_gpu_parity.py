@@ -13,7 +13,7 @@ META_KEYS = ("row_indices", "column_indices", "offsets", "column_indices_t", "of
              "block_offsets_t")
 
 
-@pytest.fixture(scope="module", params=["0", "1", "3", "auto"], ids=["tile128", "pair256", "row256", "auto"])
+@pytest.fixture(scope="module", params=["0", "1", "2", "3", "auto"], ids=["tile128", "pair256", "wide512", "row256", "auto"])
 def stk(request):
     """The package with the matmul kernel choice forced (128x128 tiles per CTA / 256x256 supertiles
     on CTA pairs) or left to the per-topology heuristic."""

@@ -263,7 +263,7 @@ def test_autograd_wiring_matches_dense_calculus(monkeypatch):
 
 def test_products_reject_mixed_dtypes_and_unknown_kernel_modes():
     """float16 and bfloat16 operands in one product would be reinterpreted bit for bit: the launchers
-    refuse them before anything else (no GPU needed).  pair_mode values other than 0, 1, 3 are
+    refuse them before anything else (no GPU needed).  pair_mode values outside 0..3 are
     rejected by the C entry points."""
     from stk_b200.backend import kernels, lib
     h = lambda *shape: torch.zeros(*shape, dtype=torch.float16)
@@ -279,7 +279,7 @@ def test_products_reject_mixed_dtypes_and_unknown_kernel_modes():
         kernels.sdd(h(128, 128), b(128, 128), (128, 128), h(1, 128, 128), off, idx, idx)
     l = lib.load()
     null = ctypes.c_void_p(0)
-    assert l.stk_b200_sdd(null, null, null, null, null, null, 128, 128, 128, 1, 0, 128, 0, 128, 0, 2, 0, null, null, null) == -2
+    assert l.stk_b200_sdd(null, null, null, null, null, null, 128, 128, 128, 1, 0, 128, 0, 128, 0, 4, 0, null, null, null) == -2
     assert l.stk_b200_dsd(null, null, null, null, null, null, 128, 128, 128, 1, 0, 0, 128, 128, 0, 7, null, null) == -2
     assert l.stk_b200_pair_plan(null, null, 0, null, 0, null) == -2
     assert l.stk_b200_pair_plan(null, null, 4, null, 0, null) == -1
