@@ -35,7 +35,7 @@ TOKEN_BLOCK = 16384          # tokens are generated in blocks of this size, each
 METRIC = "nnz_block_tflops_dmoe_xl_fwd_sdd_dsd"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, recorded from an ncu capture of
 # `python bench.py --shrink 8 --kernels-only` (see profiles/); scaled by the blocks of the launch.
-NCU_DRAM_BYTES_PER_BLOCK = None
+NCU_DRAM_BYTES_PER_BLOCK = 155033   # (5.14 GB sdd+gelu + 3.89 GB dsd) / 2 launches / 29120 blocks
 
 
 def measured_peaks():
@@ -464,9 +464,9 @@ def run_ours(args):
         "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": peak_used,
                      "unit": "TFLOP/s", "frac": round(achieved / peak_used, 4),
                      "traffic": None if NCU_DRAM_BYTES_PER_BLOCK is None else NCU_DRAM_BYTES_PER_BLOCK * nnz_local,
-                     "traffic_unit": "DRAM bytes per launch, scaled from a recorded ncu capture of a smaller case",
+                     "traffic_unit": "DRAM bytes per launch (mean of the two), scaled by blocks from a recorded ncu capture of the 1/8 case",
                      "algorithmic_flops_per_launch": flops_product_local,
-                     "kernel": "bsmm_pair_kernel (sdd+gelu and dsd launches of rank 0)",
+                     "kernel": "bsmm_pair_kernel (sdd+gelu) and bsmm_wide_kernel (dsd): the two product launches of rank 0",
                      "peak_kind": peak_kind + (" bf16 sustained (launches of several ms run under the power cap)"
                                                if long_launch else " bf16 burst"),
                      "frac_of_burst_peak": round(achieved / peak_tflops, 4),

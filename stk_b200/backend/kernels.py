@@ -30,6 +30,18 @@ PAIR_MODE = os.environ.get("STK_B200_PAIR_MODE", "auto")
 # at 112 (in bursts of a few launches, where nothing is power-limited: 0.91 at 8, 0.98 at 16, 0.98 - 1.02
 # from 32 on).
 WIDE_MIN_LIST_BLOCKS = int(os.environ.get("STK_B200_WIDE_MIN_LIST_BLOCKS", "48"))
+# ... and only when the 256x512 items still come in at least this many rounds over the CTA pairs: half
+# as many, twice as long items leave a longer tail (BASELINE configs[2], Zipf-imbalanced, 2048 dense
+# columns: 524 wide items are 7.1 rounds of 74 and ran 7 % behind 1048 narrow ones).
+WIDE_MIN_ROUNDS = 8
+_PAIRS_RESIDENT = {}
+
+
+def _pairs_resident(device):
+    n = _PAIRS_RESIDENT.get(device)
+    if n is None:
+        n = _PAIRS_RESIDENT[device] = max(1, torch.cuda.get_device_properties(device).multi_processor_count // 2)
+    return n
 # DSD / DDS products that do not take the pair kernel run the 128x256 row kernel in these modes when
 # the dense operand has at least 256 columns (DSD) / rows (DDS); "3" never takes the pair kernel.
 ROW_KERNEL_MODES = ("3", "auto")
@@ -180,14 +192,16 @@ def _use_pairs(kind, offsets, row_indices, column_indices, block_cols, offsets_t
     return int({"rows": rows, "cols": cols, "tiles": tiles}[kind] >= PAIR_THRESHOLD[kind])
 
 
-def _pair_shape(pairs, nnz, num_lists, dense_extent):
+def _pair_shape(pairs, nnz, num_lists, dense_extent, device):
     """pair_mode of a DSD / DDS product that takes the pair kernel: 1 = 256x256 tiles, 2 = 256x512."""
     if pairs != 1:
         return pairs
     if PAIR_MODE == "2":
         return 2
-    if PAIR_MODE == "auto" and dense_extent >= 4 * BLOCK and nnz >= WIDE_MIN_LIST_BLOCKS * num_lists:
-        return 2
+    if PAIR_MODE == "auto" and nnz >= WIDE_MIN_LIST_BLOCKS * num_lists:
+        items = ((num_lists + 1) // 2) * ((dense_extent + 4 * BLOCK - 1) // (4 * BLOCK))
+        if items >= WIDE_MIN_ROUNDS * _pairs_resident(device):
+            return 2
     return 1
 
 
@@ -290,7 +304,7 @@ def dsd(shape, data, offsets, row_indices, column_indices, offsets_t, column_ind
     if pairs == 0 and N >= 2 * BLOCK and PAIR_MODE in ROW_KERNEL_MODES:
         pairs = 3            # one block row x 256 dense columns per CTA
     plan = pair_plan(meta[0], meta[1]) if pairs == 1 else None
-    pairs = _pair_shape(pairs, data.shape[0], M // BLOCK, N)
+    pairs = _pair_shape(pairs, data.shape[0], M // BLOCK, N, out.device)
     with _lib.on_device(out.device):
         rc = _lib.entry("stk_b200_dsd", meta[1])(
             _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),
@@ -321,7 +335,7 @@ def dds(lhs, shape, data, offsets, row_indices, column_indices, offsets_t, colum
     if pairs == 0 and M >= 2 * BLOCK and PAIR_MODE in ROW_KERNEL_MODES:
         pairs = 3            # 256 dense rows x one block column per CTA
     plan = pair_plan(meta[0], meta[1]) if pairs == 1 else None
-    pairs = _pair_shape(pairs, data.shape[0], N // BLOCK, M)
+    pairs = _pair_shape(pairs, data.shape[0], N // BLOCK, M, out.device)
     with _lib.on_device(out.device):
         rc = _lib.entry("stk_b200_dds", meta[1])(
             _lib.ptr(lhs), _lib.ptr(data), _lib.ptr(meta[0]), _lib.ptr(meta[1]), _lib.ptr(meta[2]),
