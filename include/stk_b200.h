@@ -35,6 +35,7 @@ extern "C" {
 /* element types of the matmul operands */
 #define STK_F16 0
 #define STK_BF16 1
+#define STK_F8E4M3 2   /* sdd / dsd / dds: 8-bit float operands (1 byte each), bf16 output; see below */
 
 /* epilogue of stk_b200_sdd */
 #define STK_EPILOGUE_NONE 0
@@ -81,6 +82,17 @@ int stk_b200_device_status(int* status_host);
  * block lists are long.  Any other value is STK_ERR_BAD_DIMS.
  * All modes give the same results; modes 1 and 2 need every block row's column_indices (and every
  * block column's column_indices_t) in ascending order, and take the same pair_plan.
+ *
+ * dtype (sdd / dsd / dds): STK_F16 or STK_BF16 - operands and output in that format - or STK_F8E4M3:
+ * every operand (lhs, rhs, the sparse values read by dsd / dds) is an 8-bit float, e4m3, one byte per
+ * element, and the output (the blocks written by sdd, the dense result of dsd / dds) is bf16; fp32
+ * accumulation as always, no scaling (a caller that quantised with scales applies their product to
+ * the result).  Not in the reference.  The 8-bit kernels (tcgen05.mma kind::f8f6f4, 128 of K per
+ * pipeline stage) read both operands with K contiguous, so only these layouts are accepted, anything
+ * else is STK_ERR_BAD_LAYOUT: sdd with lhs row-major and rhs column-major; dsd with trans_sparse = 0
+ * and rhs column-major; dds with lhs row-major and trans_sparse = 1.  Leading dimensions of 8-bit
+ * operands are multiples of 16 elements.  pair_mode 0, 1 and 2; 3 is STK_ERR_BAD_DTYPE, and
+ * so are the epilogues with an auxiliary tensor.
  */
 
 /*

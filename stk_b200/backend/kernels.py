@@ -274,13 +274,37 @@ def _check_blocks(data):
         raise DimensionError("sparse values must be contiguous")
 
 
+FP8 = torch.float8_e4m3fn
+
+
 def _same_dtype(what, *tensors):
     """The kernels read every operand with one element type; mixed float16 / bfloat16 operands would
-    be reinterpreted bit for bit."""
+    be reinterpreted bit for bit.  The last tensors are the outputs: with float8_e4m3fn operands (an
+    extension; fp32 accumulation as always) they are bfloat16."""
     dtypes = {t.dtype for t in tensors if t is not None}
+    if FP8 in dtypes:
+        if dtypes != {FP8, torch.bfloat16}:
+            raise ValueError(f"{what}: float8_e4m3fn operands go with each other and a bfloat16 output, got "
+                             + ", ".join(sorted(str(d) for d in dtypes)))
+        return
     if len(dtypes) > 1:
         raise ValueError(f"{what}: all operands and the output must share one dtype, got "
                          + ", ".join(sorted(str(d) for d in dtypes)))
+
+
+def _k_major(x, k_dim):
+    """(tensor, colmajor, ld) of a 2-D float8 operand with its K dimension (k_dim: 0 or 1) contiguous,
+    which is the only layout the 8-bit kernels read; anything else is copied once."""
+    if x.dim() != 2:
+        raise DimensionError(f"expected a 2-D dense operand, got {x.dim()}-D")
+    other = 1 - k_dim
+    ld = x.stride(other)
+    if not (x.stride(k_dim) == 1 and ld >= x.shape[k_dim] and ld % 16 == 0 and x.data_ptr() % 16 == 0):
+        x = x.contiguous() if k_dim == 1 else x.t().contiguous().t()
+        ld = x.stride(other)
+        if ld % 16 != 0:
+            raise DimensionError("float8 operands need a K extent that is a multiple of 16")
+    return x, (1 if k_dim == 0 else 0), ld
 
 
 def dsd(shape, data, offsets, row_indices, column_indices, offsets_t, column_indices_t,
@@ -294,14 +318,17 @@ def dsd(shape, data, offsets, row_indices, column_indices, offsets_t, column_ind
     N = rhs.shape[1]
     _validate_matmul_dims(M, K, N)
     _check_blocks(data)
-    rhs, rhs_colmajor, ld_rhs = _dense_layout(rhs)
+    fp8 = data.dtype == FP8
+    if fp8 and transpose_a:
+        raise ValueError("dsd with float8 blocks reads them as stored (their columns are K); transpose_a is not supported")
+    rhs, rhs_colmajor, ld_rhs = _k_major(rhs, 0) if fp8 else _dense_layout(rhs)
     if transpose_a:
         meta = (offsets_t, column_indices_t, block_offsets_t)
         pairs = _use_pairs("cols", offsets, row_indices, column_indices, M // BLOCK, offsets_t, column_indices_t)
     else:
         meta = (offsets, column_indices, None)
         pairs = _use_pairs("rows", offsets, row_indices, column_indices, K // BLOCK, offsets_t, column_indices_t)
-    if pairs == 0 and N >= 2 * BLOCK and PAIR_MODE in ROW_KERNEL_MODES:
+    if pairs == 0 and N >= 2 * BLOCK and PAIR_MODE in ROW_KERNEL_MODES and not fp8:
         pairs = 3            # one block row x 256 dense columns per CTA
     plan = pair_plan(meta[0], meta[1]) if pairs == 1 else None
     pairs = _pair_shape(pairs, data.shape[0], M // BLOCK, N, out.device)
@@ -325,14 +352,18 @@ def dds(lhs, shape, data, offsets, row_indices, column_indices, offsets_t, colum
     N = shape[1]
     _validate_matmul_dims(M, K, N)
     _check_blocks(data)
-    lhs, lhs_colmajor, ld_lhs = _dense_layout(lhs)
+    fp8 = data.dtype == FP8
+    if fp8 and not transpose_b:
+        raise ValueError("dds with float8 blocks reads them transposed (their columns are K): pass the sparse "
+                         "operand as a .t() view")
+    lhs, lhs_colmajor, ld_lhs = _k_major(lhs, 1) if fp8 else _dense_layout(lhs)
     if transpose_b:
         meta = (offsets, column_indices, None)
         pairs = _use_pairs("rows", offsets, row_indices, column_indices, K // BLOCK, offsets_t, column_indices_t)
     else:
         meta = (offsets_t, column_indices_t, block_offsets_t)
         pairs = _use_pairs("cols", offsets, row_indices, column_indices, N // BLOCK, offsets_t, column_indices_t)
-    if pairs == 0 and M >= 2 * BLOCK and PAIR_MODE in ROW_KERNEL_MODES:
+    if pairs == 0 and M >= 2 * BLOCK and PAIR_MODE in ROW_KERNEL_MODES and not fp8:
         pairs = 3            # 256 dense rows x one block column per CTA
     plan = pair_plan(meta[0], meta[1]) if pairs == 1 else None
     pairs = _pair_shape(pairs, data.shape[0], N // BLOCK, M, out.device)
@@ -363,17 +394,20 @@ def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices, epilogue=0, 
     N = rhs.shape[1]
     _validate_matmul_dims(M, K, N)
     _check_blocks(out)
-    lhs, lhs_colmajor, ld_lhs = _dense_layout(lhs)
-    rhs, rhs_colmajor, ld_rhs = _dense_layout(rhs)
+    fp8 = lhs.dtype == FP8
+    if fp8 and epilogue in (2, 3):
+        raise ValueError("the training epilogues are not available with float8 operands")
+    lhs, lhs_colmajor, ld_lhs = _k_major(lhs, 1) if fp8 else _dense_layout(lhs)
+    rhs, rhs_colmajor, ld_rhs = _k_major(rhs, 0) if fp8 else _dense_layout(rhs)
     pairs = _use_pairs("tiles", offsets, row_indices, column_indices, N // BLOCK)
-    if pairs == 0 and (PAIR_MODE == "3" or (PAIR_MODE == "auto" and out.shape[0] >= SDD_ROW_MIN_BLOCKS)):
+    if pairs == 0 and not fp8 and (PAIR_MODE == "3" or (PAIR_MODE == "auto" and out.shape[0] >= SDD_ROW_MIN_BLOCKS)):
         pairs = 3            # two blocks of a block row per 128x256 tile
     plan = pair_plan(offsets, column_indices) if pairs == 1 else None
     with _lib.on_device(out.device):
         rc = _lib.entry("stk_b200_sdd", column_indices)(
             _lib.ptr(lhs), _lib.ptr(rhs), _lib.ptr(out), _lib.ptr(offsets), _lib.ptr(row_indices),
             _lib.ptr(column_indices), M, N, K, out.shape[0], lhs_colmajor, ld_lhs, rhs_colmajor,
-            ld_rhs, _lib.dtype_code(out.dtype), pairs, epilogue, _lib.ptr(aux), _lib.ptr(plan),
+            ld_rhs, _lib.dtype_code(lhs.dtype), pairs, epilogue, _lib.ptr(aux), _lib.ptr(plan),
             _lib.stream_ptr(out.device))
     _lib.check(rc, "stk_b200_sdd")
 

@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(_PKG, "libstk_b200.so")
 
 STK_F16 = 0
 STK_BF16 = 1
+STK_F8E4M3 = 2
 
 _c_i64 = ctypes.c_int64
 _c_int = ctypes.c_int
@@ -167,4 +168,6 @@ def dtype_code(dtype):
         return STK_F16
     if dtype == torch.bfloat16:
         return STK_BF16
-    raise ValueError(f"stk_b200 matmuls support float16 and bfloat16 operands, got {dtype}")
+    if dtype == torch.float8_e4m3fn:
+        return STK_F8E4M3
+    raise ValueError(f"stk_b200 matmuls support float16, bfloat16 and float8_e4m3fn operands, got {dtype}")

@@ -10,7 +10,8 @@ namespace stk {
 
 static int check_dtype_dims(int dtype, int64_t M, int64_t N, int64_t K, int64_t nnz, int64_t k_mult,
                             int pair_mode) {
-  if (dtype != STK_F16 && dtype != STK_BF16) return STK_ERR_BAD_DTYPE;
+  if (dtype != STK_F16 && dtype != STK_BF16 && dtype != STK_F8E4M3) return STK_ERR_BAD_DTYPE;
+  if (dtype == STK_F8E4M3 && pair_mode == 3) return STK_ERR_BAD_DTYPE;  // the 128x256 kernels are 16-bit only
   if (M <= 0 || N <= 0 || K <= 0 || nnz < 0 || M % kBlk || N % kBlk || K % k_mult) return STK_ERR_BAD_DIMS;
   if (pair_mode < 0 || pair_mode > 3) return STK_ERR_BAD_DIMS;
   if (nnz * kBlk > INT32_MAX - 2 * kBlk || M > INT32_MAX / 2 || N > INT32_MAX / 2 || K > INT32_MAX / 2 ||
@@ -28,6 +29,13 @@ static int row_raster_group(int64_t nnz, int64_t num_lists) {
   if (g < 1) g = 1;
   if (g > num_lists) g = num_lists;
   return static_cast<int>(g);
+}
+
+// 8-bit float operands: one byte per element, so a 16-byte-aligned row needs a multiple of 16 elements.
+static int check_dense8(const void* ptr, int64_t ld, int64_t min_ld) {
+  if (ptr == nullptr) return STK_ERR_NULL_POINTER;
+  if (!aligned16(ptr) || ld < min_ld || (ld % 16) != 0) return STK_ERR_BAD_LAYOUT;
+  return STK_OK;
 }
 
 }  // namespace stk
@@ -49,20 +57,30 @@ static int sdd_impl(const void* lhs, const void* rhs, void* out, const int32_t* 
   if (out == nullptr || row_indices.null() || column_indices.null()) return STK_ERR_NULL_POINTER;
   if (pair_mode && pair_mode != 3 && offsets == nullptr) return STK_ERR_NULL_POINTER;
   if (!aligned16(out)) return STK_ERR_BAD_LAYOUT;
-  if ((rc = check_dense(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) return rc;
-  if ((rc = check_dense(rhs, ld_rhs, rhs_colmajor ? K : N)) != STK_OK) return rc;
+  const int in8 = dtype == STK_F8E4M3 ? 1 : 0;
+  const int out_fmt = in8 ? STK_BF16 : dtype;
+  if (in8) {
+    // both operands K-major: lhs row-major, rhs column-major; plain or GeLU epilogue
+    if (lhs_colmajor || !rhs_colmajor || has_aux) return STK_ERR_BAD_LAYOUT;
+    if ((rc = check_dense8(lhs, ld_lhs, K)) != STK_OK) return rc;
+    if ((rc = check_dense8(rhs, ld_rhs, K)) != STK_OK) return rc;
+  } else {
+    if ((rc = check_dense(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) return rc;
+    if ((rc = check_dense(rhs, ld_rhs, rhs_colmajor ? K : N)) != STK_OK) return rc;
+  }
 
   CUtensorMap tmA, tmB;
   // lhs [M,K]: row-major means K contiguous.
   if ((rc = encode_dense(&tmA, lhs, dtype, M, K, ld_lhs, !lhs_colmajor)) != STK_OK) return rc;
   // rhs [K,N]: row-major means N contiguous; column-major means K contiguous.
   if ((rc = encode_dense(&tmB, rhs, dtype, N, K, ld_rhs, rhs_colmajor)) != STK_OK) return rc;
-  const int k_steps = static_cast<int>((K + kBK - 1) / kBK);
+  const int stage_k = in8 ? 2 * kBK : kBK;
+  const int k_steps = static_cast<int>((K + stage_k - 1) / stage_k);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   CUtensorMap tmC;  // the output blocks as one [nnz*128, 128] matrix, stored 128 x 64 at a time
-  if ((rc = encode_map(&tmC, out, dtype, kBlk, nnz * kBlk, kBlk, kBlk)) != STK_OK) return rc;
+  if ((rc = encode_map(&tmC, out, out_fmt, kBlk, nnz * kBlk, kBlk, kBlk)) != STK_OK) return rc;
   CUtensorMap tmX = tmC;  // the auxiliary tensor has the layout of out
-  if (has_aux && (rc = encode_map(&tmX, aux, dtype, kBlk, nnz * kBlk, kBlk, kBlk)) != STK_OK) return rc;
+  if (has_aux && (rc = encode_map(&tmX, aux, out_fmt, kBlk, nnz * kBlk, kBlk, kBlk)) != STK_OK) return rc;
 
   if (pair_mode == 3) {  // two blocks of a block row per tile
     BsmmParams p{};
@@ -111,7 +129,8 @@ static int sdd_impl(const void* lhs, const void* rhs, void* out, const int32_t* 
     p.mode = kModeSDD;
     p.a_mn = lhs_colmajor ? 1 : 0;
     p.b_mn = rhs_colmajor ? 0 : 1;
-    p.fmt = dtype;
+    p.fmt = out_fmt;
+    p.in8 = in8;
     p.epilogue = epilogue;
     p.inner = segments;
     p.num_items = row_pairs * segments;
@@ -130,7 +149,8 @@ static int sdd_impl(const void* lhs, const void* rhs, void* out, const int32_t* 
   p.mode = kModeSDD;
   p.a_mn = lhs_colmajor ? 1 : 0;
   p.b_mn = rhs_colmajor ? 0 : 1;
-  p.fmt = dtype;
+  p.fmt = out_fmt;
+  p.in8 = in8;
   p.epilogue = epilogue;
   p.num_tiles = static_cast<int>(nnz);
   p.tiles_inner = 1;
@@ -159,7 +179,15 @@ static int dsd_impl(const void* data, const int32_t* offsets, IndexArray column_
   if (data == nullptr || offsets == nullptr || column_indices.null()) return STK_ERR_NULL_POINTER;
   if (trans_sparse && block_offsets == nullptr) return STK_ERR_NULL_POINTER;
   if (!aligned16(data)) return STK_ERR_BAD_LAYOUT;
-  if ((rc = check_dense(rhs, ld_rhs, rhs_colmajor ? K : N)) != STK_OK) return rc;
+  const int in8 = dtype == STK_F8E4M3 ? 1 : 0;
+  const int out_fmt = in8 ? STK_BF16 : dtype;
+  if (in8) {
+    // both operands K-major: the blocks as stored, rhs column-major
+    if (trans_sparse || !rhs_colmajor) return STK_ERR_BAD_LAYOUT;
+    if ((rc = check_dense8(rhs, ld_rhs, K)) != STK_OK) return rc;
+  } else if ((rc = check_dense(rhs, ld_rhs, rhs_colmajor ? K : N)) != STK_OK) {
+    return rc;
+  }
 
   CUtensorMap tmA, tmB;
   // A = data[blk] as stored (its columns are K) or transposed (its columns are M).
@@ -167,7 +195,7 @@ static int dsd_impl(const void* data, const int32_t* offsets, IndexArray column_
   if ((rc = encode_dense(&tmB, rhs, dtype, N, K, ld_rhs, rhs_colmajor)) != STK_OK) return rc;
 
   CUtensorMap tmC;
-  if ((rc = encode_map(&tmC, out, dtype, N, M, ld_out, kBlk)) != STK_OK) return rc;
+  if ((rc = encode_map(&tmC, out, out_fmt, N, M, ld_out, kBlk)) != STK_OK) return rc;
 
   if (pair_mode == 3) {  // one block row x 256 dense columns per CTA
     BsmmParams p{};
@@ -191,7 +219,8 @@ static int dsd_impl(const void* data, const int32_t* offsets, IndexArray column_
     p.mode = kModeDSD;
     p.a_mn = trans_sparse ? 1 : 0;
     p.b_mn = rhs_colmajor ? 0 : 1;
-    p.fmt = dtype;
+    p.fmt = out_fmt;
+    p.in8 = in8;
     p.num_lists = static_cast<int>(M / kBlk);
     // dense columns per work item: 256, or 512 (two accumulators fed by one sparse tile)
     const int64_t panel = pair_mode == 2 ? 4 * kBlk : 2 * kBlk;
@@ -213,7 +242,8 @@ static int dsd_impl(const void* data, const int32_t* offsets, IndexArray column_
   p.mode = kModeDSD;
   p.a_mn = trans_sparse ? 1 : 0;
   p.b_mn = rhs_colmajor ? 0 : 1;
-  p.fmt = dtype;
+  p.fmt = out_fmt;
+  p.in8 = in8;
   p.tiles_inner = static_cast<int>(N / kBlk);
   p.num_tiles = static_cast<int>((M / kBlk) * (N / kBlk));
   p.col_idx = column_indices;
@@ -239,7 +269,15 @@ static int dds_impl(const void* lhs, const void* data, const int32_t* offsets, I
   if (data == nullptr || offsets == nullptr || column_indices.null()) return STK_ERR_NULL_POINTER;
   if (!trans_sparse && block_offsets == nullptr) return STK_ERR_NULL_POINTER;
   if (!aligned16(data)) return STK_ERR_BAD_LAYOUT;
-  if ((rc = check_dense(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) return rc;
+  const int in8 = dtype == STK_F8E4M3 ? 1 : 0;
+  const int out_fmt = in8 ? STK_BF16 : dtype;
+  if (in8) {
+    // both operands K-major: lhs row-major, the blocks used transposed (their columns are K)
+    if (lhs_colmajor || !trans_sparse) return STK_ERR_BAD_LAYOUT;
+    if ((rc = check_dense8(lhs, ld_lhs, K)) != STK_OK) return rc;
+  } else if ((rc = check_dense(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) {
+    return rc;
+  }
 
   CUtensorMap tmA, tmB;
   if ((rc = encode_dense(&tmA, lhs, dtype, M, K, ld_lhs, !lhs_colmajor)) != STK_OK) return rc;
@@ -247,7 +285,7 @@ static int dds_impl(const void* lhs, const void* data, const int32_t* offsets, I
   if ((rc = encode_sparse(&tmB, data, dtype, nnz, trans_sparse)) != STK_OK) return rc;
 
   CUtensorMap tmC;
-  if ((rc = encode_map(&tmC, out, dtype, N, M, ld_out, kBlk)) != STK_OK) return rc;
+  if ((rc = encode_map(&tmC, out, out_fmt, N, M, ld_out, kBlk)) != STK_OK) return rc;
 
   if (pair_mode == 3) {  // 256 dense rows x one block column per CTA
     BsmmParams p{};
@@ -271,7 +309,8 @@ static int dds_impl(const void* lhs, const void* data, const int32_t* offsets, I
     p.mode = kModeDDS;
     p.a_mn = lhs_colmajor ? 1 : 0;
     p.b_mn = trans_sparse ? 0 : 1;
-    p.fmt = dtype;
+    p.fmt = out_fmt;
+    p.in8 = in8;
     p.num_lists = static_cast<int>(N / kBlk);
     // dense rows per work item: 256, or 512 (two accumulators fed by one sparse tile)
     const int64_t panel = pair_mode == 2 ? 4 * kBlk : 2 * kBlk;
@@ -293,7 +332,8 @@ static int dds_impl(const void* lhs, const void* data, const int32_t* offsets, I
   p.mode = kModeDDS;
   p.a_mn = lhs_colmajor ? 1 : 0;
   p.b_mn = trans_sparse ? 0 : 1;
-  p.fmt = dtype;
+  p.fmt = out_fmt;
+  p.in8 = in8;
   p.tiles_inner = static_cast<int>(M / kBlk);
   p.num_tiles = static_cast<int>((M / kBlk) * (N / kBlk));
   p.col_idx = column_indices;

@@ -59,6 +59,7 @@ enum : uint32_t { kFlagFirst = 1u, kFlagLast = 2u, kFlagEnd = 4u };
 struct PairParams {
   int mode;
   int a_mn, b_mn, fmt;
+  int in8;          // 1: 8-bit float operands (e4m3), both K-major; fmt then only names the output format
   int epilogue;     // kEpilogueNone / kEpilogueGelu
   int num_items;    // static work items, dealt round-robin to the CTA pairs
   int inner;        // DSD: N supertiles per row pair; DDS: M supertiles per column pair; SDD: segments per row pair
@@ -76,11 +77,24 @@ struct PairParams {
   unsigned int* pace;   // counter of finished items that keeps the CTA pairs in step (see pace_gate), or nullptr
 };
 
-// Two-pointer merge of the K lists of a pair of block rows (DSD) / block columns (DDS).
+// Two-pointer merge of the K lists of a pair of block rows (DSD) / block columns (DDS).  The heads of
+// both lists (column and data index) are held in registers and reloaded as soon as a list advances, so
+// that the loads of one step are in flight while the step before it waits for its pipeline stage:
+// with 8-bit operands a stage is a whole block and the walk runs once per stage.
 struct MergeWalker {
   IndexArray col;
   const int32_t* blk;
   int ia, a1, ib, b1;
+  int ca, cb;  // columns of the head blocks, kNoBlock for an exhausted list
+  int ba, bb;  // their indices into data
+  __device__ __forceinline__ void load_a() {
+    ca = ia < a1 ? col[ia] : kNoBlock;
+    ba = ia < a1 ? (blk ? __ldg(blk + ia) : ia) : kNoBlock;
+  }
+  __device__ __forceinline__ void load_b() {
+    cb = ib < b1 ? col[ib] : kNoBlock;
+    bb = ib < b1 ? (blk ? __ldg(blk + ib) : ib) : kNoBlock;
+  }
   // Lists la and la + 1 (part 0), or list la alone (part 1).
   __device__ __forceinline__ void init(const PairParams& p, int la, int part = 0) {
     col = p.col_idx;
@@ -94,21 +108,24 @@ struct MergeWalker {
     } else {
       ib = b1 = 0;
     }
+    load_a();
+    load_b();
   }
   __device__ __forceinline__ bool empty() const { return ia >= a1 && ib >= b1; }
   // Next K position; blk_a / blk_b = index into data of the block each list has there, or kNoBlock.
   __device__ __forceinline__ void next(int& kpos, int& blk_a, int& blk_b) {
-    const int ca = ia < a1 ? col[ia] : kNoBlock;
-    const int cb = ib < b1 ? col[ib] : kNoBlock;
     kpos = min(ca, cb);
     blk_a = blk_b = kNoBlock;
-    if (ca == kpos) {
-      blk_a = blk ? __ldg(blk + ia) : ia;
+    const bool take_a = ca == kpos, take_b = cb == kpos;
+    if (take_a) {
+      blk_a = ba;
       ++ia;
+      load_a();
     }
-    if (cb == kpos) {
-      blk_b = blk ? __ldg(blk + ib) : ib;
+    if (take_b) {
+      blk_b = bb;
       ++ib;
+      load_b();
     }
   }
 };
@@ -259,7 +276,8 @@ __device__ __forceinline__ void pace_gate(const unsigned int* pace, unsigned int
   }
 }
 
-template <bool kTrain>
+// kF8: 8-bit float operands (kind::f8f6f4); a stage then covers 128 of K, i.e. a whole sparse block.
+template <bool kTrain, bool kF8 = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1)
 bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX,
@@ -363,7 +381,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           while (ok && w.next(u, blk)) {
             const int mn_elem = ((is_a ? it.r : 2 * u) + rank) * kBlk;
             for (int ks = 0; ks < p.k_steps && ok; ++ks)
-              produce(mn_elem, ks * kBK,
+              produce(mn_elem, ks * (kF8 ? 2 * kBK : kBK),
                       (ks == 0 ? kFlagFirst : 0u) | (ks == p.k_steps - 1 ? kFlagLast : 0u));
           }
         } else {
@@ -386,8 +404,12 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               mn_elem = it.inner * 2 * kBlk + rank * kBlk;
               k_elem = kpos * kBlk;
             }
-            produce(mn_elem, k_elem, first);
-            if (ok) produce(mn_elem, k_elem + kBK, last);
+            if constexpr (kF8) {
+              produce(mn_elem, k_elem, first | last);  // one stage holds the block's whole K
+            } else {
+              produce(mn_elem, k_elem, first);
+              if (ok) produce(mn_elem, k_elem + kBK, last);
+            }
             first = 0u;
           }
         }
@@ -408,7 +430,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (rank == 0 && lane == 0) {
-      const uint32_t idesc = make_idesc_f16(p.fmt, p.a_mn, p.b_mn, 256, 256);
+      const uint32_t idesc = kF8 ? make_idesc_f8(256, 256) : make_idesc_f16(p.fmt, p.a_mn, p.b_mn, 256, 256);
       const uint32_t a_lo0 = smem_desc_lo(smem_base, p.a_mn ? kOperandTileBytes / 2 : 16u);
       const uint32_t b_lo0 = smem_desc_lo(smem_base + kOperandTileBytes, p.b_mn ? kOperandTileBytes / 2 : 16u);
       const uint32_t a_kstep = (p.a_mn ? kUmmaK * 128u : kUmmaK * 2u) >> 4;
@@ -440,12 +462,12 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint32_t b_lo = b_lo0 + stage * (kStageBytes >> 4);
         const int next_stage = stage + 1 == kPStages ? 0 : stage + 1;
         const uint32_t next_phase = stage + 1 == kPStages ? phase ^ 1u : phase;
-        umma_f16_pair(d_tmem, smem_desc_join(a_lo), smem_desc_join(b_lo), idesc, (flags & kFlagFirst) ? 0u : 1u);
-        umma_f16_pair(d_tmem, smem_desc_join(a_lo + a_kstep), smem_desc_join(b_lo + b_kstep), idesc, 1u);
+        umma_pair<kF8>(d_tmem, smem_desc_join(a_lo), smem_desc_join(b_lo), idesc, (flags & kFlagFirst) ? 0u : 1u);
+        umma_pair<kF8>(d_tmem, smem_desc_join(a_lo + a_kstep), smem_desc_join(b_lo + b_kstep), idesc, 1u);
         ready = mbar_test_wait(full_bar(next_stage), next_phase);
         const uint32_t next_flags = stage_flags[next_stage];  // not waited for here; only used if `ready`
-        umma_f16_pair(d_tmem, smem_desc_join(a_lo + 2 * a_kstep), smem_desc_join(b_lo + 2 * b_kstep), idesc, 1u);
-        umma_f16_pair(d_tmem, smem_desc_join(a_lo + 3 * a_kstep), smem_desc_join(b_lo + 3 * b_kstep), idesc, 1u);
+        umma_pair<kF8>(d_tmem, smem_desc_join(a_lo + 2 * a_kstep), smem_desc_join(b_lo + 2 * b_kstep), idesc, 1u);
+        umma_pair<kF8>(d_tmem, smem_desc_join(a_lo + 3 * a_kstep), smem_desc_join(b_lo + 3 * b_kstep), idesc, 1u);
         umma_commit_pair(empty_bar(stage), 3);  // frees the stage in both CTAs
         if (flags & kFlagLast) {
           umma_commit_pair(tfull_bar(acc), 3);  // accumulator halves ready in both CTAs
@@ -573,6 +595,8 @@ static int pair_device_info(PairDeviceInfo** out) {
     if (cudaFuncSetAttribute(bsmm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kPSmemBytes) != cudaSuccess ||
         cudaFuncSetAttribute(bsmm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kPSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(bsmm_pair_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kPSmemBytes) != cudaSuccess) {
       cudaGetLastError();
       return STK_ERR_LAUNCH;
@@ -647,9 +671,11 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = kUseDependentLaunch ? 1 : 0;
-  const cudaError_t err = p.epilogue >= kEpilogueGeluKeep
-                              ? cudaLaunchKernelEx(&cfg, bsmm_pair_kernel<true>, tmA, tmB, tmC, tmX, p)
-                              : cudaLaunchKernelEx(&cfg, bsmm_pair_kernel<false>, tmA, tmB, tmC, tmX, p);
+  if (p.in8 && (p.epilogue >= kEpilogueGeluKeep || p.a_mn || p.b_mn)) return STK_ERR_BAD_LAYOUT;
+  const cudaError_t err =
+      p.in8 ? cudaLaunchKernelEx(&cfg, bsmm_pair_kernel<false, true>, tmA, tmB, tmC, tmX, p)
+      : p.epilogue >= kEpilogueGeluKeep ? cudaLaunchKernelEx(&cfg, bsmm_pair_kernel<true>, tmA, tmB, tmC, tmX, p)
+                                        : cudaLaunchKernelEx(&cfg, bsmm_pair_kernel<false>, tmA, tmB, tmC, tmX, p);
   return err == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 

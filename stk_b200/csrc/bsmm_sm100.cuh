@@ -108,7 +108,8 @@ struct BsmmParams {
   int mode;
   int a_mn;        // 1: A tile is M-contiguous in memory (transposed operand), 0: K-contiguous
   int b_mn;        // 1: B tile is N-contiguous in memory, 0: K-contiguous
-  int fmt;         // STK_F16 / STK_BF16
+  int fmt;         // STK_F16 / STK_BF16: format of the 16-bit operands, and of the output always
+  int in8;         // 1: the operands are 8-bit floats (e4m3), both K-major; a stage then holds 128 of K
   int epilogue;    // kEpilogueNone / kEpilogueGelu
   int num_tiles;
   int tiles_inner; // DSD: number of N tiles (n runs fastest); DDS: number of M tiles (m runs fastest)
@@ -153,7 +154,7 @@ __device__ __forceinline__ TileInfo tile_info(const BsmmParams& p, int tile) {
       t.j0 = p.offsets[t.tn];
       t.j1 = p.offsets[t.tn + 1];
     }
-    t.nk = 2 * (t.j1 - t.j0);
+    t.nk = (p.in8 ? 1 : 2) * (t.j1 - t.j0);  // a block is 128 of K: two stages of 16-bit operands, one of 8-bit
   }
   return t;
 }
@@ -339,7 +340,10 @@ __device__ __forceinline__ void drain_to_output(uint32_t t_addr, int col0, int n
   }
 }
 
-template <bool kTrain>
+// kF8: the operands are 8-bit floats (tcgen05.mma kind::f8f6f4, 32 of K per instruction); the byte
+// geometry of a stage is the same (128 rows of 128 bytes per operand, four MMAs), only the K it covers
+// doubles.
+template <bool kTrain, bool kF8 = false>
 __global__ void __launch_bounds__(kThreads, 1)
 bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX,
@@ -414,11 +418,13 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         phase ^= 1u;
       }
     };
+    constexpr int kStageK = kF8 ? 2 * kBK : kBK;        // K elements per stage
+    constexpr int kStagesPerBlock = kBlk / kStageK;
     for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
       const TileInfo t = tile_info(p, tile);
       if (p.mode == kModeSDD) {
         for (int ks = 0; ks < t.nk && ok; ++ks)
-          produce(t.tm * kBlk, ks * kBK, t.tn * kBlk, ks * kBK);
+          produce(t.tm * kBlk, ks * kStageK, t.tn * kBlk, ks * kStageK);
       } else {
         for (int jb = t.j0; jb < t.j1 && ok; jb += 32) {
           // The warp fetches the metadata of up to 32 blocks at once, then replays it.
@@ -432,17 +438,17 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           for (int i = 0; i < cnt && ok; ++i) {
             const int col = __shfl_sync(0xffffffffu, my_col, i);
             const int blk = __shfl_sync(0xffffffffu, my_blk, i);
-            for (int ks = 0; ks < 2 && ok; ++ks) {
+            for (int ks = 0; ks < kStagesPerBlock && ok; ++ks) {
               if (p.mode == kModeDSD) {
                 // sparse A, dense B
                 const int a_mn_elem = p.a_mn ? 0 : blk * kBlk;
-                const int a_k_elem = p.a_mn ? blk * kBlk + ks * kBK : ks * kBK;
-                produce(a_mn_elem, a_k_elem, t.tn * kBlk, col * kBlk + ks * kBK);
+                const int a_k_elem = p.a_mn ? blk * kBlk + ks * kStageK : ks * kStageK;
+                produce(a_mn_elem, a_k_elem, t.tn * kBlk, col * kBlk + ks * kStageK);
               } else {
                 // dense A, sparse B
                 const int b_mn_elem = p.b_mn ? 0 : blk * kBlk;
-                const int b_k_elem = p.b_mn ? blk * kBlk + ks * kBK : ks * kBK;
-                produce(t.tm * kBlk, col * kBlk + ks * kBK, b_mn_elem, b_k_elem);
+                const int b_k_elem = p.b_mn ? blk * kBlk + ks * kStageK : ks * kStageK;
+                produce(t.tm * kBlk, col * kBlk + ks * kStageK, b_mn_elem, b_k_elem);
               }
             }
           }
@@ -452,7 +458,7 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_f16(p.fmt, p.a_mn, p.b_mn, kBlk);
+      const uint32_t idesc = kF8 ? make_idesc_f8(kBlk) : make_idesc_f16(p.fmt, p.a_mn, p.b_mn, kBlk);
       // Descriptor low words of stage 0 and their step per 16 elements of K and per stage.
       const uint32_t a_lo0 = smem_desc_lo(smem_base, p.a_mn ? kOperandTileBytes / 2 : 16u);
       const uint32_t b_lo0 = smem_desc_lo(smem_base + kOperandTileBytes, p.b_mn ? kOperandTileBytes / 2 : 16u);
@@ -488,11 +494,11 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const uint32_t b_lo = b_lo0 + stage * (kStageBytes >> 4);
           const int next_stage = stage + 1 == kStages ? 0 : stage + 1;
           const uint32_t next_phase = stage + 1 == kStages ? phase ^ 1u : phase;
-          umma_f16(d_tmem, smem_desc_join(a_lo), smem_desc_join(b_lo), idesc, accumulate);
-          umma_f16(d_tmem, smem_desc_join(a_lo + a_kstep), smem_desc_join(b_lo + b_kstep), idesc, 1u);
+          umma<kF8>(d_tmem, smem_desc_join(a_lo), smem_desc_join(b_lo), idesc, accumulate);
+          umma<kF8>(d_tmem, smem_desc_join(a_lo + a_kstep), smem_desc_join(b_lo + b_kstep), idesc, 1u);
           ready = mbar_test_wait(full_bar(next_stage), next_phase);
-          umma_f16(d_tmem, smem_desc_join(a_lo + 2 * a_kstep), smem_desc_join(b_lo + 2 * b_kstep), idesc, 1u);
-          umma_f16(d_tmem, smem_desc_join(a_lo + 3 * a_kstep), smem_desc_join(b_lo + 3 * b_kstep), idesc, 1u);
+          umma<kF8>(d_tmem, smem_desc_join(a_lo + 2 * a_kstep), smem_desc_join(b_lo + 2 * b_kstep), idesc, 1u);
+          umma<kF8>(d_tmem, smem_desc_join(a_lo + 3 * a_kstep), smem_desc_join(b_lo + 3 * b_kstep), idesc, 1u);
           accumulate = 1u;
           umma_commit(empty_bar(stage));  // the stage is free once these MMAs have read it
           stage = next_stage;
@@ -589,18 +595,21 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
   return fn;
 }
 
-// Tensor map of a 2-D 16-bit tensor: `inner` contiguous elements per row, `outer` rows,
-// `ld` elements between rows; boxes of 64 x box_outer with the 128-byte swizzle.
+// Tensor map of a 2-D tensor of 16-bit elements (STK_F16 / STK_BF16) or bytes (STK_F8E4M3): `inner`
+// contiguous elements per row, `outer` rows, `ld` elements between rows; boxes of 128 bytes x
+// box_outer with the 128-byte swizzle.
 static int encode_map(CUtensorMap* tm, const void* base, int dtype, int64_t inner, int64_t outer,
                       int64_t ld, int box_outer) {
   PFN_cuTensorMapEncodeTiled_v12000 fn = get_encode_fn();
   if (fn == nullptr) return STK_ERR_DRIVER;
+  const bool bytes = dtype == STK_F8E4M3;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2u};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_outer)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * (bytes ? 1u : 2u)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(bytes ? 2 * kBK : kBK), static_cast<cuuint32_t>(box_outer)};
   const cuuint32_t estr[2] = {1u, 1u};
   const CUresult r =
-      fn(tm, dtype == STK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+      fn(tm, bytes ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                   : dtype == STK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
          2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -665,6 +674,8 @@ static int device_info(DeviceInfo** out) {
     if (cudaFuncSetAttribute(bsmm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
             cudaSuccess ||
         cudaFuncSetAttribute(bsmm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(bsmm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kSmemBytes) != cudaSuccess) {
       cudaGetLastError();
       return STK_ERR_LAUNCH;
@@ -701,8 +712,10 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensor
   const int rc = device_info(&d);
   if (rc != STK_OK) return rc;
   const int grid = p.num_tiles < d->sms ? p.num_tiles : d->sms;
+  if (p.in8 && (p.epilogue >= kEpilogueGeluKeep || p.a_mn || p.b_mn)) return STK_ERR_BAD_LAYOUT;
   const cudaError_t err =
-      p.epilogue >= kEpilogueGeluKeep
+      p.in8 ? launch_dependent(bsmm_kernel<false, true>, grid, kThreads, kSmemBytes, stream, tmA, tmB, tmC, tmX, p)
+      : p.epilogue >= kEpilogueGeluKeep
           ? launch_dependent(bsmm_kernel<true>, grid, kThreads, kSmemBytes, stream, tmA, tmB, tmC, tmX, p)
           : launch_dependent(bsmm_kernel<false>, grid, kThreads, kSmemBytes, stream, tmA, tmB, tmC, tmX, p);
   return err == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;

@@ -70,6 +70,8 @@ __device__ __forceinline__ void drain_rows_direct(uint32_t t_addr, int ncols, in
   }
 }
 
+// kF8: 8-bit float operands (kind::f8f6f4): a stage covers 128 of K, i.e. one sparse block.
+template <bool kF8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1)
 bsmm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const PairParams p) {
@@ -157,19 +159,20 @@ bsmm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             mn_elem = it.inner * 4 * kBlk + rank * kBlk;  // D0; D1 is 256 further
             k_elem = kpos * kBlk;
           }
-          for (int ks = 0; ks < 2 && ok; ++ks) {
+          constexpr int kStageK = kF8 ? 2 * kBK : kBK;  // K elements per stage
+          for (int ks = 0; ks < kBlk / kStageK && ok; ++ks) {
             ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
             if (!ok) break;
             if (arms) {
-              stage_flags[stage] = ks == 0 ? first : last;
+              stage_flags[stage] = (ks == 0 ? first : 0u) | (ks == kBlk / kStageK - 1 ? last : 0u);
               mbar_arrive_expect_tx(full_bar(stage), 2 * kWStageBytes);
             }
             const uint32_t dst = dst0 + stage * kWStageBytes;
             const uint32_t bar = leader_full0 + 8u * stage;
-            load_operand_pair(tm, dst, bar, mn_major, mn_elem, k_elem + ks * kBK);
+            load_operand_pair(tm, dst, bar, mn_major, mn_elem, k_elem + ks * kStageK);
             if (!sparse_side)
               load_operand_pair(tm, dst + kOperandTileBytes, bar, mn_major, mn_elem + 2 * kBlk,
-                                k_elem + ks * kBK);
+                                k_elem + ks * kStageK);
             if (++stage == kWStages) {
               stage = 0;
               phase ^= 1u;
@@ -193,7 +196,7 @@ bsmm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer (leader CTA only)
     if (rank == 0 && lane == 0) {
-      const uint32_t idesc = make_idesc_f16(p.fmt, p.a_mn, p.b_mn, 256, 256);
+      const uint32_t idesc = kF8 ? make_idesc_f8(256, 256) : make_idesc_f16(p.fmt, p.a_mn, p.b_mn, 256, 256);
       const int s_mn = dsd ? p.a_mn : p.b_mn, d_mn = dsd ? p.b_mn : p.a_mn;
       const uint32_t s_lo0 = smem_desc_lo(smem_base, s_mn ? kOperandTileBytes / 2 : 16u);
       const uint32_t d_lo0 = smem_desc_lo(smem_base + kOperandTileBytes, d_mn ? kOperandTileBytes / 2 : 16u);
@@ -215,12 +218,12 @@ bsmm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint64_t d0 = smem_desc_join(d_lo + k * d_kstep);
           const uint64_t d1 = smem_desc_join(d_lo + (kOperandTileBytes >> 4) + k * d_kstep);
           if (which != 1) {
-            if (dsd) umma_f16_pair(tmem_base, s_desc, d0, idesc, accumulate);
-            else umma_f16_pair(tmem_base, d0, s_desc, idesc, accumulate);
+            if (dsd) umma_pair<kF8>(tmem_base, s_desc, d0, idesc, accumulate);
+            else umma_pair<kF8>(tmem_base, d0, s_desc, idesc, accumulate);
           }
           if (which != 0) {
-            if (dsd) umma_f16_pair(tmem_base + kPAccCols, s_desc, d1, idesc, accumulate);
-            else umma_f16_pair(tmem_base + kPAccCols, d1, s_desc, idesc, accumulate);
+            if (dsd) umma_pair<kF8>(tmem_base + kPAccCols, s_desc, d1, idesc, accumulate);
+            else umma_pair<kF8>(tmem_base + kPAccCols, d1, s_desc, idesc, accumulate);
           }
           accumulate = 1u;
           if (probe && k == 1) {
@@ -372,7 +375,9 @@ static int launch_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, const Pai
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return STK_ERR_LAUNCH;
   if (!opted_in[dev]) {
-    if (cudaFuncSetAttribute(bsmm_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(bsmm_wide_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kWSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(bsmm_wide_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kWSmemBytes) != cudaSuccess) {
       cudaGetLastError();
       return STK_ERR_LAUNCH;
@@ -392,7 +397,10 @@ static int launch_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, const Pai
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = kUseDependentLaunch ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, bsmm_wide_kernel, tmA, tmB, p) == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
+  if (p.in8 && (p.a_mn || p.b_mn)) return STK_ERR_BAD_LAYOUT;
+  const cudaError_t err = p.in8 ? cudaLaunchKernelEx(&cfg, bsmm_wide_kernel<true>, tmA, tmB, p)
+                                : cudaLaunchKernelEx(&cfg, bsmm_wide_kernel<false>, tmA, tmB, p);
+  return err == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
 
 }  // namespace stk

@@ -182,6 +182,23 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
       : "memory");
 }
 
+// The same for 8-bit float operands (kind::f8f6f4: 32 of K per instruction).
+__device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                        uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+template <bool kF8>
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                     uint32_t accumulate) {
+  if constexpr (kF8) umma_f8(d_tmem, a_desc, b_desc, idesc, accumulate);
+  else umma_f16(d_tmem, a_desc, b_desc, idesc, accumulate);
+}
+
 // Arrive on `bar` once every tcgen05 operation this thread issued so far has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
@@ -279,6 +296,21 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, 
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma_f8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+template <bool kF8>
+__device__ __forceinline__ void umma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  if constexpr (kF8) umma_f8_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
+  else umma_f16_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
+}
 // Arrive on the barrier at the same shared-memory offset in every CTA of `cta_mask` once the
 // MMAs issued so far have completed.
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
@@ -331,6 +363,16 @@ __host__ __device__ __forceinline__ uint32_t make_idesc_f16(int fmt, int a_mn_ma
   d |= static_cast<uint32_t>(fmt) << 10;  // B format
   d |= static_cast<uint32_t>(a_mn_major) << 15;
   d |= static_cast<uint32_t>(b_mn_major) << 16;
+  d |= static_cast<uint32_t>(n >> 3) << 17;
+  d |= static_cast<uint32_t>(m >> 4) << 24;
+  return d;
+}
+
+// Instruction descriptor for kind::f8f6f4 with e4m3 operands (format code 0 in both fields), both
+// K-major, fp32 accumulation.
+__host__ __device__ __forceinline__ uint32_t make_idesc_f8(int n, int m = 128) {
+  uint32_t d = 0;
+  d |= 1u << 4;  // D format: F32
   d |= static_cast<uint32_t>(n >> 3) << 17;
   d |= static_cast<uint32_t>(m >> 4) << 24;
   return d;

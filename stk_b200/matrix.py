@@ -67,8 +67,8 @@ def _validate_matrix(shape, data, row_indices, column_indices, offsets):
                          f"Got data on {data.device}, row_indices on {row_indices.device} "
                          f"column_indices on {column_indices.device} and "
                          f"offsets on {offsets.device}.")
-    if data.dtype not in (torch.float16, torch.bfloat16):
-        raise ValueError(f"Expected float16 or bfloat16 data. Got {data.dtype} data.")
+    if data.dtype not in (torch.float16, torch.bfloat16, torch.float8_e4m3fn):
+        raise ValueError(f"Expected float16, bfloat16 or float8_e4m3fn data. Got {data.dtype} data.")
     for name, t in (("row_indices", row_indices), ("column_indices", column_indices)):
         if t.dtype not in (torch.int16, torch.int32):
             raise ValueError(f"Expected int16 or int32 {name}. Got {t.dtype} {name}.")
@@ -137,8 +137,8 @@ class Matrix(torch.nn.Module):
         extension; the reference leaves it as a TODO) converts the values only - the metadata keeps
         its integer types."""
         if isinstance(device, torch.dtype):
-            if device not in (torch.float16, torch.bfloat16):
-                raise ValueError(f"Expected float16 or bfloat16 data. Got {device}.")
+            if device not in (torch.float16, torch.bfloat16, torch.float8_e4m3fn):
+                raise ValueError(f"Expected float16, bfloat16 or float8_e4m3fn data. Got {device}.")
             self._data = self._data.to(device)
             return self
         for name in ("_data", "_row_indices", "_column_indices", "_offsets", "_column_indices_t",

@@ -13,6 +13,18 @@ def _fields(m):
             m.block_offsets_t)
 
 
+# float8_e4m3fn operands (not in the reference): fp32 accumulation, bfloat16 result, forward only.  The
+# 8-bit kernels read both operands with K contiguous, so a dense operand in the other layout is copied
+# once, dsd takes the sparse operand as stored and dds as a .t() view.
+def _is_fp8(*tensors):
+    return any(t.dtype == kernels.FP8 for t in tensors)
+
+
+def _no_grad_fp8(*tensors):
+    if torch.is_grad_enabled() and any(t.requires_grad for t in tensors):
+        raise ValueError("float8 products are forward only; call them under torch.no_grad()")
+
+
 def dsd(a, b, out=None):
     """dense = a @ b with a sparse (possibly a .t() view) and b dense.
 
@@ -22,13 +34,20 @@ def dsd(a, b, out=None):
     """
     assert isinstance(a, Matrix)
     assert isinstance(b, torch.Tensor)
+    if out is None and _is_fp8(a.data, b):
+        _no_grad_fp8(a.data, b)
+        out = torch.empty((a.size()[0], b.shape[1]), dtype=torch.bfloat16, device=b.device)
+        kernels.dsd(a.size(), *_fields(a), not a.is_contiguous(), b, out)
+        return out
     if out is None:
         return sputnik.dsd(a.size(), *_fields(a), not a.is_contiguous(), b)
     if torch.is_grad_enabled() and (a.data.requires_grad or b.requires_grad):
         raise ValueError("dsd(out=...) does not record a gradient; call it under torch.no_grad()")
-    if (out.dim() != 2 or out.shape[0] != a.size()[0] or out.shape[1] != b.shape[1] or out.dtype != b.dtype
+    want = torch.bfloat16 if _is_fp8(a.data, b) else b.dtype
+    if (out.dim() != 2 or out.shape[0] != a.size()[0] or out.shape[1] != b.shape[1] or out.dtype != want
             or out.stride(1) != 1 or out.device != b.device):
-        raise ValueError("out must be a row-major [a.size(0), b.size(1)] tensor of b's dtype on b's device")
+        raise ValueError("out must be a row-major [a.size(0), b.size(1)] tensor of b's dtype (bfloat16 for "
+                         "float8 operands) on b's device")
     kernels.dsd(a.size(), *_fields(a), not a.is_contiguous(), b, out)
     return out
 
@@ -37,6 +56,11 @@ def dds(a, b):
     """dense = a @ b with a dense and b sparse (possibly a .t() view)."""
     assert isinstance(a, torch.Tensor)
     assert isinstance(b, Matrix)
+    if _is_fp8(a, b.data):
+        _no_grad_fp8(a, b.data)
+        out = torch.empty((a.shape[0], b.size()[1]), dtype=torch.bfloat16, device=a.device)
+        kernels.dds(a, b.size(), *_fields(b), not b.is_contiguous(), out)
+        return out
     return sputnik.dds(a, b.size(), *_fields(b), not b.is_contiguous())
 
 
@@ -46,7 +70,12 @@ def sdd(a, b, topo):
     assert isinstance(b, torch.Tensor)
     assert isinstance(topo, Matrix)
     assert topo.is_contiguous()
-    out = sputnik.sdd(a, b, topo.size(), *_fields(topo))
+    if _is_fp8(a, b):
+        _no_grad_fp8(a, b)
+        out = torch.empty(topo.data.shape, dtype=torch.bfloat16, device=a.device)
+        kernels.sdd(a, b, topo.size(), out, topo.offsets, topo.row_indices, topo.column_indices)
+    else:
+        out = sputnik.sdd(a, b, topo.size(), *_fields(topo))
     return Matrix(topo.size(), out, topo.row_indices, topo.column_indices, topo.offsets,
                   topo.column_indices_t, topo.offsets_t, topo.block_offsets_t)
 
@@ -64,7 +93,7 @@ def sdd_gelu(a, b, topo):
     assert isinstance(b, torch.Tensor)
     assert isinstance(topo, Matrix)
     assert topo.is_contiguous()
-    out = torch.empty(topo.data.shape, dtype=a.dtype, device=a.device)
+    out = torch.empty(topo.data.shape, dtype=torch.bfloat16 if _is_fp8(a, b) else a.dtype, device=a.device)
     kernels.sdd(a, b, topo.size(), out, topo.offsets, topo.row_indices, topo.column_indices,
                 epilogue=1)
     return Matrix(topo.size(), out, topo.row_indices, topo.column_indices, topo.offsets,

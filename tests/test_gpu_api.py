@@ -311,3 +311,60 @@ def test_more_than_32767_blocks_per_side(stk):
         stk.Matrix(m.size(), m.data, m.row_indices.to(torch.int16), m.column_indices.to(torch.int16), m.offsets,
                    m.column_indices_t, m.offsets_t, m.block_offsets_t)
 
+
+
+@pytest.mark.parametrize("mode", ["0", "1", "2", "auto"])
+def test_float8_products_match_the_dequantized_reference(stk, mode):
+    """float8_e4m3fn operands (an extension): every product equals the fp32 product of the dequantized
+    operands up to the one bfloat16 rounding of the result, in the 128x128 kernel and on CTA pairs, for
+    a K that is not a multiple of a pipeline stage (416 = 3 * 128 + 32) and with operands handed over
+    in the layout the 8-bit kernels do not read (they are copied once)."""
+    from stk_b200 import dmoe
+    from stk_b200.backend import kernels
+    F8 = torch.float8_e4m3fn
+    np.random.seed(31)
+    torch.manual_seed(31)
+    cases = [stk.random.randn((512, 768), 0.5, 128).to("cuda"),
+             dmoe.block_diagonal_topology(torch.tensor([2, 1, 0, 3]) * 128, 256, torch.float16, "cuda")]
+    cases[1].data.normal_(0, 0.5)
+    saved = kernels.PAIR_MODE
+    kernels.PAIR_MODE = mode
+    try:
+        for topo in cases:
+            rows, cols = topo.size()
+            dense16 = lambda m: stk.ops.to_dense(m).float()
+            pattern = dense16(stk.ops.ones_like(topo))
+            for _ in range(2):          # the second round runs with the kernel-choice statistics known
+                # sdd: [rows, 416] x [416, cols] on the topology
+                a = torch.randn(rows, 416, device="cuda").to(F8)
+                b = torch.randn(cols, 416, device="cuda").to(F8)          # stored [N, K]: K contiguous
+                ref = (a.float() @ b.float().t()) * pattern
+                out = stk.ops.sdd(a, b.t(), topo)
+                assert out.data.dtype == torch.bfloat16
+                assert_product_close(dense16(out), ref, "fp8 sdd")
+                out = stk.ops.sdd(a, b.t().contiguous(), topo)             # N contiguous: copied to K-major
+                assert_product_close(dense16(out), ref, "fp8 sdd, copied rhs")
+                gelu = stk.ops.sdd_gelu(a, b.t(), topo)
+                assert_product_close(dense16(gelu), torch.nn.functional.gelu(ref) * pattern, "fp8 sdd + gelu")
+                # dsd: S [rows, cols] (fp8 blocks) x [cols, 256]
+                s8 = stk.Matrix(topo.size(), (topo.data.float() * 2).to(F8), topo.row_indices, topo.column_indices,
+                                topo.offsets, topo.column_indices_t, topo.offsets_t, topo.block_offsets_t)
+                s8.validate()
+                s_dense = dense16(stk.Matrix(topo.size(), s8.data.to(torch.bfloat16), topo.row_indices,
+                                             topo.column_indices, topo.offsets, topo.column_indices_t,
+                                             topo.offsets_t, topo.block_offsets_t))
+                r = torch.randn(256, cols, device="cuda").to(F8)           # stored [N, K]
+                y = stk.ops.dsd(s8, r.t())
+                assert y.dtype == torch.bfloat16
+                assert_product_close(y, s_dense @ r.float().t(), "fp8 dsd")
+                assert_product_close(stk.ops.dsd(s8, r.t().contiguous()), s_dense @ r.float().t(), "fp8 dsd, copied rhs")
+                # dds: [256, cols] x S^T [cols, rows]
+                lhs = torch.randn(256, cols, device="cuda").to(F8)
+                z = stk.ops.dds(lhs, s8.t())
+                assert_product_close(z, lhs.float() @ s_dense.t(), "fp8 dds")
+                with pytest.raises(ValueError):
+                    stk.ops.dsd(s8.t(), torch.randn(rows, 256, device="cuda").to(F8))
+                with pytest.raises(ValueError):
+                    stk.ops.dds(torch.randn(256, rows, device="cuda").to(F8), s8)
+    finally:
+        kernels.PAIR_MODE = saved
