@@ -496,7 +496,8 @@ def run_ours(args):
 def extra_sections(peak_gbs):
     """The other benchmark configurations and the conversion kernels, one GPU: configs[1] (forward
     products, fp16), configs[2] (six forward + backward products), configs[3] (random sparsity sweep),
-    each against cuBLAS of the same FLOPs; achieved GB/s of the metadata / conversion kernels."""
+    each against cuBLAS of the same FLOPs; achieved GB/s of the metadata / conversion kernels; the
+    float8 form of the dMoE forward products."""
     from stk_b200 import benchmarks
     torch.cuda.empty_cache()
     out = {}
@@ -513,6 +514,11 @@ def extra_sections(peak_gbs):
         meta = benchmarks.meta_kernels(peak_gbs=peak_gbs)
         out["roofline_meta"] = {"bound": "hbm", "peak": peak_gbs, "unit": "GB/s",
                                 "achieved": "algorithmic bytes / CUDA-event time per call", "kernels": meta}
+        torch.cuda.empty_cache()
+        out["fp8"] = {"workload": "the two forward products of BASELINE.json configs[4] / 8 (8 experts x 4096 rows, h=4096, "
+                                  "f=14336) with float8_e4m3fn operands, bf16 output; against the same products in bf16 and "
+                                  "against cuBLASLt's float8 GEMM of the same FLOPs (torch._scaled_mm), interleaved",
+                      "products": benchmarks.products_fp8()}
     return out
 
 
