@@ -326,3 +326,23 @@ def test_float8_entry_points_refuse_layouts_they_cannot_read():
         kernels.sdd(f8(128, 128), h(128, 128), (128, 128), h(1, 128, 128), off, idx, idx)
     with pytest.raises(ValueError, match="float8_e4m3fn operands go with"):
         kernels.sdd(f8(128, 128), f8(128, 128), (128, 128), h(1, 128, 128), off, idx, idx)
+
+
+def test_wide_shape_is_chosen_by_list_length_and_rounds(monkeypatch):
+    """kernels._pair_shape: the 256x512 shape needs long lists (48 blocks on average) and enough items
+    for eight rounds over the CTA pairs; forced modes override; only pair-kernel products are asked."""
+    from stk_b200.backend import kernels
+    monkeypatch.setattr(kernels, "_pairs_resident", lambda device: 74)
+    monkeypatch.setattr(kernels, "PAIR_MODE", "auto")
+    dev = torch.device("cpu")
+    lists = 260                                            # block rows of a dMoE shard: 130 list pairs
+    assert kernels._pair_shape(1, 112 * lists, lists, 4096, dev) == 2      # 130 * 8 = 1040 items, long lists
+    assert kernels._pair_shape(1, 40 * lists, lists, 4096, dev) == 1       # lists too short
+    assert kernels._pair_shape(1, 112 * lists, lists, 2048, dev) == 1      # 130 * 4 = 520 items: under 8 rounds
+    assert kernels._pair_shape(1, 112 * 136, 136, 4096, dev) == 1          # 68 * 8 = 544 items
+    assert kernels._pair_shape(3, 112 * lists, lists, 4096, dev) == 3      # not a pair-kernel product
+    assert kernels._pair_shape(0, 112 * lists, lists, 4096, dev) == 0
+    monkeypatch.setattr(kernels, "PAIR_MODE", "2")
+    assert kernels._pair_shape(1, 8 * lists, lists, 256, dev) == 2
+    monkeypatch.setattr(kernels, "PAIR_MODE", "1")
+    assert kernels._pair_shape(1, 112 * lists, lists, 4096, dev) == 1
