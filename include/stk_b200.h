@@ -239,7 +239,8 @@ int stk_b200_transpose_meta_static(const int16_t* row_indices, const int16_t* co
  * 3. mask_to_indices: row-major list of the set positions as int16 row / column indices.
  * 4. gather_blocks: data[p] = x[r_p*b:+b, c_p*b:+b], copied bit-exactly.  `offsets` (the CSR offsets of
  *    step 2; may be NULL) lets blocks smaller than 64 be copied by block-row strips instead of one
- *    CTA per block.
+ *    CTA per block.  A listed block outside the matrix is not read: it becomes zeros and
+ *    STK_ERR_BAD_DIMS is recorded in the device status word.
  */
 int stk_b200_block_mask(const void* x, int64_t rows, int64_t cols, int64_t ld,
                         int blocking, int elem_bytes, uint8_t* mask, void* stream);

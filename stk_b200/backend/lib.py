@@ -74,6 +74,35 @@ for _name in ("sdd", "dsd", "dds", "pair_stats", "pair_plan", "row_indices", "tr
 
 _lib = None
 
+# STK_B200_NVTX=1: every call into the library that launches kernels is wrapped in an NVTX range named
+# after its entry point (stk_b200_sdd, stk_b200_ep_dispatch, ...), so that a timeline shows which
+# product or exchange step a kernel belongs to.  Off by default: a range costs two calls per launch.
+NVTX = os.environ.get("STK_B200_NVTX", "0") == "1"
+_UNTRACED = ("stk_b200_error_string", "stk_b200_device_status")
+
+
+class _Traced:
+    """The loaded library with its launching entry points wrapped in NVTX ranges."""
+
+    def __init__(self, lib):
+        self._lib, self._wrapped = lib, {}
+
+    def __getattr__(self, name):
+        fn = self._wrapped.get(name)
+        if fn is None:
+            raw = getattr(self._lib, name)
+            if name in _UNTRACED or name.endswith("_bytes"):
+                fn = raw
+            else:
+                def fn(*args, _raw=raw, _name=name):
+                    torch.cuda.nvtx.range_push(_name)
+                    try:
+                        return _raw(*args)
+                    finally:
+                        torch.cuda.nvtx.range_pop()
+            self._wrapped[name] = fn
+        return fn
+
 
 def load():
     """Load the shared library once and attach the argument types."""
@@ -89,8 +118,8 @@ def load():
         fn = getattr(lib, name)  # AttributeError here means a stale library
         fn.restype = restype
         fn.argtypes = argtypes
-    _lib = lib
-    return lib
+    _lib = _Traced(lib) if NVTX else lib
+    return _lib
 
 
 def error_string(code):

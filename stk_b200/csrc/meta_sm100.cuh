@@ -349,15 +349,21 @@ __global__ void mask_to_indices_kernel(const uint8_t* __restrict__ mask, int blo
 
 // Vector path: one CTA per block, 16-byte copies, rows of the block are contiguous in `data`.
 __global__ void __launch_bounds__(256)
-gather_blocks_vec_kernel(const uint16_t* __restrict__ x, int64_t ld, int blocking,
-                         IndexArray row_indices, IndexArray column_indices,
+gather_blocks_vec_kernel(const uint16_t* __restrict__ x, int64_t ld, int blocking, int block_rows,
+                         int block_cols, IndexArray row_indices, IndexArray column_indices,
                          uint16_t* __restrict__ data) {
   const int64_t p = blockIdx.x;
   const int vec_per_row = blocking / 8;
   const int nvec = blocking * vec_per_row;
-  const uint16_t* src = x + static_cast<int64_t>(row_indices[p]) * blocking * ld +
-                        static_cast<int64_t>(column_indices[p]) * blocking;
+  const int br = row_indices[p], bc = column_indices[p];
   uint4* dst = reinterpret_cast<uint4*>(data + p * blocking * blocking);
+  if (br < 0 || br >= block_rows || bc < 0 || bc >= block_cols) {
+    // a block outside the matrix is never read: its values become zeros and the call is reported
+    if (threadIdx.x == 0) report_status(STK_ERR_BAD_DIMS);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) dst[v] = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  const uint16_t* src = x + static_cast<int64_t>(br) * blocking * ld + static_cast<int64_t>(bc) * blocking;
   for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
     const int r = v / vec_per_row, c = v - r * vec_per_row;
     dst[v] = __ldg(reinterpret_cast<const uint4*>(src + r * ld) + c);
@@ -365,17 +371,22 @@ gather_blocks_vec_kernel(const uint16_t* __restrict__ x, int64_t ld, int blockin
 }
 
 template <typename T>
-__global__ void gather_blocks_generic_kernel(const T* __restrict__ x, int64_t ld, int blocking,
-                                             IndexArray row_indices, IndexArray column_indices,
-                                             int64_t total, T* __restrict__ data) {
+__global__ void gather_blocks_generic_kernel(const T* __restrict__ x, int64_t ld, int blocking, int block_rows,
+                                             int block_cols, IndexArray row_indices,
+                                             IndexArray column_indices, int64_t total, T* __restrict__ data) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const int64_t bb = static_cast<int64_t>(blocking) * blocking;
   const int64_t p = i / bb;
   const int rem = static_cast<int>(i - p * bb);
   const int r = rem / blocking, c = rem - r * blocking;
-  data[i] = x[(static_cast<int64_t>(row_indices[p]) * blocking + r) * ld +
-              static_cast<int64_t>(column_indices[p]) * blocking + c];
+  const int br = row_indices[p], bc = column_indices[p];
+  if (br < 0 || br >= block_rows || bc < 0 || bc >= block_cols) {
+    if (rem == 0) report_status(STK_ERR_BAD_DIMS);
+    data[i] = 0;
+    return;
+  }
+  data[i] = x[(static_cast<int64_t>(br) * blocking + r) * ld + static_cast<int64_t>(bc) * blocking + c];
 }
 
 // ------------------------------------------------------------------------------------------
@@ -605,6 +616,8 @@ static int gather_blocks_impl(const void* x, int64_t rows, int64_t cols, int64_t
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool vec = elem_bytes == 2 && blocking % 8 == 0 && ld % 8 == 0 && ptr_aligned16(x) &&
                    ptr_aligned16(data);
+  if (rows / blocking > INT32_MAX || cols / blocking > INT32_MAX) return STK_ERR_TOO_LARGE;
+  const int block_rows = static_cast<int>(rows / blocking), block_cols = static_cast<int>(cols / blocking);
   if (vec && blocking < 64 && offsets != nullptr) {
     const int64_t R = rows / blocking;
     for (int64_t br0 = 0; br0 < R; br0 += kMaxGridY) {
@@ -616,7 +629,7 @@ static int gather_blocks_impl(const void* x, int64_t rows, int64_t cols, int64_t
     }
   } else if (vec) {
     gather_blocks_vec_kernel<<<static_cast<unsigned>(nnz), 256, 0, s>>>(
-        static_cast<const uint16_t*>(x), ld, blocking, row_indices, column_indices,
+        static_cast<const uint16_t*>(x), ld, blocking, block_rows, block_cols, row_indices, column_indices,
         static_cast<uint16_t*>(data));
   } else {
     const int64_t total = nnz * blocking * blocking;
@@ -624,12 +637,12 @@ static int gather_blocks_impl(const void* x, int64_t rows, int64_t cols, int64_t
     if (blocks > INT32_MAX) return STK_ERR_TOO_LARGE;
     if (elem_bytes == 2)
       gather_blocks_generic_kernel<uint16_t><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
-          static_cast<const uint16_t*>(x), ld, blocking, row_indices, column_indices, total,
-          static_cast<uint16_t*>(data));
+          static_cast<const uint16_t*>(x), ld, blocking, block_rows, block_cols, row_indices, column_indices,
+          total, static_cast<uint16_t*>(data));
     else
       gather_blocks_generic_kernel<uint32_t><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
-          static_cast<const uint32_t*>(x), ld, blocking, row_indices, column_indices, total,
-          static_cast<uint32_t*>(data));
+          static_cast<const uint32_t*>(x), ld, blocking, block_rows, block_cols, row_indices, column_indices,
+          total, static_cast<uint32_t*>(data));
   }
   return launch_status();
 }

@@ -239,6 +239,22 @@ def test_topology_kernel_refuses_bins_that_do_not_add_up(stk):
         assert lib.device_status() == -2
 
 
+def test_gather_blocks_never_reads_a_block_outside_the_matrix(stk):
+    """A block index outside [0, block rows) x [0, block columns) used to be turned into an address; it
+    now yields a block of zeros and STK_ERR_BAD_DIMS, in the 16-byte kernel and in the element-wise one."""
+    from stk_b200.backend import kernels, lib
+    for blocking, dtype in ((128, torch.float16), (4, torch.float32)):
+        x = torch.randn(4 * blocking, 3 * blocking, device="cuda").to(dtype)
+        rows = torch.tensor([0, 3, 7, 1], dtype=torch.int16, device="cuda")       # 7: outside
+        cols = torch.tensor([2, 0, 1, -1], dtype=torch.int16, device="cuda")      # -1: outside
+        data = kernels.gather_blocks(x, blocking, rows, cols)
+        torch.cuda.synchronize()
+        assert lib.device_status() == -2
+        b = blocking
+        assert torch.equal(data[0], x[0:b, 2 * b:3 * b]) and torch.equal(data[1], x[3 * b:4 * b, 0:b])
+        assert not data[2].any() and not data[3].any()
+
+
 def _as_int32(stk, m):
     i32 = lambda t: t.to(torch.int32)
     return stk.Matrix(m.size(), m.data, i32(m.row_indices), i32(m.column_indices), m.offsets)

@@ -346,3 +346,19 @@ def test_wide_shape_is_chosen_by_list_length_and_rounds(monkeypatch):
     assert kernels._pair_shape(1, 8 * lists, lists, 256, dev) == 2
     monkeypatch.setattr(kernels, "PAIR_MODE", "1")
     assert kernels._pair_shape(1, 112 * lists, lists, 4096, dev) == 1
+
+
+def test_nvtx_wrapper_passes_calls_through(monkeypatch):
+    """lib._Traced (STK_B200_NVTX=1) wraps launching entry points in an NVTX range and leaves their
+    arguments and results alone; size queries and status reads are not wrapped."""
+    from stk_b200.backend import lib
+    raw = lib.load()
+    raw = getattr(raw, "_lib", raw)
+    events = []
+    monkeypatch.setattr(torch.cuda.nvtx, "range_push", lambda name: events.append(("push", name)))
+    monkeypatch.setattr(torch.cuda.nvtx, "range_pop", lambda: events.append(("pop",)))
+    traced = lib._Traced(raw)
+    assert traced.stk_b200_pair_plan_bytes(100) == 4 * 204 and events == []
+    null = ctypes.c_void_p(0)
+    assert traced.stk_b200_pair_plan(null, null, 0, null, 0, null) == -2
+    assert events == [("push", "stk_b200_pair_plan"), ("pop",)]
