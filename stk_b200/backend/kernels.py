@@ -30,10 +30,12 @@ PAIR_MODE = os.environ.get("STK_B200_PAIR_MODE", "auto")
 # at 112 (in bursts of a few launches, where nothing is power-limited: 0.91 at 8, 0.98 at 16, 0.98 - 1.02
 # from 32 on).
 WIDE_MIN_LIST_BLOCKS = int(os.environ.get("STK_B200_WIDE_MIN_LIST_BLOCKS", "48"))
-# ... and only when the 256x512 items still come in at least this many rounds over the CTA pairs: half
-# as many, twice as long items leave a longer tail (BASELINE configs[2], Zipf-imbalanced, 2048 dense
-# columns: 524 wide items are 7.1 rounds of 74 and ran 7 % behind 1048 narrow ones).
-WIDE_MIN_ROUNDS = 8
+# ... and only when that gain survives the longer tail of half as many, twice as long items: the items
+# are dealt in rounds over the CTA pairs, a launch lasts ceil(items / pairs) rounds, and the wide shape is
+# taken when its share of useful rounds times WIDE_GAIN beats the 256x256 shape's (BASELINE configs[2],
+# Zipf-imbalanced, 2048 dense columns: 524 wide items are 7.1 rounds of 74, i.e. 8, and ran 7 % behind
+# 1048 narrow ones in 15).
+WIDE_GAIN = 1.05
 _PAIRS_RESIDENT = {}
 
 
@@ -199,8 +201,11 @@ def _pair_shape(pairs, nnz, num_lists, dense_extent, device):
     if PAIR_MODE == "2":
         return 2
     if PAIR_MODE == "auto" and nnz >= WIDE_MIN_LIST_BLOCKS * num_lists:
-        items = ((num_lists + 1) // 2) * ((dense_extent + 4 * BLOCK - 1) // (4 * BLOCK))
-        if items >= WIDE_MIN_ROUNDS * _pairs_resident(device):
+        pairs_on_gpu, groups = _pairs_resident(device), (num_lists + 1) // 2
+        useful = lambda items: items / (pairs_on_gpu * -(-items // pairs_on_gpu))
+        wide_items = groups * ((dense_extent + 4 * BLOCK - 1) // (4 * BLOCK))
+        narrow_items = groups * ((dense_extent + 2 * BLOCK - 1) // (2 * BLOCK))
+        if useful(wide_items) * WIDE_GAIN > useful(narrow_items):
             return 2
     return 1
 

@@ -329,8 +329,8 @@ def test_float8_entry_points_refuse_layouts_they_cannot_read():
 
 
 def test_wide_shape_is_chosen_by_list_length_and_rounds(monkeypatch):
-    """kernels._pair_shape: the 256x512 shape needs long lists (48 blocks on average) and enough items
-    for eight rounds over the CTA pairs; forced modes override; only pair-kernel products are asked."""
+    """kernels._pair_shape: the 256x512 shape needs long lists (48 blocks on average) and a tail of
+    rounds that does not eat its gain; forced modes override; only pair-kernel products are asked."""
     from stk_b200.backend import kernels
     monkeypatch.setattr(kernels, "_pairs_resident", lambda device: 74)
     monkeypatch.setattr(kernels, "PAIR_MODE", "auto")
@@ -338,8 +338,9 @@ def test_wide_shape_is_chosen_by_list_length_and_rounds(monkeypatch):
     lists = 260                                            # block rows of a dMoE shard: 130 list pairs
     assert kernels._pair_shape(1, 112 * lists, lists, 4096, dev) == 2      # 130 * 8 = 1040 items, long lists
     assert kernels._pair_shape(1, 40 * lists, lists, 4096, dev) == 1       # lists too short
-    assert kernels._pair_shape(1, 112 * lists, lists, 2048, dev) == 1      # 130 * 4 = 520 items: under 8 rounds
-    assert kernels._pair_shape(1, 112 * 136, 136, 4096, dev) == 1          # 68 * 8 = 544 items
+    assert kernels._pair_shape(1, 112 * lists, lists, 2048, dev) == 1      # 520 items: 7.03 rounds cost 8
+    assert kernels._pair_shape(1, 112 * 136, 136, 4096, dev) == 1          # 544 items: 7.35 rounds cost 8
+    assert kernels._pair_shape(1, 112 * 146, 146, 4096, dev) == 2          # 584 items: 7.9 rounds cost 8
     assert kernels._pair_shape(3, 112 * lists, lists, 4096, dev) == 3      # not a pair-kernel product
     assert kernels._pair_shape(0, 112 * lists, lists, 4096, dev) == 0
     monkeypatch.setattr(kernels, "PAIR_MODE", "2")
