@@ -372,57 +372,68 @@ ep_zero_padding_kernel(const int32_t* __restrict__ counts_all, int world, int ex
 
 // Sorted position q (slots ordered by expert: slot order[q], expert segments offsets[e..e+1]) goes to
 // row dest_base[e] + (q - offsets[e]) of the buffer of rank e / local: the row of token order[q] / k,
-// and the tag (this rank << 40 | slot) into the owner's tag array.  Only the slots whose expert lies
-// in chunk `chunk` of its owner are handled (chunks = 1: all).  One warp per slot.
+// and the tag (this rank << 40 | slot) into the owner's tag array.  Only the experts of chunk `chunk`
+// of every owner are handled (chunks = 1: all).  A warp per row, the warps of a bounded grid striding
+// over one expert's rows after the other: a grid of a few CTAs per SM leaves the block scheduler free
+// to start the product kernels of another stream next to it (a CTA per eight rows did not: 32768
+// queued CTAs kept the first products waiting until the NEXT chunk's push had been dealt out).
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ order,
                    const int32_t* __restrict__ offsets, const int64_t* __restrict__ dest_base,
                    const uint64_t* __restrict__ peer_bufs, const uint64_t* __restrict__ peer_tags,
-                   int64_t slots, int k, int experts, int local, int rank, int chunk, int chunks,
+                   int k, int world, int local, int rank, int chunk, int chunks,
                    int vec_per_row, int64_t cap_rows) {
-  const int64_t q = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int warp0 = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (q >= slots) return;
-  int lo = 0, hi = experts;  // last e with offsets[e] <= q
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (offsets[mid] <= q) lo = mid; else hi = mid;
+  // local experts le with ep_chunk_of(le) == chunk
+  const int le0 = static_cast<int>((static_cast<long long>(chunk) * local + chunks - 1) / chunks);
+  const int le1 = static_cast<int>((static_cast<long long>(chunk + 1) * local + chunks - 1) / chunks);
+  for (int owner = 0; owner < world; ++owner) {
+    int64_t* tags = reinterpret_cast<int64_t*>(peer_tags[owner]);
+    uint4* buf = reinterpret_cast<uint4*>(peer_bufs[owner]);
+    for (int le = le0; le < le1; ++le) {
+      const int e = owner * local + le;
+      const int begin = offsets[e], n = offsets[e + 1] - begin;
+      const int64_t base = dest_base[e];
+      for (int i = warp0; i < n; i += nwarps) {
+        const int64_t row = base + i;
+        if (row < 0 || row >= cap_rows) {
+          if (lane == 0) report_status(STK_ERR_WORKSPACE);
+          continue;
+        }
+        const int32_t slot = order[begin + i];
+        if (lane == 0) tags[row] = (static_cast<int64_t>(rank) << 40) | slot;
+        const uint4* in = x + static_cast<int64_t>(slot / k) * vec_per_row;
+        uint4* out = buf + row * vec_per_row;
+        for (int v = lane; v < vec_per_row; v += 32) out[v] = __ldg(in + v);
+      }
+    }
   }
-  const int e = lo, owner = e / local;
-  if (chunks > 1 && ep_chunk_of(e - owner * local, local, chunks) != chunk) return;
-  const int64_t row = dest_base[e] + (q - offsets[e]);
-  const int32_t slot = order[q];
-  if (row < 0 || row >= cap_rows) {
-    if (lane == 0) report_status(STK_ERR_WORKSPACE);
-    return;
-  }
-  if (lane == 0)
-    reinterpret_cast<int64_t*>(peer_tags[owner])[row] = (static_cast<int64_t>(rank) << 40) | slot;
-  const uint4* in = x + static_cast<int64_t>(slot / k) * vec_per_row;
-  uint4* out = reinterpret_cast<uint4*>(peer_bufs[owner]) + row * vec_per_row;
-  for (int v = lane; v < vec_per_row; v += 32) out[v] = __ldg(in + v);
 }
 
 // The way back: rows [row0, row0 + n_rows) of this rank's result go to the home rank's slot-ordered
-// buffer, row tag & mask of rank tag >> 40; padding rows (tag < 0) go nowhere.  One warp per row.
+// buffer, row tag & mask of rank tag >> 40; padding rows (tag < 0) go nowhere.  A warp per row, bounded
+// grid as above.
 __global__ void __launch_bounds__(256)
 ep_return_kernel(const uint4* __restrict__ result, const int64_t* __restrict__ tags,
                  const uint64_t* __restrict__ peer_slots, int64_t row0, int64_t n_rows, int world,
                  int vec_per_row, int64_t slot_cap) {
-  const int64_t w = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (w >= n_rows) return;
-  const int64_t row = row0 + w;
-  const int64_t tag = tags[row];
-  if (tag < 0) return;
-  const int64_t home = tag >> 40, slot = tag & kTagRowMask;
-  if (home >= world || slot >= slot_cap) {
-    if (lane == 0) report_status(STK_ERR_WORKSPACE);
-    return;
+  for (int64_t w = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; w < n_rows; w += nwarps) {
+    const int64_t row = row0 + w;
+    const int64_t tag = tags[row];
+    if (tag < 0) continue;
+    const int64_t home = tag >> 40, slot = tag & kTagRowMask;
+    if (home >= world || slot >= slot_cap) {
+      if (lane == 0) report_status(STK_ERR_WORKSPACE);
+      continue;
+    }
+    const uint4* in = result + row * vec_per_row;
+    uint4* out = reinterpret_cast<uint4*>(peer_slots[home]) + slot * vec_per_row;
+    for (int v = lane; v < vec_per_row; v += 32) out[v] = __ldg(in + v);
   }
-  const uint4* in = result + row * vec_per_row;
-  uint4* out = reinterpret_cast<uint4*>(peer_slots[home]) + slot * vec_per_row;
-  for (int v = lane; v < vec_per_row; v += 32) out[v] = __ldg(in + v);
 }
 
 }  // namespace stk
@@ -521,6 +532,22 @@ extern "C" int stk_b200_dmoe_topology_i32(const int32_t* bin_rows, int experts, 
                             block_offsets_t, stream);
 }
 
+namespace stk {
+// CTAs of a push kernel (ep_dispatch, ep_return): three per SM - few enough to be resident all at
+// once next to a product kernel's CTAs (no shared memory, 256 threads), enough warps to fill NVLink.
+static int64_t ep_push_grid() {
+  static int sms[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (sms[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return -1;
+    sms[dev] = n;
+  }
+  return 3ll * sms[dev];
+}
+}  // namespace stk
+
 extern "C" int stk_b200_ep_share_counts(const int32_t* offsets, const uint64_t* peer_counts, int world,
                                         int experts, int rank, void* stream) {
   if (!offsets || !peer_counts) return STK_ERR_NULL_POINTER;
@@ -580,9 +607,12 @@ extern "C" int stk_b200_ep_dispatch(const void* x, const int32_t* order, const i
       row_bytes % 16 != 0 || cap_rows < 0)
     return STK_ERR_BAD_DIMS;
   if (slots > INT32_MAX) return STK_ERR_TOO_LARGE;
-  const int64_t blocks = (slots * 32 + 255) / 256;
+  int64_t blocks = (slots * 32 + 255) / 256;  // a warp per row at most
+  const int64_t bound = stk::ep_push_grid();
+  if (bound <= 0) return STK_ERR_LAUNCH;
+  if (blocks > bound) blocks = bound;
   stk::ep_dispatch_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(x), order, offsets, dest_base, peer_bufs, peer_tags, slots, top_k, experts,
+      static_cast<const uint4*>(x), order, offsets, dest_base, peer_bufs, peer_tags, top_k, world,
       experts / world, rank, chunk, chunks, static_cast<int>(row_bytes / 16), cap_rows);
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
 }
@@ -594,8 +624,10 @@ extern "C" int stk_b200_ep_return(const void* result, const int64_t* tags, const
   if (!result || !tags || !peer_slots) return STK_ERR_NULL_POINTER;
   if (row0 < 0 || n_rows < 0 || world < 1 || row_bytes <= 0 || row_bytes % 16 != 0 || slot_cap < 0)
     return STK_ERR_BAD_DIMS;
-  const int64_t blocks = (n_rows * 32 + 255) / 256;
-  if (blocks > INT32_MAX) return STK_ERR_TOO_LARGE;
+  int64_t blocks = (n_rows * 32 + 255) / 256;
+  const int64_t bound = stk::ep_push_grid();
+  if (bound <= 0) return STK_ERR_LAUNCH;
+  if (blocks > bound) blocks = bound;
   stk::ep_return_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(result), tags, peer_slots, row0, n_rows, world,
       static_cast<int>(row_bytes / 16), slot_cap);
