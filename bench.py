@@ -1,6 +1,6 @@
 """Benchmark of the block-sparse matmul hot path: one forward pass of a sharded dMoE layer.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--shrink S]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--shrink S] [--timeline]
 
 Workload (BASELINE.json configs[4], bf16, 128x128 blocks): T = 131072 tokens, hidden 4096, ffn 14336 per
 expert, E = 64 experts, top-2 routing from the softmax of N(0,1) logits, every expert's bin padded to
@@ -320,6 +320,11 @@ def run_ours(args):
         step = lambda: layer.step(x_dev, ids_dev, probs_dev)
         for _ in range(args.warmup):
             step()
+        if args.timeline:
+            print_timeline(step, rank, distributed)
+            if distributed:
+                dist.destroy_process_group()
+            return
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()      # before the barrier: the other ranks must not time its start-up
@@ -493,6 +498,31 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def print_timeline(step, rank, distributed):
+    """--timeline: start, end and duration (us, relative to the step's first kernel) of every kernel of
+    one step on rank 0, both streams, from torch's profiler - where the exchange and the products
+    overlap and where they wait for one another.  Not a timing run: the profiler slows the host."""
+    import torch.distributed as dist
+    from torch.profiler import profile, ProfilerActivity
+    torch.cuda.synchronize()
+    if distributed:
+        dist.barrier()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+    if rank == 0:
+        events = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                        key=lambda e: e.time_range.start)
+        last = events[2 * (len(events) // 3):]
+        t0 = last[0].time_range.start
+        for e in last:
+            print(f"{e.time_range.start - t0:10.1f} {e.time_range.end - t0:10.1f} "
+                  f"{e.time_range.end - e.time_range.start:9.1f} us  {e.name[:80]}", flush=True)
+    if distributed:
+        dist.barrier()
+
+
 def extra_sections(peak_gbs):
     """The other benchmark configurations and the conversion kernels, one GPU: configs[1] (forward
     products, fp16), configs[2] (six forward + backward products), configs[3] (random sparsity sweep),
@@ -641,6 +671,8 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--shrink", type=int, default=1, choices=(1, 2, 4, 8),
                     help="divide tokens and experts by this (8: the per-GPU problem of an 8-GPU run)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print the kernel timeline of one step on rank 0 instead of timing")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the end-to-end, extra-configuration and CPU legs (short run for profilers)")
     args = ap.parse_args()

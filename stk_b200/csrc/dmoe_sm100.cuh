@@ -370,14 +370,19 @@ ep_zero_padding_kernel(const int32_t* __restrict__ counts_all, int world, int ex
   if (lane == 0 && tags != nullptr) tags[row] = -1;
 }
 
+// The push kernels run beside the product kernels of another stream, one CTA per SM: a 256x256 pair
+// kernel CTA leaves 1.8 KiB of an SM's shared memory, and every resident CTA costs 1 KiB of it whether
+// it asks for shared memory or not, so exactly one more CTA fits; 512 threads x 32 registers fit
+// beside the product CTA's 352 x 120.
+constexpr int kPushThreads = 512;
+
 // Sorted position q (slots ordered by expert: slot order[q], expert segments offsets[e..e+1]) goes to
 // row dest_base[e] + (q - offsets[e]) of the buffer of rank e / local: the row of token order[q] / k,
 // and the tag (this rank << 40 | slot) into the owner's tag array.  Only the experts of chunk `chunk`
-// of every owner are handled (chunks = 1: all).  A warp per row, the warps of a bounded grid striding
-// over one expert's rows after the other: a grid of a few CTAs per SM leaves the block scheduler free
-// to start the product kernels of another stream next to it (a CTA per eight rows did not: 32768
-// queued CTAs kept the first products waiting until the NEXT chunk's push had been dealt out).
-__global__ void __launch_bounds__(256)
+// of every owner are handled (chunks = 1: all).  A warp per row, the warps of the one-CTA-per-SM grid
+// striding over one expert's rows after the other (a CTA per eight rows, 32768 queued CTAs, kept the
+// first products waiting until the NEXT chunk's push had been dealt out).
+__global__ void __launch_bounds__(kPushThreads, 4)  // 32 registers
 ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ order,
                    const int32_t* __restrict__ offsets, const int64_t* __restrict__ dest_base,
                    const uint64_t* __restrict__ peer_bufs, const uint64_t* __restrict__ peer_tags,
@@ -415,7 +420,7 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ orde
 // The way back: rows [row0, row0 + n_rows) of this rank's result go to the home rank's slot-ordered
 // buffer, row tag & mask of rank tag >> 40; padding rows (tag < 0) go nowhere.  A warp per row, bounded
 // grid as above.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kPushThreads, 4)
 ep_return_kernel(const uint4* __restrict__ result, const int64_t* __restrict__ tags,
                  const uint64_t* __restrict__ peer_slots, int64_t row0, int64_t n_rows, int world,
                  int vec_per_row, int64_t slot_cap) {
@@ -533,8 +538,19 @@ extern "C" int stk_b200_dmoe_topology_i32(const int32_t* bin_rows, int experts, 
 }
 
 namespace stk {
-// CTAs of a push kernel (ep_dispatch, ep_return): three per SM - few enough to be resident all at
-// once next to a product kernel's CTAs (no shared memory, 256 threads), enough warps to fill NVLink.
+// CTAs of a push kernel (ep_dispatch, ep_return): one per SM (see kPushThreads).
+// An SM splits one array between L1 and shared memory and changes the split only when it is empty:
+// the kernels that run beside the product kernels (which take the largest shared-memory split) ask
+// for the same split, or their CTAs would keep product CTAs off their SMs until they have finished.
+static bool ep_prefer_product_carveout() {
+  const int most = cudaSharedmemCarveoutMaxShared;
+  const bool ok =
+      cudaFuncSetAttribute(ep_dispatch_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, most) == cudaSuccess &&
+      cudaFuncSetAttribute(ep_return_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, most) == cudaSuccess &&
+      cudaFuncSetAttribute(ep_barrier_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, most) == cudaSuccess;
+  if (!ok) cudaGetLastError();
+  return ok;
+}
 static int64_t ep_push_grid() {
   static int sms[64] = {};
   int dev = 0;
@@ -542,9 +558,10 @@ static int64_t ep_push_grid() {
   if (sms[dev] == 0) {
     int n = 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return -1;
+    if (!ep_prefer_product_carveout()) return -1;
     sms[dev] = n;
   }
-  return 3ll * sms[dev];
+  return sms[dev];
 }
 }  // namespace stk
 
@@ -561,6 +578,7 @@ extern "C" int stk_b200_ep_barrier(const uint64_t* peer_flags, int world, int ra
                                    int64_t timeout_ms, void* stream) {
   if (!peer_flags) return STK_ERR_NULL_POINTER;
   if (world < 1 || world > 64 || rank < 0 || rank >= world || epoch < 1 || timeout_ms < 1) return STK_ERR_BAD_DIMS;
+  if (stk::ep_push_grid() <= 0) return STK_ERR_LAUNCH;  // (sets the kernels' shared-memory split once per device)
   stk::ep_barrier_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(
       peer_flags, world, rank, static_cast<long long>(epoch),
       static_cast<unsigned long long>(timeout_ms) * 1000000ull);
@@ -607,11 +625,11 @@ extern "C" int stk_b200_ep_dispatch(const void* x, const int32_t* order, const i
       row_bytes % 16 != 0 || cap_rows < 0)
     return STK_ERR_BAD_DIMS;
   if (slots > INT32_MAX) return STK_ERR_TOO_LARGE;
-  int64_t blocks = (slots * 32 + 255) / 256;  // a warp per row at most
+  int64_t blocks = (slots * 32 + stk::kPushThreads - 1) / stk::kPushThreads;  // a warp per row at most
   const int64_t bound = stk::ep_push_grid();
   if (bound <= 0) return STK_ERR_LAUNCH;
   if (blocks > bound) blocks = bound;
-  stk::ep_dispatch_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  stk::ep_dispatch_kernel<<<static_cast<unsigned>(blocks), stk::kPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), order, offsets, dest_base, peer_bufs, peer_tags, top_k, world,
       experts / world, rank, chunk, chunks, static_cast<int>(row_bytes / 16), cap_rows);
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
@@ -624,11 +642,11 @@ extern "C" int stk_b200_ep_return(const void* result, const int64_t* tags, const
   if (!result || !tags || !peer_slots) return STK_ERR_NULL_POINTER;
   if (row0 < 0 || n_rows < 0 || world < 1 || row_bytes <= 0 || row_bytes % 16 != 0 || slot_cap < 0)
     return STK_ERR_BAD_DIMS;
-  int64_t blocks = (n_rows * 32 + 255) / 256;
+  int64_t blocks = (n_rows * 32 + stk::kPushThreads - 1) / stk::kPushThreads;
   const int64_t bound = stk::ep_push_grid();
   if (bound <= 0) return STK_ERR_LAUNCH;
   if (blocks > bound) blocks = bound;
-  stk::ep_return_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  stk::ep_return_kernel<<<static_cast<unsigned>(blocks), stk::kPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(result), tags, peer_slots, row0, n_rows, world,
       static_cast<int>(row_bytes / 16), slot_cap);
   return cudaGetLastError() == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;
