@@ -176,11 +176,20 @@ class Layer:
                                               chunks=chunks)
         self.last_topology = None
 
-    def experts_mlp(self, x_rows, bin_rows, block_rows, first_local_expert, out=None):
-        """sdd -> GeLU -> dsd on rows in padded expert order; the GeLU runs in the SDD kernel's epilogue
-        (stk.ops.sdd_gelu), so this is two kernel launches (plus the small topology kernel)."""
-        n = bin_rows.numel()
+    def topology(self, bin_rows, block_rows):
+        """The block-diagonal topology of rows in padded expert order, with the pair kernels' work-item
+        table computed (it hangs on the topology's index tensor; both products use it)."""
+        from stk_b200.backend import kernels
         topo = self.dmoe.topology_from_bins(bin_rows, block_rows, FFN, DTYPE, self.dev, materialize=False)
+        kernels.pair_plan(topo.offsets, topo.column_indices)
+        return topo
+
+    def experts_mlp(self, x_rows, bin_rows, block_rows, first_local_expert, out=None, topo=None):
+        """sdd -> GeLU -> dsd on rows in padded expert order; the GeLU runs in the SDD kernel's epilogue
+        (stk.ops.sdd_gelu), so this is two kernel launches (plus the two small kernels of `topology`)."""
+        n = bin_rows.numel()
+        if topo is None:
+            topo = self.topology(bin_rows, block_rows)
         c0, c1 = first_local_expert * FFN, (first_local_expert + n) * FFN
         self.last_topology = topo
         return self.stk.ops.dsd(self.stk.ops.sdd_gelu(x_rows, self.w1[:, c0:c1], topo), self.w2[c0:c1], out=out)
@@ -195,9 +204,10 @@ class Layer:
             return dmoe.combine_tokens(y, position, probs, x.shape[0], TOP_K)
         per, chunks = self.local, self.exchange.chunks
 
-        def run_chunk(c, rows, bin_rows, block_rows, out):
-            self.experts_mlp(rows, bin_rows, block_rows, -(-c * per // chunks), out=out)
-        return self.exchange.forward(x, ids, probs, run_chunk)
+        def run_chunk(c, rows, bin_rows, block_rows, out, topo):
+            self.experts_mlp(rows, bin_rows, block_rows, -(-c * per // chunks), out=out, topo=topo)
+        return self.exchange.forward(x, ids, probs, run_chunk,
+                                     prepare_fn=lambda c, bin_rows, block_rows: self.topology(bin_rows, block_rows))
 
 
 def reference_rows(layer, x, ids, probs, sample):

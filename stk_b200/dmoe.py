@@ -388,7 +388,7 @@ class PeerExchange:
         self.result = torch.empty((self.capacity_rows, out_hidden), dtype=dtype, device=self.device)
         self._totals_host = torch.zeros(3 + chunks, dtype=torch.int64).pin_memory()
         self._epoch = [0, 0]
-        self._side = None
+        self._side = self._prep = None
 
     def _allocate(self, group):
         import torch.distributed._symmetric_memory as symm_mem
@@ -515,14 +515,20 @@ class PeerExchange:
         self.barrier(0)
         return self.gather_slots(state["tokens"], weights)
 
-    def forward(self, x, expert_ids, weights, expert_fn):
+    def forward(self, x, expert_ids, weights, expert_fn, prepare_fn=None):
         """One expert-parallel step with the exchange overlapped chunk by chunk.
 
         expert_fn(chunk, x_rows, bin_rows, block_rows, out_rows) runs the experts' MLP of one chunk:
         x_rows [rows, hidden] are the padded bins of the chunk's experts (bin_rows int32 on the
         device, one entry per expert of the chunk; block_rows their sum, a host int) and the result
         goes into out_rows [rows, out_hidden].  While chunk c is computed on the current stream, the
-        rows of chunk c + 1 arrive and the results of chunk c - 1 travel home on a second stream."""
+        rows of chunk c + 1 arrive and the results of chunk c - 1 travel home on a second stream.
+
+        prepare_fn(chunk, bin_rows, block_rows), optional, is called for every chunk as soon as the
+        bin sizes are known, before any rows are waited for, and what it returns is handed to
+        expert_fn as a sixth argument: the place for work that depends on the bin sizes only (the
+        chunk's topology, the pair kernel's work-item table), which would otherwise sit between the
+        products of one chunk and the next."""
         dev, chunks = self.device, self.chunks
         if self._side is None:
             self._side = torch.cuda.Stream(dev)
@@ -543,14 +549,40 @@ class PeerExchange:
             used_on_side.record_stream(side)
         t = self.totals()
         per = self.local_experts
+        bounds = [(-(-c * per // chunks), -(-(c + 1) * per // chunks)) for c in range(chunks)]  # le*chunks//per == c
+        prepared, ready = [None] * chunks, [None] * chunks
+
+        def prepare(c):
+            # chunk 0 on the current stream (its products come next); the others on a stream of their
+            # own, issued right after the products of the chunk before them, so that they run beside
+            # those products and the host never keeps the first products waiting
+            if prepare_fn is None or not t[3 + c]:
+                return
+            e0, e1 = bounds[c]
+            with torch.cuda.stream(main if c == 0 else self._prep):
+                prepared[c] = prepare_fn(c, bin_rows[e0:e1], t[3 + c] // self.block)
+                if c:
+                    ready[c] = torch.cuda.Event()
+                    ready[c].record(self._prep)
+
+        if prepare_fn is not None:
+            if self._prep is None:
+                self._prep = torch.cuda.Stream(dev)
+            self._prep.wait_stream(main)
+            prepare(0)
         row0 = 0
         for c in range(chunks):
             rows = t[3 + c]
-            e0, e1 = -(-c * per // chunks), -(-(c + 1) * per // chunks)     # experts with le*chunks//per == c
+            e0, e1 = bounds[c]
             main.wait_event(pushed[c])
+            if ready[c] is not None:
+                main.wait_event(ready[c])
             if rows:
+                extra = () if prepare_fn is None else (prepared[c],)
                 expert_fn(c, self.buf.recv[row0:row0 + rows], bin_rows[e0:e1], rows // self.block,
-                          self.result[row0:row0 + rows])
+                          self.result[row0:row0 + rows], *extra)
+            if c + 1 < chunks:
+                prepare(c + 1)
             done = torch.cuda.Event()
             done.record(main)
             with torch.cuda.stream(side):
@@ -562,6 +594,10 @@ class PeerExchange:
             home = torch.cuda.Event()
             home.record(side)
         main.wait_event(home)
+        if prepare_fn is not None:
+            # what prepare_fn allocated on its stream was read by the products on the current one: the
+            # stream's next allocations (which may reuse that memory) come after them
+            self._prep.wait_stream(main)
         return self.gather_slots(x.shape[0], weights)
 
 
