@@ -166,6 +166,17 @@ def _two_gpu_worker(rank, world, port, result_queue):
                 assert rows.shape[0] == block_rows * 128 == int(bin_rows.sum()) * 128
                 torch.mul(rows, 3, out=out)
             ok &= torch.equal(chunked.forward(x, ids, w, triple), want)
+
+            # with a prepare step: what it returns for a chunk (made on another stream, from the bin
+            # sizes alone) reaches that chunk's expert function
+            def scale_for(chunk, bin_rows, block_rows):
+                return torch.full((1,), 3.0, dtype=torch.float16, device=dev), int(bin_rows.sum())
+
+            def scaled(chunk, rows, bin_rows, block_rows, out, prepared):
+                factor, blocks = prepared
+                assert blocks == block_rows
+                torch.mul(rows, factor, out=out)
+            ok &= torch.equal(chunked.forward(x, ids, w, scaled, prepare_fn=scale_for), want)
             x = x + 1
         torch.cuda.synchronize()
         ok &= lib.device_status() == 0
