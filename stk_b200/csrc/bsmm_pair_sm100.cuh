@@ -266,8 +266,16 @@ __device__ __forceinline__ PairItem decode_item(const PairParams& p, int item) {
 #define STK_PACE_PAIRS 1
 #endif
 constexpr bool kPacePairs = STK_PACE_PAIRS != 0;
-constexpr unsigned int kPaceSlack = 3;          // pairs that may still be busy when a round starts
-constexpr unsigned long long kPaceLimitNs = 12000;
+// (Measured on the full-size dMoE products: slack 0, 3, 8 and limits of 12 and 40 us are level; a limit
+// of 4 us gives up too early and costs the DSD 5 %.)
+#ifndef STK_PACE_SLACK
+#define STK_PACE_SLACK 3
+#endif
+#ifndef STK_PACE_LIMIT_NS
+#define STK_PACE_LIMIT_NS 12000
+#endif
+constexpr unsigned int kPaceSlack = STK_PACE_SLACK;  // pairs that may still be busy when a round starts
+constexpr unsigned long long kPaceLimitNs = STK_PACE_LIMIT_NS;
 __device__ __forceinline__ void pace_gate(const unsigned int* pace, unsigned int target) {
   const unsigned long long t0 = globaltimer_ns();
   while (*reinterpret_cast<const volatile unsigned int*>(pace) < target) {
