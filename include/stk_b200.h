@@ -233,7 +233,8 @@ int stk_b200_transpose_meta_static(const int16_t* row_indices, const int16_t* co
  *
  * 1. block_mask: mask[br*Cb+bc] = 1 iff block (br,bc) of x holds an element that is not +-0
  *    (NaN and Inf count as nonzero, as sum(|x|) != 0 does in the reference).
- *    x: [rows, cols] row-major with leading dimension ld (elements), elem_bytes in {2,4}.
+ *    x: [rows, cols] row-major with leading dimension ld (elements), elem_bytes in {2,4}, or 1 for
+ *    8-bit floats (sign bit 0x80; element-wise kernels only, as in gather_blocks and to_dense).
  * 2. mask_to_offsets: offsets[0]=0, offsets[r+1] = number of set bytes in mask rows 0..r.
  *    The caller reads offsets[R] back to size data / row_indices / column_indices.
  * 3. mask_to_indices: row-major list of the set positions as int16 row / column indices.

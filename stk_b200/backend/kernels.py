@@ -454,8 +454,8 @@ def transpose_meta(row_indices, column_indices, block_cols):
 
 def _elem_bytes(t):
     n = t.element_size()
-    if n not in (2, 4):
-        raise ValueError(f"conversion kernels handle 2- and 4-byte elements, got {t.dtype}")
+    if n not in (2, 4) and t.dtype != FP8:
+        raise ValueError(f"conversion kernels handle 2- and 4-byte elements and float8_e4m3fn, got {t.dtype}")
     return n
 
 

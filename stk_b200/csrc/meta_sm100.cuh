@@ -619,7 +619,7 @@ static int gather_blocks_impl(const void* x, int64_t rows, int64_t cols, int64_t
   if (blocking <= 0 || rows < 0 || cols < 0 || nnz < 0 || rows % blocking || cols % blocking ||
       ld < cols)
     return STK_ERR_BAD_DIMS;
-  if (elem_bytes != 2 && elem_bytes != 4) return STK_ERR_BAD_DTYPE;
+  if (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4) return STK_ERR_BAD_DTYPE;
   if (nnz == 0) return STK_OK;
   if (nnz > INT32_MAX || cols > INT32_MAX) return STK_ERR_TOO_LARGE;
   if (x == nullptr || data == nullptr || row_indices.null() || column_indices.null())
@@ -646,7 +646,11 @@ static int gather_blocks_impl(const void* x, int64_t rows, int64_t cols, int64_t
     const int64_t total = nnz * blocking * blocking;
     const int64_t blocks = (total + 255) / 256;
     if (blocks > INT32_MAX) return STK_ERR_TOO_LARGE;
-    if (elem_bytes == 2)
+    if (elem_bytes == 1)
+      gather_blocks_generic_kernel<uint8_t><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+          static_cast<const uint8_t*>(x), ld, blocking, block_rows, block_cols, row_indices, column_indices,
+          total, static_cast<uint8_t*>(data));
+    else if (elem_bytes == 2)
       gather_blocks_generic_kernel<uint16_t><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
           static_cast<const uint16_t*>(x), ld, blocking, block_rows, block_cols, row_indices, column_indices,
           total, static_cast<uint16_t*>(data));
@@ -663,7 +667,7 @@ static int to_dense_impl(const void* data, const int32_t* offsets, IndexArray co
                          void* out, int64_t ld_out, void* stream) {
   if (blocking <= 0 || block_rows < 0 || block_cols < 0 || ld_out < block_cols * blocking)
     return STK_ERR_BAD_DIMS;
-  if (elem_bytes != 2 && elem_bytes != 4) return STK_ERR_BAD_DTYPE;
+  if (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4) return STK_ERR_BAD_DTYPE;
   const long long limit = index_limit(column_indices.wide);
   if (block_rows > limit || block_cols > limit || block_cols * blocking > INT32_MAX ||
       block_rows > (1 << 28))
@@ -694,7 +698,11 @@ static int to_dense_impl(const void* data, const int32_t* offsets, IndexArray co
     const int64_t rows = block_rows * blocking, cols = block_cols * blocking;
     const int64_t blocks = (rows * cols + 255) / 256;
     if (blocks > INT32_MAX) return STK_ERR_TOO_LARGE;
-    if (elem_bytes == 2)
+    if (elem_bytes == 1)
+      to_dense_generic_kernel<uint8_t><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+          static_cast<const uint8_t*>(data), offsets, column_indices, blocking, rows, cols,
+          static_cast<uint8_t*>(out), ld_out);
+    else if (elem_bytes == 2)
       to_dense_generic_kernel<uint16_t><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
           static_cast<const uint16_t*>(data), offsets, column_indices, blocking, rows, cols,
           static_cast<uint16_t*>(out), ld_out);
@@ -751,7 +759,7 @@ extern "C" int stk_b200_block_mask(const void* x, int64_t rows, int64_t cols, in
                                    int blocking, int elem_bytes, uint8_t* mask, void* stream) {
   if (blocking <= 0 || rows < 0 || cols < 0 || rows % blocking || cols % blocking || ld < cols)
     return STK_ERR_BAD_DIMS;
-  if (elem_bytes != 2 && elem_bytes != 4) return STK_ERR_BAD_DTYPE;
+  if (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4) return STK_ERR_BAD_DTYPE;
   if (rows == 0 || cols == 0) return STK_OK;
   if (x == nullptr || mask == nullptr) return STK_ERR_NULL_POINTER;
   const int64_t R = rows / blocking, Cb = cols / blocking;
@@ -772,7 +780,10 @@ extern "C" int stk_b200_block_mask(const void* x, int64_t rows, int64_t cols, in
     const int64_t nb = R * Cb;
     if ((nb + 255) / 256 > INT32_MAX) return STK_ERR_TOO_LARGE;
     const unsigned blocks = static_cast<unsigned>((nb + 255) / 256);
-    if (elem_bytes == 2)
+    if (elem_bytes == 1)  // 8-bit floats: the element-wise kernels only
+      block_mask_generic_kernel<uint8_t, 0x7f><<<blocks, 256, 0, s>>>(
+          static_cast<const uint8_t*>(x), ld, blocking, static_cast<int>(R), static_cast<int>(Cb), mask);
+    else if (elem_bytes == 2)
       block_mask_generic_kernel<uint16_t, 0x7fff><<<blocks, 256, 0, s>>>(
           static_cast<const uint16_t*>(x), ld, blocking, static_cast<int>(R), static_cast<int>(Cb), mask);
     else

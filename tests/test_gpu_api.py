@@ -384,3 +384,24 @@ def test_float8_products_match_the_dequantized_reference(stk, mode):
                     stk.ops.dds(torch.randn(256, rows, device="cuda").to(F8), s8)
     finally:
         kernels.PAIR_MODE = saved
+
+
+def test_float8_matrices_convert_like_16_bit_ones(stk):
+    """to_sparse / to_dense / ones_like of float8_e4m3fn data (element-wise kernels): the same topology and
+    the same values as the bfloat16 matrix they were quantised from, -0 counting as zero."""
+    F8 = torch.float8_e4m3fn
+    torch.manual_seed(5)
+    for blocking in (128, 16):
+        keep = (torch.rand(6, 5) < 0.4).repeat_interleave(blocking, 0).repeat_interleave(blocking, 1)
+        dense = (torch.randn(6 * blocking, 5 * blocking) * keep).to(F8)
+        dense[:blocking, :blocking] = torch.tensor(-0.0).to(F8)           # a block of -0: not a block
+        wide = dense.to(torch.bfloat16).cuda()
+        m8, m16 = stk.ops.to_sparse(dense.cuda(), blocking), stk.ops.to_sparse(wide, blocking)
+        m8.validate()
+        assert m8.data.dtype == F8
+        for a, b in ((m8.row_indices, m16.row_indices), (m8.column_indices, m16.column_indices), (m8.offsets, m16.offsets),
+                     (m8.column_indices_t, m16.column_indices_t), (m8.block_offsets_t, m16.block_offsets_t)):
+            assert torch.equal(a, b)
+        assert torch.equal(m8.data.view(torch.uint8), m16.data.to(F8).view(torch.uint8))
+        back = stk.ops.to_dense(m8)
+        assert back.dtype == F8 and torch.equal(back.to(torch.bfloat16), stk.ops.to_dense(m16))

@@ -53,7 +53,7 @@ def test_argument_validation_happens_before_any_launch():
     assert l.stk_b200_transpose_meta(null, null, -1, 4, null, null, null, null, 0, null) == -2
     assert l.stk_b200_transpose_meta(null, null, 4, 40000, null, null, null, null, 0, null) == -9
     assert l.stk_b200_block_mask(null, 8, 8, 8, 3, 2, null, null) == -2
-    assert l.stk_b200_block_mask(null, 8, 8, 8, 8, 1, null, null) == -3
+    assert l.stk_b200_block_mask(null, 8, 8, 8, 8, 3, null, null) == -3
     assert l.stk_b200_to_dense(null, null, null, 2, 2, 8, 8, null, 16, null) == -3
     # workspace sizing: small problems need none, large ones a bounded amount
     ws = l.stk_b200_transpose_meta_workspace_bytes
