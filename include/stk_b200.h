@@ -88,11 +88,10 @@ int stk_b200_device_status(int* status_host);
  * element, and the output (the blocks written by sdd, the dense result of dsd / dds) is bf16; fp32
  * accumulation as always, no scaling (a caller that quantised with scales applies their product to
  * the result).  Not in the reference.  The 8-bit kernels (tcgen05.mma kind::f8f6f4, 128 of K per
- * pipeline stage) read both operands with K contiguous, so only these layouts are accepted, anything
- * else is STK_ERR_BAD_LAYOUT: sdd with lhs row-major and rhs column-major; dsd with trans_sparse = 0
- * and rhs column-major; dds with lhs row-major and trans_sparse = 1.  Leading dimensions of 8-bit
- * operands are multiples of 16 elements.  pair_mode 0, 1 and 2; 3 is STK_ERR_BAD_DTYPE, and
- * so are the epilogues with an auxiliary tensor.
+ * pipeline stage) take the same layouts as the 16-bit ones (row- or column-major dense operands,
+ * blocks as stored or transposed).  Leading dimensions of 8-bit operands are multiples of 16
+ * elements.  pair_mode 0, 1 and 2; 3 is STK_ERR_BAD_DTYPE, and the epilogues with an auxiliary
+ * tensor are STK_ERR_BAD_DIMS.
  */
 
 /*

@@ -263,9 +263,10 @@ def _dense_layout(x):
     rows, cols = x.shape
     s0, s1 = x.stride()
     aligned = x.data_ptr() % 16 == 0
-    if s1 == 1 and s0 >= cols and s0 % 8 == 0 and aligned:
+    unit = 16 // x.element_size()          # rows start on 16-byte boundaries
+    if s1 == 1 and s0 >= cols and s0 % unit == 0 and aligned:
         return x, 0, s0
-    if s0 == 1 and s1 >= rows and s1 % 8 == 0 and aligned:
+    if s0 == 1 and s1 >= rows and s1 % unit == 0 and aligned:
         return x, 1, s1
     x = x.contiguous()
     return x, 0, x.stride(0)
@@ -297,21 +298,6 @@ def _same_dtype(what, *tensors):
                          + ", ".join(sorted(str(d) for d in dtypes)))
 
 
-def _k_major(x, k_dim):
-    """(tensor, colmajor, ld) of a 2-D float8 operand with its K dimension (k_dim: 0 or 1) contiguous,
-    which is the only layout the 8-bit kernels read; anything else is copied once."""
-    if x.dim() != 2:
-        raise DimensionError(f"expected a 2-D dense operand, got {x.dim()}-D")
-    other = 1 - k_dim
-    ld = x.stride(other)
-    if not (x.stride(k_dim) == 1 and ld >= x.shape[k_dim] and ld % 16 == 0 and x.data_ptr() % 16 == 0):
-        x = x.contiguous() if k_dim == 1 else x.t().contiguous().t()
-        ld = x.stride(other)
-        if ld % 16 != 0:
-            raise DimensionError("float8 operands need a K extent that is a multiple of 16")
-    return x, (1 if k_dim == 0 else 0), ld
-
-
 def dsd(shape, data, offsets, row_indices, column_indices, offsets_t, column_indices_t,
         block_offsets_t, transpose_a, rhs, out):
     """out = op(S) @ rhs, S given by its blocked CSR-COO fields; `shape` is op(S)'s shape."""
@@ -324,9 +310,7 @@ def dsd(shape, data, offsets, row_indices, column_indices, offsets_t, column_ind
     _validate_matmul_dims(M, K, N)
     _check_blocks(data)
     fp8 = data.dtype == FP8
-    if fp8 and transpose_a:
-        raise ValueError("dsd with float8 blocks reads them as stored (their columns are K); transpose_a is not supported")
-    rhs, rhs_colmajor, ld_rhs = _k_major(rhs, 0) if fp8 else _dense_layout(rhs)
+    rhs, rhs_colmajor, ld_rhs = _dense_layout(rhs)
     if transpose_a:
         meta = (offsets_t, column_indices_t, block_offsets_t)
         pairs = _use_pairs("cols", offsets, row_indices, column_indices, M // BLOCK, offsets_t, column_indices_t)
@@ -358,10 +342,7 @@ def dds(lhs, shape, data, offsets, row_indices, column_indices, offsets_t, colum
     _validate_matmul_dims(M, K, N)
     _check_blocks(data)
     fp8 = data.dtype == FP8
-    if fp8 and not transpose_b:
-        raise ValueError("dds with float8 blocks reads them transposed (their columns are K): pass the sparse "
-                         "operand as a .t() view")
-    lhs, lhs_colmajor, ld_lhs = _k_major(lhs, 1) if fp8 else _dense_layout(lhs)
+    lhs, lhs_colmajor, ld_lhs = _dense_layout(lhs)
     if transpose_b:
         meta = (offsets, column_indices, None)
         pairs = _use_pairs("rows", offsets, row_indices, column_indices, K // BLOCK, offsets_t, column_indices_t)
@@ -402,8 +383,8 @@ def sdd(lhs, rhs, shape, out, offsets, row_indices, column_indices, epilogue=0, 
     fp8 = lhs.dtype == FP8
     if fp8 and epilogue in (2, 3):
         raise ValueError("the training epilogues are not available with float8 operands")
-    lhs, lhs_colmajor, ld_lhs = _k_major(lhs, 1) if fp8 else _dense_layout(lhs)
-    rhs, rhs_colmajor, ld_rhs = _k_major(rhs, 0) if fp8 else _dense_layout(rhs)
+    lhs, lhs_colmajor, ld_lhs = _dense_layout(lhs)
+    rhs, rhs_colmajor, ld_rhs = _dense_layout(rhs)
     pairs = _use_pairs("tiles", offsets, row_indices, column_indices, N // BLOCK)
     if pairs == 0 and not fp8 and (PAIR_MODE == "3" or (PAIR_MODE == "auto" and out.shape[0] >= SDD_ROW_MIN_BLOCKS)):
         pairs = 3            # two blocks of a block row per 128x256 tile

@@ -314,8 +314,8 @@ def train_step(dev="cuda"):
 def products_fp8(dev="cuda", experts=8, rows_per_expert=4096, hidden=4096, ffn=14336):
     """The forward products of one GPU's share of the dMoE-XL layer (BASELINE configs[4] / 8) with
     float8_e4m3fn operands against the same products in bfloat16 and against cuBLASLt's float8 GEMM
-    (torch._scaled_mm, unit scales) of the same useful FLOPs.  Both weights are stored with the
-    contraction dimension contiguous ([E*f, h] for w1, [h, E*f] for w2), as the 8-bit kernels read them."""
+    (torch._scaled_mm, unit scales) of the same useful FLOPs.  The weights are stored as in bench.py:
+    w1 [E*f, h] (K contiguous), w2 [E*f, h] row-major (N contiguous), in both formats."""
     from stk_b200 import dmoe
     f8 = torch.float8_e4m3fn
     rows = experts * rows_per_expert
@@ -323,22 +323,21 @@ def products_fp8(dev="cuda", experts=8, rows_per_expert=4096, hidden=4096, ffn=1
     topo = dmoe.topology_from_bins(bins, rows // 128, ffn, torch.bfloat16, dev, materialize=False)
     x = torch.randn(rows, hidden, device=dev, dtype=torch.bfloat16)
     w1 = torch.randn(experts * ffn, hidden, device=dev, dtype=torch.bfloat16) * 0.02      # [E*f, h]
-    w2t = torch.randn(hidden, experts * ffn, device=dev, dtype=torch.bfloat16) * 0.02     # [h, E*f]
-    w2 = w2t.t().contiguous()                                                             # [E*f, h] for bf16
-    x8, w18, w2t8 = x.to(f8), w1.to(f8), w2t.to(f8)
+    w2 = torch.randn(experts * ffn, hidden, device=dev, dtype=torch.bfloat16) * 0.02      # [E*f, h]
+    x8, w18, w28 = x.to(f8), w1.to(f8), w2.to(f8)
     act = stk.ops.sdd(x, w1.t(), topo)
     act8 = stk.Matrix(topo.size(), act.data.to(f8), topo.row_indices, topo.column_indices, topo.offsets,
                       topo.column_indices_t, topo.offsets_t, topo.block_offsets_t)
     y = torch.empty(rows, hidden, device=dev, dtype=torch.bfloat16)
     one = torch.ones((), device=dev)
-    wa8, wb8 = w18[:ffn], w2t8[:, :ffn].contiguous()                 # one expert's weights for the dense twins
+    wa8, wb8 = w18[:ffn], w28[:ffn].t().contiguous()                 # one expert's weights, K contiguous, for the dense twins
     a28 = torch.randn(rows, ffn, device=dev, dtype=torch.bfloat16).to(f8)
     flops = 2.0 * rows * ffn * hidden
     out = []
     for name, fn16, fn8, twin in (
             ("sdd x@w1", lambda: stk.ops.sdd(x, w1.t(), topo), lambda: stk.ops.sdd(x8, w18.t(), topo),
              lambda: torch._scaled_mm(x8, wa8.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)),
-            ("dsd h@w2", lambda: stk.ops.dsd(act, w2, out=y), lambda: stk.ops.dsd(act8, w2t8.t(), out=y),
+            ("dsd h@w2", lambda: stk.ops.dsd(act, w2, out=y), lambda: stk.ops.dsd(act8, w28, out=y),
              lambda: torch._scaled_mm(a28, wb8.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16))):
         ms = time_interleaved({"bf16": fn16, "fp8": fn8, "cublaslt_fp8": twin}, rounds=5, iters=4)
         out.append({"product": name, "bf16_tflops": round(flops / ms["bf16"] / 1e9, 1),

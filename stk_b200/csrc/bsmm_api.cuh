@@ -60,10 +60,9 @@ static int sdd_impl(const void* lhs, const void* rhs, void* out, const int32_t* 
   const int in8 = dtype == STK_F8E4M3 ? 1 : 0;
   const int out_fmt = in8 ? STK_BF16 : dtype;
   if (in8) {
-    // both operands K-major: lhs row-major, rhs column-major; plain or GeLU epilogue
-    if (lhs_colmajor || !rhs_colmajor || has_aux) return STK_ERR_BAD_LAYOUT;
-    if ((rc = check_dense8(lhs, ld_lhs, K)) != STK_OK) return rc;
-    if ((rc = check_dense8(rhs, ld_rhs, K)) != STK_OK) return rc;
+    if (has_aux) return STK_ERR_BAD_DIMS;  // plain or GeLU epilogue only
+    if ((rc = check_dense8(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) return rc;
+    if ((rc = check_dense8(rhs, ld_rhs, rhs_colmajor ? K : N)) != STK_OK) return rc;
   } else {
     if ((rc = check_dense(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) return rc;
     if ((rc = check_dense(rhs, ld_rhs, rhs_colmajor ? K : N)) != STK_OK) return rc;
@@ -182,9 +181,7 @@ static int dsd_impl(const void* data, const int32_t* offsets, IndexArray column_
   const int in8 = dtype == STK_F8E4M3 ? 1 : 0;
   const int out_fmt = in8 ? STK_BF16 : dtype;
   if (in8) {
-    // both operands K-major: the blocks as stored, rhs column-major
-    if (trans_sparse || !rhs_colmajor) return STK_ERR_BAD_LAYOUT;
-    if ((rc = check_dense8(rhs, ld_rhs, K)) != STK_OK) return rc;
+    if ((rc = check_dense8(rhs, ld_rhs, rhs_colmajor ? K : N)) != STK_OK) return rc;
   } else if ((rc = check_dense(rhs, ld_rhs, rhs_colmajor ? K : N)) != STK_OK) {
     return rc;
   }
@@ -272,9 +269,7 @@ static int dds_impl(const void* lhs, const void* data, const int32_t* offsets, I
   const int in8 = dtype == STK_F8E4M3 ? 1 : 0;
   const int out_fmt = in8 ? STK_BF16 : dtype;
   if (in8) {
-    // both operands K-major: lhs row-major, the blocks used transposed (their columns are K)
-    if (lhs_colmajor || !trans_sparse) return STK_ERR_BAD_LAYOUT;
-    if ((rc = check_dense8(lhs, ld_lhs, K)) != STK_OK) return rc;
+    if ((rc = check_dense8(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) return rc;
   } else if ((rc = check_dense(lhs, ld_lhs, lhs_colmajor ? M : K)) != STK_OK) {
     return rc;
   }

@@ -207,9 +207,11 @@ struct TileWalker {
 
 __device__ __forceinline__ void load_operand_pair(const CUtensorMap* tm, uint32_t smem_dst,
                                                   uint32_t leader_bar, int mn_major, int mn_elem,
-                                                  int k_elem) {
+                                                  int k_elem, bool bytes8 = false) {
   if (!mn_major) {
     tma_load_2d_pair(smem_dst, tm, leader_bar, k_elem, mn_elem);
+  } else if (bytes8) {
+    tma_load_2d_pair(smem_dst, tm, leader_bar, mn_elem, k_elem);  // see load_operand
   } else {
     tma_load_3d_pair(smem_dst, tm, leader_bar, 0, k_elem, mn_elem >> 6);
   }
@@ -368,7 +370,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_arrive_expect_tx(full_bar(stage), 2 * kStageBytes);
         }
         load_operand_pair(tm, dst0 + stage * kStageBytes, leader_full0 + 8u * stage, mn_major, mn_elem,
-                          k_elem);
+                          k_elem, kF8);
         if (++stage == kPStages) {
           stage = 0;
           phase ^= 1u;
@@ -438,11 +440,13 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (rank == 0 && lane == 0) {
-      const uint32_t idesc = kF8 ? make_idesc_f8(256, 256) : make_idesc_f16(p.fmt, p.a_mn, p.b_mn, 256, 256);
+      const uint32_t idesc =
+          kF8 ? make_idesc_f8(p.a_mn, p.b_mn, 256, 256) : make_idesc_f16(p.fmt, p.a_mn, p.b_mn, 256, 256);
       const uint32_t a_lo0 = smem_desc_lo(smem_base, p.a_mn ? kOperandTileBytes / 2 : 16u);
       const uint32_t b_lo0 = smem_desc_lo(smem_base + kOperandTileBytes, p.b_mn ? kOperandTileBytes / 2 : 16u);
-      const uint32_t a_kstep = (p.a_mn ? kUmmaK * 128u : kUmmaK * 2u) >> 4;
-      const uint32_t b_kstep = (p.b_mn ? kUmmaK * 128u : kUmmaK * 2u) >> 4;
+      constexpr uint32_t kMnStep = (kF8 ? 2u : 1u) * kUmmaK * 128u;  // see bsmm_kernel
+      const uint32_t a_kstep = (p.a_mn ? kMnStep : kUmmaK * 2u) >> 4;
+      const uint32_t b_kstep = (p.b_mn ? kMnStep : kUmmaK * 2u) >> 4;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -679,7 +683,7 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = kUseDependentLaunch ? 1 : 0;
-  if (p.in8 && (p.epilogue >= kEpilogueGeluKeep || p.a_mn || p.b_mn)) return STK_ERR_BAD_LAYOUT;
+  if (p.in8 && p.epilogue >= kEpilogueGeluKeep) return STK_ERR_BAD_DIMS;
   const cudaError_t err =
       p.in8 ? cudaLaunchKernelEx(&cfg, bsmm_pair_kernel<false, true>, tmA, tmB, tmC, tmX, p)
       : p.epilogue >= kEpilogueGeluKeep ? cudaLaunchKernelEx(&cfg, bsmm_pair_kernel<true>, tmA, tmB, tmC, tmX, p)

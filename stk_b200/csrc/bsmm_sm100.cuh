@@ -163,10 +163,14 @@ __device__ __forceinline__ TileInfo tile_info(const BsmmParams& p, int tile) {
 //   K-major : 2-D box {64 (K), 128 (M/N)} at (k_elem, mn_elem).
 //   MN-major: 3-D box {64 (M/N), 64 (K), 2 (groups of 64 M/N)} at (0, k_elem, mn_elem / 64); the two
 //             groups land 8 KiB apart, which is the leading byte offset of the UMMA descriptor.
+//   8-bit MN-major (bytes8): 128 elements of M/N fill a swizzle row, so the tile is one 2-D box
+//             {128 (M/N), 128 (K)} at (mn_elem, k_elem).
 __device__ __forceinline__ void load_operand(const CUtensorMap* tm, uint32_t smem_dst, uint32_t bar,
-                                             int mn_major, int mn_elem, int k_elem) {
+                                             int mn_major, int mn_elem, int k_elem, bool bytes8 = false) {
   if (!mn_major) {
     tma_load_2d(smem_dst, tm, bar, k_elem, mn_elem);
+  } else if (bytes8) {
+    tma_load_2d(smem_dst, tm, bar, mn_elem, k_elem);
   } else {
     tma_load_3d(smem_dst, tm, bar, 0, k_elem, mn_elem >> 6);
   }
@@ -406,8 +410,8 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           const uint32_t b_dst = a_dst + kOperandTileBytes;
           mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
-          load_operand(&tmA, a_dst, full_bar(stage), p.a_mn, a_mn_elem, a_k_elem);
-          load_operand(&tmB, b_dst, full_bar(stage), p.b_mn, b_mn_elem, b_k_elem);
+          load_operand(&tmA, a_dst, full_bar(stage), p.a_mn, a_mn_elem, a_k_elem, kF8);
+          load_operand(&tmB, b_dst, full_bar(stage), p.b_mn, b_mn_elem, b_k_elem, kF8);
         } else {
           ok = 0;
         }
@@ -458,12 +462,15 @@ bsmm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = kF8 ? make_idesc_f8(kBlk) : make_idesc_f16(p.fmt, p.a_mn, p.b_mn, kBlk);
+      const uint32_t idesc = kF8 ? make_idesc_f8(p.a_mn, p.b_mn, kBlk) : make_idesc_f16(p.fmt, p.a_mn, p.b_mn, kBlk);
       // Descriptor low words of stage 0 and their step per 16 elements of K and per stage.
       const uint32_t a_lo0 = smem_desc_lo(smem_base, p.a_mn ? kOperandTileBytes / 2 : 16u);
       const uint32_t b_lo0 = smem_desc_lo(smem_base + kOperandTileBytes, p.b_mn ? kOperandTileBytes / 2 : 16u);
-      const uint32_t a_kstep = (p.a_mn ? kUmmaK * 128u : kUmmaK * 2u) >> 4;
-      const uint32_t b_kstep = (p.b_mn ? kUmmaK * 128u : kUmmaK * 2u) >> 4;
+      // bytes between the operand slices of two consecutive MMAs: 32 bytes along a K-major row, or the
+      // rows of one MMA's K (16 for 16-bit, 32 for 8-bit operands) x 128 bytes in an MN-major tile
+      constexpr uint32_t kMnStep = (kF8 ? 2u : 1u) * kUmmaK * 128u;
+      const uint32_t a_kstep = (p.a_mn ? kMnStep : kUmmaK * 2u) >> 4;
+      const uint32_t b_kstep = (p.b_mn ? kMnStep : kUmmaK * 2u) >> 4;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -618,8 +625,12 @@ static int encode_map(CUtensorMap* tm, const void* base, int dtype, int64_t inne
 
 // Tensor map of an operand whose contiguous dimension is M/N (`mn` elements per row, `k` rows, `ld`
 // elements between rows), described in three dimensions {64, k, mn/64} with boxes {64, 64, 2}.
+static int encode_map(CUtensorMap* tm, const void* base, int dtype, int64_t inner, int64_t outer,
+                      int64_t ld, int box_outer);
 static int encode_map_mn_major(CUtensorMap* tm, const void* base, int dtype, int64_t mn, int64_t k,
                                int64_t ld) {
+  // bytes: 128 elements of M/N are one swizzle row, the tile is a plain 2-D box {128 M/N, 128 K}
+  if (dtype == STK_F8E4M3) return encode_map(tm, base, dtype, mn, k, ld, kBlk);
   PFN_cuTensorMapEncodeTiled_v12000 fn = get_encode_fn();
   if (fn == nullptr) return STK_ERR_DRIVER;
   const cuuint64_t dims[3] = {static_cast<cuuint64_t>(kBK), static_cast<cuuint64_t>(k),
@@ -712,7 +723,7 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensor
   const int rc = device_info(&d);
   if (rc != STK_OK) return rc;
   const int grid = p.num_tiles < d->sms ? p.num_tiles : d->sms;
-  if (p.in8 && (p.epilogue >= kEpilogueGeluKeep || p.a_mn || p.b_mn)) return STK_ERR_BAD_LAYOUT;
+  if (p.in8 && p.epilogue >= kEpilogueGeluKeep) return STK_ERR_BAD_DIMS;
   const cudaError_t err =
       p.in8 ? launch_dependent(bsmm_kernel<false, true>, grid, kThreads, kSmemBytes, stream, tmA, tmB, tmC, tmX, p)
       : p.epilogue >= kEpilogueGeluKeep

@@ -169,10 +169,10 @@ bsmm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
             const uint32_t dst = dst0 + stage * kWStageBytes;
             const uint32_t bar = leader_full0 + 8u * stage;
-            load_operand_pair(tm, dst, bar, mn_major, mn_elem, k_elem + ks * kStageK);
+            load_operand_pair(tm, dst, bar, mn_major, mn_elem, k_elem + ks * kStageK, kF8);
             if (!sparse_side)
               load_operand_pair(tm, dst + kOperandTileBytes, bar, mn_major, mn_elem + 2 * kBlk,
-                                k_elem + ks * kStageK);
+                                k_elem + ks * kStageK, kF8);
             if (++stage == kWStages) {
               stage = 0;
               phase ^= 1u;
@@ -196,12 +196,14 @@ bsmm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer (leader CTA only)
     if (rank == 0 && lane == 0) {
-      const uint32_t idesc = kF8 ? make_idesc_f8(256, 256) : make_idesc_f16(p.fmt, p.a_mn, p.b_mn, 256, 256);
+      const uint32_t idesc =
+          kF8 ? make_idesc_f8(p.a_mn, p.b_mn, 256, 256) : make_idesc_f16(p.fmt, p.a_mn, p.b_mn, 256, 256);
       const int s_mn = dsd ? p.a_mn : p.b_mn, d_mn = dsd ? p.b_mn : p.a_mn;
       const uint32_t s_lo0 = smem_desc_lo(smem_base, s_mn ? kOperandTileBytes / 2 : 16u);
       const uint32_t d_lo0 = smem_desc_lo(smem_base + kOperandTileBytes, d_mn ? kOperandTileBytes / 2 : 16u);
-      const uint32_t s_kstep = (s_mn ? kUmmaK * 128u : kUmmaK * 2u) >> 4;
-      const uint32_t d_kstep = (d_mn ? kUmmaK * 128u : kUmmaK * 2u) >> 4;
+      constexpr uint32_t kMnStep = (kF8 ? 2u : 1u) * kUmmaK * 128u;  // see bsmm_kernel
+      const uint32_t s_kstep = (s_mn ? kMnStep : kUmmaK * 2u) >> 4;
+      const uint32_t d_kstep = (d_mn ? kMnStep : kUmmaK * 2u) >> 4;
       int stage = 0;
       uint32_t phase = 0, tile_phase = 0;
       // As in the pair kernel: the next stage's barrier is probed between the MMAs of this one.
@@ -397,7 +399,6 @@ static int launch_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, const Pai
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = kUseDependentLaunch ? 1 : 0;
-  if (p.in8 && (p.a_mn || p.b_mn)) return STK_ERR_BAD_LAYOUT;
   const cudaError_t err = p.in8 ? cudaLaunchKernelEx(&cfg, bsmm_wide_kernel<true>, tmA, tmB, p)
                                 : cudaLaunchKernelEx(&cfg, bsmm_wide_kernel<false>, tmA, tmB, p);
   return err == cudaSuccess ? STK_OK : STK_ERR_LAUNCH;

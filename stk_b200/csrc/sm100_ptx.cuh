@@ -368,11 +368,13 @@ __host__ __device__ __forceinline__ uint32_t make_idesc_f16(int fmt, int a_mn_ma
   return d;
 }
 
-// Instruction descriptor for kind::f8f6f4 with e4m3 operands (format code 0 in both fields), both
-// K-major, fp32 accumulation.
-__host__ __device__ __forceinline__ uint32_t make_idesc_f8(int n, int m = 128) {
+// Instruction descriptor for kind::f8f6f4 with e4m3 operands (format code 0 in both fields), fp32
+// accumulation; 8-bit operands may be K-major or MN-major like 16-bit ones.
+__host__ __device__ __forceinline__ uint32_t make_idesc_f8(int a_mn_major, int b_mn_major, int n, int m = 128) {
   uint32_t d = 0;
   d |= 1u << 4;  // D format: F32
+  d |= static_cast<uint32_t>(a_mn_major) << 15;
+  d |= static_cast<uint32_t>(b_mn_major) << 16;
   d |= static_cast<uint32_t>(n >> 3) << 17;
   d |= static_cast<uint32_t>(m >> 4) << 24;
   return d;

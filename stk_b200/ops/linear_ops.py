@@ -13,9 +13,8 @@ def _fields(m):
             m.block_offsets_t)
 
 
-# float8_e4m3fn operands (not in the reference): fp32 accumulation, bfloat16 result, forward only.  The
-# 8-bit kernels read both operands with K contiguous, so a dense operand in the other layout is copied
-# once, dsd takes the sparse operand as stored and dds as a .t() view.
+# float8_e4m3fn operands (not in the reference): fp32 accumulation, bfloat16 result, forward only; the
+# same operand layouts and .t() views as with 16-bit operands.
 def _is_fp8(*tensors):
     return any(t.dtype == kernels.FP8 for t in tensors)
 

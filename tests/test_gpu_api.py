@@ -331,10 +331,10 @@ def test_more_than_32767_blocks_per_side(stk):
 
 @pytest.mark.parametrize("mode", ["0", "1", "2", "auto"])
 def test_float8_products_match_the_dequantized_reference(stk, mode):
-    """float8_e4m3fn operands (an extension): every product equals the fp32 product of the dequantized
-    operands up to the one bfloat16 rounding of the result, in the 128x128 kernel and on CTA pairs, for
-    a K that is not a multiple of a pipeline stage (416 = 3 * 128 + 32) and with operands handed over
-    in the layout the 8-bit kernels do not read (they are copied once)."""
+    """float8_e4m3fn operands (an extension): every product, in every operand layout the 16-bit products
+    take (row- / column-major dense operands, blocks as stored or transposed), equals the fp32 product of
+    the dequantized operands up to the one bfloat16 rounding of the result - in the 128x128 kernel and on
+    CTA pairs in both shapes, for a K that is not a multiple of a pipeline stage (416 = 3 * 128 + 32)."""
     from stk_b200 import dmoe
     from stk_b200.backend import kernels
     F8 = torch.float8_e4m3fn
@@ -343,6 +343,7 @@ def test_float8_products_match_the_dequantized_reference(stk, mode):
     cases = [stk.random.randn((512, 768), 0.5, 128).to("cuda"),
              dmoe.block_diagonal_topology(torch.tensor([2, 1, 0, 3]) * 128, 256, torch.float16, "cuda")]
     cases[1].data.normal_(0, 0.5)
+    rand8 = lambda *shape: torch.randn(*shape, device="cuda").to(F8)
     saved = kernels.PAIR_MODE
     kernels.PAIR_MODE = mode
     try:
@@ -350,38 +351,37 @@ def test_float8_products_match_the_dequantized_reference(stk, mode):
             rows, cols = topo.size()
             dense16 = lambda m: stk.ops.to_dense(m).float()
             pattern = dense16(stk.ops.ones_like(topo))
+            s8 = stk.Matrix(topo.size(), (topo.data.float() * 2).to(F8), topo.row_indices, topo.column_indices,
+                            topo.offsets, topo.column_indices_t, topo.offsets_t, topo.block_offsets_t)
+            s8.validate()
+            s_dense = dense16(stk.Matrix(topo.size(), s8.data.to(torch.bfloat16), topo.row_indices,
+                                         topo.column_indices, topo.offsets, topo.column_indices_t,
+                                         topo.offsets_t, topo.block_offsets_t))
             for _ in range(2):          # the second round runs with the kernel-choice statistics known
-                # sdd: [rows, 416] x [416, cols] on the topology
-                a = torch.randn(rows, 416, device="cuda").to(F8)
-                b = torch.randn(cols, 416, device="cuda").to(F8)          # stored [N, K]: K contiguous
-                ref = (a.float() @ b.float().t()) * pattern
-                out = stk.ops.sdd(a, b.t(), topo)
-                assert out.data.dtype == torch.bfloat16
-                assert_product_close(dense16(out), ref, "fp8 sdd")
-                out = stk.ops.sdd(a, b.t().contiguous(), topo)             # N contiguous: copied to K-major
-                assert_product_close(dense16(out), ref, "fp8 sdd, copied rhs")
-                gelu = stk.ops.sdd_gelu(a, b.t(), topo)
+                # sdd: [rows, 416] x [416, cols] on the topology, the four layout combinations
+                a, at = rand8(rows, 416), rand8(416, rows)            # lhs row-major / stored transposed
+                b, bt = rand8(416, cols), rand8(cols, 416)            # rhs row-major / stored transposed
+                for lhs in (a, at.t()):
+                    for rhs in (b, bt.t()):
+                        ref = (lhs.float() @ rhs.float()) * pattern
+                        out = stk.ops.sdd(lhs, rhs, topo)
+                        assert out.data.dtype == torch.bfloat16
+                        assert_product_close(dense16(out), ref, "fp8 sdd")
+                gelu = stk.ops.sdd_gelu(a, bt.t(), topo)
+                ref = (a.float() @ bt.float().t()) * pattern
                 assert_product_close(dense16(gelu), torch.nn.functional.gelu(ref) * pattern, "fp8 sdd + gelu")
-                # dsd: S [rows, cols] (fp8 blocks) x [cols, 256]
-                s8 = stk.Matrix(topo.size(), (topo.data.float() * 2).to(F8), topo.row_indices, topo.column_indices,
-                                topo.offsets, topo.column_indices_t, topo.offsets_t, topo.block_offsets_t)
-                s8.validate()
-                s_dense = dense16(stk.Matrix(topo.size(), s8.data.to(torch.bfloat16), topo.row_indices,
-                                             topo.column_indices, topo.offsets, topo.column_indices_t,
-                                             topo.offsets_t, topo.block_offsets_t))
-                r = torch.randn(256, cols, device="cuda").to(F8)           # stored [N, K]
-                y = stk.ops.dsd(s8, r.t())
-                assert y.dtype == torch.bfloat16
-                assert_product_close(y, s_dense @ r.float().t(), "fp8 dsd")
-                assert_product_close(stk.ops.dsd(s8, r.t().contiguous()), s_dense @ r.float().t(), "fp8 dsd, copied rhs")
-                # dds: [256, cols] x S^T [cols, rows]
-                lhs = torch.randn(256, cols, device="cuda").to(F8)
-                z = stk.ops.dds(lhs, s8.t())
-                assert_product_close(z, lhs.float() @ s_dense.t(), "fp8 dds")
-                with pytest.raises(ValueError):
-                    stk.ops.dsd(s8.t(), torch.randn(rows, 256, device="cuda").to(F8))
-                with pytest.raises(ValueError):
-                    stk.ops.dds(torch.randn(256, rows, device="cuda").to(F8), s8)
+                # dsd: op(S) x dense, S as stored and transposed, dense row- and column-major
+                for op_s, op_dense, inner in ((s8, s_dense, cols), (s8.t(), s_dense.t(), rows)):
+                    r, rt = rand8(inner, 256), rand8(256, inner)
+                    for rhs in (r, rt.t()):
+                        y = stk.ops.dsd(op_s, rhs)
+                        assert y.dtype == torch.bfloat16
+                        assert_product_close(y, op_dense @ rhs.float(), "fp8 dsd")
+                # dds: dense x op(S)
+                for op_s, op_dense, inner in ((s8, s_dense, rows), (s8.t(), s_dense.t(), cols)):
+                    l, lt = rand8(256, inner), rand8(inner, 256)
+                    for lhs in (l, lt.t()):
+                        assert_product_close(stk.ops.dds(lhs, op_s), lhs.float() @ op_dense, "fp8 dds")
     finally:
         kernels.PAIR_MODE = saved
 

@@ -304,20 +304,19 @@ def test_matrix_accepts_int32_block_indices():
         full(i32.long(), i32.long()).validate()
 
 
-def test_float8_entry_points_refuse_layouts_they_cannot_read():
-    """dtype 2 (float8 e4m3 operands): both operands must have K contiguous, the row kernels do not
-    take part, and the Python launchers refuse mixed operand types before anything runs."""
+def test_float8_entry_points_check_their_arguments():
+    """dtype 2 (float8 e4m3 operands): rows of 8-bit operands start on 16-byte boundaries, the 128x256
+    kernels and the training epilogues do not take part, and the Python launchers refuse mixed operand
+    types before anything runs."""
     from stk_b200.backend import kernels, lib
     l = lib.load()
     null, fake = ctypes.c_void_p(0), ctypes.c_void_p(1 << 20)
-    # sdd: lhs column-major, then rhs row-major
-    assert l.stk_b200_sdd(fake, fake, fake, fake, fake, fake, 128, 128, 128, 1, 1, 128, 1, 128, 2, 0, 0, null, null, null) == -4
-    assert l.stk_b200_sdd(fake, fake, fake, fake, fake, fake, 128, 128, 128, 1, 0, 128, 0, 128, 2, 0, 0, null, null, null) == -4
-    # dsd with the blocks transposed, dds with the blocks as stored
-    assert l.stk_b200_dsd(fake, fake, fake, fake, fake, fake, 128, 128, 128, 1, 1, 1, 128, 128, 2, 0, null, null) == -4
-    assert l.stk_b200_dds(fake, fake, fake, fake, fake, fake, 128, 128, 128, 1, 0, 128, 0, 128, 2, 0, null, null) == -4
-    # the 128x256 kernels are 16-bit only
+    # a leading dimension that is not a multiple of 16 elements
+    assert l.stk_b200_sdd(fake, fake, fake, fake, fake, fake, 128, 128, 128, 1, 0, 136, 1, 128, 2, 0, 0, null, null, null) == -4
+    assert l.stk_b200_dsd(fake, fake, fake, fake, fake, fake, 128, 128, 128, 1, 0, 0, 136, 128, 2, 0, null, null) == -4
+    # the 128x256 kernels are 16-bit only; no auxiliary tensor with 8-bit operands
     assert l.stk_b200_dsd(fake, fake, fake, fake, fake, fake, 128, 256, 128, 1, 0, 1, 128, 256, 2, 3, null, null) == -3
+    assert l.stk_b200_sdd(fake, fake, fake, fake, fake, fake, 128, 128, 128, 1, 0, 128, 1, 128, 2, 0, 2, fake, null, null) == -2
     f8 = lambda *shape: torch.zeros(*shape).to(torch.float8_e4m3fn)
     h = lambda *shape: torch.zeros(*shape, dtype=torch.float16)
     idx = torch.zeros(1, dtype=torch.int16)
