@@ -65,6 +65,10 @@ const char* stk_b200_error_string(int code);
  * No counterpart in the reference (its kernels cannot report anything).
  */
 int stk_b200_device_status(int* status_host);
+/* Diagnostic for STK_ERR_DEVICE_TIMEOUT: which wait ran out first (0: none), read and cleared like the
+ * status word: warp of the waiting thread | its CTA's rank in the cluster << 8 | shared-memory address
+ * of the barrier << 12 | awaited parity << 31.  Synchronises the device. */
+int stk_b200_timeout_site(unsigned int* site_host);
 
 /*
  * pair_mode (sdd / dsd / dds): 0 runs one 128x128 output tile per CTA.  1 runs 256x256 supertiles on

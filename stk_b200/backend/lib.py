@@ -25,6 +25,7 @@ SIGNATURES = {
     "stk_b200_version": (_c_int, []),
     "stk_b200_error_string": (ctypes.c_char_p, [_c_int]),
     "stk_b200_device_status": (_c_int, [ctypes.POINTER(_c_int)]),
+    "stk_b200_timeout_site": (_c_int, [ctypes.POINTER(ctypes.c_uint)]),
     "stk_b200_sdd": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64,
                               _c_i64, _c_int, _c_i64, _c_int, _c_i64, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr]),
     "stk_b200_dsd": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64,
@@ -78,7 +79,7 @@ _lib = None
 # after its entry point (stk_b200_sdd, stk_b200_ep_dispatch, ...), so that a timeline shows which
 # product or exchange step a kernel belongs to.  Off by default: a range costs two calls per launch.
 NVTX = os.environ.get("STK_B200_NVTX", "0") == "1"
-_UNTRACED = ("stk_b200_error_string", "stk_b200_device_status")
+_UNTRACED = ("stk_b200_error_string", "stk_b200_device_status", "stk_b200_timeout_site")
 
 
 class _Traced:

@@ -431,7 +431,13 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // The leader tells its MMA issuer that the stream is over.
       if (arms && ok) {
         if (mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+          // Unlike a real stage, whose barrier only completes when its bytes have landed (long after
+          // the tag was written), this arrival completes the phase at once: the tag has to be
+          // visible first.  (Without the fence the MMA issuer, probing the barrier at that moment, was
+          // seen to read the slot's old tag - once in some thousand launches of tiny products - take the
+          // slot for a stage and wait for ever for the next.)
           stage_flags[stage] = kFlagEnd;
+          __threadfence_block();
           mbar_arrive(full_bar(stage));
         }
       }
@@ -462,8 +468,10 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!ready) {
           const bool got = mbar_wait(full_bar(stage), phase, abort_flag);
           if (!got) break;
-          flags = stage_flags[stage];
         }
+        // read here, not with the probe: a probe that finds the phase complete may have raced with the
+        // producer's arrival (see the end-of-stream tag)
+        flags = stage_flags[stage];
         if (flags & kFlagEnd) break;
         if (flags & kFlagFirst) {
           if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) break;
@@ -477,7 +485,6 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         umma_pair<kF8>(d_tmem, smem_desc_join(a_lo), smem_desc_join(b_lo), idesc, (flags & kFlagFirst) ? 0u : 1u);
         umma_pair<kF8>(d_tmem, smem_desc_join(a_lo + a_kstep), smem_desc_join(b_lo + b_kstep), idesc, 1u);
         ready = mbar_test_wait(full_bar(next_stage), next_phase);
-        const uint32_t next_flags = stage_flags[next_stage];  // not waited for here; only used if `ready`
         umma_pair<kF8>(d_tmem, smem_desc_join(a_lo + 2 * a_kstep), smem_desc_join(b_lo + 2 * b_kstep), idesc, 1u);
         umma_pair<kF8>(d_tmem, smem_desc_join(a_lo + 3 * a_kstep), smem_desc_join(b_lo + 3 * b_kstep), idesc, 1u);
         umma_commit_pair(empty_bar(stage), 3);  // frees the stage in both CTAs
@@ -488,7 +495,6 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         stage = next_stage;
         phase = next_phase;
-        flags = next_flags;
       }
     }
     __syncwarp();

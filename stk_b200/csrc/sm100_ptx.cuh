@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "status.cuh"
+
 namespace stk {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -80,6 +82,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag != 0) return false;
       if (globaltimer_ns() - t0 > kWaitLimitNs) {
         *abort_flag = 1;
+        uint32_t rank;
+        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+        atomicCAS(&g_timeout_site, 0u,
+                  (threadIdx.x >> 5) | (rank << 8) | ((bar & 0x7ffffu) << 12) | (parity << 31));
         return false;
       }
     }

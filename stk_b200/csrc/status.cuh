@@ -10,4 +10,8 @@ __device__ int g_device_status = 0;
 // Keeps the first reported problem.
 __device__ __forceinline__ void report_status(int code) { atomicCAS(&g_device_status, 0, code); }
 
+// Where the first bounded wait ran out: warp | cluster rank << 8 | barrier's shared-memory offset << 12 |
+// parity << 31 (0: no wait has run out).  A diagnostic next to the status word, cleared with it.
+__device__ unsigned int g_timeout_site = 0;
+
 }  // namespace stk

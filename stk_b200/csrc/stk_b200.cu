@@ -29,6 +29,18 @@ extern "C" const char* stk_b200_error_string(int code) {
   }
 }
 
+extern "C" int stk_b200_timeout_site(unsigned int* site_host) {
+  if (site_host == nullptr) return STK_ERR_NULL_POINTER;
+  unsigned int v = 0;
+  if (cudaMemcpyFromSymbol(&v, stk::g_timeout_site, sizeof(v)) != cudaSuccess) return STK_ERR_LAUNCH;
+  if (v != 0) {
+    const unsigned int zero = 0;
+    if (cudaMemcpyToSymbol(stk::g_timeout_site, &zero, sizeof(zero)) != cudaSuccess) return STK_ERR_LAUNCH;
+  }
+  *site_host = v;
+  return STK_OK;
+}
+
 extern "C" int stk_b200_device_status(int* status_host) {
   if (status_host == nullptr) return STK_ERR_NULL_POINTER;
   int v = 0;
