@@ -468,10 +468,8 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!ready) {
           const bool got = mbar_wait(full_bar(stage), phase, abort_flag);
           if (!got) break;
+          flags = stage_flags[stage];
         }
-        // read here, not with the probe: a probe that finds the phase complete may have raced with the
-        // producer's arrival (see the end-of-stream tag)
-        flags = stage_flags[stage];
         if (flags & kFlagEnd) break;
         if (flags & kFlagFirst) {
           if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) break;
@@ -485,6 +483,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         umma_pair<kF8>(d_tmem, smem_desc_join(a_lo), smem_desc_join(b_lo), idesc, (flags & kFlagFirst) ? 0u : 1u);
         umma_pair<kF8>(d_tmem, smem_desc_join(a_lo + a_kstep), smem_desc_join(b_lo + b_kstep), idesc, 1u);
         ready = mbar_test_wait(full_bar(next_stage), next_phase);
+        const uint32_t next_flags = stage_flags[next_stage];  // not waited for here; only used if `ready`
         umma_pair<kF8>(d_tmem, smem_desc_join(a_lo + 2 * a_kstep), smem_desc_join(b_lo + 2 * b_kstep), idesc, 1u);
         umma_pair<kF8>(d_tmem, smem_desc_join(a_lo + 3 * a_kstep), smem_desc_join(b_lo + 3 * b_kstep), idesc, 1u);
         umma_commit_pair(empty_bar(stage), 3);  // frees the stage in both CTAs
@@ -495,6 +494,7 @@ bsmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         stage = next_stage;
         phase = next_phase;
+        flags = next_flags;
       }
     }
     __syncwarp();

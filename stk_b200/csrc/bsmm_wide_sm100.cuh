@@ -212,7 +212,7 @@ bsmm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t flags = 0;
       // The MMAs of one K step (64) of the stage: which = 0 / 1 for one accumulator, 2 for both.
       auto issue = [&](int st, int which, uint32_t accumulate, bool probe, int probe_stage, uint32_t probe_phase,
-                       bool& probe_ready) {
+                       bool& probe_ready, uint32_t& probe_flags) {
         const uint32_t s_lo = s_lo0 + st * (kWStageBytes >> 4);
         const uint32_t d_lo = d_lo0 + st * (kWStageBytes >> 4);
 #pragma unroll
@@ -231,14 +231,18 @@ bsmm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           accumulate = 1u;
           if (probe && k == 1) {
             probe_ready = mbar_test_wait(full_bar(probe_stage), probe_phase);
+            probe_flags = stage_flags[probe_stage];  // only used if `probe_ready`
           }
         }
       };
       bool unused_ready = false;
+      uint32_t unused_flags = 0;
       bool alive = true;
       while (alive) {
-        if (!ready && !mbar_wait(full_bar(stage), phase, abort_flag)) break;
-        flags = stage_flags[stage];  // read here, not with the probe (see the pair kernel)
+        if (!ready) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) break;
+          flags = stage_flags[stage];
+        }
         if (flags & kFlagEnd) break;
         if (flags & kFlagFirst) {
           // Head of an item.  The epilogue hands back accumulator 0 first, then accumulator 1: the
@@ -251,7 +255,7 @@ bsmm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           int n_head = 0, st = stage;
           uint32_t ph = phase, fl = flags;
           while (true) {
-            issue(st, kWStagger ? 0 : 2, n_head == 0 ? 0u : 1u, false, 0, 0, unused_ready);
+            issue(st, kWStagger ? 0 : 2, n_head == 0 ? 0u : 1u, false, 0, 0, unused_ready, unused_flags);
             head_flags[n_head++] = fl;
             if (!kWStagger || (fl & kFlagLast) || n_head == kWStages) break;
             st = st + 1 == kWStages ? 0 : st + 1;
@@ -264,7 +268,7 @@ bsmm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (!mbar_wait(tempty_bar(1), tile_phase ^ 1u, abort_flag)) break;
           tc_fence_after();
           for (int i = 0; i < n_head; ++i) {
-            if (kWStagger) issue(stage, 1, i == 0 ? 0u : 1u, false, 0, 0, unused_ready);
+            if (kWStagger) issue(stage, 1, i == 0 ? 0u : 1u, false, 0, 0, unused_ready, unused_flags);
             umma_commit_pair(empty_bar(stage), 3);
             if (head_flags[i] & kFlagLast) {
               umma_commit_pair(tfull_bar, 3);
@@ -281,7 +285,8 @@ bsmm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_fence_after();
         const int next_stage = stage + 1 == kWStages ? 0 : stage + 1;
         const uint32_t next_phase = stage + 1 == kWStages ? phase ^ 1u : phase;
-        issue(stage, 2, 1u, true, next_stage, next_phase, ready);
+        uint32_t next_flags = 0;
+        issue(stage, 2, 1u, true, next_stage, next_phase, ready, next_flags);
         umma_commit_pair(empty_bar(stage), 3);
         if (flags & kFlagLast) {
           umma_commit_pair(tfull_bar, 3);
@@ -289,6 +294,7 @@ bsmm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         stage = next_stage;
         phase = next_phase;
+        flags = next_flags;
       }
     }
     __syncwarp();

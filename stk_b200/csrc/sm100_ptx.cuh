@@ -65,6 +65,14 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 // Longest time any single wait may take before the kernel declares itself stuck.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
+// Out of line: inlined into every wait, these few instructions cost the SDD main loop 4 % (the waits sit
+// in the single-thread issue loops, whose register allocation and layout they disturbed).
+__device__ __noinline__ void record_timeout_site(uint32_t bar, uint32_t parity) {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  atomicCAS(&g_timeout_site, 0u, (threadIdx.x >> 5) | (rank << 8) | ((bar & 0x7ffffu) << 12) | (parity << 31));
+}
+
 // Bounded wait.  `abort_flag` is a CTA-wide shared word: once any role has given up,
 // every other wait in the CTA returns false quickly so that the CTA can tear down.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
@@ -82,10 +90,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag != 0) return false;
       if (globaltimer_ns() - t0 > kWaitLimitNs) {
         *abort_flag = 1;
-        uint32_t rank;
-        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-        atomicCAS(&g_timeout_site, 0u,
-                  (threadIdx.x >> 5) | (rank << 8) | ((bar & 0x7ffffu) << 12) | (parity << 31));
+        record_timeout_site(bar, parity);
         return false;
       }
     }

@@ -405,3 +405,44 @@ def test_float8_matrices_convert_like_16_bit_ones(stk):
         assert torch.equal(m8.data.view(torch.uint8), m16.data.to(F8).view(torch.uint8))
         back = stk.ops.to_dense(m8)
         assert back.dtype == F8 and torch.equal(back.to(torch.bfloat16), stk.ops.to_dense(m16))
+
+
+@pytest.mark.parametrize("mode", ["1", "2"])
+def test_tiny_products_launched_back_to_back_stay_exact(stk, mode):
+    """Thousands of launches on topologies whose work items are one to three blocks long, different kinds of
+    products following one another without a pause: every result is bit-identical to the first, and no
+    bounded wait runs out.  (The end-of-stream tag of the CTA-pair kernels once raced with the MMA
+    issuer's probe of the next stage; a launch in a few thousand then hung until its wait limit.)"""
+    from stk_b200 import dmoe
+    from stk_b200.backend import kernels, lib
+    saved = kernels.PAIR_MODE
+    kernels.PAIR_MODE = mode
+    try:
+        for experts, cols_per_expert in ((5, 3), (80, 1)):
+            g = torch.Generator().manual_seed(experts)
+            bin_rows = torch.randint(1, 4, (experts,), generator=g)
+            bin_rows[experts // 2] = 0
+            topo = dmoe.block_diagonal_topology(bin_rows * 128, cols_per_expert * 128, torch.float16, "cuda")
+            rows, cols = topo.size()
+            a = (torch.randn(rows, 256, generator=g) * 0.1).half().cuda()
+            b = (torch.randn(256, cols, generator=g) * 0.1).half().cuda()
+            right = (torch.randn(cols, 384, generator=g) * 0.1).half().cuda()
+            left_t = (torch.randn(rows, 384, generator=g) * 0.1).half().cuda()
+            got = stk.ops.sdd(a, b, topo)
+            products = {"dsd": lambda: stk.ops.dsd(got, right), "dsd T": lambda: stk.ops.dsd(got.t(), left_t),
+                        "dds": lambda: stk.ops.dds(left_t.t(), got), "sdd": lambda: stk.ops.sdd(a, b, topo).data}
+            for name, fn in products.items():
+                first = fn().clone()
+                different = 0
+                for i in range(500):
+                    out = fn()
+                    if i % 3 == 0:
+                        stk.ops.sdd(a, b, topo)
+                    if i % 5 == 0:
+                        stk.ops.dsd(got, right)
+                    different += int(not torch.equal(out, first))
+                torch.cuda.synchronize()
+                assert different == 0, f"{name}: {different} of 500 results differ from the first"
+                assert lib.device_status() == 0, name
+    finally:
+        kernels.PAIR_MODE = saved
