@@ -69,6 +69,9 @@ int stk_b200_device_status(int* status_host);
  * status word: warp of the waiting thread | its CTA's rank in the cluster << 8 | shared-memory address
  * of the barrier << 12 | awaited parity << 31.  Synchronises the device. */
 int stk_b200_timeout_site(unsigned int* site_host);
+/* Diagnostic for STK_ERR_TENSOR_MAP: the CUresult of the calling thread's last cuTensorMapEncodeTiled
+ * (0 = success; 1 = CUDA_ERROR_INVALID_VALUE: an address, stride or extent the hardware cannot describe). */
+int stk_b200_last_tensor_map_error(void);
 
 /*
  * pair_mode (sdd / dsd / dds): 0 runs one 128x128 output tile per CTA.  1 runs 256x256 supertiles on
@@ -266,6 +269,21 @@ int stk_b200_gather_blocks(const void* x, int64_t rows, int64_t cols, int64_t ld
 int stk_b200_to_dense(const void* data, const int32_t* offsets, const int16_t* column_indices,
                       int64_t block_rows, int64_t block_cols, int blocking, int elem_bytes,
                       void* out, int64_t ld_out, void* stream);
+
+/*
+ * regroup_blocks: products of matrices with 16, 32 or 64 blocks.  The reference's kernels exist for
+ * 128 x 128 blocks only (stk/backend/triton_kernels.py:8-11 TritonConfig, BLOCK_SIZE = 128 in every launch);
+ * here a matrix with smaller blocks runs as the matrix of the 128 x 128 blocks that contain its blocks,
+ * zero where it has none, which is exact.  This call moves the values: fine = [nnz, b, b],
+ * coarse = [coarse_blocks, 128, 128] (zero-filled by the caller when to_coarse = 1),
+ * slot[p] = coarse block * q*q + (block row % q) * q + block column % q with q = 128 / b.
+ * to_coarse = 1: coarse[slot] = fine;  to_coarse = 0: fine = coarse[slot].  Bit-exact copies; both
+ * buffers 16-byte aligned; a slot outside [0, coarse_blocks * q*q) is skipped (zeros when gathering)
+ * and reported as STK_ERR_BAD_DIMS through stk_b200_device_status.
+ */
+int stk_b200_regroup_blocks(void* fine, void* coarse, const int32_t* slot, int64_t nnz,
+                            int64_t coarse_blocks, int blocking, int elem_bytes, int to_coarse,
+                            void* stream);
 
 /*
  * dMoE plumbing around the products (the callers' side of stk.Matrix / sdd / dsd in a dropless-MoE

@@ -29,7 +29,7 @@ def custom_fwd(fwd):
     def wrapper(*args, **kwargs):
         if not torch.is_autocast_enabled():
             return fwd(*args, **kwargs)
-        dtype = torch.get_autocast_gpu_dtype()
+        dtype = torch.get_autocast_dtype("cuda")
         with torch.autocast(device_type="cuda", enabled=False):
             return fwd(*_cast_tree(args, dtype), **_cast_tree(kwargs, dtype))
     return wrapper

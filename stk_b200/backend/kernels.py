@@ -511,6 +511,26 @@ def gather_blocks(x, blocking, row_idx, col_idx, offsets=None):
     return data
 
 
+def regroup_blocks(fine, coarse, slot, to_coarse):
+    """Moves [nnz, b, b] blocks (b = 16, 32, 64) into (to_coarse) or out of their places inside the
+    [n, 128, 128] blocks of `coarse`; slot[p] = coarse block * q*q + (block row % q) * q + block column % q,
+    q = 128 // b.  Bit-exact copies; places no block maps to are left as they are."""
+    _require_cuda(fine, coarse, slot)
+    if fine.dtype != coarse.dtype:
+        raise ValueError(f"regroup_blocks: one dtype for both sides, got {fine.dtype} and {coarse.dtype}")
+    if fine.dim() != 3 or fine.shape[1] != fine.shape[2] or coarse.dim() != 3 or tuple(coarse.shape[1:]) != (BLOCK, BLOCK):
+        raise DimensionError(f"regroup_blocks: expected [nnz, b, b] and [n, {BLOCK}, {BLOCK}] blocks, got "
+                             f"{tuple(fine.shape)} and {tuple(coarse.shape)}")
+    if not fine.is_contiguous() or not coarse.is_contiguous() or slot.dtype != torch.int32 or slot.numel() != fine.shape[0]:
+        raise DimensionError("regroup_blocks: contiguous blocks and one int32 slot per block")
+    with _lib.on_device(fine.device):
+        rc = _lib.load().stk_b200_regroup_blocks(
+            _lib.ptr(fine) if fine.numel() else None, _lib.ptr(coarse) if coarse.numel() else None,
+            _lib.ptr(slot) if slot.numel() else None, fine.shape[0], coarse.shape[0], fine.shape[1],
+            _elem_bytes(fine), int(bool(to_coarse)), _lib.stream_ptr(fine.device))
+    _lib.check(rc, "stk_b200_regroup_blocks")
+
+
 def to_dense(data, offsets, column_indices, block_rows, block_cols, blocking):
     """Dense [R*b, Cb*b] tensor with the blocks in place and zeros elsewhere."""
     _require_cuda(data, offsets, column_indices)

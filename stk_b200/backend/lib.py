@@ -26,6 +26,7 @@ SIGNATURES = {
     "stk_b200_error_string": (ctypes.c_char_p, [_c_int]),
     "stk_b200_device_status": (_c_int, [ctypes.POINTER(_c_int)]),
     "stk_b200_timeout_site": (_c_int, [ctypes.POINTER(ctypes.c_uint)]),
+    "stk_b200_last_tensor_map_error": (_c_int, []),
     "stk_b200_sdd": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64,
                               _c_i64, _c_int, _c_i64, _c_int, _c_i64, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr]),
     "stk_b200_dsd": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64,
@@ -49,6 +50,7 @@ SIGNATURES = {
                                         _c_i64, _c_ptr, _c_ptr]),
     "stk_b200_to_dense": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_int, _c_ptr,
                                    _c_i64, _c_ptr]),
+    "stk_b200_regroup_blocks": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_int, _c_int, _c_ptr]),
     "stk_b200_gather_rows": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_ptr]),
     "stk_b200_scatter_rows": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_ptr]),
     "stk_b200_weighted_sum_rows": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_i64, _c_int,
@@ -79,7 +81,8 @@ _lib = None
 # after its entry point (stk_b200_sdd, stk_b200_ep_dispatch, ...), so that a timeline shows which
 # product or exchange step a kernel belongs to.  Off by default: a range costs two calls per launch.
 NVTX = os.environ.get("STK_B200_NVTX", "0") == "1"
-_UNTRACED = ("stk_b200_error_string", "stk_b200_device_status", "stk_b200_timeout_site")
+_UNTRACED = ("stk_b200_error_string", "stk_b200_device_status", "stk_b200_timeout_site",
+             "stk_b200_last_tensor_map_error")
 
 
 class _Traced:
@@ -132,6 +135,8 @@ def check(code, what):
     if code == 0:
         return
     msg = f"{what}: {error_string(code)} (status {code})"
+    if code == -5:
+        msg += f", CUresult {load().stk_b200_last_tensor_map_error()}"
     if code in (-1, -2, -3, -4, -9):
         raise ValueError(msg)
     raise RuntimeError(msg)

@@ -602,6 +602,24 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
   return fn;
 }
 
+// cuTensorMapEncodeTiled wants a CUDA context current on the calling thread.  A thread that has made no runtime
+// call that binds one yet (a freshly started autograd worker whose first work is one of these products: its
+// allocations came out of a cache) gets CUDA_ERROR_INVALID_CONTEXT; binding the thread's device's primary
+// context and encoding again is what any later runtime call would have done.
+template <typename... Args>
+static CUresult encode_tiled(PFN_cuTensorMapEncodeTiled_v12000 fn, Args... args) {
+  CUresult r = fn(args...);
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaSetDevice(dev) == cudaSuccess) r = fn(args...);
+  }
+  return r;
+}
+
+// The driver's answer to the last tensor-map encoding of this thread (a CUresult; 0 = success), for
+// stk_b200_last_tensor_map_error.
+static thread_local int g_last_encode_result = 0;
+
 // Tensor map of a 2-D tensor of 16-bit elements (STK_F16 / STK_BF16) or bytes (STK_F8E4M3): `inner`
 // contiguous elements per row, `outer` rows, `ld` elements between rows; boxes of 128 bytes x
 // box_outer with the 128-byte swizzle.
@@ -615,11 +633,12 @@ static int encode_map(CUtensorMap* tm, const void* base, int dtype, int64_t inne
   const cuuint32_t box[2] = {static_cast<cuuint32_t>(bytes ? 2 * kBK : kBK), static_cast<cuuint32_t>(box_outer)};
   const cuuint32_t estr[2] = {1u, 1u};
   const CUresult r =
-      fn(tm, bytes ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+      encode_tiled(fn, tm, bytes ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                    : dtype == STK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
          2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  g_last_encode_result = static_cast<int>(r);
   return r == CUDA_SUCCESS ? STK_OK : STK_ERR_TENSOR_MAP;
 }
 
@@ -639,10 +658,11 @@ static int encode_map_mn_major(CUtensorMap* tm, const void* base, int dtype, int
   const cuuint32_t box[3] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(kBK), 2u};
   const cuuint32_t estr[3] = {1u, 1u, 1u};
   const CUresult r =
-      fn(tm, dtype == STK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+      encode_tiled(fn, tm, dtype == STK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
          3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  g_last_encode_result = static_cast<int>(r);
   return r == CUDA_SUCCESS ? STK_OK : STK_ERR_TENSOR_MAP;
 }
 

@@ -840,6 +840,58 @@ extern "C" int stk_b200_gather_blocks_i32(const void* x, int64_t rows, int64_t c
                             IndexArray{column_indices, 1}, nnz, data, stream);
 }
 
+// ------------------------------------------------------------------------------------------
+// regroup_blocks: b x b blocks (b = 16, 32 or 64) <-> their places inside 128 x 128 blocks, which is how the
+// matmul kernels (built for 128 x 128 blocks) run products of matrices with smaller blocks: slot[p] =
+// coarse block * q*q + (block row % q) * q + block column % q with q = 128 / b.  16-byte copies, a thread
+// per vector, consecutive threads along a block's rows.
+__global__ void __launch_bounds__(256)
+regroup_blocks_kernel(uint4* __restrict__ fine, uint4* __restrict__ coarse, const int32_t* __restrict__ slot,
+                      int64_t total_vecs, int64_t coarse_slots, int blocking, int vec_per_row, int to_coarse) {
+  const int q = 128 / blocking;
+  const int vecs_per_block = blocking * vec_per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total_vecs;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t p = i / vecs_per_block;
+    const int v = static_cast<int>(i - p * vecs_per_block);
+    const int row = v / vec_per_row, cv = v - row * vec_per_row;
+    const int64_t s = slot[p];
+    if (s < 0 || s >= coarse_slots) {
+      // a slot outside the coarse matrix is never touched: gathered values become zeros, the call is reported
+      if (v == 0) report_status(STK_ERR_BAD_DIMS);
+      if (!to_coarse) fine[i] = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
+    const int64_t cb = s / (q * q);
+    const int within = static_cast<int>(s - cb * (q * q));
+    const int rq = within / q, cq = within - rq * q;
+    const int64_t ci = (cb * 128 + rq * blocking + row) * (static_cast<int64_t>(vec_per_row) * q) + cq * vec_per_row + cv;
+    if (to_coarse) coarse[ci] = fine[i];
+    else fine[i] = coarse[ci];
+  }
+}
+
+extern "C" int stk_b200_regroup_blocks(void* fine, void* coarse, const int32_t* slot, int64_t nnz,
+                                       int64_t coarse_blocks, int blocking, int elem_bytes, int to_coarse,
+                                       void* stream) {
+  if ((blocking != 16 && blocking != 32 && blocking != 64) || nnz < 0 || coarse_blocks < 0) return STK_ERR_BAD_DIMS;
+  if (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4) return STK_ERR_BAD_DTYPE;
+  if (nnz == 0) return STK_OK;
+  if (fine == nullptr || coarse == nullptr || slot == nullptr) return STK_ERR_NULL_POINTER;
+  if (!ptr_aligned16(fine) || !ptr_aligned16(coarse)) return STK_ERR_BAD_LAYOUT;
+  const int q = 128 / blocking;
+  if (coarse_blocks > INT32_MAX / (q * q)) return STK_ERR_TOO_LARGE;
+  const int vec_per_row = blocking * elem_bytes / 16;
+  const int64_t total = nnz * blocking * vec_per_row;
+  int64_t blocks = (total + 255) / 256;
+  const int64_t cap = 148 * 16;
+  if (blocks > cap) blocks = cap;
+  regroup_blocks_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint4*>(fine), static_cast<uint4*>(coarse), slot, total, coarse_blocks * q * q, blocking,
+      vec_per_row, to_coarse);
+  return launch_status();
+}
+
 extern "C" int stk_b200_to_dense(const void* data, const int32_t* offsets,
                                  const int16_t* column_indices, int64_t block_rows,
                                  int64_t block_cols, int blocking, int elem_bytes, void* out,

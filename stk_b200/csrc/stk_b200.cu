@@ -29,6 +29,8 @@ extern "C" const char* stk_b200_error_string(int code) {
   }
 }
 
+extern "C" int stk_b200_last_tensor_map_error(void) { return stk::g_last_encode_result; }
+
 extern "C" int stk_b200_timeout_site(unsigned int* site_host) {
   if (site_host == nullptr) return STK_ERR_NULL_POINTER;
   unsigned int v = 0;

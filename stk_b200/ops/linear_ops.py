@@ -6,6 +6,7 @@ import torch
 
 from stk_b200.backend import kernels, sputnik
 from stk_b200.matrix import Matrix
+from stk_b200.ops import small_blocks
 
 
 def _fields(m):
@@ -33,6 +34,8 @@ def dsd(a, b, out=None):
     """
     assert isinstance(a, Matrix)
     assert isinstance(b, torch.Tensor)
+    if a.blocking in small_blocks.SMALL_BLOCKINGS:      # 16-, 32-, 64-blocks run inside the 128-blocks that contain them
+        return dsd(small_blocks.as_blocks_of_128(a), b, out)
     if out is None and _is_fp8(a.data, b):
         _no_grad_fp8(a.data, b)
         out = torch.empty((a.size()[0], b.shape[1]), dtype=torch.bfloat16, device=b.device)
@@ -55,6 +58,8 @@ def dds(a, b):
     """dense = a @ b with a dense and b sparse (possibly a .t() view)."""
     assert isinstance(a, torch.Tensor)
     assert isinstance(b, Matrix)
+    if b.blocking in small_blocks.SMALL_BLOCKINGS:
+        return dds(a, small_blocks.as_blocks_of_128(b))
     if _is_fp8(a, b.data):
         _no_grad_fp8(a, b.data)
         out = torch.empty((a.shape[0], b.size()[1]), dtype=torch.bfloat16, device=a.device)
@@ -69,6 +74,9 @@ def sdd(a, b, topo):
     assert isinstance(b, torch.Tensor)
     assert isinstance(topo, Matrix)
     assert topo.is_contiguous()
+    if topo.blocking in small_blocks.SMALL_BLOCKINGS:
+        containing, coarse = small_blocks.topology_of_128(topo, a.dtype)
+        return small_blocks.from_blocks_of_128(sdd(a, b, containing), coarse, topo)
     if _is_fp8(a, b):
         _no_grad_fp8(a, b)
         out = torch.empty(topo.data.shape, dtype=torch.bfloat16, device=a.device)
@@ -92,6 +100,9 @@ def sdd_gelu(a, b, topo):
     assert isinstance(b, torch.Tensor)
     assert isinstance(topo, Matrix)
     assert topo.is_contiguous()
+    if topo.blocking in small_blocks.SMALL_BLOCKINGS:
+        containing, coarse = small_blocks.topology_of_128(topo, a.dtype)
+        return small_blocks.from_blocks_of_128(sdd_gelu(a, b, containing), coarse, topo)
     out = torch.empty(topo.data.shape, dtype=torch.bfloat16 if _is_fp8(a, b) else a.dtype, device=a.device)
     kernels.sdd(a, b, topo.size(), out, topo.offsets, topo.row_indices, topo.column_indices,
                 epilogue=1)

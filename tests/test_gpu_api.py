@@ -446,3 +446,38 @@ def test_tiny_products_launched_back_to_back_stay_exact(stk, mode):
                 assert lib.device_status() == 0, name
     finally:
         kernels.PAIR_MODE = saved
+
+
+def test_first_product_of_a_fresh_autograd_thread():
+    """The backward pass runs on a worker thread that has no CUDA context bound until some runtime call binds
+    one; when its first work is a product whose buffers come out of the allocator's cache, the tensor-map
+    encoding is that thread's first driver call (it once answered CUDA_ERROR_INVALID_CONTEXT).  A fresh
+    process, so that the worker thread is new."""
+    import subprocess
+    import sys
+    script = r"""
+import numpy as np, torch
+import stk_b200 as stk
+from stk_b200.backend import kernels, lib
+kernels.PAIR_MODE = "0"
+np.random.seed(1)
+topo = stk.random.mask(256, 384, 0.0, 128).to("cuda")
+vals = (torch.randn(6, 128, 128) * 0.1).half().cuda().requires_grad_(True)
+s = stk.Matrix(topo.size(), vals, topo.row_indices, topo.column_indices, topo.offsets,
+               topo.column_indices_t, topo.offsets_t, topo.block_offsets_t)
+d = (torch.randn(384, 128) * 0.1).half().cuda()
+warm = torch.empty(6, 128, 128, dtype=torch.float16, device="cuda")   # the backward's buffer will reuse this
+del warm
+out = stk.ops.dsd(s, d)
+out.backward(torch.ones_like(out))
+want = torch.ones(256, 128).double() @ d.double().cpu().t()
+got = stk.ops.to_dense(stk.Matrix(topo.size(), vals.grad, topo.row_indices, topo.column_indices, topo.offsets,
+                                  topo.column_indices_t, topo.offsets_t, topo.block_offsets_t)).double().cpu()
+assert (got - want).abs().max().item() < 0.05, (got - want).abs().max().item()
+assert lib.device_status() == 0
+print("fresh thread ok")
+"""
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    done = subprocess.run([sys.executable, "-c", script], cwd=root, capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0 and "fresh thread ok" in done.stdout, done.stdout[-2000:] + done.stderr[-2000:]

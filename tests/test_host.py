@@ -55,6 +55,13 @@ def test_argument_validation_happens_before_any_launch():
     assert l.stk_b200_block_mask(null, 8, 8, 8, 3, 2, null, null) == -2
     assert l.stk_b200_block_mask(null, 8, 8, 8, 8, 3, null, null) == -3
     assert l.stk_b200_to_dense(null, null, null, 2, 2, 8, 8, null, 16, null) == -3
+    # regroup_blocks: blockings 16 / 32 / 64, element sizes 1 / 2 / 4, aligned buffers
+    assert l.stk_b200_regroup_blocks(null, null, null, 4, 1, 48, 2, 1, null) == -2
+    assert l.stk_b200_regroup_blocks(null, null, null, 4, 1, 128, 2, 1, null) == -2
+    assert l.stk_b200_regroup_blocks(null, null, null, 4, 1, 64, 3, 1, null) == -3
+    assert l.stk_b200_regroup_blocks(null, null, null, 0, 0, 64, 2, 1, null) == 0
+    assert l.stk_b200_regroup_blocks(null, null, null, 4, 1, 64, 2, 1, null) == -1
+    assert l.stk_b200_regroup_blocks(ctypes.c_void_p(8), ctypes.c_void_p(16), ctypes.c_void_p(16), 4, 1, 64, 2, 1, null) == -4
     # workspace sizing: small problems need none, large ones a bounded amount
     ws = l.stk_b200_transpose_meta_workspace_bytes
     assert ws(16, 8) == 0 and ws(0, 100) == 0
@@ -362,3 +369,27 @@ def test_nvtx_wrapper_passes_calls_through(monkeypatch):
     null = ctypes.c_void_p(0)
     assert traced.stk_b200_pair_plan(null, null, 0, null, 0, null) == -2
     assert events == [("push", "stk_b200_pair_plan"), ("pop",)]
+
+
+def test_small_block_products_refuse_what_they_cannot_regroup():
+    """Blockings other than 16 / 32 / 64 / 128, and sparse shapes that are not multiples of 128, are refused
+    on the host before anything runs."""
+    import stk_b200 as stk
+    from stk_b200.backend import kernels
+    from stk_b200.ops import small_blocks
+
+    def matrix(rows, cols, blocking):
+        idx = torch.zeros(1, dtype=torch.int16)
+        off = torch.zeros(rows // blocking + 1, dtype=torch.int32)
+        off[1:] = 1
+        off_t = torch.zeros(cols // blocking + 1, dtype=torch.int32)
+        off_t[1:] = 1
+        return stk.Matrix(torch.Size((rows, cols)), torch.ones(1, blocking, blocking, dtype=torch.float16), idx, idx.clone(),
+                          off, idx.clone(), off_t, torch.zeros(1, dtype=torch.int32))
+
+    with pytest.raises(kernels.DimensionError):
+        small_blocks.coarse_topology(matrix(256, 256, 8))
+    with pytest.raises(kernels.DimensionError):
+        small_blocks.coarse_topology(matrix(192, 256, 64))
+    with pytest.raises(kernels.DimensionError):
+        stk.ops.dsd(matrix(256, 320, 64).t(), torch.zeros(256, 128, dtype=torch.float16))
