@@ -347,6 +347,44 @@ def products_fp8(dev="cuda", experts=8, rows_per_expert=4096, hidden=4096, ffn=1
     return out
 
 
+def products_small_blocks(dev="cuda", size=8192, density=0.25):
+    """Products with 64- and 32-blocks (run inside their containing 128-blocks) beside the same products with
+    128-blocks at the same density; useful TFLOP/s count the small blocks' own elements only.  Two 64-block
+    topologies: `clustered` = every kept 128-block is full of small blocks (no MMA work wasted), `scattered`
+    = small blocks kept independently (at density d a 128-block is kept with probability 1 - (1-d)^4 and is
+    a quarter to fully used).  Also the copy kernel alone, in GB/s of the bytes it reads and writes."""
+    from stk_b200.ops import small_blocks
+    dtype = torch.bfloat16
+    out = []
+    b = torch.randn(size, size, device=dev).to(dtype)
+    a = torch.randn(size, size, device=dev).to(dtype)
+    for blocking, kind in ((128, "as is"), (64, "clustered"), (64, "scattered"), (32, "scattered")):
+        np.random.seed(0)
+        if kind == "clustered":
+            big = stk.random.mask(size, size, 1 - density, 128)
+            keep = stk.ops.to_dense(big.to(dev)).to(dtype)
+            topo = stk.ops.to_sparse(keep, blocking)
+        else:
+            topo = stk.random.mask(size, size, 1 - density, blocking).to(dev)
+        nnz = topo.data.shape[0]
+        s = stk.Matrix(topo.size(), torch.randn(nnz, blocking, blocking, device=dev).to(dtype), topo.row_indices,
+                       topo.column_indices, topo.offsets, topo.column_indices_t, topo.offsets_t, topo.block_offsets_t)
+        flops = 2.0 * nnz * blocking * blocking * size
+        ms = time_interleaved({"dsd": lambda: stk.ops.dsd(s, b), "sdd": lambda: stk.ops.sdd(a, b, s)}, rounds=3, iters=3)
+        row = {"blocking": blocking, "topology": kind, "blocks": nnz,
+               "dsd_us": round(ms["dsd"] * 1e3, 1), "dsd_tflops": round(flops / ms["dsd"] / 1e9, 1),
+               "sdd_us": round(ms["sdd"] * 1e3, 1), "sdd_tflops": round(flops / ms["sdd"] / 1e9, 1),
+               "containing_128_blocks": nnz, "copy_us": None, "copy_gbs": None}
+        if blocking != 128:
+            coarse = small_blocks.coarse_topology(s)
+            big_vals = torch.zeros((coarse.blocks, 128, 128), dtype=dtype, device=dev)
+            copy_ms = _time_ms(lambda: kernels.regroup_blocks(s.data, big_vals, coarse.slot, True), iters=10, warm=3)
+            row.update(containing_128_blocks=coarse.blocks, copy_us=round(copy_ms * 1e3, 1),
+                       copy_gbs=round(2.0 * s.data.numel() * 2 / copy_ms / 1e6, 1))
+        out.append(row)
+    return out
+
+
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "c2"
     if which == "train":
@@ -364,6 +402,10 @@ if __name__ == "__main__":
                 print("| product | bf16 TFLOP/s | fp8 TFLOP/s | fp8 us | cuBLASLt fp8 TFLOP/s | fp8 / cuBLASLt |\n|---|---|---|---|---|---|")
                 for r in products_fp8():
                     print(f"| {r['product']} | {r['bf16_tflops']} | {r['fp8_tflops']} | {r['fp8_us']} | {r['cublaslt_fp8_tflops']} | {r['fp8_vs_cublaslt']} |", flush=True)
+            elif which == "small":
+                print("| blocking | topology | blocks | containing 128-blocks | dsd us | dsd useful TFLOP/s | sdd us | sdd useful TFLOP/s | copy us | copy GB/s |\n|---|---|---|---|---|---|---|---|---|---|")
+                for r in products_small_blocks():
+                    print(f"| {r['blocking']} | {r['topology']} | {r['blocks']} | {r['containing_128_blocks']} | {r['dsd_us']} | {r['dsd_tflops']} | {r['sdd_us']} | {r['sdd_tflops']} | {r['copy_us']} | {r['copy_gbs']} |", flush=True)
             elif which == "c2":
                 info, lines = products_c2(all_modes=True)
                 _print_table(f"dMoE fwd+bwd products, T=32768 h=2048 f=8192 E=16 bf16; {info}", lines)
