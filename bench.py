@@ -295,6 +295,8 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     distributed = world > 1
+    torch.cuda.set_device(dev)
+    cores_near_gpu = dmoe.bind_host_to_gpu_node(dev) if os.environ.get("STK_B200_BIND_HOST", "1") == "1" else 0
     if distributed:
         dist.init_process_group("nccl", device_id=dev)
     lib.load()
@@ -469,7 +471,8 @@ def run_ours(args):
                 "d2h_bytes_per_step": tokens * HIDDEN * 2,
                 "includes": "per step and rank: H2D tokens + routing, the whole device step, D2H result",
                 "overlap": "dmoe.HostPipeline: H2D of step i+1 and D2H of step i-1 run on their own streams "
-                           "while step i computes"},
+                           "while step i computes",
+                "host_cores_near_gpu": cores_near_gpu},
         "gpu_launches": launches_per_step(world, 1 if world == 1 else layer.exchange.chunks) * args.steps * repeats,
         "gpu_launches_per_step": launches_per_step(world, 1 if world == 1 else layer.exchange.chunks),
         "clocks": clocks,

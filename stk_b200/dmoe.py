@@ -602,6 +602,36 @@ class PeerExchange:
 
 
 # ------------------------------------------------------------------------------ batches from host memory
+def bind_host_to_gpu_node(device):
+    """Restricts the calling process to the CPU cores next to `device` (the cores NVML reports for the GPU's
+    NUMA node, intersected with the cores the process may use), so that pinned host buffers allocated
+    afterwards and the copy threads live on that node: with one process per GPU, host <-> device copies of
+    several ranks then do not cross the socket interconnect.  Only reads NVML; changes this process's
+    scheduling affinity, nothing of the GPU's.  Returns the number of cores kept, or 0 when nothing was changed
+    (NVML or the affinity call unavailable, or the GPU's cores are not among the allowed ones)."""
+    import os
+    try:
+        import pynvml
+        device = torch.device(device)
+        props = torch.cuda.get_device_properties(device)
+        pynvml.nvmlInit()
+        try:
+            handle = pynvml.nvmlDeviceGetHandleByPciBusId(
+                f"{props.pci_domain_id:08x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0".encode())
+            words = (os.cpu_count() + 63) // 64
+            mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        finally:
+            pynvml.nvmlShutdown()
+        near = {64 * w + b for w, word in enumerate(mask) for b in range(64) if (int(word) >> b) & 1}
+        keep = near & os.sched_getaffinity(0)
+        if not keep or keep == os.sched_getaffinity(0):
+            return 0
+        os.sched_setaffinity(0, keep)
+        return len(keep)
+    except Exception:          # no NVML, no such call on this platform, not permitted: leave the process as it is
+        return 0
+
+
 class HostPipeline:
     """Feeds a device step with batches that live in pinned host memory and returns its results to
     pinned host memory, with the copies of neighbouring batches overlapping the step: the inputs of

@@ -115,3 +115,13 @@ def test_expert_parallel_exchange_two_ranks(tmp_path):
     port = 29500 + os.getpid() % 2000
     mp.spawn(_exchange_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     assert os.path.exists(tmp_path / "ok0") and os.path.exists(tmp_path / "ok1")
+
+
+def test_binding_the_host_side_to_a_gpu_changes_nothing_without_one():
+    """No CUDA device, no NVML: the call reports 0 cores kept and leaves the process's affinity alone."""
+    import os
+    from stk_b200 import dmoe
+    before = os.sched_getaffinity(0)
+    assert dmoe.bind_host_to_gpu_node("cuda:0") == 0 or torch.cuda.is_available()
+    if not torch.cuda.is_available():
+        assert os.sched_getaffinity(0) == before
