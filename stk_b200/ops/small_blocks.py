@@ -106,7 +106,10 @@ class _Regroup(torch.autograd.Function):
 def _regroup(values, slot, coarse_blocks, blocking, to_coarse):
     values = values.contiguous()
     if to_coarse:
-        out = torch.zeros((coarse_blocks, BLOCK, BLOCK), dtype=values.dtype, device=values.device)
+        q = BLOCK // blocking
+        # every small block has its own place, so as many blocks as places means no place is left to zero
+        make = torch.empty if slot.numel() == coarse_blocks * q * q else torch.zeros
+        out = make((coarse_blocks, BLOCK, BLOCK), dtype=values.dtype, device=values.device)
         kernels.regroup_blocks(values, out, slot, True)
     else:
         out = torch.empty((slot.numel(), blocking, blocking), dtype=values.dtype, device=values.device)

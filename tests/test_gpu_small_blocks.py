@@ -173,3 +173,21 @@ def test_shapes_that_small_blocks_cannot_take(stk):
     topo8 = _topology(stk, 256, 256, 0.5, 8, 4).to("cuda")
     with pytest.raises(kernels.DimensionError):
         stk.ops.dsd(topo8, torch.zeros(256, 128, dtype=torch.float16, device="cuda"))
+
+
+def test_small_blocks_that_fill_their_128_blocks(stk):
+    """A topology whose small blocks tile their 128-blocks completely takes the copy without a zero fill."""
+    rows, cols = 256, 384
+    np.random.seed(6)
+    keep128 = oracle.dense_mask(rows, cols, 0.5, 128).to(torch.float16)
+    for blocking in (32, 64):
+        g = torch.Generator().manual_seed(blocking)
+        dense = keep128 * (torch.rand(rows, cols, generator=g) + 0.5).half()
+        s = stk.ops.to_sparse(dense.cuda(), blocking)
+        from stk_b200.ops import small_blocks
+        coarse = small_blocks.coarse_topology(s)
+        assert s.row_indices.numel() == coarse.blocks * (128 // blocking) ** 2
+        right = (torch.randn(cols, 128, generator=g) * 0.1).half()
+        assert_product_close(stk.ops.dsd(s, right.cuda()), oracle.dsd(dense, right, torch.float16), "dsd")
+        left = (torch.randn(128, rows, generator=g) * 0.1).half()
+        assert_product_close(stk.ops.dds(left.cuda(), s), oracle.dds(left, dense, torch.float16), "dds")
